@@ -1,0 +1,163 @@
+// Per-token-group (1x128) FP8 quantisation of bf16 activations.  HBM-bound: 16-byte loads,
+// half-warp shuffle absmax on packed bf16x2, power-of-two scale by exponent arithmetic, packed
+// e4m3x2 converts and 8-byte stores.  Algorithmic traffic: 2 B in + 1 B out per element and one
+// 4 B scale per 128 elements.
+#include "common.cuh"
+
+namespace kbn {
+
+constexpr float kFp8Max = 448.0f;
+
+struct GroupScale {
+    float scale;   // what is stored
+    float inv;     // multiplier used when the scale is a power of two
+};
+
+template <bool UE8M0>
+__device__ __forceinline__ GroupScale make_scale(float absmax, float eps) {
+    GroupScale r;
+    float a = fmaxf(absmax, eps);
+    if (UE8M0) {
+        uint32_t f = ue8m0_scale_field(a);
+        r.scale = __uint_as_float(f << 23);
+        r.inv = __uint_as_float((254u - f) << 23);
+    } else {
+        r.scale = __fdiv_rn(a, kFp8Max);
+        r.inv = 0.0f;
+    }
+    return r;
+}
+
+// x/scale for one packed bf16 pair -> two e4m3 bytes.  With a power-of-two scale the multiply by
+// its reciprocal is the same correctly rounded real number as the reference's division.
+template <bool UE8M0>
+__device__ __forceinline__ uint32_t quant_pair(uint32_t w, const GroupScale& s) {
+    float lo = bf16_lo(w), hi = bf16_hi(w);
+    if (UE8M0) {
+        lo = __fmul_rn(lo, s.inv);
+        hi = __fmul_rn(hi, s.inv);
+    } else {
+        lo = fminf(fmaxf(__fdiv_rn(lo, s.scale), -kFp8Max), kFp8Max);
+        hi = fminf(fmaxf(__fdiv_rn(hi, s.scale), -kFp8Max), kFp8Max);
+    }
+    return pack_e4m3x2(lo, hi);
+}
+
+__device__ __forceinline__ float halfwarp_absmax(uint4 v) {
+    uint32_t m = max_bf16x2(max_bf16x2(abs_bf16x2(v.x), abs_bf16x2(v.y)),
+                            max_bf16x2(abs_bf16x2(v.z), abs_bf16x2(v.w)));
+#pragma unroll
+    for (int o = 8; o >= 1; o >>= 1) m = max_bf16x2(m, __shfl_xor_sync(0xffffffffu, m, o));
+    return fmaxf(bf16_lo(m), bf16_hi(m));
+}
+
+// One half-warp per group, U groups per half-warp with all loads issued before any use.
+template <bool UE8M0, int U>
+__global__ void __launch_bounds__(256)
+quant_1x128_kernel(const __nv_bfloat16* __restrict__ x, int64_t M, int64_t K, int64_t ld_x,
+                   uint8_t* __restrict__ q, int64_t ld_q, float* __restrict__ scale, int64_t s_row,
+                   int64_t s_grp, float eps) {
+    const int64_t G = (K + 127) >> 7;
+    const int64_t NG = M * G;
+    const int j = threadIdx.x & 15;
+    const int64_t g0 = ((int64_t)blockIdx.x * 16 + (threadIdx.x >> 4)) * U;
+
+    uint4 v[U];
+    int64_t row[U];
+    int col[U];
+    bool live[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        int64_t gi = g0 + u;
+        bool valid = gi < NG;
+        int64_t m = valid ? gi / G : 0;
+        int g = valid ? (int)(gi - m * G) : 0;
+        row[u] = m;
+        col[u] = g * 128 + j * 8;
+        live[u] = valid && col[u] < K;
+        v[u] = live[u] ? __ldcs(reinterpret_cast<const uint4*>(x + m * ld_x + col[u])) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        GroupScale s = make_scale<UE8M0>(halfwarp_absmax(v[u]), eps);
+        if (live[u]) {
+            uint2 o;
+            o.x = quant_pair<UE8M0>(v[u].x, s) | (quant_pair<UE8M0>(v[u].y, s) << 16);
+            o.y = quant_pair<UE8M0>(v[u].z, s) | (quant_pair<UE8M0>(v[u].w, s) << 16);
+            *reinterpret_cast<uint2*>(q + row[u] * ld_q + col[u]) = o;
+            if (j == 0) scale[row[u] * s_row + (int64_t)(col[u] >> 7) * s_grp] = s.scale;
+        }
+    }
+}
+
+// Any K / any alignment: one warp per group, element-wise accesses.
+template <bool UE8M0>
+__global__ void __launch_bounds__(256)
+quant_1x128_generic_kernel(const __nv_bfloat16* __restrict__ x, int64_t M, int64_t K, int64_t ld_x,
+                           uint8_t* __restrict__ q, int64_t ld_q, float* __restrict__ scale,
+                           int64_t s_row, int64_t s_grp, float eps) {
+    const int64_t G = (K + 127) >> 7;
+    const int64_t gi = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (gi >= M * G) return;
+    const int lane = threadIdx.x & 31;
+    const int64_t m = gi / G;
+    const int64_t k0 = (gi - m * G) * 128;
+    const uint16_t* xr = reinterpret_cast<const uint16_t*>(x) + m * ld_x;
+    float val[4];
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        int64_t k = k0 + lane + 32 * i;
+        val[i] = k < K ? __uint_as_float((uint32_t)xr[k] << 16) : 0.0f;
+        amax = fmaxf(amax, fabsf(val[i]));
+    }
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    GroupScale s = make_scale<UE8M0>(amax, eps);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        int64_t k = k0 + lane + 32 * i;
+        if (k < K) {
+            float f = UE8M0 ? __fmul_rn(val[i], s.inv)
+                            : fminf(fmaxf(__fdiv_rn(val[i], s.scale), -kFp8Max), kFp8Max);
+            q[m * ld_q + k] = (uint8_t)(pack_e4m3x2(f, 0.0f) & 0xffu);
+        }
+    }
+    if (lane == 0) scale[m * s_row + (k0 >> 7) * s_grp] = s.scale;
+}
+
+}  // namespace kbn
+
+extern "C" int kbn_quant_1x128(const void* x, int64_t M, int64_t K, int64_t ld_x, void* q, int64_t ld_q,
+                               float* scale, int64_t s_row, int64_t s_grp, float eps, int ue8m0,
+                               kbn_stream_t stream) {
+    using namespace kbn;
+    KBN_REQUIRE(M >= 0 && K >= 0, KBN_ERR_ARG, "kbn_quant_1x128: negative size (M=%lld K=%lld)", (long long)M, (long long)K);
+    if (M == 0 || K == 0) return KBN_OK;
+    KBN_REQUIRE(x && q && scale, KBN_ERR_ARG, "kbn_quant_1x128: null pointer");
+    KBN_REQUIRE(ld_x >= K && ld_q >= K, KBN_ERR_ARG, "kbn_quant_1x128: row stride smaller than K");
+    KBN_REQUIRE(eps >= 1e-30f && eps < 1e30f, KBN_ERR_ARG, "kbn_quant_1x128: eps %g outside [1e-30, 1e30)", (double)eps);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int64_t G = (K + 127) / 128, NG = M * G;
+    const auto* xb = static_cast<const __nv_bfloat16*>(x);
+    auto* qb = static_cast<uint8_t*>(q);
+    const bool fast = (K % 8 == 0) && (ld_x % 8 == 0) && (ld_q % 8 == 0) && aligned16(x) && ((reinterpret_cast<uintptr_t>(q) & 7u) == 0);
+    if (fast) {
+        constexpr int U = 4;
+        int64_t blocks = (NG + 16 * U - 1) / (16 * U);
+        KBN_REQUIRE(blocks < (1ll << 31), KBN_ERR_ARG, "kbn_quant_1x128: too many groups");
+        if (ue8m0)
+            quant_1x128_kernel<true, U><<<(unsigned)blocks, 256, 0, st>>>(xb, M, K, ld_x, qb, ld_q, scale, s_row, s_grp, eps);
+        else
+            quant_1x128_kernel<false, U><<<(unsigned)blocks, 256, 0, st>>>(xb, M, K, ld_x, qb, ld_q, scale, s_row, s_grp, eps);
+    } else {
+        int64_t blocks = (NG + 7) / 8;
+        KBN_REQUIRE(blocks < (1ll << 31), KBN_ERR_ARG, "kbn_quant_1x128: too many groups");
+        if (ue8m0)
+            quant_1x128_generic_kernel<true><<<(unsigned)blocks, 256, 0, st>>>(xb, M, K, ld_x, qb, ld_q, scale, s_row, s_grp, eps);
+        else
+            quant_1x128_generic_kernel<false><<<(unsigned)blocks, 256, 0, st>>>(xb, M, K, ld_x, qb, ld_q, scale, s_row, s_grp, eps);
+    }
+    KBN_CHECK_LAUNCH();
+    return KBN_OK;
+}

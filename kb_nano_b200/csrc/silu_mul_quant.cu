@@ -1,0 +1,201 @@
+// Fused SiLU(gate)*up + 1x128 FP8 quantisation (the step between the two MoE/MLP projections).
+// HBM-bound: per output group of 128 it reads 256 B of gate and 256 B of up and writes 128 B
+// of fp8 plus one fp32 scale.
+//
+// Exact rounding of silu: the reference rounds g/(1+exp(-g)) (fp32, IEEE ops on a correctly
+// rounded exp) to bf16 before the multiply.  There are only 65536 possible gates, so the
+// kernel evaluates a 5-instruction approximation (ex2.approx / rcp.approx, error < 2^-20
+// relative for |g| <= 8) and falls back to a device-resident table of exactly rounded results
+// when the approximation lands within 64 fp32 ulps of a bf16 rounding boundary or |g| > 8.
+// The table is filled once per device by silu_table_kernel (fp64 exp rounded to fp32, then the
+// reference's fp32 add and divide).
+#include "common.cuh"
+
+namespace kbn {
+
+constexpr float kFp8MaxS = 448.0f;
+
+__device__ uint16_t g_silu_table[65536];
+
+__global__ void silu_table_kernel(uint16_t* __restrict__ table) {
+    uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= 65536u) return;
+    float g = __uint_as_float(i << 16);
+    float e = (float)exp(-(double)g);              // correctly rounded fp32 exp(-g)
+    float s = __fdiv_rn(g, __fadd_rn(1.0f, e));
+    table[i] = __bfloat16_as_ushort(__float2bfloat16_rn(s));
+}
+
+__device__ __forceinline__ float silu_approx(float g) {
+    float e, r;
+    asm("ex2.approx.f32 %0, %1;" : "=f"(e) : "f"(g * -1.4426950408889634f));
+    asm("rcp.approx.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+    return g * r;
+}
+
+// true when the fast value cannot be trusted to round to the same bf16 as the exact one
+__device__ __forceinline__ bool silu_needs_table(float g, float s) {
+    uint32_t low = __float_as_uint(s) & 0xffffu;
+    return !(fabsf(g) <= 8.0f) || (low - 0x7fc0u) <= 0x80u;
+}
+
+// packed bf16x2 gate, up -> packed bf16x2 y = bf16(bf16(silu(g)) * up)
+__device__ __forceinline__ uint32_t silu_mul_pair(uint32_t g2, uint32_t u2, const uint16_t* __restrict__ table) {
+    float g0 = bf16_lo(g2), g1 = bf16_hi(g2);
+    float s0 = silu_approx(g0), s1 = silu_approx(g1);
+    uint32_t sb = pack_bf16x2(s0, s1);
+    if (silu_needs_table(g0, s0)) sb = (sb & 0xffff0000u) | table[g2 & 0xffffu];
+    if (silu_needs_table(g1, s1)) sb = (sb & 0x0000ffffu) | ((uint32_t)table[g2 >> 16] << 16);
+    return mul_bf16x2(sb, u2);
+}
+
+__device__ __forceinline__ float halfwarp_absmax4(uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    uint32_t m = max_bf16x2(max_bf16x2(abs_bf16x2(a), abs_bf16x2(b)), max_bf16x2(abs_bf16x2(c), abs_bf16x2(d)));
+#pragma unroll
+    for (int o = 8; o >= 1; o >>= 1) m = max_bf16x2(m, __shfl_xor_sync(0xffffffffu, m, o));
+    return fmaxf(bf16_lo(m), bf16_hi(m));
+}
+
+template <bool UE8M0>
+__device__ __forceinline__ uint32_t quant_pair_s(uint32_t w, float scale, float inv) {
+    float lo = bf16_lo(w), hi = bf16_hi(w);
+    if (UE8M0) {
+        lo = __fmul_rn(lo, inv);
+        hi = __fmul_rn(hi, inv);
+    } else {
+        lo = fminf(fmaxf(__fdiv_rn(lo, scale), -kFp8MaxS), kFp8MaxS);
+        hi = fminf(fmaxf(__fdiv_rn(hi, scale), -kFp8MaxS), kFp8MaxS);
+    }
+    return pack_e4m3x2(lo, hi);
+}
+
+// One half-warp per output group, U groups per half-warp (2*U 16-byte loads in flight per lane).
+template <bool UE8M0, int U>
+__global__ void __launch_bounds__(256)
+silu_mul_quant_kernel(const __nv_bfloat16* __restrict__ in, int64_t M, int64_t N2, int64_t ld_in,
+                      uint8_t* __restrict__ q, int64_t ld_q, float* __restrict__ scale, int64_t s_row,
+                      int64_t s_grp, float eps, const uint16_t* __restrict__ table) {
+    const int64_t G = N2 >> 7;
+    const int64_t NG = M * G;
+    const int j = threadIdx.x & 15;
+    const int64_t g0 = ((int64_t)blockIdx.x * 16 + (threadIdx.x >> 4)) * U;
+
+    uint4 gv[U], uv[U];
+    int64_t row[U];
+    int col[U];
+    bool live[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        int64_t gi = g0 + u;
+        live[u] = gi < NG;
+        int64_t m = live[u] ? gi / G : 0;
+        int g = live[u] ? (int)(gi - m * G) : 0;
+        row[u] = m;
+        col[u] = g * 128 + j * 8;
+        const __nv_bfloat16* p = in + m * ld_in + col[u];
+        gv[u] = live[u] ? __ldcs(reinterpret_cast<const uint4*>(p)) : make_uint4(0, 0, 0, 0);
+        uv[u] = live[u] ? __ldcs(reinterpret_cast<const uint4*>(p + N2)) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        uint32_t y0 = silu_mul_pair(gv[u].x, uv[u].x, table);
+        uint32_t y1 = silu_mul_pair(gv[u].y, uv[u].y, table);
+        uint32_t y2 = silu_mul_pair(gv[u].z, uv[u].z, table);
+        uint32_t y3 = silu_mul_pair(gv[u].w, uv[u].w, table);
+        float a = fmaxf(halfwarp_absmax4(y0, y1, y2, y3), eps);
+        float sc, inv = 0.0f;
+        if (UE8M0) {
+            uint32_t f = ue8m0_scale_field(a);
+            sc = __uint_as_float(f << 23);
+            inv = __uint_as_float((254u - f) << 23);
+        } else {
+            sc = __fdiv_rn(a, kFp8MaxS);
+        }
+        if (live[u]) {
+            uint2 o;
+            o.x = quant_pair_s<UE8M0>(y0, sc, inv) | (quant_pair_s<UE8M0>(y1, sc, inv) << 16);
+            o.y = quant_pair_s<UE8M0>(y2, sc, inv) | (quant_pair_s<UE8M0>(y3, sc, inv) << 16);
+            *reinterpret_cast<uint2*>(q + row[u] * ld_q + col[u]) = o;
+            if (j == 0) scale[row[u] * s_row + (int64_t)(col[u] >> 7) * s_grp] = sc;
+        }
+    }
+}
+
+// all 65536 gates through the same device function the main kernel uses (up = 1.0)
+__global__ void silu_probe_kernel(uint16_t* __restrict__ out, const uint16_t* __restrict__ table) {
+    uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= 32768u) return;
+    uint32_t g2 = (2u * i) | ((2u * i + 1u) << 16);
+    uint32_t y = silu_mul_pair(g2, 0x3f803f80u, table);
+    out[2 * i] = (uint16_t)(y & 0xffffu);
+    out[2 * i + 1] = (uint16_t)(y >> 16);
+}
+
+// Table pointer of the current device; the first call per device enqueues the fill on `st`.
+static int silu_table_for_stream(cudaStream_t st, const uint16_t** out) {
+    static std::atomic<int> ready[64];
+    int dev = 0;
+    KBN_CUDA(cudaGetDevice(&dev));
+    KBN_REQUIRE(dev >= 0 && dev < 64, KBN_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+    uint16_t* table = nullptr;
+    KBN_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&table), g_silu_table));
+    if (!ready[dev].load(std::memory_order_acquire)) {
+        // Enqueued on the caller's stream, so the caller's kernel is ordered after it; a second
+        // thread racing here merely refills the same values.  The device-wide sync makes the
+        // table visible to every other stream before the flag is published.
+        silu_table_kernel<<<256, 256, 0, st>>>(table);
+        KBN_CHECK_LAUNCH();
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        cudaStreamIsCapturing(st, &cap);
+        if (cap == cudaStreamCaptureStatusNone) {
+            KBN_CUDA(cudaStreamSynchronize(st));
+            ready[dev].store(1, std::memory_order_release);
+        }
+    }
+    *out = table;
+    return KBN_OK;
+}
+
+}  // namespace kbn
+
+extern "C" int kbn_silu_mul_quant_1x128(const void* in, int64_t M, int64_t N2, int64_t ld_in, void* q,
+                                        int64_t ld_q, float* scale, int64_t s_row, int64_t s_grp, float eps,
+                                        int ue8m0, kbn_stream_t stream) {
+    using namespace kbn;
+    KBN_REQUIRE(M >= 0 && N2 >= 0, KBN_ERR_ARG, "kbn_silu_mul_quant_1x128: negative size");
+    if (M == 0 || N2 == 0) return KBN_OK;
+    KBN_REQUIRE(in && q && scale, KBN_ERR_ARG, "kbn_silu_mul_quant_1x128: null pointer");
+    KBN_REQUIRE(N2 % 128 == 0, KBN_ERR_ARG, "kbn_silu_mul_quant_1x128: N2=%lld must be a multiple of 128", (long long)N2);
+    KBN_REQUIRE(ld_in >= 2 * N2 && ld_q >= N2, KBN_ERR_ARG, "kbn_silu_mul_quant_1x128: row stride too small");
+    KBN_REQUIRE(ld_in % 8 == 0 && ld_q % 8 == 0 && aligned16(in) && ((reinterpret_cast<uintptr_t>(q) & 7u) == 0),
+                KBN_ERR_ARG, "kbn_silu_mul_quant_1x128: pointers/strides must be 16-byte (in) and 8-byte (q) aligned");
+    KBN_REQUIRE(eps >= 1e-30f && eps < 1e30f, KBN_ERR_ARG, "kbn_silu_mul_quant_1x128: eps %g outside [1e-30, 1e30)", (double)eps);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const uint16_t* table = nullptr;
+    int rc = silu_table_for_stream(st, &table);
+    if (rc != KBN_OK) return rc;
+    constexpr int U = 2;
+    const int64_t NG = M * (N2 / 128);
+    int64_t blocks = (NG + 16 * U - 1) / (16 * U);
+    KBN_REQUIRE(blocks < (1ll << 31), KBN_ERR_ARG, "kbn_silu_mul_quant_1x128: too many groups");
+    const auto* ib = static_cast<const __nv_bfloat16*>(in);
+    auto* qb = static_cast<uint8_t*>(q);
+    if (ue8m0)
+        silu_mul_quant_kernel<true, U><<<(unsigned)blocks, 256, 0, st>>>(ib, M, N2, ld_in, qb, ld_q, scale, s_row, s_grp, eps, table);
+    else
+        silu_mul_quant_kernel<false, U><<<(unsigned)blocks, 256, 0, st>>>(ib, M, N2, ld_in, qb, ld_q, scale, s_row, s_grp, eps, table);
+    KBN_CHECK_LAUNCH();
+    return KBN_OK;
+}
+
+extern "C" int kbn_silu_bf16_table(void* out_u16, kbn_stream_t stream) {
+    using namespace kbn;
+    KBN_REQUIRE(out_u16, KBN_ERR_ARG, "kbn_silu_bf16_table: null pointer");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const uint16_t* table = nullptr;
+    int rc = silu_table_for_stream(st, &table);
+    if (rc != KBN_OK) return rc;
+    silu_probe_kernel<<<128, 256, 0, st>>>(static_cast<uint16_t*>(out_u16), table);
+    KBN_CHECK_LAUNCH();
+    return KBN_OK;
+}

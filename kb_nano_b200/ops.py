@@ -1,0 +1,177 @@
+"""Tensor-level entry points: validate torch tensors, pass raw pointers to the C ABI.
+
+PyTorch is used for device memory and streams only; every function enqueues hand-written
+sm_100a kernels on the current stream of the tensors' device and returns without syncing.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+
+FP8 = torch.float8_e4m3fn
+GROUP = 128
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _cuda(*tensors: torch.Tensor) -> torch.device:
+    dev = tensors[0].device
+    for t in tensors:
+        if not t.is_cuda:
+            raise ValueError("kb_nano_b200 ops need CUDA tensors (there is no CPU path)")
+        if t.device != dev:
+            raise ValueError("all tensors must be on the same device")
+    return dev
+
+
+class _on:
+    """Make the tensors' device current for the duration of a call (no-op when it already is)."""
+
+    def __init__(self, dev: torch.device):
+        self.guard = None if dev.index == torch.cuda.current_device() else torch.cuda.device(dev)
+
+    def __enter__(self):
+        if self.guard is not None:
+            self.guard.__enter__()
+
+    def __exit__(self, *a):
+        if self.guard is not None:
+            self.guard.__exit__(*a)
+
+
+def _scale_strides(scale: torch.Tensor, rows: int, groups: int) -> tuple[int, int]:
+    if scale.dtype != torch.float32 or scale.dim() != 2 or tuple(scale.shape) != (rows, groups):
+        raise ValueError(f"scale must be float32 [{rows}, {groups}], got {scale.dtype} {tuple(scale.shape)}")
+    return scale.stride(0), scale.stride(1)
+
+
+def per_token_group_quant_fp8(x: torch.Tensor, out_fp8: torch.Tensor, out_scale: torch.Tensor,
+                              use_ue8m0: bool = True, eps: float = 1e-10) -> None:
+    """In-place 1x128 quantisation: x bf16 [M,K] -> out_fp8 [M,K], out_scale fp32 [M,ceil(K/128)] (any strides)."""
+    dev = _cuda(x, out_fp8, out_scale)
+    if x.dim() != 2 or x.dtype != torch.bfloat16:
+        raise ValueError(f"x must be bf16 [M,K], got {x.dtype} {tuple(x.shape)}")
+    if out_fp8.dtype != FP8 or tuple(out_fp8.shape) != tuple(x.shape):
+        raise ValueError("out_fp8 must be float8_e4m3fn with x's shape")
+    if x.stride(1) != 1 or out_fp8.stride(1) != 1:
+        raise ValueError("x and out_fp8 must be contiguous along K")
+    m, k = x.shape
+    s_row, s_grp = _scale_strides(out_scale, m, (k + GROUP - 1) // GROUP)
+    with _on(dev):
+        _lib.check(_lib.load().kbn_quant_1x128(x.data_ptr(), m, k, x.stride(0) if m > 1 else k, out_fp8.data_ptr(),
+                                               out_fp8.stride(0) if m > 1 else k, out_scale.data_ptr(), s_row, s_grp,
+                                               eps, int(use_ue8m0), _stream(x)))
+
+
+def silu_mul_quant_fp8(inp: torch.Tensor, out_fp8: torch.Tensor, out_scale: torch.Tensor,
+                       use_ue8m0: bool = True, eps: float = 1e-10) -> None:
+    """inp bf16 [M, 2*N2] (gate|up) -> out_fp8 [M,N2], out_scale fp32 [M,N2/128] (any strides)."""
+    dev = _cuda(inp, out_fp8, out_scale)
+    if inp.dim() != 2 or inp.dtype != torch.bfloat16 or inp.stride(1) != 1:
+        raise ValueError("inp must be bf16 [M, 2*N2], contiguous along the last dim")
+    m, n = inp.shape
+    n2 = n // 2
+    if n % 2 or n2 % GROUP:
+        raise ValueError(f"N//2={n2} must be a multiple of {GROUP}")
+    if out_fp8.dtype != FP8 or tuple(out_fp8.shape) != (m, n2) or out_fp8.stride(1) != 1:
+        raise ValueError("out_fp8 must be float8_e4m3fn [M, N2], contiguous along the last dim")
+    s_row, s_grp = _scale_strides(out_scale, m, n2 // GROUP)
+    with _on(dev):
+        _lib.check(_lib.load().kbn_silu_mul_quant_1x128(inp.data_ptr(), m, n2, inp.stride(0) if m > 1 else n,
+                                                        out_fp8.data_ptr(), out_fp8.stride(0) if m > 1 else n2,
+                                                        out_scale.data_ptr(), s_row, s_grp, eps, int(use_ue8m0),
+                                                        _stream(inp)))
+
+
+def silu_bf16_table(device: torch.device | str = "cuda") -> torch.Tensor:
+    """bf16 [65536]: silu(g) rounded to bf16 for every gate bit pattern g, as the fused kernel computes it."""
+    out = torch.empty(65536, dtype=torch.int16, device=device)
+    with _on(out.device):
+        _lib.check(_lib.load().kbn_silu_bf16_table(out.data_ptr(), _stream(out)))
+    return out.view(torch.bfloat16)
+
+
+def _check_ab(a: torch.Tensor, b: torch.Tensor, k: int) -> None:
+    if a.dtype != FP8 or b.dtype != FP8:
+        raise ValueError("A and B must be float8_e4m3fn")
+    if not a.is_contiguous() or not b.is_contiguous():
+        raise ValueError("A and B must be contiguous (K-major)")
+    if a.shape[-1] != k or b.shape[-1] != k:
+        raise ValueError("A and B disagree on K")
+
+
+def _check_sb(sb: torch.Tensor, lead: tuple, n: int, k: int) -> torch.Tensor:
+    want = (*lead, (n + 127) // 128, (k + 127) // 128)
+    if sb.dtype != torch.float32 or tuple(sb.shape) != want:
+        raise ValueError(f"weight scale must be float32 {want}, got {sb.dtype} {tuple(sb.shape)}")
+    return sb if sb.is_contiguous() else sb.contiguous()
+
+
+def fp8_gemm_nt(a_q: torch.Tensor, a_s: torch.Tensor, b_q: torch.Tensor, b_s: torch.Tensor, out: torch.Tensor) -> None:
+    """out bf16 [M,N] = (a_q, a_s [M,K/128]) @ (b_q [N,K], b_s [N/128,K/128])^T, written in place."""
+    dev = _cuda(a_q, a_s, b_q, b_s, out)
+    m, k = a_q.shape
+    n = b_q.shape[0]
+    _check_ab(a_q, b_q, k)
+    sa_row, sa_grp = _scale_strides(a_s, m, (k + 127) // 128)
+    b_s = _check_sb(b_s, (), n, k)
+    if out.dtype != torch.bfloat16 or tuple(out.shape) != (m, n) or out.stride(1) != 1:
+        raise ValueError("out must be bf16 [M,N], contiguous along N")
+    with _on(dev):
+        _lib.check(_lib.load().kbn_fp8_gemm_nt(a_q.data_ptr(), a_s.data_ptr(), sa_row, sa_grp, b_q.data_ptr(),
+                                               b_s.data_ptr(), out.data_ptr(), out.stride(0) if m > 1 else n, m, n, k,
+                                               _stream(out)))
+
+
+def m_grouped_fp8_gemm_nt_contiguous(a_q, a_s, b_q, b_s, out, expert_ids) -> None:
+    """Rows of a_q [M_sum,K] use expert expert_ids[row] of b_q [E,N,K]; rows with id < 0 are not written."""
+    dev = _cuda(a_q, a_s, b_q, b_s, out, expert_ids)
+    m, k = a_q.shape
+    e, n, _ = b_q.shape
+    _check_ab(a_q, b_q, k)
+    sa_row, sa_grp = _scale_strides(a_s, m, (k + 127) // 128)
+    b_s = _check_sb(b_s, (e,), n, k)
+    if out.dtype != torch.bfloat16 or tuple(out.shape) != (m, n) or out.stride(1) != 1:
+        raise ValueError("out must be bf16 [M_sum,N], contiguous along N")
+    if expert_ids.dtype != torch.int32 or expert_ids.numel() != m or not expert_ids.is_contiguous():
+        raise ValueError("expert_ids must be contiguous int32 [M_sum]")
+    with _on(dev):
+        _lib.check(_lib.load().kbn_fp8_grouped_gemm_contig(a_q.data_ptr(), a_s.data_ptr(), sa_row, sa_grp,
+                                                           b_q.data_ptr(), b_s.data_ptr(), out.data_ptr(),
+                                                           out.stride(0) if m > 1 else n, expert_ids.data_ptr(),
+                                                           m, n, k, e, _stream(out)))
+
+
+def m_grouped_fp8_gemm_nt_masked(a_q, a_s, b_q, b_s, out, masked_m) -> None:
+    """a_q [E,max_m,K], a_s [E,max_m,K/128], b_q [E,N,K], out bf16 [E,max_m,N]; rows >= masked_m[e] untouched."""
+    dev = _cuda(a_q, a_s, b_q, b_s, out, masked_m)
+    e, max_m, k = a_q.shape
+    n = b_q.shape[1]
+    _check_ab(a_q, b_q, k)
+    if b_q.shape[0] != e:
+        raise ValueError("A and B disagree on the number of experts")
+    if a_s.dtype != torch.float32 or tuple(a_s.shape) != (e, max_m, (k + 127) // 128):
+        raise ValueError("a_s must be float32 [E, max_m, ceil(K/128)]")
+    b_s = _check_sb(b_s, (e,), n, k)
+    if out.dtype != torch.bfloat16 or tuple(out.shape) != (e, max_m, n) or not out.is_contiguous():
+        raise ValueError("out must be contiguous bf16 [E,max_m,N]")
+    if masked_m.dtype != torch.int32 or masked_m.numel() != e or not masked_m.is_contiguous():
+        raise ValueError("masked_m must be contiguous int32 [E]")
+    with _on(dev):
+        _lib.check(_lib.load().kbn_fp8_grouped_gemm_masked(a_q.data_ptr(), a_s.data_ptr(), a_s.stride(0), a_s.stride(1),
+                                                           a_s.stride(2), b_q.data_ptr(), b_s.data_ptr(), out.data_ptr(),
+                                                           masked_m.data_ptr(), e, max_m, n, k, _stream(out)))
+
+
+def gemm_status(device: torch.device | str = "cuda") -> int:
+    """0 unless a bounded wait inside a GEMM kernel has ever run out in this process (synchronises)."""
+    dev = torch.device(device)
+    out = ctypes.c_int32(0)
+    with _on(dev if dev.index is not None else torch.device("cuda", torch.cuda.current_device())):
+        _lib.check(_lib.load().kbn_gemm_status(ctypes.byref(out), torch.cuda.current_stream().cuda_stream))
+    return int(out.value)

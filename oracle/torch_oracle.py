@@ -1,0 +1,169 @@
+"""CPU oracle, torch edition.  TEST INFRASTRUCTURE ONLY.
+
+A restatement, in plain torch CPU ops, of the torch path kb-nano's reference uses to
+define the FP8 W8A8 hot path.  Only tests/, the smoke check and bench.py's CPU-baseline
+legs may import this module; the product package never does.
+
+Reference lines each function follows (paths relative to the kb-nano tree):
+  quant_1x128           tasks/reference/L1/fp8_linear.py:41-64
+  silu_mul_bf16         tasks/baseline/L1/silu_mul_quant_fp8.py:54-60
+                        (== tasks/reference/L1/silu_and_mul.py:18-21 on bf16 input)
+  silu_mul_quant_1x128  tasks/baseline/L1/silu_mul_quant_fp8.py:54-76
+  block_quant_128x128   bench/kernels/scenario_registry.py:185-221
+  dequant_rows/_blocks  tasks/reference/L1/fp8_linear.py:26-38
+  gemm_nt_dequant       tasks/reference/L1/fp8_linear.py:100-104 applied to quantised A
+  grouped_gemm_contig   tasks/reference/L1/moe_grouped_gemm.py:39-91 (per-expert matmul)
+  grouped_gemm_masked   same arithmetic in the [E, max_m, K] layout (no reference call site)
+  route_sigmoid_topk    tasks/baseline/L1/grouped_topk.py:119-174 with n_group=1, no bias
+  route_softmax_topk    tasks/reference/L1/topk_softmax.py:46-52
+  moe_layer             tasks/baseline/L2/fused_experts.py:246-283,119-136
+                        (quant -> GEMM1 -> silu*up+quant -> GEMM2 -> weighted sum over top-k
+                        in the activation dtype)
+"""
+from __future__ import annotations
+
+import torch
+
+GROUP = 128
+FP8 = torch.float8_e4m3fn
+FP8_MAX = 448.0
+
+
+def _scale_from_absmax(absmax: torch.Tensor, eps: float, ue8m0: bool) -> torch.Tensor:
+    s = absmax.clamp_min(eps) / FP8_MAX
+    if ue8m0:
+        s = torch.pow(2.0, torch.ceil(torch.log2(s)))
+    return s
+
+
+def quant_1x128(x: torch.Tensor, eps: float = 1e-10, ue8m0: bool = True):
+    """x [M,K] (bf16/fp32) -> (q e4m3 [M,K], scale fp32 [M, ceil(K/128)])."""
+    m, k = x.shape
+    g = (k + GROUP - 1) // GROUP
+    xf = x.float()
+    if g * GROUP != k:
+        pad = xf.new_zeros(m, g * GROUP)
+        pad[:, :k] = xf
+    else:
+        pad = xf
+    s = _scale_from_absmax(pad.view(m, g, GROUP).abs().amax(dim=-1), eps, ue8m0)
+    full = s.repeat_interleave(GROUP, dim=-1)[:, :k]
+    q = torch.clamp(xf / full, -FP8_MAX, FP8_MAX).to(FP8)
+    return q, s
+
+
+def silu_mul_bf16(x: torch.Tensor) -> torch.Tensor:
+    """x [M, 2*N2] bf16 -> bf16 [M, N2]: silu in fp32, rounded to bf16, times up in bf16."""
+    n2 = x.shape[-1] // 2
+    g = x[..., :n2].float()
+    s = (g / (1.0 + torch.exp(-g))).to(x.dtype)
+    return s * x[..., n2:]
+
+
+def silu_mul_quant_1x128(x: torch.Tensor, eps: float = 1e-10, ue8m0: bool = True):
+    return quant_1x128(silu_mul_bf16(x), eps, ue8m0)
+
+
+def block_quant_128x128(w: torch.Tensor, eps: float = 1e-10, ue8m0: bool = True):
+    """w [..., R, C] -> (q e4m3 same shape, scale fp32 [..., ceil(R/128), ceil(C/128)])."""
+    shp = w.shape
+    r, c = shp[-2], shp[-1]
+    rb, cb = (r + 127) // 128, (c + 127) // 128
+    flat = w.reshape(-1, r, c).float()
+    pad = flat.new_zeros(flat.shape[0], rb * 128, cb * 128)
+    pad[:, :r, :c] = flat
+    s = _scale_from_absmax(pad.view(-1, rb, 128, cb, 128).abs().amax(dim=(2, 4)), eps, ue8m0)
+    full = s.repeat_interleave(128, dim=-2).repeat_interleave(128, dim=-1)[:, :r, :c]
+    q = torch.clamp(flat / full, -FP8_MAX, FP8_MAX).to(FP8).reshape(shp)
+    return q, s.reshape(*shp[:-2], rb, cb)
+
+
+def dequant_rows(q: torch.Tensor, s: torch.Tensor) -> torch.Tensor:
+    k = q.shape[-1]
+    return q.float() * s.float().repeat_interleave(GROUP, dim=-1)[..., :k]
+
+
+def dequant_blocks(q: torch.Tensor, s: torch.Tensor) -> torch.Tensor:
+    r, c = q.shape[-2], q.shape[-1]
+    full = s.float().repeat_interleave(128, dim=-2).repeat_interleave(128, dim=-1)[..., :r, :c]
+    return q.float() * full
+
+
+def gemm_nt_dequant(a_q, sa, w_q, sw, bias=None) -> torch.Tensor:
+    out = torch.nn.functional.linear(dequant_rows(a_q, sa), dequant_blocks(w_q, sw),
+                                     bias.float() if bias is not None else None)
+    return out.to(torch.bfloat16)
+
+
+def fp8_linear(x_bf16, w_q, sw, bias=None) -> torch.Tensor:
+    k = w_q.shape[-1]
+    x2 = x_bf16.reshape(-1, k)
+    a_q, sa = quant_1x128(x2)
+    out = gemm_nt_dequant(a_q, sa, w_q, sw, bias)
+    return out.view(*x_bf16.shape[:-1], w_q.shape[0])
+
+
+def grouped_gemm_contig(a_q, sa, b_q, sb, row_expert, out=None) -> torch.Tensor:
+    """Rows with row_expert < 0 are left untouched (zero if `out` is not given)."""
+    m, n = a_q.shape[0], b_q.shape[1]
+    if out is None:
+        out = torch.zeros(m, n, dtype=torch.bfloat16)
+    a_d = dequant_rows(a_q, sa)
+    for e in torch.unique(row_expert).tolist():
+        if e < 0:
+            continue
+        rows = (row_expert == e).nonzero().flatten()
+        out[rows] = (a_d[rows] @ dequant_blocks(b_q[e], sb[e]).t()).to(torch.bfloat16)
+    return out
+
+
+def grouped_gemm_masked(a_q, sa, b_q, sb, masked_m, out=None) -> torch.Tensor:
+    e_l, max_m, _ = a_q.shape
+    n = b_q.shape[1]
+    if out is None:
+        out = torch.zeros(e_l, max_m, n, dtype=torch.bfloat16)
+    for e in range(e_l):
+        mm = int(masked_m[e])
+        if mm == 0:
+            continue
+        out[e, :mm] = (dequant_rows(a_q[e, :mm], sa[e, :mm]) @ dequant_blocks(b_q[e], sb[e]).t()).to(torch.bfloat16)
+    return out
+
+
+def route_sigmoid_topk(logits: torch.Tensor, k: int):
+    scores = torch.sigmoid(logits.float())
+    w, ids = torch.topk(scores, k, dim=-1, sorted=True)
+    w = w / w.sum(dim=-1, keepdim=True)
+    return w, ids.to(torch.int32)
+
+
+def route_softmax_topk(logits: torch.Tensor, k: int):
+    probs = torch.softmax(logits.float(), dim=-1)
+    w, ids = torch.topk(probs, k, dim=-1, sorted=True)
+    w = w / w.sum(dim=-1, keepdim=True)
+    return w, ids.to(torch.int32)
+
+
+def moe_layer(x, w13_q, w13_s, w2_q, w2_s, topk_w, topk_ids, experts=None) -> torch.Tensor:
+    """FP8 MoE expert pipeline on CPU, per expert.
+
+    `experts` restricts the computation to a subset of expert ids (pairs routed elsewhere
+    contribute nothing); used for bounded CPU samples and for the per-rank view of the
+    expert-parallel layer.
+    """
+    t, h = x.shape
+    a_q, sa = quant_1x128(x)
+    a_d = dequant_rows(a_q, sa)
+    acc = torch.zeros(t, topk_ids.shape[1], h, dtype=x.dtype)
+    ids = topk_ids.long()
+    todo = torch.unique(ids).tolist() if experts is None else list(experts)
+    for e in todo:
+        tok, slot = (ids == e).nonzero(as_tuple=True)
+        if tok.numel() == 0:
+            continue
+        h1 = (a_d[tok] @ dequant_blocks(w13_q[e], w13_s[e]).t()).to(torch.bfloat16)
+        q2, s2 = silu_mul_quant_1x128(h1)
+        h2 = (dequant_rows(q2, s2) @ dequant_blocks(w2_q[e], w2_s[e]).t()).to(torch.bfloat16)
+        acc[tok, slot] = h2
+    # dtype promotion as in the reference: bf16 rows times the router's weights (fp32 or bf16)
+    return (acc * topk_w.unsqueeze(-1)).sum(dim=1).to(x.dtype)
