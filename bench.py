@@ -1,0 +1,635 @@
+#!/usr/bin/env python
+"""Benchmark of the FP8 W8A8 hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
+
+Prints ONE JSON line.  A "step" is one pass of the hot path over one batch of seeded synthetic
+input.  `value` is device-timed with the inputs resident in HBM; `e2e` repeats the measurement
+through the public API with pinned HOST buffers (H2D of the step's inputs and D2H of its result
+inside the timed region).  `roofline` is for the dominant kernel, timed with CUDA events on the
+launching stream; `cpu_baseline` times the CPU oracle on a bounded sample of the same workload.
+`--impl reference` times the reference's CPU path (the torch edition of the oracle: the reference is
+Python and its CPU path is torch) on the host cores for the same workload and metric.
+
+Workloads (BASELINE.json configs): ep_moe (configs[3]: DeepSeek-V3-shaped expert-parallel MoE layer,
+128 tokens per rank, masked layout; the default, the one that shards over GPUs), moe_c3
+(configs[2]), moe_c5 (configs[4]), silu_c2 (configs[1]), quant_c1 and gemm_c1 (configs[0]).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+FP8 = torch.float8_e4m3fn
+
+
+# ------------------------------------------------------------------------------------------------
+# helpers
+# ------------------------------------------------------------------------------------------------
+
+def measured_peaks() -> dict:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]),
+                "bf16_tflops_sustained": float(p.get("bf16_tflops_sustained", p["bf16_tflops"])), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs."""
+
+    def __init__(self, index: int, period_s: float = 0.005):
+        self.index, self.period = index, period_s
+        self.samples, self.active = [], False
+        self._stop = threading.Event()
+        self._thr = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        while not self._stop.is_set():
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)
+                reasons = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h) if hasattr(nv, "nvmlDeviceGetCurrentClocksEventReasons") \
+                    else nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                if self.active:
+                    self.samples.append((mhz, reasons))
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def start(self):
+        if self.nv is not None:
+            self._thr = threading.Thread(target=self._run, daemon=True)
+            self._thr.start()
+
+    def stop(self) -> dict:
+        self._stop.set()
+        if self._thr is not None:
+            self._thr.join(timeout=1.0)
+        if self.nv is None or not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        nv = self.nv
+        mhz = sorted(s[0] for s in self.samples)
+        bits = 0
+        for _, r in self.samples:
+            bits |= r
+        names = {"sw_power_cap": 0x4, "hw_slowdown": 0x8, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40,
+                 "hw_power_brake": 0x80, "sync_boost": 0x10, "display_clock": 0x100, "applications_clocks": 0x2}
+        try:
+            mx = nv.nvmlDeviceGetMaxClockInfo(self.h, nv.NVML_CLOCK_SM)
+        except Exception:
+            mx = None
+        return {"sm_mhz": mhz[len(mhz) // 2], "sm_max_mhz": mx, "reasons": [k for k, v in names.items() if bits & v],
+                "samples": len(mhz)}
+
+
+def dist_info():
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", str(rank)))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    return rank, local, world
+
+
+class Timed:
+    """K steps, each bracketed by CUDA events on the current stream; an optional L2 flush runs between
+    steps outside the events.  Whole region bracketed by barrier + synchronize; max over ranks."""
+
+    def __init__(self, world: int, flush_bytes: int = 0, device=None):
+        self.world = world
+        self.flush = torch.empty(flush_bytes, dtype=torch.uint8, device=device) if flush_bytes else None
+
+    def barrier(self):
+        if self.world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    def run(self, step, steps: int, warmup: int, sampler: ClockSampler | None = None) -> float:
+        for i in range(warmup):
+            step(i)
+        self.barrier()
+        if sampler is not None:
+            sampler.active = True
+        evs = []
+        for i in range(steps):
+            if self.flush is not None:
+                self.flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            step(warmup + i)
+            b.record()
+            evs.append((a, b))
+        self.barrier()
+        if sampler is not None:
+            sampler.active = False
+        total_ms = sum(a.elapsed_time(b) for a, b in evs)
+        if self.world > 1:
+            t = torch.tensor([total_ms], dtype=torch.float64, device="cuda")
+            torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+            total_ms = float(t.item())
+        return total_ms / steps
+
+
+def cpu_threads() -> int:
+    n = os.cpu_count() or 1
+    try:
+        n = min(n, len(os.sched_getaffinity(0)))
+    except Exception:
+        pass
+    return n
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU side (oracle port): used by cpu_baseline and by --impl reference
+# ------------------------------------------------------------------------------------------------
+
+def cpu_silu_c2(rows: int, reps: int):
+    from kb_nano_b200 import inputs
+    from oracle import torch_oracle as to
+    x = inputs.activations(rows, 4096, seed=0, outlier_frac=1e-3)
+    to.silu_mul_quant_1x128(x)
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        to.silu_mul_quant_1x128(x)
+    dt = (time.perf_counter() - t0) / reps
+    byts = rows * (4096 * 2 + 2048 + 64)
+    return byts / dt / 1e9, dt, f"{rows} of 16384 rows, {reps} passes, torch CPU port"
+
+
+def cpu_quant(m: int, k: int, reps: int):
+    from kb_nano_b200 import inputs
+    from oracle import torch_oracle as to
+    x = inputs.activations(m, k, seed=0)
+    to.quant_1x128(x)
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        to.quant_1x128(x)
+    dt = (time.perf_counter() - t0) / reps
+    return (3 * m * k + 4 * m * (k // 128)) / dt / 1e9, dt, f"[{m},{k}] full size, {reps} passes, torch CPU port"
+
+
+def cpu_gemm_c1(n_cols: int, reps: int):
+    from kb_nano_b200 import inputs
+    from oracle import torch_oracle as to
+    x = inputs.activations(512, 7168, seed=0)
+    w_q, w_s = inputs.weight(n_cols, 7168, seed=1)
+    a_q, a_s = to.quant_1x128(x)
+    to.gemm_nt_dequant(a_q, a_s, w_q, w_s)
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        to.gemm_nt_dequant(a_q, a_s, w_q, w_s)
+    dt = (time.perf_counter() - t0) / reps
+    return 2.0 * 512 * n_cols * 7168 / dt / 1e12, dt, f"N={n_cols} of 4096 output columns (time is linear in N), {reps} passes, torch CPU port"
+
+
+def cpu_moe(t: int, h: int, i: int, e: int, topk: int, routing: str, n_experts_sample: int, reps: int):
+    """Times the oracle's MoE layer restricted to the first `n_experts_sample` experts that have tokens and
+    scales to the whole layer by the share of (token, slot) pairs those experts hold."""
+    from kb_nano_b200 import inputs
+    from oracle import torch_oracle as to
+    x = inputs.activations(t, h, seed=0)
+    logits = inputs.router_logits(t, e, seed=0)
+    tw, ti = (inputs.route_sigmoid_topk if routing == "sigmoid" else inputs.route_softmax_topk)(logits, topk)
+    counts = torch.bincount(ti.reshape(-1).long(), minlength=e)
+    chosen = [int(x_) for x_ in torch.nonzero(counts).flatten()[:n_experts_sample]]
+    w13_q = torch.zeros(e, 1, 1, dtype=torch.uint8).view(FP8)   # placeholders, indexed per expert below
+    store13, store2 = {}, {}
+    for ex in chosen:
+        store13[ex] = inputs.weight(2 * i, h, seed=1 * 1000003 + ex)
+        store2[ex] = inputs.weight(h, i, seed=2 * 1000003 + ex)
+
+    class _Pick:
+        def __init__(self, d, j):
+            self.d, self.j = d, j
+
+        def __getitem__(self, ex):
+            return self.d[ex][self.j]
+
+    def one():
+        return to.moe_layer(x, _Pick(store13, 0), _Pick(store13, 1), _Pick(store2, 0), _Pick(store2, 1), tw, ti, experts=chosen)
+
+    one()
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        one()
+    dt = (time.perf_counter() - t0) / reps
+    share = float(counts[chosen].sum()) / float(counts.sum())
+    # dequantising an expert's weights costs the same however few rows it has: scale by experts, not pairs,
+    # when rows per expert are few
+    active = int((counts > 0).sum())
+    est_full = dt * max(active / len(chosen), 1.0) if t * topk / e < 64 else dt / share
+    del w13_q
+    return t / est_full, dt, (f"{len(chosen)} of {active} active experts with their routed rows ({share * 100:.1f}% of pairs), "
+                              f"{reps} passes, torch CPU port; whole layer extrapolated")
+
+
+# ------------------------------------------------------------------------------------------------
+# GPU workloads
+# ------------------------------------------------------------------------------------------------
+
+def wl_silu_c2(args, rank, world, dev, sampler):
+    from kb_nano_b200 import _lib, inputs, ops
+    m, n = 16384, 4096
+    nbuf = 4
+    xs = [inputs.activations(m, n, seed=b, device=dev, outlier_frac=1e-3) for b in range(nbuf)]
+    q = torch.empty(m, n // 2, dtype=FP8, device=dev)
+    s = torch.empty(n // 256, m, device=dev).t()
+    byts = m * n * 2 + m * n // 2 + 4 * m * (n // 256)
+    timer = Timed(world, 0, dev)
+    l0 = _lib.launch_count()
+    ms = timer.run(lambda i: ops.silu_mul_quant_fp8(xs[i % nbuf], q, s), args.steps, args.warmup, sampler)
+    launches = _lib.launch_count() - l0
+    # e2e: pinned host input, device result copied back
+    host_in = [x.cpu().pin_memory() for x in xs[:2]]
+    d_in = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+    h_q = torch.empty(m, n // 2, dtype=torch.uint8).pin_memory()
+    h_s = torch.empty(n // 256, m, dtype=torch.float32).pin_memory()
+
+    def e2e_step(i):
+        d_in.copy_(host_in[i % 2], non_blocking=True)
+        ops.silu_mul_quant_fp8(d_in, q, s)
+        h_q.copy_(q.view(torch.uint8), non_blocking=True)
+        h_s.copy_(s.t(), non_blocking=True)
+
+    ms_e2e = Timed(world, 0, dev).run(e2e_step, max(3, args.steps // 4), 2)
+    peaks = measured_peaks()
+    gbs = byts / (ms * 1e-3) / 1e9
+    return {
+        "metric": "fused SiLU*Mul+FP8 quant throughput", "value": gbs * world, "unit": "GB/s", "ms_per_step": ms,
+        "dtype": "bf16->e4m3 (fp32 math)", "scaling": "weak",
+        "config": {"workload": "silu_c2: BASELINE configs[1], bf16 [16384, 2x2048] -> e4m3 [16384,2048] + UE8M0 scales [16384,16]",
+                   "l2": "4 rotating input buffers (537 MB > 126 MB L2)", "replicas": world},
+        "e2e": {"value": byts / (ms_e2e * 1e-3) / 1e9 * world, "unit": "GB/s", "h2d_bytes_per_step": m * n * 2,
+                "d2h_bytes_per_step": m * n // 2 + 4 * m * (n // 256)},
+        "gpu_launches": launches // (args.steps + args.warmup) * args.steps,
+        "roofline": {"bound": "hbm", "kernel": "silu_mul_quant_kernel", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": gbs / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
+                     "algorithmic_bytes_per_launch": byts},
+        "_cpu": lambda: cpu_silu_c2(2048, 3),
+    }
+
+
+def wl_quant_c1(args, rank, world, dev, sampler, m=512, k=7168):
+    from kb_nano_b200 import _lib, inputs, ops
+    x = inputs.activations(m, k, seed=0, device=dev)
+    q = torch.empty(m, k, dtype=FP8, device=dev)
+    s = torch.empty(k // 128, m, device=dev).t()
+    byts = 3 * m * k + 4 * m * (k // 128)
+    l0 = _lib.launch_count()
+    ms = Timed(world, 256 << 20, dev).run(lambda i: ops.per_token_group_quant_fp8(x, q, s), args.steps, args.warmup, sampler)
+    launches = _lib.launch_count() - l0
+    hx = x.cpu().pin_memory()
+    dx = torch.empty_like(x)
+    hq = torch.empty(m, k, dtype=torch.uint8).pin_memory()
+
+    def e2e_step(i):
+        dx.copy_(hx, non_blocking=True)
+        ops.per_token_group_quant_fp8(dx, q, s)
+        hq.copy_(q.view(torch.uint8), non_blocking=True)
+
+    ms_e2e = Timed(world, 256 << 20, dev).run(e2e_step, args.steps, 2)
+    peaks = measured_peaks()
+    gbs = byts / (ms * 1e-3) / 1e9
+    return {
+        "metric": "1x128 FP8 activation quant throughput", "value": gbs * world, "unit": "GB/s", "ms_per_step": ms,
+        "dtype": "bf16->e4m3", "scaling": "weak",
+        "config": {"workload": f"quant_{'c1' if m == 512 else 'c3'}: activation of BASELINE configs[{0 if m == 512 else 2}], bf16 [{m},{k}], column-major UE8M0 scales",
+                   "l2": "256 MB flush buffer written between steps", "replicas": world},
+        "e2e": {"value": byts / (ms_e2e * 1e-3) / 1e9 * world, "unit": "GB/s", "h2d_bytes_per_step": m * k * 2, "d2h_bytes_per_step": m * k},
+        "gpu_launches": launches // (args.steps + args.warmup) * args.steps,
+        "roofline": {"bound": "hbm", "kernel": "quant_1x128_kernel", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": gbs / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"], "algorithmic_bytes_per_launch": byts},
+        "_cpu": lambda: cpu_quant(m, k, 20 if m == 512 else 3),
+    }
+
+
+def wl_gemm_c1(args, rank, world, dev, sampler):
+    from kb_nano_b200 import _lib, inputs, ops
+    m, n, k = 512, 4096, 7168
+    x = inputs.activations(m, k, seed=0, device=dev)
+    w_q, w_s = inputs.weight(n, k, seed=1, device=dev)
+    a_q = torch.empty(m, k, dtype=FP8, device=dev)
+    a_s = torch.empty(k // 128, m, device=dev).t()
+    out = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+    ops.per_token_group_quant_fp8(x, a_q, a_s)
+    flop = 2.0 * m * n * k
+    l0 = _lib.launch_count()
+    ms = Timed(world, 256 << 20, dev).run(lambda i: ops.fp8_gemm_nt(a_q, a_s, w_q, w_s, out), args.steps, args.warmup, sampler)
+    launches = _lib.launch_count() - l0
+    hx = x.cpu().pin_memory()
+    dx = torch.empty_like(x)
+    hout = torch.empty(m, n, dtype=torch.bfloat16).pin_memory()
+
+    def e2e_step(i):   # the Fp8Linear call: quant + GEMM on a host activation, result back on the host
+        dx.copy_(hx, non_blocking=True)
+        ops.per_token_group_quant_fp8(dx, a_q, a_s)
+        ops.fp8_gemm_nt(a_q, a_s, w_q, w_s, out)
+        hout.copy_(out, non_blocking=True)
+
+    ms_e2e = Timed(world, 256 << 20, dev).run(e2e_step, args.steps, 2)
+    peaks = measured_peaks()
+    tf = flop / (ms * 1e-3) / 1e12
+    fp8_peak = 2.0 * peaks["bf16_tflops"]
+    assert ops.gemm_status(dev) == 0
+    return {
+        "metric": "block-scaled FP8 GEMM throughput", "value": tf * world, "unit": "TFLOP/s", "ms_per_step": ms,
+        "dtype": "e4m3 x e4m3 -> fp32 -> bf16", "scaling": "weak",
+        "config": {"workload": "gemm_c1: BASELINE configs[0], M=512 K=7168 N=4096, 1x128 / 128x128 UE8M0 scales",
+                   "l2": "256 MB flush buffer written between steps", "replicas": world},
+        "e2e": {"value": flop / (ms_e2e * 1e-3) / 1e12 * world, "unit": "TFLOP/s", "h2d_bytes_per_step": m * k * 2, "d2h_bytes_per_step": m * n * 2},
+        "gpu_launches": launches // (args.steps + args.warmup) * args.steps,
+        "roofline": {"bound": "tensor", "kernel": "fp8_gemm_kernel", "achieved": tf, "peak": fp8_peak, "unit": "TFLOP/s", "frac": tf / fp8_peak,
+                     "traffic": None, "peak_source": peaks["source"] + " bf16 burst x2 (no FP8 entry in MEASURED_PEAKS.json)",
+                     "frac_of_nominal_4500": tf / 4500.0, "algorithmic_flop_per_launch": flop},
+        "_cpu": lambda: cpu_gemm_c1(512, 3),
+    }
+
+
+def build_moe_inputs(t, h, i, e, topk, routing, dev, seed=0):
+    from kb_nano_b200 import inputs
+    x = inputs.activations(t, h, seed=seed, device=dev)
+    logits = inputs.router_logits(t, e, seed=seed, device=dev)
+    tw, ti = (inputs.route_sigmoid_topk if routing == "sigmoid" else inputs.route_softmax_topk)(logits, topk)
+    w13_q, w13_s = inputs.expert_weights(e, 2 * i, h, seed=1, device=dev)
+    w2_q, w2_s = inputs.expert_weights(e, h, i, seed=2, device=dev)
+    return x, tw.contiguous(), ti.contiguous(), w13_q, w13_s, w2_q, w2_s
+
+
+def wl_moe_single(args, rank, world, dev, sampler, name):
+    """One-GPU MoE layer in the contiguous grouped layout (configs[2] / configs[4])."""
+    from kb_nano_b200 import _lib, moe, ops
+    if name == "moe_c3":
+        t, h, i, e, topk, routing = 4096, 7168, 2048, 256, 8, "sigmoid"
+        desc = "moe_c3: BASELINE configs[2], DeepSeek-V3-shaped FP8 MoE layer, 4096 tokens, 256 experts, top-8, contiguous layout"
+    else:
+        t, h, i, e, topk, routing = 16384, 4096, 14336, 8, 2, "softmax"
+        desc = "moe_c5: BASELINE configs[4], Mixtral-8x7B-shaped FP8 MoE layer, 16384 tokens, 8 experts, top-2, contiguous layout"
+    x, tw, ti, w13_q, w13_s, w2_q, w2_s = build_moe_inputs(t, h, i, e, topk, routing, dev)
+    sc = moe.get_scratch(t, topk, e, h, i, dev)
+    out = torch.empty(t, h, dtype=torch.bfloat16, device=dev)
+
+    def step(_):
+        moe.fused_experts_fp8(x, w13_q, w2_q, tw, ti, e, w13_s, w2_s, scratch=sc, out=out)
+
+    l0 = _lib.launch_count()
+    ms = Timed(world, 0, dev).run(step, args.steps, args.warmup, sampler)
+    launches = _lib.launch_count() - l0
+    # dominant kernel: the two grouped GEMM launches, timed alone with events on the same inputs
+    evs = []
+    for _ in range(max(3, min(args.steps, 10))):
+        a, b, c = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+        a.record()
+        ops.m_grouped_fp8_gemm_nt_contiguous(sc.a_perm, sc.a_s_perm, w13_q, w13_s, sc.mm1(i), sc.row_expert)
+        b.record()
+        ops.silu_mul_quant_fp8(sc.mm1(i), sc.a2_q, sc.a2_s)
+        c.record()
+        d, f = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        d.record()
+        ops.m_grouped_fp8_gemm_nt_contiguous(sc.a2_q, sc.a2_s, w2_q, w2_s, sc.mm2(h), sc.row_expert)
+        f.record()
+        evs.append((a, b, d, f))
+    torch.cuda.synchronize()
+    gemm_ms = sum(a.elapsed_time(b) + d.elapsed_time(f) for a, b, d, f in evs) / len(evs) / 2.0   # per launch
+    pairs = t * topk
+    active = int((torch.bincount(ti.reshape(-1).long(), minlength=e) > 0).sum())
+    g1 = active * 2 * i * h + pairs * h + pairs * 2 * i * 2 + 4 * pairs * (h // 128)
+    g2 = active * h * i + pairs * i + pairs * h * 2 + 4 * pairs * (i // 128)
+    flop = 2.0 * pairs * (2 * i * h + h * i)
+    peaks = measured_peaks()
+    assert ops.gemm_status(dev) == 0
+    # e2e through the public layer call with pinned host activations / routing and the result copied back
+    hx, htw, hti = x.cpu().pin_memory(), tw.cpu().pin_memory(), ti.cpu().pin_memory()
+    dx, dtw, dti = torch.empty_like(x), torch.empty_like(tw), torch.empty_like(ti)
+    hout = torch.empty(t, h, dtype=torch.bfloat16).pin_memory()
+
+    def e2e_step(_):
+        dx.copy_(hx, non_blocking=True)
+        dtw.copy_(htw, non_blocking=True)
+        dti.copy_(hti, non_blocking=True)
+        moe.fused_experts_fp8(dx, w13_q, w2_q, dtw, dti, e, w13_s, w2_s, scratch=sc, out=out)
+        hout.copy_(out, non_blocking=True)
+
+    ms_e2e = Timed(world, 0, dev).run(e2e_step, max(3, args.steps // 2), 2)
+    hbm_bound = (pairs / e) < 562      # rows per expert below the machine balance: weights dominate
+    if hbm_bound:
+        ach = (g1 + g2) / 2.0 / (gemm_ms * 1e-3) / 1e9
+        roof = {"bound": "hbm", "kernel": "fp8_gemm_kernel (grouped, 2 launches per layer)", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                "frac": ach / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"], "algorithmic_bytes_per_launch": (g1 + g2) / 2.0,
+                "tflops": flop / 2.0 / (gemm_ms * 1e-3) / 1e12}
+    else:
+        ach = flop / 2.0 / (gemm_ms * 1e-3) / 1e12
+        roof = {"bound": "tensor", "kernel": "fp8_gemm_kernel (grouped, 2 launches per layer)", "achieved": ach, "peak": 2.0 * peaks["bf16_tflops_sustained"],
+                "unit": "TFLOP/s", "frac": ach / (2.0 * peaks["bf16_tflops_sustained"]), "traffic": None,
+                "peak_source": peaks["source"] + " bf16 sustained x2 (no FP8 entry in MEASURED_PEAKS.json)",
+                "frac_of_nominal_4500": ach / 4500.0, "algorithmic_flop_per_launch": flop / 2.0}
+    n_cpu = 4 if name == "moe_c3" else 1
+    return {
+        "metric": "FP8 MoE layer throughput", "value": t / (ms * 1e-3) * world, "unit": "tokens/s", "ms_per_step": ms,
+        "dtype": "e4m3 x e4m3 -> fp32 -> bf16", "scaling": "weak",
+        "config": {"workload": desc, "l2": "expert weights (>= 1.4 GB) exceed the 126 MB L2", "replicas": world,
+                   "layer_hbm_gbs": (g1 + g2 + 3 * t * h + pairs * (h + 2 * 2 * i + i) + (topk + 1) * t * h * 2) / (ms * 1e-3) / 1e9,
+                   "layer_tflops": flop / (ms * 1e-3) / 1e12},
+        "e2e": {"value": t / (ms_e2e * 1e-3) * world, "unit": "tokens/s", "h2d_bytes_per_step": t * h * 2 + t * topk * 8, "d2h_bytes_per_step": t * h * 2},
+        "gpu_launches": launches // (args.steps + args.warmup) * args.steps,
+        "roofline": roof,
+        "_cpu": lambda: cpu_moe(t, h, i, e, topk, routing, n_cpu, 1),
+    }
+
+
+def wl_ep_moe(args, rank, world, dev, sampler):
+    """BASELINE configs[3]: DeepSeek-V3-shaped MoE layer, experts split over the ranks, 128 tokens per rank,
+    masked layout with at most 256 rows per expert, dispatch/combine by peer stores over NVLink."""
+    from kb_nano_b200 import _lib, ep, inputs, ops
+    t, h, i, e, topk, max_m = 128, 7168, 2048, 256, 8, 256
+    lo, hi = ep.expert_range(rank, world, e)
+    e_l = hi - lo
+    x = inputs.activations(t, h, seed=rank, device=dev)
+    tw, ti = inputs.route_sigmoid_topk(inputs.router_logits(t, e, seed=rank, device=dev), topk)
+    tw, ti = tw.contiguous(), ti.contiguous()
+    w13_q, w13_s = inputs.expert_weights(e_l, 2 * i, h, seed=1, device=dev, first=lo)
+    w2_q, w2_s = inputs.expert_weights(e_l, h, i, seed=2, device=dev, first=lo)
+    layer = ep.EpMoe(rank, world, e, h, i, max_tokens=t, topk=topk, max_m=max_m, device=dev)
+    out = torch.empty(t, h, dtype=torch.bfloat16, device=dev)
+
+    def step(_):
+        layer.forward(x, ti, tw, w13_q, w13_s, w2_q, w2_s, out=out)
+
+    l0 = _lib.launch_count()
+    ms = Timed(world, 0, dev).run(step, args.steps, args.warmup, sampler)
+    launches = _lib.launch_count() - l0
+    layer.check()
+    # rows every local expert receives (routing of all ranks is reproducible from the seeds)
+    counts = torch.zeros(e, dtype=torch.long)
+    for r in range(world):
+        _, ti_r = inputs.route_sigmoid_topk(inputs.router_logits(t, e, seed=r), topk)
+        counts += torch.bincount(ti_r.reshape(-1).long(), minlength=e)
+    local = counts[lo:hi]
+    assert int(local.max()) <= max_m
+    # dominant kernel: the two masked grouped GEMM launches, timed alone on buffers of the same shape and row counts
+    masked = local.to(torch.int32).to(dev)
+    a1 = torch.empty(e_l, max_m, h, dtype=torch.uint8, device=dev).random_(0, 120).view(FP8)
+    s1 = torch.full((e_l, max_m, h // 128), 2.0 ** -7, device=dev)
+    o1 = torch.empty(e_l, max_m, 2 * i, dtype=torch.bfloat16, device=dev)
+    a2 = torch.empty(e_l, max_m, i, dtype=torch.uint8, device=dev).random_(0, 120).view(FP8)
+    s2 = torch.full((e_l, max_m, i // 128), 2.0 ** -7, device=dev)
+    o2 = torch.empty(e_l, max_m, h, dtype=torch.bfloat16, device=dev)
+    evs = []
+    for k_ in range(3 + max(3, min(args.steps, 10))):
+        a, b, c, d = (torch.cuda.Event(enable_timing=True) for _ in range(4))
+        a.record()
+        ops.m_grouped_fp8_gemm_nt_masked(a1, s1, w13_q, w13_s, o1, masked)
+        b.record()
+        c.record()
+        ops.m_grouped_fp8_gemm_nt_masked(a2, s2, w2_q, w2_s, o2, masked)
+        d.record()
+        if k_ >= 3:
+            evs.append((a, b, c, d))
+    torch.cuda.synchronize()
+    gemm_ms = sum(a.elapsed_time(b) + c.elapsed_time(d) for a, b, c, d in evs) / len(evs) / 2.0
+    del a1, a2, o1, o2
+    active, rows = int((local > 0).sum()), int(local.sum())
+    g1 = active * 2 * i * h + rows * h + rows * 2 * i * 2 + 4 * rows * (h // 128)
+    g2 = active * h * i + rows * i + rows * h * 2 + 4 * rows * (i // 128)
+    peaks = measured_peaks()
+    ach = (g1 + g2) / 2.0 / (gemm_ms * 1e-3) / 1e9
+    assert ops.gemm_status(dev) == 0
+    # e2e: pinned host activations and routing in, result back to the host
+    hx, htw, hti = x.cpu().pin_memory(), tw.cpu().pin_memory(), ti.cpu().pin_memory()
+    dx, dtw, dti = torch.empty_like(x), torch.empty_like(tw), torch.empty_like(ti)
+    hout = torch.empty(t, h, dtype=torch.bfloat16).pin_memory()
+
+    def e2e_step(_):
+        dx.copy_(hx, non_blocking=True)
+        dtw.copy_(htw, non_blocking=True)
+        dti.copy_(hti, non_blocking=True)
+        layer.forward(dx, dti, dtw, w13_q, w13_s, w2_q, w2_s, out=out)
+        hout.copy_(out, non_blocking=True)
+
+    ms_e2e = Timed(world, 0, dev).run(e2e_step, args.steps, 3)
+    layer.check()
+    layer.close()
+    flop = 2.0 * t * topk * world * 3 * i * h
+    return {
+        "metric": "EP FP8 MoE layer throughput", "value": t * world / (ms * 1e-3), "unit": "tokens/s", "ms_per_step": ms,
+        "dtype": "e4m3 x e4m3 -> fp32 -> bf16", "scaling": "weak",
+        "config": {"workload": "ep_moe: BASELINE configs[3], DeepSeek-V3-shaped FP8 MoE layer (hidden 7168, intermediate 2048, 256 experts, "
+                               "top-8 sigmoid routing), expert-parallel, 128 tokens per rank, masked layout, <=256 rows per expert",
+                   "parallelism": f"ep{world}", "experts_per_rank": e_l, "global_tokens": t * world,
+                   "l2": f"local expert weights ({e_l * 3 * i * h / 1e9:.2f} GB) exceed the 126 MB L2",
+                   "exchange": "peer stores over NVLink (dispatch fp8 rows + scales, combine bf16 rows), release/acquire flags",
+                   "layer_tflops": flop / world / (ms * 1e-3) / 1e12},
+        "e2e": {"value": t * world / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": t * h * 2 + t * topk * 8, "d2h_bytes_per_step": t * h * 2},
+        "gpu_launches": launches // (args.steps + args.warmup) * args.steps,
+        "roofline": {"bound": "hbm", "kernel": "fp8_gemm_kernel (masked grouped, 2 launches per layer; rank 0)", "achieved": ach, "peak": peaks["hbm_gbs"],
+                     "unit": "GB/s", "frac": ach / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
+                     "algorithmic_bytes_per_launch": (g1 + g2) / 2.0, "gemm_ms_per_launch": gemm_ms},
+        "_cpu": lambda: cpu_moe(t, h, i, e, topk, "sigmoid", 8, 1),
+    }
+
+
+WORKLOADS = {
+    "ep_moe": wl_ep_moe,
+    "silu_c2": wl_silu_c2,
+    "quant_c1": wl_quant_c1,
+    "gemm_c1": wl_gemm_c1,
+    "quant_c3": lambda *a: wl_quant_c1(*a, m=4096, k=7168),
+    "moe_c3": lambda *a: wl_moe_single(*a, "moe_c3"),
+    "moe_c5": lambda *a: wl_moe_single(*a, "moe_c5"),
+}
+DEFAULT_WORKLOAD = "ep_moe"
+
+
+def reference_arm(args, rank, world):
+    """The reference's CPU path for the workload (torch on the host cores), rank 0 only."""
+    if rank != 0:
+        return
+    torch.set_num_threads(cpu_threads())
+    wl = args.workload
+    reps = max(1, min(args.steps, 3))
+    if wl == "silu_c2":
+        v, dt, sample = cpu_silu_c2(4096, reps)
+        metric, unit = "fused SiLU*Mul+FP8 quant throughput", "GB/s"
+    elif wl in ("quant_c1", "quant_c3"):
+        v, dt, sample = cpu_quant(512 if wl == "quant_c1" else 4096, 7168, max(reps, 10) if wl == "quant_c1" else reps)
+        metric, unit = "1x128 FP8 activation quant throughput", "GB/s"
+    elif wl == "gemm_c1":
+        v, dt, sample = cpu_gemm_c1(1024, reps)
+        metric, unit = "block-scaled FP8 GEMM throughput", "TFLOP/s"
+    elif wl == "moe_c5":
+        v, dt, sample = cpu_moe(16384, 4096, 14336, 8, 2, "softmax", 1, 1)
+        metric, unit = "FP8 MoE layer throughput", "tokens/s"
+    elif wl == "moe_c3":
+        v, dt, sample = cpu_moe(4096, 7168, 2048, 256, 8, "sigmoid", 8, 1)
+        metric, unit = "FP8 MoE layer throughput", "tokens/s"
+    else:
+        v, dt, sample = cpu_moe(128 * world, 7168, 2048, 256, 8, "sigmoid", 8, 1)
+        metric, unit = "FP8 MoE layer throughput", "tokens/s"
+    line = {"impl": "reference", "metric": metric, "value": v, "unit": unit, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32 (torch CPU)", "data": "synthetic",
+            "config": {"workload": wl},
+            "cpu_baseline": {"value": v, "unit": unit, "cores": cpu_threads(), "kind": "port", "sample": sample},
+            "e2e": {"value": v, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    rank, local, world = dist_info()
+    if args.impl == "reference":
+        reference_arm(args, rank, world)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the hot path has no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        torch.distributed.init_process_group("nccl", device_id=dev)
+    from kb_nano_b200 import _lib
+    _lib.load()
+    sampler = ClockSampler(local)
+    sampler.start()
+    res = WORKLOADS[args.workload](args, rank, world, dev, sampler)
+    clocks = sampler.stop()
+    cpu_fn = res.pop("_cpu", None)
+    line = {"metric": res["metric"], "value": res["value"], "unit": res["unit"], "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": res["ms_per_step"], "higher_is_better": True, "scaling": res["scaling"], "vs_baseline": None, "dtype": res["dtype"],
+            "data": "synthetic", "config": res["config"], "e2e": res["e2e"], "gpu_launches": res["gpu_launches"], "roofline": res["roofline"],
+            "clocks": clocks}
+    if rank == 0 and world == 1 and cpu_fn is not None and not args.no_cpu_baseline:
+        torch.set_num_threads(cpu_threads())
+        v, dt, sample = cpu_fn()
+        line["cpu_baseline"] = {"value": v, "unit": res["unit"], "cores": cpu_threads(), "kind": "port", "sample": sample}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        torch.distributed.barrier()
+        torch.distributed.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

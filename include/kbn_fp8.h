@@ -60,6 +60,18 @@ int kbn_silu_mul_quant_1x128(const void* in, int64_t M, int64_t N2, int64_t ld_i
                              int64_t ld_q, float* scale, int64_t s_row, int64_t s_grp, float eps,
                              int ue8m0, kbn_stream_t stream);
 
+/* Same kernel restricted to the rows that hold data, for the two grouped-GEMM layouts (the rows it
+ * skips are neither read nor written):
+ *   _rows:   expert-contiguous layout, row m is processed iff row_expert[m] >= 0;
+ *   _masked: in [E, max_m, 2*N2] -> q [E, max_m, N2], row-major scales [E, max_m, N2/128], UE8M0,
+ *            eps 1e-10; row (e, m) is processed iff m < masked_m[e].
+ * kb-nano runs its kernel over every row of the padded buffer (tasks/baseline/L2/fused_experts.py:269-274). */
+int kbn_silu_mul_quant_1x128_rows(const void* in, int64_t M, int64_t N2, int64_t ld_in, void* q,
+                                  int64_t ld_q, float* scale, int64_t s_row, int64_t s_grp, float eps,
+                                  int ue8m0, const int32_t* row_expert, kbn_stream_t stream);
+int kbn_silu_mul_quant_1x128_masked(const void* in, int64_t E, int64_t max_m, int64_t N2, void* q,
+                                    float* scale, const int32_t* masked_m, kbn_stream_t stream);
+
 /* silu(gate)->bf16 for all 65536 gate bit patterns, as the kernel above computes it
  * (out: 65536 x uint16 on the device).  Used by the exhaustive parity test. */
 int kbn_silu_bf16_table(void* out_u16, kbn_stream_t stream);
@@ -101,6 +113,65 @@ int kbn_fp8_grouped_gemm_masked(const void* A, const float* sa, int64_t sa_exp, 
 /* Device status word of the GEMM kernels' bounded waits: 0 = no wait ever ran out in this
  * process.  Host pointer out; synchronises `stream` first. */
 int kbn_gemm_status(int32_t* host_out, kbn_stream_t stream);
+
+/*
+ * Token permutation around the two grouped GEMMs of the FP8 MoE expert pipeline.  Together they
+ * stand behind _deepgemm_permute / _deepgemm_unpermute_and_reduce
+ * (tasks/baseline/L2/fused_experts.py:42-116,119-136).
+ *
+ * kbn_moe_aligned_rows: row capacity of the expert-contiguous buffers,
+ *   round_up(T*topk + E*127, 128)  (_compute_aligned_M, tasks/baseline/L2/fused_experts.py:32-39).
+ * kbn_moe_permute: a_q [T,K] fp8 + a_s [T,K/128] fp32 (row-major) + topk_ids [T,topk] int32 ->
+ *   a_perm [M_cap,K], a_s_perm [M_cap,K/128]: rows grouped by expert, each expert's segment
+ *     starting on a multiple of 128 rows, pairs kept in (token, slot) order inside a segment;
+ *     padding rows are left unwritten;
+ *   row_expert int32 [M_cap]: expert of each row, -1 for padding;
+ *   dest_row int32 [T,topk]: row each (token, slot) went to (-1 if its expert id is out of range).
+ *   workspace: kbn_moe_permute_workspace_bytes(T, topk, E) bytes of device scratch.
+ * kbn_moe_unpermute_combine: out[t,:] = sum_s topk_w[t,s] * rows[dest_row[t,s],:], fp32
+ *   accumulation in slot order, bf16 [T,H] out; rows is bf16 with row stride ld_rows.
+ */
+int64_t kbn_moe_aligned_rows(int64_t T, int64_t topk, int64_t E);
+int64_t kbn_moe_permute_workspace_bytes(int64_t T, int64_t topk, int64_t E);
+int kbn_moe_permute(const void* a_q, const float* a_s, const int32_t* topk_ids, int64_t T,
+                    int64_t topk, int64_t K, int64_t E, void* a_perm, float* a_s_perm,
+                    int32_t* row_expert, int32_t* dest_row, int64_t M_cap, void* workspace,
+                    int64_t workspace_bytes, kbn_stream_t stream);
+int kbn_moe_unpermute_combine(const void* rows, int64_t ld_rows, const int32_t* dest_row,
+                              const float* topk_w, int64_t T, int64_t topk, int64_t H, void* out,
+                              kbn_stream_t stream);
+
+/*
+ * Expert-parallel FP8 MoE layer over the GPUs of one NVLink/NVSwitch box, one process per GPU.
+ * Experts are split in contiguous blocks (rank r owns experts [r*E/R, (r+1)*E/R)); tokens stay on
+ * their source rank.  Dispatch and combine are peer stores over NVLink issued by this library's
+ * kernels; arrival is signalled with release/acquire flags whose waits are bounded (about 1 s).
+ * It takes the place of the tensor-parallel all-reduce that ends kb-nano's MoE layers
+ * (tasks/baseline/L1/allreduce.py:37-48 called from tasks/baseline/L2/deepseek_moe.py:301-302,
+ * qwen3_moe.py:185-186, mixtral_moe.py:80-81); kb-nano has no expert-parallel path of its own.
+ *
+ * Bootstrap (not the hot path; allocates with cudaMalloc and maps peers with CUDA IPC):
+ *   kbn_ep_create on every rank (its GPU current) -> kbn_ep_ipc_handle -> exchange the 64-byte
+ *   handles by any host channel -> kbn_ep_attach(all handles, rank order).  world == 1 needs no attach.
+ * kbn_ep_moe_forward: x bf16 [T,H] local tokens, topk_ids int32 [T,topk] GLOBAL expert ids,
+ *   topk_w fp32 [T,topk]; w13 fp8 [E/R,2I,H] + w13_s fp32 [E/R,2I/128,H/128], w2 fp8 [E/R,H,I] +
+ *   w2_s [E/R,H/128,I/128] of the LOCAL experts; out bf16 [T,H].  Every rank must call it the same
+ *   number of times (also with T == 0).  An expert can take at most max_m rows per call.
+ * kbn_ep_status: 4 int32 {code, phase, peer, detail}; code 0 = ok, 10 = an expert overflowed max_m
+ *   rows (detail = expert), 11 = expert id out of range, 20 = a wait on peer `peer` ran out in
+ *   phase 1 (dispatch) or 2 (combine).  Synchronises `stream`.
+ */
+typedef struct kbn_ep_ctx kbn_ep_ctx;
+int kbn_ep_create(int rank, int world, int64_t experts_total, int64_t max_m, int64_t hidden,
+                  int64_t inter, int64_t max_tokens, int64_t topk, kbn_ep_ctx** out);
+int kbn_ep_ipc_handle(kbn_ep_ctx* ctx, void* out64);
+int kbn_ep_attach(kbn_ep_ctx* ctx, const void* handles);
+int64_t kbn_ep_symmetric_bytes(kbn_ep_ctx* ctx);
+int kbn_ep_moe_forward(kbn_ep_ctx* ctx, const void* x_bf16, const int32_t* topk_ids,
+                       const float* topk_w, int64_t T, const void* w13, const float* w13_s,
+                       const void* w2, const float* w2_s, void* out_bf16, kbn_stream_t stream);
+int kbn_ep_status(kbn_ep_ctx* ctx, int32_t* host_out4, kbn_stream_t stream);
+int kbn_ep_destroy(kbn_ep_ctx* ctx);
 
 #ifdef __cplusplus
 }

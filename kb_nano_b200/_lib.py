@@ -7,7 +7,6 @@ from __future__ import annotations
 import ctypes
 import os
 
-from . import build as _build
 
 _i64 = ctypes.c_int64
 _i32 = ctypes.c_int
@@ -22,10 +21,23 @@ SIGNATURES = {
     "kbn_quant_1x128": (_i32, [_ptr, _i64, _i64, _i64, _ptr, _i64, _ptr, _i64, _i64, _f32, _i32, _ptr]),
     "kbn_silu_mul_quant_1x128": (_i32, [_ptr, _i64, _i64, _i64, _ptr, _i64, _ptr, _i64, _i64, _f32, _i32, _ptr]),
     "kbn_silu_bf16_table": (_i32, [_ptr, _ptr]),
+    "kbn_silu_mul_quant_1x128_rows": (_i32, [_ptr, _i64, _i64, _i64, _ptr, _i64, _ptr, _i64, _i64, _f32, _i32, _ptr, _ptr]),
+    "kbn_silu_mul_quant_1x128_masked": (_i32, [_ptr, _i64, _i64, _i64, _ptr, _ptr, _ptr, _ptr]),
     "kbn_fp8_gemm_nt": (_i32, [_ptr, _ptr, _i64, _i64, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _ptr]),
     "kbn_fp8_grouped_gemm_contig": (_i32, [_ptr, _ptr, _i64, _i64, _ptr, _ptr, _ptr, _i64, _ptr, _i64, _i64, _i64, _i64, _ptr]),
     "kbn_fp8_grouped_gemm_masked": (_i32, [_ptr, _ptr, _i64, _i64, _i64, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _ptr]),
     "kbn_gemm_status": (_i32, [_ptr, _ptr]),
+    "kbn_moe_aligned_rows": (_i64, [_i64, _i64, _i64]),
+    "kbn_moe_permute_workspace_bytes": (_i64, [_i64, _i64, _i64]),
+    "kbn_moe_permute": (_i32, [_ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _ptr, _ptr, _ptr, _ptr, _i64, _ptr, _i64, _ptr]),
+    "kbn_ep_create": (_i32, [_i32, _i32, _i64, _i64, _i64, _i64, _i64, _i64, ctypes.POINTER(_ptr)]),
+    "kbn_ep_ipc_handle": (_i32, [_ptr, _ptr]),
+    "kbn_ep_attach": (_i32, [_ptr, _ptr]),
+    "kbn_ep_symmetric_bytes": (_i64, [_ptr]),
+    "kbn_ep_moe_forward": (_i32, [_ptr, _ptr, _ptr, _ptr, _i64, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr]),
+    "kbn_ep_status": (_i32, [_ptr, _ptr, _ptr]),
+    "kbn_ep_destroy": (_i32, [_ptr]),
+    "kbn_moe_unpermute_combine": (_i32, [_ptr, _i64, _ptr, _ptr, _i64, _i64, _i64, _ptr, _ptr]),
 }
 
 _lib = None
@@ -37,8 +49,11 @@ class KbnError(RuntimeError):
         self.code = code
 
 
+LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libkbn_fp8.so")
+
+
 def lib_path() -> str:
-    return _build.LIB_PATH
+    return LIB_PATH
 
 
 def load(build_if_missing: bool = False) -> ctypes.CDLL:
@@ -49,6 +64,7 @@ def load(build_if_missing: bool = False) -> ctypes.CDLL:
     path = lib_path()
     if not os.path.exists(path):
         if build_if_missing:
+            from . import build as _build
             _build.build()
         else:
             raise RuntimeError(

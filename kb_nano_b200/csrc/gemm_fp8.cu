@@ -3,7 +3,7 @@
 //
 //   warp 0      TMA producer: 128x128-byte A and B tiles (SWIZZLE_128B) into a kStages ring
 //   warp 1      TMEM allocation + tcgen05.mma issue: one 128x128x128 product per K-block into one
-//               of two TMEM accumulators (4 UMMAs of K=32, the first overwriting)
+//               of four TMEM accumulators (4 UMMAs of K=32, the first overwriting)
 //   warps 2..9  promotion + epilogue: each thread owns one output row and 64 columns; per K-block
 //               it reads the partial product from TMEM and does acc += partial * sa[m,kb]*sb[nb,kb]
 //               in fp32 registers (weight scales may be arbitrary fp32), then writes bf16.
@@ -25,7 +25,8 @@ constexpr int kTileBytes = kBlockM * kBlockK;            // 16 KB per operand ti
 constexpr int kStageBytes = 2 * kTileBytes;
 constexpr int kEpiWarps = 8;
 constexpr int kThreads = 32 * (2 + kEpiWarps);
-constexpr int kTmemCols = 256;                           // two 128-column fp32 accumulators
+constexpr int kAccBufs = 4;                              // TMEM accumulators in flight (MMA <-> promotion handshake)
+constexpr int kTmemCols = kAccBufs * 128;                // all 512 columns: four 128-column fp32 accumulators
 constexpr int kSwizzleGroupM = 8;                        // m-blocks that share B tiles in L2
 constexpr long long kWaitLimitCycles = 2000000000ll;     // about a second
 constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
@@ -136,13 +137,13 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     // SWIZZLE_128B tiles need 1024-byte alignment
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~(uintptr_t)1023u);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)kStages * kStageBytes);
-    // bars: [0,kStages) full, [kStages,2kStages) empty, then tmem_full[2], tmem_empty[2]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+    // bars: [0,kStages) full, [kStages,2kStages) empty, then tmem_full[kAccBufs], tmem_empty[kAccBufs]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 2 * kAccBufs);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t bar_full = ptx::smem_u32(bars), bar_empty = ptx::smem_u32(bars + kStages);
-    const uint32_t bar_tfull = ptx::smem_u32(bars + 2 * kStages), bar_tempty = ptx::smem_u32(bars + 2 * kStages + 2);
+    const uint32_t bar_tfull = ptx::smem_u32(bars + 2 * kStages), bar_tempty = ptx::smem_u32(bars + 2 * kStages + kAccBufs);
     const uint32_t smem_tiles = ptx::smem_u32(smem);
 
     if (threadIdx.x == 0) {
@@ -150,7 +151,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             ptx::mbar_init(bar_full + 8 * s, 1);
             ptx::mbar_init(bar_empty + 8 * s, 1);
         }
-        for (int b = 0; b < 2; ++b) {
+        for (int b = 0; b < kAccBufs; ++b) {
             ptx::mbar_init(bar_tfull + 8 * b, 1);
             ptx::mbar_init(bar_tempty + 8 * b, kEpiWarps);
         }
@@ -210,7 +211,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 if (!tile.compute) continue;
                 for (int kb = 0; kb < KB; ++kb, ++it) {
                     const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
-                    const uint32_t ab = it & 1u, aph = (it >> 1) & 1u;
+                    const uint32_t ab = it % kAccBufs, aph = (it / kAccBufs) & 1u;
                     if (!wait_bar(bar_tempty + 8 * ab, aph ^ 1u, w)) { ok = false; break; }
                     if (!wait_bar(bar_full + 8 * s, ph, w)) { ok = false; break; }
                     ptx::tc_fence_after();
@@ -261,7 +262,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     sa_next = row_ok ? __ldg(sa_ptr + (int64_t)(kb + 1) * p.sa_grp) : 0.0f;
                     sb_next = __ldg(sb_ptr + kb + 1);
                 }
-                const uint32_t ab = it & 1u, aph = (it >> 1) & 1u;
+                const uint32_t ab = it % kAccBufs, aph = (it / kAccBufs) & 1u;
                 if (!wait_bar(bar_tfull + 8 * ab, aph, w)) { ok = false; break; }
                 ptx::tc_fence_after();
                 const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + ab * kBlockN + half * 64;

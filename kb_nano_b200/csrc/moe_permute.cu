@@ -1,0 +1,215 @@
+// Token permutation around the two grouped GEMMs of the FP8 MoE expert pipeline.
+//
+//   permute:  quantised rows [T,K] + scales [T,K/128] + topk_ids [T,topk]
+//             -> expert-contiguous rows with 128-aligned segments (stable in (token, slot) order),
+//                per-row expert ids (-1 = padding) and the destination row of every (token, slot).
+//   combine:  out[t] = sum_s w[t,s] * rows[dest[t,s]]  (fp32 accumulation in slot order, bf16 out)
+//
+// Replaces the ~15 torch launches of kb-nano's _deepgemm_permute / _deepgemm_unpermute_and_reduce
+// (tasks/baseline/L2/fused_experts.py:42-136) with three + one kernels, no host sync and no
+// allocation: the only scratch is a caller-provided workspace of 4*(T*topk + 2*E + 2) bytes.
+// Everything here is HBM/L2-bound byte shuffling; traffic is (K + 4*K/128) bytes read and written
+// per (token, slot) for the permute and 2*H*(topk+1) bytes per token for the combine.
+#include "common.cuh"
+
+namespace kbn {
+
+constexpr int kAlign = 128;
+
+// Block e ranks, in flat (token, slot) order, the pairs routed to expert e.
+__global__ void __launch_bounds__(256)
+moe_rank_kernel(const int32_t* __restrict__ ids, int64_t n_pairs, int32_t* __restrict__ rank,
+                int32_t* __restrict__ counts) {
+    const int e = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    __shared__ int warp_tot[8];
+    __shared__ int base_s;
+    if (threadIdx.x == 0) base_s = 0;
+    __syncthreads();
+    for (int64_t i0 = 0; i0 < n_pairs; i0 += 256) {
+        const int64_t i = i0 + threadIdx.x;
+        const bool hit = i < n_pairs && ids[i] == e;
+        const unsigned bal = __ballot_sync(0xffffffffu, hit);
+        if (lane == 0) warp_tot[warp] = __popc(bal);
+        __syncthreads();
+        int before = base_s;
+        for (int w = 0; w < warp; ++w) before += warp_tot[w];
+        if (hit) rank[i] = before + __popc(bal & ((1u << lane) - 1u));
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int tot = 0;
+            for (int w = 0; w < 8; ++w) tot += warp_tot[w];
+            base_s += tot;
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) counts[e] = base_s;
+}
+
+// Aligned exclusive scan of the counts (recomputed by every block: E is small) and the per-row
+// expert id of the block's slice of rows.
+__global__ void __launch_bounds__(256)
+moe_offsets_kernel(const int32_t* __restrict__ counts, int E, int32_t* __restrict__ offsets,
+                   int32_t* __restrict__ row_expert, int64_t M_cap) {
+    extern __shared__ int32_t sm[];        // offsets[E+1], counts[E]
+    int32_t* off = sm;
+    int32_t* cnt = sm + E + 1;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = counts[e];
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int32_t acc = 0;
+        for (int e = 0; e < E; ++e) {
+            off[e] = acc;
+            acc += (cnt[e] + kAlign - 1) / kAlign * kAlign;
+        }
+        off[E] = acc;
+    }
+    __syncthreads();
+    if (blockIdx.x == 0)
+        for (int e = threadIdx.x; e <= E; e += blockDim.x) offsets[e] = off[e];
+    for (int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; r < M_cap; r += (int64_t)gridDim.x * blockDim.x) {
+        int32_t id = -1;
+        if (r < off[E]) {
+            int lo = 0, hi = E;            // largest e with off[e] <= r
+            while (hi - lo > 1) {
+                int mid = (lo + hi) >> 1;
+                if (off[mid] <= r) lo = mid; else hi = mid;
+            }
+            if (r - off[lo] < cnt[lo]) id = lo;
+        }
+        row_expert[r] = id;
+    }
+}
+
+// One warp per (token, slot): copy the fp8 row and its scales to the destination row.
+__global__ void __launch_bounds__(256)
+moe_scatter_kernel(const uint8_t* __restrict__ a_q, const float* __restrict__ a_s, const int32_t* __restrict__ ids,
+                   const int32_t* __restrict__ rank, const int32_t* __restrict__ offsets, int64_t n_pairs, int topk,
+                   int64_t K, int G, int E, uint8_t* __restrict__ a_perm, float* __restrict__ s_perm,
+                   int32_t* __restrict__ dest) {
+    const int64_t i = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (i >= n_pairs) return;
+    const int lane = threadIdx.x & 31;
+    const int e = ids[i];
+    if (e < 0 || e >= E) {
+        if (lane == 0) dest[i] = -1;
+        return;
+    }
+    const int64_t t = i / topk;
+    const int64_t d = (int64_t)offsets[e] + rank[i];
+    const uint4* src = reinterpret_cast<const uint4*>(a_q + t * K);
+    uint4* dst = reinterpret_cast<uint4*>(a_perm + d * K);
+    for (int v = lane; v < (int)(K >> 4); v += 32) dst[v] = __ldg(src + v);
+    for (int g = lane; g < G; g += 32) s_perm[d * G + g] = __ldg(a_s + t * G + g);
+    if (lane == 0) dest[i] = (int32_t)d;
+}
+
+// out[t, :] = sum_s w[t,s] * rows[dest[t,s], :]; 8 columns (16 bytes) per thread.
+template <int TOPK>
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(const __nv_bfloat16* __restrict__ rows, int64_t ld_rows, const int32_t* __restrict__ dest,
+                   const float* __restrict__ w, int64_t T, int topk_rt, int64_t H, __nv_bfloat16* __restrict__ out) {
+    const int64_t t = blockIdx.y;
+    const int64_t c = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
+    if (c >= H) return;
+    const int topk = TOPK > 0 ? TOPK : topk_rt;
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    auto add = [&](int s) {
+        const int32_t d = dest[t * topk + s];
+        if (d < 0) return;
+        const float ws = w[t * topk + s];
+        const uint4 v = __ldcs(reinterpret_cast<const uint4*>(rows + (int64_t)d * ld_rows + c));
+        acc[0] = fmaf(ws, bf16_lo(v.x), acc[0]); acc[1] = fmaf(ws, bf16_hi(v.x), acc[1]);
+        acc[2] = fmaf(ws, bf16_lo(v.y), acc[2]); acc[3] = fmaf(ws, bf16_hi(v.y), acc[3]);
+        acc[4] = fmaf(ws, bf16_lo(v.z), acc[4]); acc[5] = fmaf(ws, bf16_hi(v.z), acc[5]);
+        acc[6] = fmaf(ws, bf16_lo(v.w), acc[6]); acc[7] = fmaf(ws, bf16_hi(v.w), acc[7]);
+    };
+    if (TOPK > 0) {
+#pragma unroll
+        for (int s = 0; s < TOPK; ++s) add(s);
+    } else {
+        for (int s = 0; s < topk; ++s) add(s);
+    }
+    uint4 o;
+    o.x = pack_bf16x2(acc[0], acc[1]);
+    o.y = pack_bf16x2(acc[2], acc[3]);
+    o.z = pack_bf16x2(acc[4], acc[5]);
+    o.w = pack_bf16x2(acc[6], acc[7]);
+    *reinterpret_cast<uint4*>(out + t * H + c) = o;
+}
+
+}  // namespace kbn
+
+extern "C" int64_t kbn_moe_aligned_rows(int64_t T, int64_t topk, int64_t E) {
+    int64_t m = T * topk + E * (kbn::kAlign - 1);
+    return (m + kbn::kAlign - 1) / kbn::kAlign * kbn::kAlign;
+}
+
+extern "C" int64_t kbn_moe_permute_workspace_bytes(int64_t T, int64_t topk, int64_t E) {
+    return 4 * (T * topk + 2 * E + 2);
+}
+
+extern "C" int kbn_moe_permute(const void* a_q, const float* a_s, const int32_t* topk_ids, int64_t T, int64_t topk,
+                               int64_t K, int64_t E, void* a_perm, float* a_s_perm, int32_t* row_expert,
+                               int32_t* dest_row, int64_t M_cap, void* workspace, int64_t workspace_bytes,
+                               kbn_stream_t stream) {
+    using namespace kbn;
+    KBN_REQUIRE(T >= 0 && topk > 0 && K > 0 && E > 0, KBN_ERR_ARG, "kbn_moe_permute: bad sizes");
+    KBN_REQUIRE(K % 128 == 0, KBN_ERR_ARG, "kbn_moe_permute: K=%lld must be a multiple of 128", (long long)K);
+    KBN_REQUIRE(E <= 4096, KBN_ERR_UNSUPPORTED, "kbn_moe_permute: at most 4096 experts");
+    KBN_REQUIRE(M_cap >= kbn_moe_aligned_rows(T, topk, E), KBN_ERR_ARG, "kbn_moe_permute: M_cap=%lld below the aligned row bound %lld",
+                (long long)M_cap, (long long)kbn_moe_aligned_rows(T, topk, E));
+    KBN_REQUIRE(M_cap < (1ll << 31) && T * topk < (1ll << 31), KBN_ERR_ARG, "kbn_moe_permute: too many rows");
+    KBN_REQUIRE(a_perm && a_s_perm && row_expert && dest_row && workspace, KBN_ERR_ARG, "kbn_moe_permute: null pointer");
+    KBN_REQUIRE(workspace_bytes >= kbn_moe_permute_workspace_bytes(T, topk, E), KBN_ERR_ARG, "kbn_moe_permute: workspace too small");
+    KBN_REQUIRE(aligned16(a_perm) && (T == 0 || aligned16(a_q)), KBN_ERR_ARG, "kbn_moe_permute: rows must be 16-byte aligned");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int64_t n_pairs = T * topk;
+    int32_t* counts = static_cast<int32_t*>(workspace);
+    int32_t* offsets = counts + E;
+    int32_t* rank = offsets + E + 1;
+    if (n_pairs > 0) KBN_REQUIRE(a_q && a_s && topk_ids, KBN_ERR_ARG, "kbn_moe_permute: null pointer");
+    moe_rank_kernel<<<(unsigned)E, 256, 0, st>>>(topk_ids, n_pairs, rank, counts);
+    KBN_CHECK_LAUNCH();
+    const int off_blocks = (int)((M_cap + 255) / 256 < 64 ? (M_cap + 255) / 256 : 64);
+    moe_offsets_kernel<<<off_blocks > 0 ? off_blocks : 1, 256, (size_t)(2 * E + 1) * 4, st>>>(counts, (int)E, offsets, row_expert, M_cap);
+    KBN_CHECK_LAUNCH();
+    if (n_pairs > 0) {
+        moe_scatter_kernel<<<(unsigned)((n_pairs + 7) / 8), 256, 0, st>>>(
+            static_cast<const uint8_t*>(a_q), a_s, topk_ids, rank, offsets, n_pairs, (int)topk, K, (int)(K / 128), (int)E,
+            static_cast<uint8_t*>(a_perm), a_s_perm, dest_row);
+        KBN_CHECK_LAUNCH();
+    }
+    return KBN_OK;
+}
+
+extern "C" int kbn_moe_unpermute_combine(const void* rows, int64_t ld_rows, const int32_t* dest_row, const float* topk_w,
+                                         int64_t T, int64_t topk, int64_t H, void* out, kbn_stream_t stream) {
+    using namespace kbn;
+    KBN_REQUIRE(T >= 0 && topk > 0 && H > 0, KBN_ERR_ARG, "kbn_moe_unpermute_combine: bad sizes");
+    if (T == 0) return KBN_OK;
+    KBN_REQUIRE(rows && dest_row && topk_w && out, KBN_ERR_ARG, "kbn_moe_unpermute_combine: null pointer");
+    KBN_REQUIRE(H % 8 == 0 && ld_rows % 8 == 0 && aligned16(rows) && aligned16(out), KBN_ERR_ARG,
+                "kbn_moe_unpermute_combine: H and ld_rows must be multiples of 8 and pointers 16-byte aligned");
+    KBN_REQUIRE(T < 65536ll * 32768ll, KBN_ERR_ARG, "kbn_moe_unpermute_combine: too many tokens");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    dim3 grid((unsigned)((H / 8 + 255) / 256), (unsigned)T);
+    KBN_REQUIRE(T <= 2147483647ll, KBN_ERR_ARG, "kbn_moe_unpermute_combine: too many tokens");
+    const auto* r = static_cast<const __nv_bfloat16*>(rows);
+    auto* o = static_cast<__nv_bfloat16*>(out);
+    // grid.y is limited to 65535: fold tokens if needed
+    if (T > 65535) {
+        for (int64_t t0 = 0; t0 < T; t0 += 65535) {
+            int64_t tn = T - t0 < 65535 ? T - t0 : 65535;
+            dim3 g2(grid.x, (unsigned)tn);
+            moe_combine_kernel<0><<<g2, 256, 0, st>>>(r, ld_rows, dest_row + t0 * topk, topk_w + t0 * topk, tn, (int)topk, H, o + t0 * H);
+            KBN_CHECK_LAUNCH();
+        }
+        return KBN_OK;
+    }
+    if (topk == 8) moe_combine_kernel<8><<<grid, 256, 0, st>>>(r, ld_rows, dest_row, topk_w, T, 8, H, o);
+    else if (topk == 2) moe_combine_kernel<2><<<grid, 256, 0, st>>>(r, ld_rows, dest_row, topk_w, T, 2, H, o);
+    else moe_combine_kernel<0><<<grid, 256, 0, st>>>(r, ld_rows, dest_row, topk_w, T, (int)topk, H, o);
+    KBN_CHECK_LAUNCH();
+    return KBN_OK;
+}

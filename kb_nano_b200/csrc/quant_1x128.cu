@@ -51,41 +51,39 @@ __device__ __forceinline__ float halfwarp_absmax(uint4 v) {
     return fmaxf(bf16_lo(m), bf16_hi(m));
 }
 
-// One half-warp per group, U groups per half-warp with all loads issued before any use.
+// One half-warp per chunk of U consecutive groups of one row; all loads are issued before any use.
+// Index arithmetic is 32-bit with a single division per thread (chunk -> row).
 template <bool UE8M0, int U>
 __global__ void __launch_bounds__(256)
-quant_1x128_kernel(const __nv_bfloat16* __restrict__ x, int64_t M, int64_t K, int64_t ld_x,
-                   uint8_t* __restrict__ q, int64_t ld_q, float* __restrict__ scale, int64_t s_row,
-                   int64_t s_grp, float eps) {
-    const int64_t G = (K + 127) >> 7;
-    const int64_t NG = M * G;
-    const int j = threadIdx.x & 15;
-    const int64_t g0 = ((int64_t)blockIdx.x * 16 + (threadIdx.x >> 4)) * U;
+quant_1x128_kernel(const __nv_bfloat16* __restrict__ x, uint32_t K, int64_t ld_x, uint8_t* __restrict__ q,
+                   int64_t ld_q, float* __restrict__ scale, int64_t s_row, int64_t s_grp, float eps,
+                   uint32_t G, uint32_t chunks_per_row, uint32_t n_chunks) {
+    const uint32_t j = threadIdx.x & 15u;
+    const uint32_t chunk = blockIdx.x * 16u + (threadIdx.x >> 4);
+    const bool valid = chunk < n_chunks;
+    const uint32_t row = valid ? chunk / chunks_per_row : 0u;
+    const uint32_t g0 = (chunk - row * chunks_per_row) * U;
+    const __nv_bfloat16* xr = x + (int64_t)row * ld_x;
+    uint8_t* qr = q + (int64_t)row * ld_q;
 
     uint4 v[U];
-    int64_t row[U];
-    int col[U];
     bool live[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-        int64_t gi = g0 + u;
-        bool valid = gi < NG;
-        int64_t m = valid ? gi / G : 0;
-        int g = valid ? (int)(gi - m * G) : 0;
-        row[u] = m;
-        col[u] = g * 128 + j * 8;
-        live[u] = valid && col[u] < K;
-        v[u] = live[u] ? __ldcs(reinterpret_cast<const uint4*>(x + m * ld_x + col[u])) : make_uint4(0, 0, 0, 0);
+        const uint32_t col = (g0 + u) * 128u + j * 8u;
+        live[u] = valid && col < K;
+        v[u] = live[u] ? __ldcs(reinterpret_cast<const uint4*>(xr + col)) : make_uint4(0, 0, 0, 0);
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
         GroupScale s = make_scale<UE8M0>(halfwarp_absmax(v[u]), eps);
         if (live[u]) {
+            const uint32_t g = g0 + u;
             uint2 o;
             o.x = quant_pair<UE8M0>(v[u].x, s) | (quant_pair<UE8M0>(v[u].y, s) << 16);
             o.y = quant_pair<UE8M0>(v[u].z, s) | (quant_pair<UE8M0>(v[u].w, s) << 16);
-            *reinterpret_cast<uint2*>(q + row[u] * ld_q + col[u]) = o;
-            if (j == 0) scale[row[u] * s_row + (int64_t)(col[u] >> 7) * s_grp] = s.scale;
+            *reinterpret_cast<uint2*>(qr + g * 128u + j * 8u) = o;
+            if (j == 0) scale[(int64_t)row * s_row + (int64_t)g * s_grp] = s.scale;
         }
     }
 }
@@ -144,12 +142,15 @@ extern "C" int kbn_quant_1x128(const void* x, int64_t M, int64_t K, int64_t ld_x
     const bool fast = (K % 8 == 0) && (ld_x % 8 == 0) && (ld_q % 8 == 0) && aligned16(x) && ((reinterpret_cast<uintptr_t>(q) & 7u) == 0);
     if (fast) {
         constexpr int U = 4;
-        int64_t blocks = (NG + 16 * U - 1) / (16 * U);
-        KBN_REQUIRE(blocks < (1ll << 31), KBN_ERR_ARG, "kbn_quant_1x128: too many groups");
+        const int64_t cpr = (G + U - 1) / U, n_chunks = M * cpr;
+        KBN_REQUIRE(K < (1ll << 31) && n_chunks < (1ll << 31), KBN_ERR_ARG, "kbn_quant_1x128: more than 2^31 groups");
+        const unsigned blocks = (unsigned)((n_chunks + 15) / 16);
         if (ue8m0)
-            quant_1x128_kernel<true, U><<<(unsigned)blocks, 256, 0, st>>>(xb, M, K, ld_x, qb, ld_q, scale, s_row, s_grp, eps);
+            quant_1x128_kernel<true, U><<<blocks, 256, 0, st>>>(xb, (uint32_t)K, ld_x, qb, ld_q, scale, s_row, s_grp, eps,
+                                                                 (uint32_t)G, (uint32_t)cpr, (uint32_t)n_chunks);
         else
-            quant_1x128_kernel<false, U><<<(unsigned)blocks, 256, 0, st>>>(xb, M, K, ld_x, qb, ld_q, scale, s_row, s_grp, eps);
+            quant_1x128_kernel<false, U><<<blocks, 256, 0, st>>>(xb, (uint32_t)K, ld_x, qb, ld_q, scale, s_row, s_grp, eps,
+                                                                  (uint32_t)G, (uint32_t)cpr, (uint32_t)n_chunks);
     } else {
         int64_t blocks = (NG + 7) / 8;
         KBN_REQUIRE(blocks < (1ll << 31), KBN_ERR_ARG, "kbn_quant_1x128: too many groups");

@@ -70,31 +70,32 @@ __device__ __forceinline__ uint32_t quant_pair_s(uint32_t w, float scale, float 
 }
 
 // One half-warp per output group, U groups per half-warp (2*U 16-byte loads in flight per lane).
-template <bool UE8M0, int U>
+// ROWS selects which rows are processed: 0 = all; 1 = rows with row_info[m] >= 0 (expert-contiguous
+// layout, -1 marks padding); 2 = rows with (m % max_m) < row_info[m / max_m] (masked layout).
+template <bool UE8M0, int U, int ROWS>
 __global__ void __launch_bounds__(256)
-silu_mul_quant_kernel(const __nv_bfloat16* __restrict__ in, int64_t M, int64_t N2, int64_t ld_in,
-                      uint8_t* __restrict__ q, int64_t ld_q, float* __restrict__ scale, int64_t s_row,
-                      int64_t s_grp, float eps, const uint16_t* __restrict__ table) {
-    const int64_t G = N2 >> 7;
-    const int64_t NG = M * G;
-    const int j = threadIdx.x & 15;
-    const int64_t g0 = ((int64_t)blockIdx.x * 16 + (threadIdx.x >> 4)) * U;
+silu_mul_quant_kernel(const __nv_bfloat16* __restrict__ in, uint32_t N2, int64_t ld_in, uint8_t* __restrict__ q,
+                      int64_t ld_q, float* __restrict__ scale, int64_t s_row, int64_t s_grp, float eps,
+                      const uint16_t* __restrict__ table, const int32_t* __restrict__ row_info, uint32_t max_m,
+                      uint32_t G, uint32_t chunks_per_row, uint32_t n_chunks) {
+    const uint32_t j = threadIdx.x & 15u;
+    const uint32_t chunk = blockIdx.x * 16u + (threadIdx.x >> 4);
+    bool valid = chunk < n_chunks;
+    const uint32_t row = valid ? chunk / chunks_per_row : 0u;
+    const uint32_t g0 = (chunk - row * chunks_per_row) * U;
+    if (ROWS == 1) valid = valid && row_info[row] >= 0;
+    if (ROWS == 2) valid = valid && (int)(row % max_m) < row_info[row / max_m];
+    const __nv_bfloat16* ir = in + (int64_t)row * ld_in;
+    uint8_t* qr = q + (int64_t)row * ld_q;
 
     uint4 gv[U], uv[U];
-    int64_t row[U];
-    int col[U];
     bool live[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-        int64_t gi = g0 + u;
-        live[u] = gi < NG;
-        int64_t m = live[u] ? gi / G : 0;
-        int g = live[u] ? (int)(gi - m * G) : 0;
-        row[u] = m;
-        col[u] = g * 128 + j * 8;
-        const __nv_bfloat16* p = in + m * ld_in + col[u];
-        gv[u] = live[u] ? __ldcs(reinterpret_cast<const uint4*>(p)) : make_uint4(0, 0, 0, 0);
-        uv[u] = live[u] ? __ldcs(reinterpret_cast<const uint4*>(p + N2)) : make_uint4(0, 0, 0, 0);
+        const uint32_t col = (g0 + u) * 128u + j * 8u;
+        live[u] = valid && (g0 + u) < G;
+        gv[u] = live[u] ? __ldcs(reinterpret_cast<const uint4*>(ir + col)) : make_uint4(0, 0, 0, 0);
+        uv[u] = live[u] ? __ldcs(reinterpret_cast<const uint4*>(ir + N2 + col)) : make_uint4(0, 0, 0, 0);
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
@@ -112,11 +113,12 @@ silu_mul_quant_kernel(const __nv_bfloat16* __restrict__ in, int64_t M, int64_t N
             sc = __fdiv_rn(a, kFp8MaxS);
         }
         if (live[u]) {
+            const uint32_t g = g0 + u;
             uint2 o;
             o.x = quant_pair_s<UE8M0>(y0, sc, inv) | (quant_pair_s<UE8M0>(y1, sc, inv) << 16);
             o.y = quant_pair_s<UE8M0>(y2, sc, inv) | (quant_pair_s<UE8M0>(y3, sc, inv) << 16);
-            *reinterpret_cast<uint2*>(q + row[u] * ld_q + col[u]) = o;
-            if (j == 0) scale[row[u] * s_row + (int64_t)(col[u] >> 7) * s_grp] = sc;
+            *reinterpret_cast<uint2*>(qr + g * 128u + j * 8u) = o;
+            if (j == 0) scale[(int64_t)row * s_row + (int64_t)g * s_grp] = sc;
         }
     }
 }
@@ -158,34 +160,70 @@ static int silu_table_for_stream(cudaStream_t st, const uint16_t** out) {
 
 }  // namespace kbn
 
-extern "C" int kbn_silu_mul_quant_1x128(const void* in, int64_t M, int64_t N2, int64_t ld_in, void* q,
-                                        int64_t ld_q, float* scale, int64_t s_row, int64_t s_grp, float eps,
-                                        int ue8m0, kbn_stream_t stream) {
-    using namespace kbn;
-    KBN_REQUIRE(M >= 0 && N2 >= 0, KBN_ERR_ARG, "kbn_silu_mul_quant_1x128: negative size");
+namespace kbn {
+
+static int launch_silu_mul_quant(const char* who, const void* in, int64_t M, int64_t N2, int64_t ld_in, void* q, int64_t ld_q,
+                                 float* scale, int64_t s_row, int64_t s_grp, float eps, int ue8m0, int rows_mode,
+                                 const int32_t* row_info, int64_t max_m, cudaStream_t st) {
+    KBN_REQUIRE(M >= 0 && N2 >= 0, KBN_ERR_ARG, "%s: negative size", who);
     if (M == 0 || N2 == 0) return KBN_OK;
-    KBN_REQUIRE(in && q && scale, KBN_ERR_ARG, "kbn_silu_mul_quant_1x128: null pointer");
-    KBN_REQUIRE(N2 % 128 == 0, KBN_ERR_ARG, "kbn_silu_mul_quant_1x128: N2=%lld must be a multiple of 128", (long long)N2);
-    KBN_REQUIRE(ld_in >= 2 * N2 && ld_q >= N2, KBN_ERR_ARG, "kbn_silu_mul_quant_1x128: row stride too small");
+    KBN_REQUIRE(in && q && scale, KBN_ERR_ARG, "%s: null pointer", who);
+    KBN_REQUIRE(rows_mode == 0 || row_info, KBN_ERR_ARG, "%s: null row information", who);
+    KBN_REQUIRE(N2 % 128 == 0, KBN_ERR_ARG, "%s: N2=%lld must be a multiple of 128", who, (long long)N2);
+    KBN_REQUIRE(ld_in >= 2 * N2 && ld_q >= N2, KBN_ERR_ARG, "%s: row stride too small", who);
     KBN_REQUIRE(ld_in % 8 == 0 && ld_q % 8 == 0 && aligned16(in) && ((reinterpret_cast<uintptr_t>(q) & 7u) == 0),
-                KBN_ERR_ARG, "kbn_silu_mul_quant_1x128: pointers/strides must be 16-byte (in) and 8-byte (q) aligned");
-    KBN_REQUIRE(eps >= 1e-30f && eps < 1e30f, KBN_ERR_ARG, "kbn_silu_mul_quant_1x128: eps %g outside [1e-30, 1e30)", (double)eps);
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
+                KBN_ERR_ARG, "%s: pointers/strides must be 16-byte (in) and 8-byte (q) aligned", who);
+    KBN_REQUIRE(eps >= 1e-30f && eps < 1e30f, KBN_ERR_ARG, "%s: eps %g outside [1e-30, 1e30)", who, (double)eps);
     const uint16_t* table = nullptr;
     int rc = silu_table_for_stream(st, &table);
     if (rc != KBN_OK) return rc;
     constexpr int U = 2;
-    const int64_t NG = M * (N2 / 128);
-    int64_t blocks = (NG + 16 * U - 1) / (16 * U);
-    KBN_REQUIRE(blocks < (1ll << 31), KBN_ERR_ARG, "kbn_silu_mul_quant_1x128: too many groups");
+    const int64_t G = N2 / 128, cpr = (G + U - 1) / U, n_chunks = M * cpr;
+    KBN_REQUIRE(2 * N2 < (1ll << 31) && n_chunks < (1ll << 31) && max_m < (1ll << 31), KBN_ERR_ARG, "%s: more than 2^31 groups", who);
     const auto* ib = static_cast<const __nv_bfloat16*>(in);
     auto* qb = static_cast<uint8_t*>(q);
-    if (ue8m0)
-        silu_mul_quant_kernel<true, U><<<(unsigned)blocks, 256, 0, st>>>(ib, M, N2, ld_in, qb, ld_q, scale, s_row, s_grp, eps, table);
-    else
-        silu_mul_quant_kernel<false, U><<<(unsigned)blocks, 256, 0, st>>>(ib, M, N2, ld_in, qb, ld_q, scale, s_row, s_grp, eps, table);
+    const unsigned nb = (unsigned)((n_chunks + 15) / 16);
+    const uint32_t mm = (uint32_t)max_m;
+#define KBN_SMQ(UE, RM)                                                                                                   \
+    silu_mul_quant_kernel<UE, U, RM><<<nb, 256, 0, st>>>(ib, (uint32_t)N2, ld_in, qb, ld_q, scale, s_row, s_grp, eps, table, \
+                                                         row_info, mm, (uint32_t)G, (uint32_t)cpr, (uint32_t)n_chunks)
+    if (ue8m0) {
+        if (rows_mode == 0) KBN_SMQ(true, 0); else if (rows_mode == 1) KBN_SMQ(true, 1); else KBN_SMQ(true, 2);
+    } else {
+        if (rows_mode == 0) KBN_SMQ(false, 0); else if (rows_mode == 1) KBN_SMQ(false, 1); else KBN_SMQ(false, 2);
+    }
+#undef KBN_SMQ
     KBN_CHECK_LAUNCH();
     return KBN_OK;
+}
+
+// masked layout [E, max_m, 2*N2] -> q [E, max_m, N2], row-major scales [E, max_m, N2/128]
+int silu_mul_quant_masked(const void* in, int64_t E, int64_t max_m, int64_t N2, void* q, float* scale,
+                          const int32_t* masked_m, cudaStream_t st) {
+    return launch_silu_mul_quant("silu_mul_quant_masked", in, E * max_m, N2, 2 * N2, q, N2, scale, N2 / 128, 1, 1e-10f, 1, 2,
+                                 masked_m, max_m, st);
+}
+
+}  // namespace kbn
+
+extern "C" int kbn_silu_mul_quant_1x128(const void* in, int64_t M, int64_t N2, int64_t ld_in, void* q,
+                                        int64_t ld_q, float* scale, int64_t s_row, int64_t s_grp, float eps,
+                                        int ue8m0, kbn_stream_t stream) {
+    return kbn::launch_silu_mul_quant("kbn_silu_mul_quant_1x128", in, M, N2, ld_in, q, ld_q, scale, s_row, s_grp, eps, ue8m0, 0,
+                                      nullptr, 1, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int kbn_silu_mul_quant_1x128_rows(const void* in, int64_t M, int64_t N2, int64_t ld_in, void* q,
+                                             int64_t ld_q, float* scale, int64_t s_row, int64_t s_grp, float eps,
+                                             int ue8m0, const int32_t* row_expert, kbn_stream_t stream) {
+    return kbn::launch_silu_mul_quant("kbn_silu_mul_quant_1x128_rows", in, M, N2, ld_in, q, ld_q, scale, s_row, s_grp, eps, ue8m0, 1,
+                                      row_expert, 1, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int kbn_silu_mul_quant_1x128_masked(const void* in, int64_t E, int64_t max_m, int64_t N2, void* q, float* scale,
+                                               const int32_t* masked_m, kbn_stream_t stream) {
+    KBN_REQUIRE(E >= 0 && max_m > 0, KBN_ERR_ARG, "kbn_silu_mul_quant_1x128_masked: bad sizes");
+    return kbn::silu_mul_quant_masked(in, E, max_m, N2, q, scale, masked_m, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int kbn_silu_bf16_table(void* out_u16, kbn_stream_t stream) {

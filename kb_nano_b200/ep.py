@@ -1,0 +1,126 @@
+"""Expert-parallel FP8 MoE layer: host side.
+
+One process per GPU.  `EpMoe` owns the C-side context (symmetric buffers, peer mappings) and calls
+`kbn_ep_moe_forward`; torch.distributed is used once, at construction, to exchange the 64-byte CUDA
+IPC handles.  The data path never touches NCCL: rows travel by peer stores issued from this
+library's kernels.
+
+Expert placement: rank r of R owns the contiguous block of experts [r*E/R, (r+1)*E/R); tokens stay
+where they are.  kb-nano shards every expert's intermediate dimension over the ranks instead and
+all-reduces the layer output (tasks/baseline/L2/deepseek_moe.py:56,301-302); it has no
+expert-parallel layer, so the single-GPU result is what this layer is checked against.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+from .ops import _on, _stream
+
+FP8 = torch.float8_e4m3fn
+STATUS_TEXT = {0: "ok", 10: "an expert received more than max_m rows", 11: "expert id out of range",
+               20: "timed out waiting for a peer's signal"}
+
+
+def expert_range(rank: int, world: int, experts_total: int) -> tuple[int, int]:
+    if experts_total % world:
+        raise ValueError(f"{experts_total} experts do not divide over {world} ranks")
+    per = experts_total // world
+    return rank * per, (rank + 1) * per
+
+
+def plan(topk_ids: torch.Tensor, world: int, experts_total: int):
+    """(destination rank, local expert index) of every (token, slot) pair -- the placement rule the
+    dispatch kernel applies."""
+    per = experts_total // world
+    ids = topk_ids.long()
+    return ids // per, ids % per
+
+
+class EpStatusError(RuntimeError):
+    pass
+
+
+class EpMoe:
+    def __init__(self, rank: int, world: int, experts_total: int, hidden: int, inter: int, max_tokens: int, topk: int,
+                 max_m: int = 256, group=None, device: torch.device | None = None):
+        self.rank, self.world = rank, world
+        self.experts_total, self.hidden, self.inter = experts_total, hidden, inter
+        self.max_tokens, self.topk, self.max_m = max_tokens, topk, max_m
+        self.lo, self.hi = expert_range(rank, world, experts_total)
+        self.device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self._lib = _lib.load()
+        self._ctx = ctypes.c_void_p()
+        with _on(self.device):
+            _lib.check(self._lib.kbn_ep_create(rank, world, experts_total, max_m, hidden, inter, max_tokens, topk,
+                                               ctypes.byref(self._ctx)))
+            if world > 1:
+                import torch.distributed as dist
+                buf = ctypes.create_string_buffer(64)
+                _lib.check(self._lib.kbn_ep_ipc_handle(self._ctx, buf))
+                handles = [None] * world
+                dist.all_gather_object(handles, bytes(buf.raw), group=group)
+                blob = b"".join(handles)
+                _lib.check(self._lib.kbn_ep_attach(self._ctx, blob))
+                dist.barrier(group=group)
+
+    @property
+    def symmetric_bytes(self) -> int:
+        return int(self._lib.kbn_ep_symmetric_bytes(self._ctx))
+
+    def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_w: torch.Tensor, w13: torch.Tensor, w13_s: torch.Tensor,
+                w2: torch.Tensor, w2_s: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        """x bf16 [T,H] (this rank's tokens), topk_ids [T,topk] global expert ids, topk_w [T,topk];
+        w13/w2 (+ scales) of this rank's experts only -> bf16 [T,H]."""
+        t = x.shape[0]
+        e_l = self.hi - self.lo
+        if x.dtype != torch.bfloat16 or x.dim() != 2 or x.shape[1] != self.hidden or not x.is_contiguous():
+            raise ValueError("x must be contiguous bf16 [T, hidden]")
+        if tuple(w13.shape) != (e_l, 2 * self.inter, self.hidden) or tuple(w2.shape) != (e_l, self.hidden, self.inter):
+            raise ValueError("w13 / w2 must hold this rank's experts: [E/R, 2I, H] and [E/R, H, I]")
+        if w13.dtype != FP8 or w2.dtype != FP8 or not w13.is_contiguous() or not w2.is_contiguous():
+            raise ValueError("w13 / w2 must be contiguous float8_e4m3fn")
+        for s_, n_, k_ in ((w13_s, 2 * self.inter, self.hidden), (w2_s, self.hidden, self.inter)):
+            if s_.dtype != torch.float32 or tuple(s_.shape) != (e_l, n_ // 128, k_ // 128) or not s_.is_contiguous():
+                raise ValueError("weight scales must be contiguous float32 [E/R, N/128, K/128]")
+        ids = topk_ids if topk_ids.dtype == torch.int32 else topk_ids.to(torch.int32)
+        ids = ids if ids.is_contiguous() else ids.contiguous()
+        w = topk_w if topk_w.dtype == torch.float32 else topk_w.float()
+        w = w if w.is_contiguous() else w.contiguous()
+        if tuple(ids.shape) != (t, self.topk) or tuple(w.shape) != (t, self.topk):
+            raise ValueError("topk_ids / topk_w must be [T, topk]")
+        if out is None:
+            out = torch.empty(t, self.hidden, dtype=torch.bfloat16, device=x.device)
+        with _on(self.device):
+            _lib.check(self._lib.kbn_ep_moe_forward(self._ctx, x.data_ptr(), ids.data_ptr(), w.data_ptr(), t, w13.data_ptr(),
+                                                    w13_s.data_ptr(), w2.data_ptr(), w2_s.data_ptr(), out.data_ptr(), _stream(x)))
+        return out
+
+    def status(self) -> dict:
+        """Synchronises; {code, phase, peer, detail, text}."""
+        arr = (ctypes.c_int32 * 4)()
+        with _on(self.device):
+            _lib.check(self._lib.kbn_ep_status(self._ctx, arr, torch.cuda.current_stream(self.device).cuda_stream))
+        code = int(arr[0])
+        return {"code": code, "phase": int(arr[1]), "peer": int(arr[2]), "detail": int(arr[3]), "text": STATUS_TEXT.get(code, "unknown")}
+
+    def check(self) -> None:
+        s = self.status()
+        if s["code"] != 0:
+            raise EpStatusError(f"expert-parallel layer on rank {self.rank}: {s}")
+
+    LAUNCHES_PER_FORWARD = 9   # quant, dispatch, wait, GEMM1, act-quant, GEMM2, send, wait, sum
+
+    def close(self) -> None:
+        if self._ctx:
+            with _on(self.device):
+                self._lib.kbn_ep_destroy(self._ctx)
+            self._ctx = ctypes.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -50,13 +50,14 @@ def weight(n: int, k: int, seed: int = 0, device="cpu", std: float = 0.02):
     return block_quant_128x128(w)
 
 
-def expert_weights(e: int, n: int, k: int, seed: int = 0, device="cpu", std: float = 0.02):
-    """[e,n,k] expert weights generated and quantised one expert at a time (sub-seed seed*1000003+i),
-    so the bf16 master of only one expert is alive at once."""
+def expert_weights(e: int, n: int, k: int, seed: int = 0, device="cpu", std: float = 0.02, first: int = 0):
+    """[e,n,k] expert weights generated and quantised one expert at a time (expert `first + i` uses
+    sub-seed seed*1000003 + first + i, so a rank that owns a block of experts generates exactly the
+    weights the whole set would have), keeping only one expert's bf16 master alive at once."""
     q = torch.empty(e, n, k, dtype=FP8, device=device)
     s = torch.empty(e, n // 128, k // 128, dtype=torch.float32, device=device)
     for i in range(e):
-        q[i], s[i] = weight(n, k, seed * 1000003 + i, device, std)
+        q[i], s[i] = weight(n, k, seed * 1000003 + first + i, device, std)
     return q, s
 
 

@@ -1,0 +1,86 @@
+"""FP8 MoE expert pipeline on one GPU: quant -> permute -> grouped GEMM1 -> fused SiLU*up+quant ->
+grouped GEMM2 -> weighted combine.  Mirrors FusedExperts._forward_deep_gemm
+(tasks/baseline/L2/fused_experts.py:246-283) step for step, with every step a kernel of this library:
+seven launches per layer, no host synchronisation, scratch buffers reused across calls.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import ops
+
+FP8 = torch.float8_e4m3fn
+
+
+class MoeScratch:
+    """Reusable device buffers for one (T, topk, E, H, I) problem size.  Layers run one after the
+    other, so one set per shape is shared (kb-nano does the same, fused_experts.py:139-206)."""
+
+    def __init__(self, t: int, topk: int, e: int, h: int, i: int, device: torch.device):
+        self.key = (t, topk, e, h, i, str(device))
+        m_cap = ops.moe_aligned_rows(t, topk, e)
+        self.m_cap = m_cap
+        self.a_q = torch.empty(t, h, dtype=FP8, device=device)
+        self.a_s = torch.empty(t, h // 128, dtype=torch.float32, device=device)
+        self.a_perm = torch.empty(m_cap, h, dtype=FP8, device=device)
+        self.a_s_perm = torch.empty(m_cap, h // 128, dtype=torch.float32, device=device)
+        self.row_expert = torch.empty(m_cap, dtype=torch.int32, device=device)
+        self.dest_row = torch.empty(t, topk, dtype=torch.int32, device=device)
+        self.workspace = torch.empty(ops.moe_permute_workspace_bytes(t, topk, e), dtype=torch.uint8, device=device)
+        # GEMM1 and GEMM2 outputs share one byte buffer, as they are never alive together
+        self.mm = torch.empty(m_cap * max(2 * i, h), dtype=torch.bfloat16, device=device)
+        self.a2_q = torch.empty(m_cap, i, dtype=FP8, device=device)
+        self.a2_s = torch.empty(i // 128, m_cap, dtype=torch.float32, device=device).t()
+
+    def mm1(self, i: int) -> torch.Tensor:
+        return self.mm[: self.m_cap * 2 * i].view(self.m_cap, 2 * i)
+
+    def mm2(self, h: int) -> torch.Tensor:
+        return self.mm[: self.m_cap * h].view(self.m_cap, h)
+
+
+_SCRATCH: dict = {}
+
+
+def get_scratch(t: int, topk: int, e: int, h: int, i: int, device: torch.device) -> MoeScratch:
+    key = (t, topk, e, h, i, str(device))
+    s = _SCRATCH.get(key)
+    if s is None:
+        _SCRATCH.clear()          # keep one size alive: the buffers are large
+        s = MoeScratch(t, topk, e, h, i, device)
+        _SCRATCH[key] = s
+    return s
+
+
+def fused_experts_fp8(hidden_states: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, topk_weights: torch.Tensor,
+                      topk_ids: torch.Tensor, num_experts: int, w13_scale: torch.Tensor, w2_scale: torch.Tensor,
+                      scratch: MoeScratch | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """hidden bf16 [T,H]; w13 fp8 [E,2I,H] + fp32 scales [E,2I/128,H/128]; w2 fp8 [E,H,I] + scales
+    [E,H/128,I/128]; topk_weights [T,topk] (fp32 or bf16), topk_ids [T,topk] int -> bf16 [T,H]."""
+    t, h = hidden_states.shape
+    e, n2, _ = w13.shape
+    i = n2 // 2
+    topk = topk_ids.shape[1]
+    if h % 128 or i % 128:
+        raise ValueError(f"hidden size {h} and intermediate size {i} must be multiples of 128")
+    dev = hidden_states.device
+    sc = scratch if scratch is not None else get_scratch(t, topk, e, h, i, dev)
+    ids = topk_ids if topk_ids.dtype == torch.int32 else topk_ids.to(torch.int32)
+    ids = ids if ids.is_contiguous() else ids.contiguous()
+    w = topk_weights if topk_weights.dtype == torch.float32 else topk_weights.float()
+    w = w if w.is_contiguous() else w.contiguous()
+    x = hidden_states if hidden_states.is_contiguous() else hidden_states.contiguous()
+    if out is None:
+        out = torch.empty(t, h, dtype=torch.bfloat16, device=dev)
+    ops.per_token_group_quant_fp8(x, sc.a_q, sc.a_s)
+    ops.moe_permute(sc.a_q, sc.a_s, ids, num_experts, sc.a_perm, sc.a_s_perm, sc.row_expert, sc.dest_row, sc.workspace)
+    mm1 = sc.mm1(i)
+    ops.m_grouped_fp8_gemm_nt_contiguous(sc.a_perm, sc.a_s_perm, w13, w13_scale, mm1, sc.row_expert)
+    ops.silu_mul_quant_fp8_rows(mm1, sc.a2_q, sc.a2_s, sc.row_expert)
+    mm2 = sc.mm2(h)
+    ops.m_grouped_fp8_gemm_nt_contiguous(sc.a2_q, sc.a2_s, w2, w2_scale, mm2, sc.row_expert)
+    ops.moe_unpermute_combine(mm2, sc.dest_row, w, out)
+    return out
+
+
+LAUNCHES_PER_LAYER = 8   # quant, rank, offsets, scatter, GEMM1, silu-mul-quant, GEMM2, combine

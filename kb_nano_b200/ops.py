@@ -88,6 +88,46 @@ def silu_mul_quant_fp8(inp: torch.Tensor, out_fp8: torch.Tensor, out_scale: torc
                                                         _stream(inp)))
 
 
+def silu_mul_quant_fp8_rows(inp: torch.Tensor, out_fp8: torch.Tensor, out_scale: torch.Tensor, row_expert: torch.Tensor,
+                            use_ue8m0: bool = True, eps: float = 1e-10) -> None:
+    """As silu_mul_quant_fp8, but only rows with row_expert[m] >= 0 are read and written (the padding
+    rows of the expert-contiguous layout are skipped)."""
+    dev = _cuda(inp, out_fp8, out_scale, row_expert)
+    m, n = inp.shape
+    n2 = n // 2
+    if inp.dtype != torch.bfloat16 or inp.stride(1) != 1 or n % 2 or n2 % GROUP:
+        raise ValueError("inp must be bf16 [M, 2*N2] with N2 a multiple of 128, contiguous along the last dim")
+    if out_fp8.dtype != FP8 or tuple(out_fp8.shape) != (m, n2) or out_fp8.stride(1) != 1:
+        raise ValueError("out_fp8 must be float8_e4m3fn [M, N2], contiguous along the last dim")
+    if row_expert.dtype != torch.int32 or row_expert.numel() != m or not row_expert.is_contiguous():
+        raise ValueError("row_expert must be contiguous int32 [M]")
+    s_row, s_grp = _scale_strides(out_scale, m, n2 // GROUP)
+    with _on(dev):
+        _lib.check(_lib.load().kbn_silu_mul_quant_1x128_rows(inp.data_ptr(), m, n2, inp.stride(0) if m > 1 else n,
+                                                             out_fp8.data_ptr(), out_fp8.stride(0) if m > 1 else n2,
+                                                             out_scale.data_ptr(), s_row, s_grp, eps, int(use_ue8m0),
+                                                             row_expert.data_ptr(), _stream(inp)))
+
+
+def silu_mul_quant_fp8_masked(inp: torch.Tensor, out_fp8: torch.Tensor, out_scale: torch.Tensor, masked_m: torch.Tensor) -> None:
+    """Masked layout: inp bf16 [E,max_m,2*N2] -> out_fp8 [E,max_m,N2], out_scale fp32 [E,max_m,N2/128]
+    (all contiguous); only rows m < masked_m[e] are processed."""
+    dev = _cuda(inp, out_fp8, out_scale, masked_m)
+    e, max_m, n = inp.shape
+    n2 = n // 2
+    if inp.dtype != torch.bfloat16 or not inp.is_contiguous() or n2 % GROUP:
+        raise ValueError("inp must be contiguous bf16 [E, max_m, 2*N2] with N2 a multiple of 128")
+    if out_fp8.dtype != FP8 or tuple(out_fp8.shape) != (e, max_m, n2) or not out_fp8.is_contiguous():
+        raise ValueError("out_fp8 must be contiguous float8_e4m3fn [E, max_m, N2]")
+    if out_scale.dtype != torch.float32 or tuple(out_scale.shape) != (e, max_m, n2 // GROUP) or not out_scale.is_contiguous():
+        raise ValueError("out_scale must be contiguous float32 [E, max_m, N2/128]")
+    if masked_m.dtype != torch.int32 or masked_m.numel() != e or not masked_m.is_contiguous():
+        raise ValueError("masked_m must be contiguous int32 [E]")
+    with _on(dev):
+        _lib.check(_lib.load().kbn_silu_mul_quant_1x128_masked(inp.data_ptr(), e, max_m, n2, out_fp8.data_ptr(),
+                                                               out_scale.data_ptr(), masked_m.data_ptr(), _stream(inp)))
+
+
 def silu_bf16_table(device: torch.device | str = "cuda") -> torch.Tensor:
     """bf16 [65536]: silu(g) rounded to bf16 for every gate bit pattern g, as the fused kernel computes it."""
     out = torch.empty(65536, dtype=torch.int16, device=device)
@@ -175,3 +215,57 @@ def gemm_status(device: torch.device | str = "cuda") -> int:
     with _on(dev if dev.index is not None else torch.device("cuda", torch.cuda.current_device())):
         _lib.check(_lib.load().kbn_gemm_status(ctypes.byref(out), torch.cuda.current_stream().cuda_stream))
     return int(out.value)
+
+
+def moe_aligned_rows(t: int, topk: int, e: int) -> int:
+    return int(_lib.load().kbn_moe_aligned_rows(t, topk, e))
+
+
+def moe_permute(a_q: torch.Tensor, a_s: torch.Tensor, topk_ids: torch.Tensor, num_experts: int,
+                a_perm: torch.Tensor, a_s_perm: torch.Tensor, row_expert: torch.Tensor, dest_row: torch.Tensor,
+                workspace: torch.Tensor) -> None:
+    """Group quantised rows by expert into 128-aligned segments (all outputs caller-allocated)."""
+    dev = _cuda(a_q, a_s, topk_ids, a_perm, a_s_perm, row_expert, dest_row, workspace)
+    t, k = a_q.shape
+    topk = topk_ids.shape[1]
+    g = k // GROUP
+    m_cap = a_perm.shape[0]
+    if a_q.dtype != FP8 or a_perm.dtype != FP8 or not a_q.is_contiguous() or not a_perm.is_contiguous() or a_perm.shape[1] != k:
+        raise ValueError("a_q / a_perm must be contiguous float8_e4m3fn with the same K")
+    if a_s.dtype != torch.float32 or tuple(a_s.shape) != (t, g) or not a_s.is_contiguous():
+        raise ValueError("a_s must be contiguous float32 [T, K/128]")
+    if a_s_perm.dtype != torch.float32 or tuple(a_s_perm.shape) != (m_cap, g) or not a_s_perm.is_contiguous():
+        raise ValueError("a_s_perm must be contiguous float32 [M_cap, K/128]")
+    if topk_ids.dtype != torch.int32 or not topk_ids.is_contiguous() or topk_ids.shape[0] != t:
+        raise ValueError("topk_ids must be contiguous int32 [T, topk]")
+    if row_expert.dtype != torch.int32 or row_expert.numel() != m_cap or not row_expert.is_contiguous():
+        raise ValueError("row_expert must be contiguous int32 [M_cap]")
+    if dest_row.dtype != torch.int32 or tuple(dest_row.shape) != (t, topk) or not dest_row.is_contiguous():
+        raise ValueError("dest_row must be contiguous int32 [T, topk]")
+    ws_bytes = workspace.numel() * workspace.element_size()
+    with _on(dev):
+        _lib.check(_lib.load().kbn_moe_permute(a_q.data_ptr(), a_s.data_ptr(), topk_ids.data_ptr(), t, topk, k, num_experts,
+                                               a_perm.data_ptr(), a_s_perm.data_ptr(), row_expert.data_ptr(),
+                                               dest_row.data_ptr(), m_cap, workspace.data_ptr(), ws_bytes, _stream(a_q)))
+
+
+def moe_permute_workspace_bytes(t: int, topk: int, e: int) -> int:
+    return int(_lib.load().kbn_moe_permute_workspace_bytes(t, topk, e))
+
+
+def moe_unpermute_combine(rows: torch.Tensor, dest_row: torch.Tensor, topk_w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t] = sum_s topk_w[t,s] * rows[dest_row[t,s]]  (bf16 rows, fp32 weights and accumulation)."""
+    dev = _cuda(rows, dest_row, topk_w, out)
+    t, topk = dest_row.shape
+    h = out.shape[1]
+    if rows.dtype != torch.bfloat16 or rows.stride(1) != 1 or rows.shape[1] != h:
+        raise ValueError("rows must be bf16 [M_cap, H], contiguous along H")
+    if out.dtype != torch.bfloat16 or tuple(out.shape) != (t, h) or not out.is_contiguous():
+        raise ValueError("out must be contiguous bf16 [T, H]")
+    if topk_w.dtype != torch.float32 or tuple(topk_w.shape) != (t, topk) or not topk_w.is_contiguous():
+        raise ValueError("topk_w must be contiguous float32 [T, topk]")
+    if dest_row.dtype != torch.int32 or not dest_row.is_contiguous():
+        raise ValueError("dest_row must be contiguous int32 [T, topk]")
+    with _on(dev):
+        _lib.check(_lib.load().kbn_moe_unpermute_combine(rows.data_ptr(), rows.stride(0), dest_row.data_ptr(),
+                                                         topk_w.data_ptr(), t, topk, h, out.data_ptr(), _stream(out)))

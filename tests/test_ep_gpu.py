@@ -1,0 +1,112 @@
+"""Expert-parallel MoE layer on GPUs.  With one visible GPU the layer runs with world size 1 (every
+"peer" store lands in the rank's own buffers), which still exercises dispatch, the signal/wait pair,
+the masked grouped GEMMs, the return path and the weighted sum.  With two or more GPUs a second test
+spawns one process per GPU and checks every rank's output against the single-process oracle."""
+import os
+
+import pytest
+import torch
+
+from oracle import torch_oracle as to
+from tests.util import assert_gemm_close
+
+pytestmark = pytest.mark.gpu
+
+
+def ep_case(world, t_per_rank, h, i, e, topk, seed):
+    from kb_nano_b200 import inputs
+    xs = [inputs.activations(t_per_rank, h, seed=seed + r) for r in range(world)]
+    routes = [inputs.route_sigmoid_topk(inputs.router_logits(t_per_rank, e, seed=seed + r), topk) for r in range(world)]
+    w13_q, w13_s = inputs.expert_weights(e, 2 * i, h, seed=seed + 100, std=0.05)
+    w2_q, w2_s = inputs.expert_weights(e, h, i, seed=seed + 200, std=0.05)
+    return xs, routes, (w13_q, w13_s, w2_q, w2_s)
+
+
+def test_ep_world1_matches_oracle(cuda_dev):
+    from kb_nano_b200 import ep, ops
+    t, h, i, e, topk = 96, 512, 256, 16, 4
+    xs, routes, (w13_q, w13_s, w2_q, w2_s) = ep_case(1, t, h, i, e, topk, seed=3)
+    d = cuda_dev
+    layer = ep.EpMoe(0, 1, e, h, i, max_tokens=128, topk=topk, max_m=64, device=d)
+    wd = [w.to(d) for w in (w13_q, w13_s, w2_q, w2_s)]
+    ref = to.moe_layer(xs[0], w13_q, w13_s, w2_q, w2_s, routes[0][0], routes[0][1])
+    for it in range(3):        # repeated calls reuse buffers, counters and flags
+        out = layer.forward(xs[0].to(d), routes[0][1].to(d), routes[0][0].to(d), *[wd[j] for j in (0, 1, 2, 3)])
+        layer.check()
+        assert ops.gemm_status(d) == 0
+        assert_gemm_close(out.cpu(), ref, f"EP world=1, call {it}")
+    # fewer tokens than max_tokens, then none at all
+    out = layer.forward(xs[0][:5].to(d), routes[0][1][:5].to(d), routes[0][0][:5].to(d), *wd)
+    assert_gemm_close(out.cpu(), ref[:5], "EP world=1, 5 tokens")
+    out = layer.forward(xs[0][:0].to(d), routes[0][1][:0].to(d), routes[0][0][:0].to(d), *wd)
+    assert out.shape == (0, h)
+    layer.check()
+    layer.close()
+
+
+def test_ep_overflow_is_reported_not_fatal(cuda_dev):
+    """More rows for one expert than max_m: the status word says so and the context stays usable."""
+    from kb_nano_b200 import ep
+    t, h, i, e, topk = 64, 256, 128, 4, 1
+    xs, routes, (w13_q, w13_s, w2_q, w2_s) = ep_case(1, t, h, i, e, topk, seed=5)
+    d = cuda_dev
+    layer = ep.EpMoe(0, 1, e, h, i, max_tokens=64, topk=topk, max_m=8, device=d)
+    ids = torch.zeros(t, 1, dtype=torch.int32)        # all 64 tokens to expert 0, room for 8
+    layer.forward(xs[0].to(d), ids.to(d), torch.ones(t, 1).to(d), w13_q.to(d), w13_s.to(d), w2_q.to(d), w2_s.to(d))
+    st = layer.status()
+    assert st["code"] == 10 and st["detail"] == 0
+    with pytest.raises(ep.EpStatusError):
+        layer.check()
+    layer.close()
+
+
+def _ep_worker(rank, world, port, t, h, i, e, topk, seed, q):
+    import torch.distributed as dist
+    from kb_nano_b200 import ep, ops
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    d = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=d)
+    try:
+        xs, routes, (w13_q, w13_s, w2_q, w2_s) = ep_case(world, t, h, i, e, topk, seed)
+        lo, hi = ep.expert_range(rank, world, e)
+        layer = ep.EpMoe(rank, world, e, h, i, max_tokens=t, topk=topk, max_m=128, device=d)
+        loc = [w[lo:hi].contiguous().to(d) for w in (w13_q, w13_s, w2_q, w2_s)]
+        ref = to.moe_layer(xs[rank], w13_q, w13_s, w2_q, w2_s, routes[rank][0], routes[rank][1])
+        ok, msg = True, ""
+        for it in range(3):
+            out = layer.forward(xs[rank].to(d), routes[rank][1].to(d), routes[rank][0].to(d), *loc)
+            st = layer.status()
+            if st["code"] != 0 or ops.gemm_status(d) != 0:
+                ok, msg = False, f"status {st}"
+                break
+            try:
+                assert_gemm_close(out.cpu(), ref, f"rank {rank} call {it}")
+            except AssertionError as ex:
+                ok, msg = False, str(ex)
+                break
+        dist.barrier()
+        layer.close()
+        q.put((rank, ok, msg))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_ep_multi_gpu_matches_oracle(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29500 + world
+    procs = [ctx.Process(target=_ep_worker, args=(r, world, port, 64, 512, 256, 16, 4, 11, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=300)
+    results = [q.get(timeout=5) for _ in range(world)]
+    for p in procs:
+        assert p.exitcode == 0
+    for rank, ok, msg in sorted(results):
+        assert ok, f"rank {rank}: {msg}"

@@ -1,0 +1,124 @@
+"""GPU parity of the MoE permutation kernels (bit-exact against kb-nano's own permute, from the
+golden fixture) and of the whole FP8 expert pipeline (tolerance rule of the GEMMs)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import torch_oracle as to
+from tests.util import assert_gemm_close, bf16_from_bits, fp8_from_bits, golden
+
+pytestmark = pytest.mark.gpu
+FP8 = torch.float8_e4m3fn
+
+
+def run_permute(a_q, a_s, ids, e, dev):
+    from kb_nano_b200 import ops
+    t, k = a_q.shape
+    topk = ids.shape[1]
+    m_cap = ops.moe_aligned_rows(t, topk, e)
+    a_perm = torch.zeros(m_cap, k, dtype=torch.uint8, device=dev).view(FP8)
+    s_perm = torch.zeros(m_cap, k // 128, device=dev)
+    row_expert = torch.full((m_cap,), -7, dtype=torch.int32, device=dev)
+    dest = torch.full((t, topk), -7, dtype=torch.int32, device=dev)
+    ws = torch.empty(ops.moe_permute_workspace_bytes(t, topk, e), dtype=torch.uint8, device=dev)
+    ops.moe_permute(a_q.to(dev), a_s.to(dev), ids.to(dev), e, a_perm, s_perm, row_expert, dest, ws)
+    return a_perm.cpu(), s_perm.cpu(), row_expert.cpu(), dest.cpu()
+
+
+def test_permute_matches_reference_layout(cuda_dev):
+    g = golden("permute")
+    e = 4
+    a_perm, s_perm, row_expert, dest = run_permute(fp8_from_bits(g["a_q"]), torch.from_numpy(g["a_s"]),
+                                                   torch.from_numpy(g["topk_ids"]), e, cuda_dev)
+    assert a_perm.shape[0] == g["a_perm"].shape[0]
+    assert (row_expert.numpy() == g["row_expert"]).all()
+    assert (dest.numpy() == g["inv_perm"]).all()
+    valid = g["row_expert"] >= 0
+    assert (a_perm.view(torch.uint8).numpy()[valid] == g["a_perm"][valid]).all()
+    assert (s_perm.numpy()[valid] == g["as_perm"][valid]).all()
+
+
+def test_combine_matches_reference(cuda_dev):
+    from kb_nano_b200 import ops
+    g = golden("permute")
+    mm2 = bf16_from_bits(g["mm2"]).to(cuda_dev)
+    out = torch.empty(g["combined"].shape, dtype=torch.bfloat16, device=cuda_dev)
+    ops.moe_unpermute_combine(mm2, torch.from_numpy(g["inv_perm"]).to(cuda_dev), torch.from_numpy(g["topk_w"]).to(cuda_dev), out)
+    ref = bf16_from_bits(g["combined"])
+    # same products; the reference rounds the fp32 sum once as well, only the summation order may differ
+    assert float((out.cpu().float() - ref.float()).abs().max()) <= 2.0 ** -7 * float(ref.float().abs().max())
+    assert_gemm_close(out.cpu(), ref, "combine")
+
+
+@pytest.mark.parametrize("t,topk,e", [(1, 1, 1), (7, 2, 3), (300, 8, 64), (128, 8, 256), (64, 4, 5)])
+def test_permute_properties(cuda_dev, t, topk, e):
+    """Stable grouping with 128-aligned segments, for shapes with empty experts and every token on one expert."""
+    gen = torch.Generator().manual_seed(t * 31 + e)
+    k = 256
+    a_q = torch.randint(0, 255, (t, k), dtype=torch.uint8, generator=gen).view(FP8)
+    a_s = torch.rand(t, k // 128, generator=gen)
+    if e == 5:
+        ids = torch.full((t, topk), 3, dtype=torch.int32)          # everything to one expert
+    else:
+        ids = torch.stack([torch.randperm(e, generator=gen)[:topk] for _ in range(t)]).to(torch.int32) if topk <= e else torch.zeros(t, topk, dtype=torch.int32)
+    a_perm, s_perm, row_expert, dest = run_permute(a_q, a_s, ids, e, cuda_dev)
+    flat = ids.reshape(-1)
+    counts = torch.bincount(flat.long(), minlength=e)
+    off = torch.zeros(e + 1, dtype=torch.long)
+    off[1:] = torch.cumsum((counts + 127) // 128 * 128, 0)
+    exp_rows = torch.full_like(row_expert, -1)
+    for x in range(e):
+        exp_rows[off[x]:off[x] + counts[x]] = x
+    assert (row_expert == exp_rows).all()
+    seen = {}
+    for i in range(flat.numel()):
+        x = int(flat[i])
+        r = seen.get(x, 0)
+        seen[x] = r + 1
+        assert int(dest.reshape(-1)[i]) == int(off[x]) + r
+    d = dest.reshape(-1).long()
+    assert (a_perm.view(torch.uint8)[d] == a_q.view(torch.uint8).repeat_interleave(topk, 0)).all()
+    assert (s_perm[d] == a_s.repeat_interleave(topk, 0)).all()
+
+
+def moe_case(t, h, i, e, topk, seed, routing):
+    from kb_nano_b200 import inputs
+    x = inputs.activations(t, h, seed=seed)
+    w13_q, w13_s = inputs.expert_weights(e, 2 * i, h, seed=seed + 1, std=0.05)
+    w2_q, w2_s = inputs.expert_weights(e, h, i, seed=seed + 2, std=0.05)
+    logits = inputs.router_logits(t, e, seed=seed)
+    tw, ti = (inputs.route_sigmoid_topk if routing == "sigmoid" else inputs.route_softmax_topk)(logits, topk)
+    return x, w13_q, w13_s, w2_q, w2_s, tw, ti
+
+
+@pytest.mark.parametrize("t,h,i,e,topk,routing", [(64, 512, 256, 8, 2, "softmax"), (200, 1024, 256, 32, 8, "sigmoid"), (1, 256, 128, 4, 2, "softmax")])
+def test_moe_layer_vs_oracle(cuda_dev, t, h, i, e, topk, routing):
+    from kb_nano_b200 import moe
+    x, w13_q, w13_s, w2_q, w2_s, tw, ti = moe_case(t, h, i, e, topk, seed=t + e, routing=routing)
+    ref = to.moe_layer(x, w13_q, w13_s, w2_q, w2_s, tw, ti)
+    d = cuda_dev
+    out = moe.fused_experts_fp8(x.to(d), w13_q.to(d), w2_q.to(d), tw.to(d), ti.to(d), e, w13_s.to(d), w2_s.to(d))
+    assert_gemm_close(out.cpu(), ref, f"moe layer t={t} e={e}")
+    # bf16 router weights (as MixtralMoE casts them) and int64 ids go through the same path
+    out2 = moe.fused_experts_fp8(x.to(d), w13_q.to(d), w2_q.to(d), tw.to(torch.bfloat16).to(d), ti.long().to(d), e, w13_s.to(d), w2_s.to(d))
+    ref2 = to.moe_layer(x, w13_q, w13_s, w2_q, w2_s, tw.to(torch.bfloat16), ti)
+    assert_gemm_close(out2.cpu(), ref2, "moe layer, bf16 weights")
+
+
+def test_fused_experts_candidate_golden(cuda_dev):
+    """The FusedExperts drop-in class on the reference-generated fixture."""
+    import importlib.util, os, sys
+    from kb_nano_b200 import candidate_dir
+    spec = importlib.util.spec_from_file_location("_candidate_impl_L2_fused_experts", os.path.join(candidate_dir(), "L2", "fused_experts.py"))
+    mod = importlib.util.module_from_spec(spec); sys.modules[spec.name] = mod; spec.loader.exec_module(mod)
+    g = golden("fused_experts")
+    d = cuda_dev
+    x = bf16_from_bits(g["x"]).to(d)
+    x0 = x.clone()
+    out = mod.FusedExperts()(x, fp8_from_bits(g["w13_q"]).to(d), fp8_from_bits(g["w2_q"]).to(d), torch.from_numpy(g["topk_w"]).to(d),
+                             torch.from_numpy(g["topk_ids"]).to(d), 4, w13_scale=torch.from_numpy(g["w13_s"]).to(d),
+                             w2_scale=torch.from_numpy(g["w2_s"]).to(d), use_fp8_w8a8=True, block_shape=[128, 128])
+    assert_gemm_close(out.cpu(), bf16_from_bits(g["out"]), "FusedExperts golden")
+    assert bool((x == x0).all())
+    with pytest.raises(NotImplementedError):
+        mod.FusedExperts()(x, x, x, x, x, 4)
