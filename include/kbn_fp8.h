@@ -110,6 +110,41 @@ int kbn_fp8_grouped_gemm_masked(const void* A, const float* sa, int64_t sa_exp, 
                                 const int32_t* masked_m, int64_t E, int64_t max_m, int64_t N,
                                 int64_t K, kbn_stream_t stream);
 
+/*
+ * UE8M0 fast path of the three GEMMs above, for scales that are all powers of two (what kb-nano's
+ * activation quantisation always produces, and its weights after the UE8M0 re-quantisation of
+ * tasks/baseline/L1/fp8_linear.py:492-499).  Same arithmetic contract and the same kb-nano call
+ * sites as the fp32-scale entry points; the scales are passed in the packed form the block-scaled
+ * tensor-core instruction reads (tcgen05.mma.kind::mxf8f6f4.block_scale), which is also the role of
+ * DeepGEMM's transform_sf_into_required_layout (tasks/baseline/L1/fp8_linear.py:502-510).
+ *   kbn_pack_sf_rows:    fp32 [rows, ceil(K/128)] (element (r,kb) at scale[r*s_row + kb*s_grp]) ->
+ *                        kbn_packed_sf_rows_bytes(rows, K) bytes.  For the masked layout pass
+ *                        rows = E*max_m (max_m % 128 == 0).
+ *   kbn_pack_sf_weights: fp32 [E, ceil(N/128), ceil(K/128)] -> kbn_packed_sf_weights_bytes(E, N, K) bytes.
+ *   kbn_count_non_pow2_scales: adds to *device_count the number of scales that are not positive
+ *                        powers of two; a caller uses it once per weight tensor to choose the path.
+ * Requirements beyond the fp32-scale kernels: contiguous-layout segments and max_m are multiples of
+ * 128 rows; all pointers 16-byte aligned.
+ */
+int64_t kbn_packed_sf_rows_bytes(int64_t rows, int64_t K);
+int64_t kbn_packed_sf_weights_bytes(int64_t E, int64_t N, int64_t K);
+int kbn_pack_sf_rows(const float* scale, int64_t rows, int64_t K, int64_t s_row, int64_t s_grp,
+                     void* packed, kbn_stream_t stream);
+int kbn_pack_sf_weights(const float* sb, int64_t E, int64_t N, int64_t K, void* packed,
+                        kbn_stream_t stream);
+int kbn_count_non_pow2_scales(const float* s, int64_t n, int32_t* device_count, kbn_stream_t stream);
+int kbn_fp8_gemm_nt_ue8m0(const void* A, const void* sfa_packed, const void* B,
+                          const void* sfb_packed, void* C, int64_t ldc, int64_t M, int64_t N,
+                          int64_t K, kbn_stream_t stream);
+int kbn_fp8_grouped_gemm_contig_ue8m0(const void* A, const void* sfa_packed, const void* B,
+                                      const void* sfb_packed, void* C, int64_t ldc,
+                                      const int32_t* row_expert, int64_t M_sum, int64_t N, int64_t K,
+                                      int64_t E, kbn_stream_t stream);
+int kbn_fp8_grouped_gemm_masked_ue8m0(const void* A, const void* sfa_packed, const void* B,
+                                      const void* sfb_packed, void* C, const int32_t* masked_m,
+                                      int64_t E, int64_t max_m, int64_t N, int64_t K,
+                                      kbn_stream_t stream);
+
 /* Device status word of the GEMM kernels' bounded waits: 0 = no wait ever ran out in this
  * process.  Host pointer out; synchronises `stream` first. */
 int kbn_gemm_status(int32_t* host_out, kbn_stream_t stream);

@@ -27,6 +27,14 @@ SIGNATURES = {
     "kbn_fp8_grouped_gemm_contig": (_i32, [_ptr, _ptr, _i64, _i64, _ptr, _ptr, _ptr, _i64, _ptr, _i64, _i64, _i64, _i64, _ptr]),
     "kbn_fp8_grouped_gemm_masked": (_i32, [_ptr, _ptr, _i64, _i64, _i64, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _ptr]),
     "kbn_gemm_status": (_i32, [_ptr, _ptr]),
+    "kbn_packed_sf_rows_bytes": (_i64, [_i64, _i64]),
+    "kbn_packed_sf_weights_bytes": (_i64, [_i64, _i64, _i64]),
+    "kbn_pack_sf_rows": (_i32, [_ptr, _i64, _i64, _i64, _i64, _ptr, _ptr]),
+    "kbn_pack_sf_weights": (_i32, [_ptr, _i64, _i64, _i64, _ptr, _ptr]),
+    "kbn_count_non_pow2_scales": (_i32, [_ptr, _i64, _ptr, _ptr]),
+    "kbn_fp8_gemm_nt_ue8m0": (_i32, [_ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _ptr]),
+    "kbn_fp8_grouped_gemm_contig_ue8m0": (_i32, [_ptr, _ptr, _ptr, _ptr, _ptr, _i64, _ptr, _i64, _i64, _i64, _i64, _ptr]),
+    "kbn_fp8_grouped_gemm_masked_ue8m0": (_i32, [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _ptr]),
     "kbn_moe_aligned_rows": (_i64, [_i64, _i64, _i64]),
     "kbn_moe_permute_workspace_bytes": (_i64, [_i64, _i64, _i64]),
     "kbn_moe_permute": (_i32, [_ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _ptr, _ptr, _ptr, _ptr, _i64, _ptr, _i64, _ptr]),

@@ -1,0 +1,115 @@
+// Tile scheduling and bounded waits shared by the two FP8 GEMM kernels (fp32-scale promotion kernel
+// and UE8M0 block-scaled kernel).
+#pragma once
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace kbn {
+
+constexpr int kBlockM = 128, kBlockK = 128;
+constexpr int kSwizzleGroupM = 8;                        // m-blocks that share B tiles in L2
+constexpr long long kWaitLimitCycles = 2000000000ll;     // about a second
+
+enum GemmMode : int { kDense = 0, kContig = 1, kMasked = 2 };
+
+struct GemmParams {
+    const float* sa;
+    int64_t sa_exp, sa_row, sa_grp;
+    const float* sb;
+    __nv_bfloat16* C;
+    int64_t ldc;
+    const int32_t* row_expert;
+    const int32_t* masked_m;
+    int32_t* status;
+    int32_t rows_total;   // rows of the 2-D view of A / C
+    int32_t N, K, E, max_m;
+    int32_t num_m_blocks, num_n_blocks, num_k_blocks, sb_nb;
+    int32_t mode;
+};
+
+struct Tile {
+    int32_t row0;      // first row in the 2-D view of A and C
+    int32_t row_end;   // rows >= row_end are not written
+    int32_t n_blk;
+    int32_t expert;
+    bool compute;      // false: nothing to do for this tile (padding block)
+};
+
+// Deterministic tile sequence; every role walks the same one.
+struct TileWalk {
+    const GemmParams& p;
+    int32_t e_cur = 0, blk_base = 0;
+    __device__ explicit TileWalk(const GemmParams& pp) : p(pp) {}
+
+    __device__ __forceinline__ int32_t masked_blocks(int32_t e) const {
+        int32_t mm = min(max(p.masked_m[e], 0), p.max_m);
+        return (mm + kBlockM - 1) / kBlockM;
+    }
+
+    __device__ bool get(int64_t t, Tile& tile) {
+        if (p.mode == kMasked) {
+            int64_t mb = t / p.num_n_blocks;
+            tile.n_blk = (int32_t)(t - mb * p.num_n_blocks);
+            while (e_cur < p.E) {
+                int32_t nb = masked_blocks(e_cur);
+                if (mb < (int64_t)blk_base + nb) break;
+                blk_base += nb;
+                ++e_cur;
+            }
+            if (e_cur >= p.E) return false;
+            tile.expert = e_cur;
+            tile.row0 = e_cur * p.max_m + (int32_t)(mb - blk_base) * kBlockM;
+            tile.row_end = e_cur * p.max_m + min(max(p.masked_m[e_cur], 0), p.max_m);
+            tile.compute = true;
+            return true;
+        }
+        const int64_t total = (int64_t)p.num_m_blocks * p.num_n_blocks;
+        if (t >= total) return false;
+        const int64_t per_group = (int64_t)kSwizzleGroupM * p.num_n_blocks;
+        const int32_t grp = (int32_t)(t / per_group);
+        const int32_t first_m = grp * kSwizzleGroupM;
+        const int32_t gsz = min(kSwizzleGroupM, p.num_m_blocks - first_m);
+        const int32_t within = (int32_t)(t - grp * per_group);
+        const int32_t m_blk = first_m + within % gsz;
+        tile.n_blk = within / gsz;
+        tile.row0 = m_blk * kBlockM;
+        tile.row_end = p.rows_total;
+        tile.expert = 0;
+        tile.compute = true;
+        if (p.mode == kContig) {
+            int32_t e = p.row_expert[tile.row0];
+            tile.expert = e;
+            tile.compute = (e >= 0 && e < p.E);
+        }
+        return true;
+    }
+};
+
+struct WaitCtx {
+    volatile int* abort_flag;   // shared memory
+    int32_t* status;            // global
+    int code;
+};
+
+// Bounded mbarrier wait.  Returns false when the CTA is aborting.
+__device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, const WaitCtx& w) {
+    if (ptx::mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (uint32_t it = 1;; ++it) {
+        if (ptx::mbar_try_wait(bar, parity)) return true;
+        if ((it & 63u) == 0u) {
+            if (*w.abort_flag) return false;
+            if (clock64() - t0 > kWaitLimitCycles) {
+                *w.abort_flag = 1;
+                atomicCAS(w.status, 0, w.code | (int)(blockIdx.x << 8));
+                return false;
+            }
+        }
+    }
+}
+
+
+// Device status word shared by all GEMM launches of the process (lives in runtime.cu).
+int gemm_status_ptr(int32_t** out);
+
+}  // namespace kbn

@@ -14,12 +14,11 @@
 // raises a CTA-wide abort flag and falls through to the common teardown (TMEM is released).
 #include <cuda.h>
 
-#include "common.cuh"
-#include "sm100_ptx.cuh"
+#include "gemm_common.cuh"
 
 namespace kbn {
 
-constexpr int kBlockM = 128, kBlockN = 128, kBlockK = 128;
+constexpr int kBlockN = 128;
 constexpr int kStages = 6;
 constexpr int kTileBytes = kBlockM * kBlockK;            // 16 KB per operand tile (fp8)
 constexpr int kStageBytes = 2 * kTileBytes;
@@ -27,109 +26,7 @@ constexpr int kEpiWarps = 8;
 constexpr int kThreads = 32 * (2 + kEpiWarps);
 constexpr int kAccBufs = 4;                              // TMEM accumulators in flight (MMA <-> promotion handshake)
 constexpr int kTmemCols = kAccBufs * 128;                // all 512 columns: four 128-column fp32 accumulators
-constexpr int kSwizzleGroupM = 8;                        // m-blocks that share B tiles in L2
-constexpr long long kWaitLimitCycles = 2000000000ll;     // about a second
 constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
-
-enum GemmMode : int { kDense = 0, kContig = 1, kMasked = 2 };
-
-struct GemmParams {
-    const float* sa;
-    int64_t sa_exp, sa_row, sa_grp;
-    const float* sb;
-    __nv_bfloat16* C;
-    int64_t ldc;
-    const int32_t* row_expert;
-    const int32_t* masked_m;
-    int32_t* status;
-    int32_t rows_total;   // rows of the 2-D view of A / C
-    int32_t N, K, E, max_m;
-    int32_t num_m_blocks, num_n_blocks, num_k_blocks, sb_nb;
-    int32_t mode;
-};
-
-struct Tile {
-    int32_t row0;      // first row in the 2-D view of A and C
-    int32_t row_end;   // rows >= row_end are not written
-    int32_t n_blk;
-    int32_t expert;
-    bool compute;      // false: nothing to do for this tile (padding block)
-};
-
-// Deterministic tile sequence; every role walks the same one.
-struct TileWalk {
-    const GemmParams& p;
-    int32_t e_cur = 0, blk_base = 0;
-    __device__ explicit TileWalk(const GemmParams& pp) : p(pp) {}
-
-    __device__ __forceinline__ int32_t masked_blocks(int32_t e) const {
-        int32_t mm = min(max(p.masked_m[e], 0), p.max_m);
-        return (mm + kBlockM - 1) / kBlockM;
-    }
-
-    __device__ bool get(int64_t t, Tile& tile) {
-        if (p.mode == kMasked) {
-            int64_t mb = t / p.num_n_blocks;
-            tile.n_blk = (int32_t)(t - mb * p.num_n_blocks);
-            while (e_cur < p.E) {
-                int32_t nb = masked_blocks(e_cur);
-                if (mb < (int64_t)blk_base + nb) break;
-                blk_base += nb;
-                ++e_cur;
-            }
-            if (e_cur >= p.E) return false;
-            tile.expert = e_cur;
-            tile.row0 = e_cur * p.max_m + (int32_t)(mb - blk_base) * kBlockM;
-            tile.row_end = e_cur * p.max_m + min(max(p.masked_m[e_cur], 0), p.max_m);
-            tile.compute = true;
-            return true;
-        }
-        const int64_t total = (int64_t)p.num_m_blocks * p.num_n_blocks;
-        if (t >= total) return false;
-        const int64_t per_group = (int64_t)kSwizzleGroupM * p.num_n_blocks;
-        const int32_t grp = (int32_t)(t / per_group);
-        const int32_t first_m = grp * kSwizzleGroupM;
-        const int32_t gsz = min(kSwizzleGroupM, p.num_m_blocks - first_m);
-        const int32_t within = (int32_t)(t - grp * per_group);
-        const int32_t m_blk = first_m + within % gsz;
-        tile.n_blk = within / gsz;
-        tile.row0 = m_blk * kBlockM;
-        tile.row_end = p.rows_total;
-        tile.expert = 0;
-        tile.compute = true;
-        if (p.mode == kContig) {
-            int32_t e = p.row_expert[tile.row0];
-            tile.expert = e;
-            tile.compute = (e >= 0 && e < p.E);
-        }
-        return true;
-    }
-};
-
-struct WaitCtx {
-    volatile int* abort_flag;   // shared memory
-    int32_t* status;            // global
-    int code;
-};
-
-// Bounded mbarrier wait.  Returns false when the CTA is aborting.
-__device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, const WaitCtx& w) {
-    if (ptx::mbar_try_wait(bar, parity)) return true;
-    const long long t0 = clock64();
-    for (uint32_t it = 1;; ++it) {
-        if (ptx::mbar_try_wait(bar, parity)) return true;
-        if ((it & 63u) == 0u) {
-            if (*w.abort_flag) return false;
-            if (clock64() - t0 > kWaitLimitCycles) {
-                *w.abort_flag = 1;
-                atomicCAS(w.status, 0, w.code | (int)(blockIdx.x << 8));
-                return false;
-            }
-        }
-    }
-}
-
-__device__ int32_t g_gemm_status = 0;
 
 __global__ void __launch_bounds__(kThreads, 1)
 fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
@@ -372,7 +269,8 @@ static int launch_gemm(const void* A, int64_t a_rows, const void* B, int64_t b_r
     if (rc != KBN_OK) return rc;
     rc = make_tmap(&tmB, B, b_rows, p.K, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
     if (rc != KBN_OK) return rc;
-    KBN_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&p.status), g_gemm_status));
+    rc = gemm_status_ptr(&p.status);
+    if (rc != KBN_OK) return rc;
     int64_t grid = sm_count();
     if (max_tiles < grid) grid = max_tiles;
     if (grid <= 0) return KBN_OK;
@@ -443,10 +341,3 @@ extern "C" int kbn_fp8_grouped_gemm_masked(const void* A, const float* sa, int64
     return launch_gemm(A, E * max_m, B, E * N, p, max_tiles, static_cast<cudaStream_t>(stream));
 }
 
-extern "C" int kbn_gemm_status(int32_t* host_out, kbn_stream_t stream) {
-    using namespace kbn;
-    KBN_REQUIRE(host_out, KBN_ERR_ARG, "kbn_gemm_status: null pointer");
-    KBN_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
-    KBN_CUDA(cudaMemcpyFromSymbol(host_out, g_gemm_status, sizeof(int32_t)));
-    return KBN_OK;
-}

@@ -1,0 +1,423 @@
+// Block-scaled FP8 GEMM, UE8M0 fast path: when every activation and weight scale is a power of two,
+// the scales ride along as UE8M0 bytes in TMEM and the tensor core applies them itself
+// (tcgen05.mma.kind::mxf8f6f4.block_scale), so a whole 128x256 output tile accumulates in TMEM over
+// all of K and is read back once.  Same three forms (dense, expert-contiguous, masked) and the
+// same tile walk as the fp32-scale kernel.
+//
+//   warp 0      producer: per K-block one TMA box of A (128 B x 128 rows), one of B (128 B x 256
+//               rows), and two plain bulk copies of the packed scale blocks (512 B + 1024 B)
+//   warp 1      TMEM allocation; per K-block three tcgen05.cp (scale blocks -> TMEM columns) and
+//               four 128x256x32 block-scaled UMMAs
+//   warps 2..9  epilogue once per tile: TMEM -> registers -> bf16 -> global
+//
+// Compared with 128x128 tiles this moves 48 KB instead of 64 KB through L2 per 128x256x128 of work,
+// which is what bounds the kernel once the weights stream from HBM.  Packed scale layout (built by
+// kbn_pack_sf_*): one 32-bit word per (row, K-block) holding the UE8M0 byte four times, stored per
+// 128-row block as [32][4] words so that word (l, i) belongs to row 32*i + l -- the order in which
+// tcgen05.cp.32x128b.warpx4 spreads a 512-byte block over TMEM lanes and columns.
+#include <cuda.h>
+
+#include "gemm_common.cuh"
+
+namespace kbn {
+namespace mx {
+
+constexpr int kBN = 256;
+constexpr int kStages = 4;
+constexpr int kABytes = kBlockM * kBlockK;          // 16 KB
+constexpr int kBBytes = kBN * kBlockK;              // 32 KB
+constexpr int kStageBytes = kABytes + kBBytes;      // 48 KB
+constexpr int kSfaBytes = 512, kSfbBytes = 1024, kSfStage = kSfaBytes + kSfbBytes;
+constexpr int kTxBytes = kStageBytes + kSfStage;
+constexpr int kEpiWarps = 8;
+constexpr int kThreads = 32 * (2 + kEpiWarps);
+constexpr int kTmemCols = 512;
+constexpr int kColSfa = 256, kColSfb = 260;         // TMEM columns of the scale factors
+constexpr size_t kSmemBytes = (size_t)kStages * (kStageBytes + kSfStage) + 1024 + 256;
+
+struct MxExtra {
+    const uint8_t* sfa;      // packed [row_blocks][KB][512 B]
+    const uint8_t* sfb;      // packed [E][KB][nb_pad][512 B]
+    int32_t nb_pad;          // 128-column blocks per expert, rounded up to even
+};
+
+__global__ void __launch_bounds__(kThreads, 1)
+fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p,
+                   const MxExtra x) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~(uintptr_t)1023u);
+    uint8_t* sf_smem = smem + (size_t)kStages * kStageBytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sf_smem + (size_t)kStages * kSfStage);
+    // bars: full[kStages], empty[kStages], tmem_full, tmem_empty
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t bar_full = ptx::smem_u32(bars), bar_empty = ptx::smem_u32(bars + kStages);
+    const uint32_t bar_tfull = ptx::smem_u32(bars + 2 * kStages), bar_tempty = ptx::smem_u32(bars + 2 * kStages + 1);
+    const uint32_t smem_tiles = ptx::smem_u32(smem), smem_sf = ptx::smem_u32(sf_smem);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            ptx::mbar_init(bar_full + 8 * s, 1);
+            ptx::mbar_init(bar_empty + 8 * s, 1);
+        }
+        ptx::mbar_init(bar_tfull, 1);
+        ptx::mbar_init(bar_tempty, kEpiWarps);
+        *abort_flag = 0;
+        ptx::fence_barrier_init();
+        ptx::fence_proxy_async();
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(ptx::smem_u32(tmem_slot), kTmemCols);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const int KB = p.num_k_blocks;
+
+    if (warp == 0) {
+        // ---------------- producer ----------------
+        if (lane == 0) {
+            ptx::prefetch_tensormap(&tmA);
+            ptx::prefetch_tensormap(&tmB);
+            WaitCtx w{abort_flag, p.status, 4};
+            TileWalk walk(p);
+            Tile tile;
+            uint32_t it = 0;
+            bool ok = true;
+            for (int64_t t = blockIdx.x; ok && walk.get(t, tile); t += gridDim.x) {
+                if (!tile.compute) continue;
+                const int32_t b_row = tile.expert * p.N + tile.n_blk * kBN;
+                const uint8_t* sfa = x.sfa + (int64_t)(tile.row0 / kBlockM) * KB * kSfaBytes;
+                const uint8_t* sfb = x.sfb + (((int64_t)tile.expert * KB) * x.nb_pad + 2 * tile.n_blk) * (int64_t)kSfaBytes;
+                for (int kb = 0; kb < KB; ++kb, ++it) {
+                    const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+                    if (!wait_bar(bar_empty + 8 * s, ph ^ 1u, w)) { ok = false; break; }
+                    const uint32_t bar = bar_full + 8 * s;
+                    ptx::mbar_arrive_expect_tx(bar, kTxBytes);
+                    const uint32_t dst = smem_tiles + s * kStageBytes;
+                    ptx::tma_load_2d(dst, &tmA, kb * kBlockK, tile.row0, bar);
+                    ptx::tma_load_2d(dst + kABytes, &tmB, kb * kBlockK, b_row, bar);
+                    const uint32_t sdst = smem_sf + s * kSfStage;
+                    ptx::bulk_load(sdst, sfa + (int64_t)kb * kSfaBytes, kSfaBytes, bar);
+                    ptx::bulk_load(sdst + kSfaBytes, sfb + (int64_t)kb * x.nb_pad * kSfaBytes, kSfbBytes, bar);
+                }
+            }
+            if (!ok) {
+                const long long t0 = clock64();
+                while (clock64() - t0 < 400000ll) __nanosleep(1000);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            WaitCtx w{abort_flag, p.status, 5};
+            TileWalk walk(p);
+            Tile tile;
+            uint32_t it = 0, tile_it = 0;
+            constexpr uint32_t idesc = ptx::umma_idesc_mx_e4m3(kBlockM, kBN, 0, 0);
+            bool ok = true;
+            for (int64_t t = blockIdx.x; ok && walk.get(t, tile); t += gridDim.x) {
+                if (!tile.compute) continue;
+                // the single accumulator must have been drained by the epilogue of the previous tile
+                if (!wait_bar(bar_tempty, (tile_it & 1u) ^ 1u, w)) { ok = false; break; }
+                ptx::tc_fence_after();
+                for (int kb = 0; kb < KB; ++kb, ++it) {
+                    const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+                    if (!wait_bar(bar_full + 8 * s, ph, w)) { ok = false; break; }
+                    ptx::tc_fence_after();
+                    const uint32_t a_addr = smem_tiles + s * kStageBytes;
+                    const uint32_t sf_addr = smem_sf + s * kSfStage;
+                    ptx::tmem_cp_32x128b_warpx4(tmem_base + kColSfa, ptx::umma_desc_sf(sf_addr));
+                    ptx::tmem_cp_32x128b_warpx4(tmem_base + kColSfb, ptx::umma_desc_sf(sf_addr + kSfaBytes));
+                    ptx::tmem_cp_32x128b_warpx4(tmem_base + kColSfb + 4, ptx::umma_desc_sf(sf_addr + 2 * kSfaBytes));
+                    const uint64_t a_desc = ptx::umma_desc_k_sw128(a_addr);
+                    const uint64_t b_desc = ptx::umma_desc_k_sw128(a_addr + kABytes);
+#pragma unroll
+                    for (int k = 0; k < kBlockK / 32; ++k)
+                        ptx::mma_mxf8f6f4_block_scale(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc, tmem_base + kColSfa,
+                                                      tmem_base + kColSfb, (kb > 0 || k > 0) ? 1u : 0u);
+                    ptx::mma_commit(bar_empty + 8 * s);
+                }
+                if (!ok) break;
+                ptx::mma_commit(bar_tfull);
+                ++tile_it;
+            }
+        }
+    } else {
+        // ---------------- epilogue ----------------
+        const int quarter = warp & 3;
+        const int half = (warp - 2) >> 2;            // columns 128*half .. 128*half+127
+        const int r_in_tile = quarter * 32 + lane;
+        WaitCtx w{abort_flag, p.status, 6};
+        TileWalk walk(p);
+        Tile tile;
+        uint32_t tile_it = 0;
+        bool ok = true;
+        for (int64_t t = blockIdx.x; ok && walk.get(t, tile); t += gridDim.x) {
+            if (!tile.compute) continue;
+            const int32_t row = tile.row0 + r_in_tile;
+            bool row_ok = row < tile.row_end;
+            if (p.mode == kContig && row_ok) row_ok = p.row_expert[row] >= 0;
+            if (!wait_bar(bar_tfull, tile_it & 1u, w)) { ok = false; break; }
+            ptx::tc_fence_after();
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + half * 128;
+            const int32_t n0 = tile.n_blk * kBN + half * 128;
+            __nv_bfloat16* crow = p.C + (int64_t)row * p.ldc + n0;
+            const bool vec_ok = (reinterpret_cast<uintptr_t>(crow) & 15u) == 0;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint32_t r[32];
+                ptx::tmem_ld_32x32(taddr + 32 * c, r);
+                ptx::tmem_ld_wait(r);
+                if (row_ok) {
+                    if (n0 + 32 * c + 32 <= p.N && vec_ok) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 8) {
+                            uint4 v;
+                            v.x = pack_bf16x2(__uint_as_float(r[j + 0]), __uint_as_float(r[j + 1]));
+                            v.y = pack_bf16x2(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                            v.z = pack_bf16x2(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
+                            v.w = pack_bf16x2(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
+                            *reinterpret_cast<uint4*>(crow + 32 * c + j) = v;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (n0 + 32 * c + j < p.N) crow[32 * c + j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+                    }
+                }
+            }
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(bar_tempty);
+            ++tile_it;
+        }
+    }
+
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// ---- scale packing -----------------------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t ue8m0_word(float s) {
+    uint32_t b = (__float_as_uint(s) >> 23) & 0xffu;
+    return b * 0x01010101u;
+}
+
+// fp32 per-row scales (any strides) -> packed blocks [row_blocks][KB][32][4] words; rows past the end get 1.0
+__global__ void pack_sf_rows_kernel(const float* __restrict__ s, int64_t rows, int KB, int64_t s_row, int64_t s_grp,
+                                    uint32_t* __restrict__ out, int64_t total_words) {
+    const int64_t w = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (w >= total_words) return;
+    const int i = (int)(w & 3), l = (int)((w >> 2) & 31);
+    const int64_t blk_kb = w >> 7;
+    const int kb = (int)(blk_kb % KB);
+    const int64_t row = (blk_kb / KB) * 128 + i * 32 + l;
+    out[w] = row < rows ? ue8m0_word(s[row * s_row + kb * s_grp]) : 0x7f7f7f7fu;
+}
+
+// fp32 128x128 block scales [E][NB][KB] -> packed [E][KB][nb_pad][128 words], every word of a block equal
+__global__ void pack_sf_weights_kernel(const float* __restrict__ sb, int E, int NB, int KB, int nb_pad,
+                                       uint32_t* __restrict__ out, int64_t total_words) {
+    const int64_t w = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (w >= total_words) return;
+    const int64_t blk = w >> 7;
+    const int nb = (int)(blk % nb_pad);
+    const int64_t ek = blk / nb_pad;
+    const int kb = (int)(ek % KB);
+    const int e = (int)(ek / KB);
+    out[w] = nb < NB ? ue8m0_word(sb[((int64_t)e * NB + nb) * KB + kb]) : 0x7f7f7f7fu;
+}
+
+// Counts scales that are not positive powers of two (mantissa bits set, zero, negative, inf/nan).
+__global__ void count_non_pow2_kernel(const float* __restrict__ s, int64_t n, int32_t* __restrict__ count) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const uint32_t b = __float_as_uint(s[i]);
+    const uint32_t e = (b >> 23) & 0xffu;
+    if ((b & 0x807fffffu) != 0u || e == 0u || e == 255u) atomicAdd(count, 1);
+}
+
+// ---- host side -----------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+static int make_tmap(CUtensorMap* tm, const void* base, int64_t rows, int64_t K, int box_rows, CUtensorMapL2promotion promo) {
+    EncodeTiledFn fn = encode_fn();
+    KBN_REQUIRE(fn, KBN_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)K};
+    cuuint32_t box[2] = {(cuuint32_t)kBlockK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, promo, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    KBN_REQUIRE(r == CUDA_SUCCESS, KBN_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d (rows=%lld K=%lld)",
+                (int)r, (long long)rows, (long long)K);
+    return KBN_OK;
+}
+
+static int check_device() {
+    static int ok[64] = {0};
+    int dev = 0;
+    KBN_CUDA(cudaGetDevice(&dev));
+    KBN_REQUIRE(dev >= 0 && dev < 64, KBN_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+    if (!ok[dev]) {
+        int major = 0;
+        KBN_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+        KBN_REQUIRE(major == 10, KBN_ERR_UNSUPPORTED, "kbn_fp8 GEMMs need an sm_100 device (found major %d)", major);
+        KBN_CUDA(cudaFuncSetAttribute(fp8_gemm_mx_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+        ok[dev] = 1;
+    }
+    return KBN_OK;
+}
+
+static inline int32_t cdiv32(int64_t a, int64_t b) { return (int32_t)((a + b - 1) / b); }
+
+static int launch(const void* A, int64_t a_rows, const void* B, int64_t b_rows, GemmParams& p, const void* sfa, const void* sfb,
+                  int64_t max_tiles, cudaStream_t st) {
+    int rc = check_device();
+    if (rc != KBN_OK) return rc;
+    KBN_REQUIRE(sfa && sfb, KBN_ERR_ARG, "fp8 gemm (ue8m0): null packed scales");
+    KBN_REQUIRE(aligned16(A) && aligned16(B) && aligned16(sfa) && aligned16(sfb), KBN_ERR_ARG, "fp8 gemm (ue8m0): pointers must be 16-byte aligned");
+    KBN_REQUIRE(p.K % 16 == 0 && p.K > 0 && p.N > 0, KBN_ERR_ARG, "fp8 gemm (ue8m0): K=%d must be a positive multiple of 16", p.K);
+    KBN_REQUIRE(a_rows < (1ll << 31) && b_rows < (1ll << 31), KBN_ERR_ARG, "fp8 gemm (ue8m0): more than 2^31 rows");
+    CUtensorMap tmA, tmB;
+    rc = make_tmap(&tmA, A, a_rows, p.K, kBlockM, CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
+    if (rc != KBN_OK) return rc;
+    rc = make_tmap(&tmB, B, b_rows, p.K, kBN, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+    if (rc != KBN_OK) return rc;
+    rc = gemm_status_ptr(&p.status);
+    if (rc != KBN_OK) return rc;
+    MxExtra x;
+    x.sfa = static_cast<const uint8_t*>(sfa);
+    x.sfb = static_cast<const uint8_t*>(sfb);
+    x.nb_pad = (cdiv32(p.N, 128) + 1) / 2 * 2;
+    int64_t grid = sm_count();
+    if (max_tiles < grid) grid = max_tiles;
+    if (grid <= 0) return KBN_OK;
+    fp8_gemm_mx_kernel<<<(unsigned)grid, kThreads, kSmemBytes, st>>>(tmA, tmB, p, x);
+    KBN_CHECK_LAUNCH();
+    return KBN_OK;
+}
+
+static void fill_params(GemmParams& p, void* C, int64_t ldc, int64_t rows, int64_t N, int64_t K, int64_t E, int64_t max_m, int mode) {
+    p.sa = nullptr; p.sb = nullptr; p.sa_exp = p.sa_row = p.sa_grp = 0;
+    p.C = static_cast<__nv_bfloat16*>(C); p.ldc = ldc;
+    p.rows_total = (int32_t)rows; p.N = (int32_t)N; p.K = (int32_t)K; p.E = (int32_t)E; p.max_m = (int32_t)max_m;
+    p.num_m_blocks = mode == kMasked ? 0 : cdiv32(rows, kBlockM);
+    p.num_n_blocks = cdiv32(N, kBN); p.num_k_blocks = cdiv32(K, kBlockK); p.sb_nb = cdiv32(N, 128);
+    p.mode = mode;
+}
+
+}  // namespace mx
+}  // namespace kbn
+
+extern "C" int64_t kbn_packed_sf_rows_bytes(int64_t rows, int64_t K) {
+    return ((rows + 127) / 128) * ((K + 127) / 128) * 512;
+}
+
+extern "C" int64_t kbn_packed_sf_weights_bytes(int64_t E, int64_t N, int64_t K) {
+    int64_t nb_pad = ((N + 127) / 128 + 1) / 2 * 2;
+    return E * ((K + 127) / 128) * nb_pad * 512;
+}
+
+extern "C" int kbn_pack_sf_rows(const float* scale, int64_t rows, int64_t K, int64_t s_row, int64_t s_grp, void* packed,
+                                kbn_stream_t stream) {
+    using namespace kbn;
+    KBN_REQUIRE(rows >= 0 && K >= 0, KBN_ERR_ARG, "kbn_pack_sf_rows: negative size");
+    const int64_t words = kbn_packed_sf_rows_bytes(rows, K) / 4;
+    if (words == 0) return KBN_OK;
+    KBN_REQUIRE(scale && packed && aligned16(packed), KBN_ERR_ARG, "kbn_pack_sf_rows: null or misaligned pointer");
+    mx::pack_sf_rows_kernel<<<(unsigned)((words + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        scale, rows, (int)((K + 127) / 128), s_row, s_grp, static_cast<uint32_t*>(packed), words);
+    KBN_CHECK_LAUNCH();
+    return KBN_OK;
+}
+
+extern "C" int kbn_pack_sf_weights(const float* sb, int64_t E, int64_t N, int64_t K, void* packed, kbn_stream_t stream) {
+    using namespace kbn;
+    KBN_REQUIRE(E >= 0 && N >= 0 && K >= 0, KBN_ERR_ARG, "kbn_pack_sf_weights: negative size");
+    const int64_t words = kbn_packed_sf_weights_bytes(E, N, K) / 4;
+    if (words == 0) return KBN_OK;
+    KBN_REQUIRE(sb && packed && aligned16(packed), KBN_ERR_ARG, "kbn_pack_sf_weights: null or misaligned pointer");
+    const int NB = (int)((N + 127) / 128);
+    mx::pack_sf_weights_kernel<<<(unsigned)((words + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        sb, (int)E, NB, (int)((K + 127) / 128), (NB + 1) / 2 * 2, static_cast<uint32_t*>(packed), words);
+    KBN_CHECK_LAUNCH();
+    return KBN_OK;
+}
+
+extern "C" int kbn_count_non_pow2_scales(const float* s, int64_t n, int32_t* device_count, kbn_stream_t stream) {
+    using namespace kbn;
+    KBN_REQUIRE(n >= 0, KBN_ERR_ARG, "kbn_count_non_pow2_scales: negative size");
+    KBN_REQUIRE(device_count, KBN_ERR_ARG, "kbn_count_non_pow2_scales: null pointer");
+    if (n == 0) return KBN_OK;
+    KBN_REQUIRE(s, KBN_ERR_ARG, "kbn_count_non_pow2_scales: null pointer");
+    mx::count_non_pow2_kernel<<<(unsigned)((n + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(s, n, device_count);
+    KBN_CHECK_LAUNCH();
+    return KBN_OK;
+}
+
+extern "C" int kbn_fp8_gemm_nt_ue8m0(const void* A, const void* sfa_packed, const void* B, const void* sfb_packed, void* C,
+                                     int64_t ldc, int64_t M, int64_t N, int64_t K, kbn_stream_t stream) {
+    using namespace kbn;
+    KBN_REQUIRE(M >= 0 && N >= 0 && K >= 0, KBN_ERR_ARG, "kbn_fp8_gemm_nt_ue8m0: negative size");
+    if (M == 0 || N == 0) return KBN_OK;
+    KBN_REQUIRE(A && B && C && ldc >= N, KBN_ERR_ARG, "kbn_fp8_gemm_nt_ue8m0: null pointer or ldc < N");
+    GemmParams p{};
+    mx::fill_params(p, C, ldc, M, N, K, 1, 0, kDense);
+    return mx::launch(A, M, B, N, p, sfa_packed, sfb_packed, (int64_t)p.num_m_blocks * p.num_n_blocks, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int kbn_fp8_grouped_gemm_contig_ue8m0(const void* A, const void* sfa_packed, const void* B, const void* sfb_packed,
+                                                 void* C, int64_t ldc, const int32_t* row_expert, int64_t M_sum, int64_t N,
+                                                 int64_t K, int64_t E, kbn_stream_t stream) {
+    using namespace kbn;
+    KBN_REQUIRE(M_sum >= 0 && N >= 0 && K >= 0 && E >= 0, KBN_ERR_ARG, "kbn_fp8_grouped_gemm_contig_ue8m0: negative size");
+    if (M_sum == 0 || N == 0 || E == 0) return KBN_OK;
+    KBN_REQUIRE(A && B && C && row_expert && ldc >= N, KBN_ERR_ARG, "kbn_fp8_grouped_gemm_contig_ue8m0: null pointer or ldc < N");
+    KBN_REQUIRE(E * N < (1ll << 31), KBN_ERR_ARG, "kbn_fp8_grouped_gemm_contig_ue8m0: E*N too large");
+    GemmParams p{};
+    mx::fill_params(p, C, ldc, M_sum, N, K, E, 0, kContig);
+    p.row_expert = row_expert;
+    return mx::launch(A, M_sum, B, E * N, p, sfa_packed, sfb_packed, (int64_t)p.num_m_blocks * p.num_n_blocks, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int kbn_fp8_grouped_gemm_masked_ue8m0(const void* A, const void* sfa_packed, const void* B, const void* sfb_packed,
+                                                 void* C, const int32_t* masked_m, int64_t E, int64_t max_m, int64_t N, int64_t K,
+                                                 kbn_stream_t stream) {
+    using namespace kbn;
+    KBN_REQUIRE(E >= 0 && max_m >= 0 && N >= 0 && K >= 0, KBN_ERR_ARG, "kbn_fp8_grouped_gemm_masked_ue8m0: negative size");
+    if (E == 0 || max_m == 0 || N == 0) return KBN_OK;
+    KBN_REQUIRE(A && B && C && masked_m, KBN_ERR_ARG, "kbn_fp8_grouped_gemm_masked_ue8m0: null pointer");
+    KBN_REQUIRE(max_m % 128 == 0, KBN_ERR_ARG, "kbn_fp8_grouped_gemm_masked_ue8m0: max_m=%lld must be a multiple of 128", (long long)max_m);
+    KBN_REQUIRE(E * N < (1ll << 31) && E * max_m < (1ll << 31), KBN_ERR_ARG, "kbn_fp8_grouped_gemm_masked_ue8m0: too large");
+    GemmParams p{};
+    mx::fill_params(p, C, N, E * max_m, N, K, E, max_m, kMasked);
+    p.masked_m = masked_m;
+    const int64_t max_tiles = E * (int64_t)((max_m + 127) / 128) * p.num_n_blocks;
+    return mx::launch(A, E * max_m, B, E * N, p, sfa_packed, sfb_packed, max_tiles, static_cast<cudaStream_t>(stream));
+}

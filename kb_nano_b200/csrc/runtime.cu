@@ -5,6 +5,10 @@
 #include "common.cuh"
 
 namespace kbn {
+int gemm_status_ptr(int32_t** out);
+}
+
+namespace kbn {
 
 static thread_local char g_err[512] = "";
 std::atomic<int64_t> g_launches{0};
@@ -28,6 +32,13 @@ int sm_count() {
     return cached[dev];
 }
 
+__device__ int32_t g_gemm_status = 0;
+
+int gemm_status_ptr(int32_t** out) {
+    KBN_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(out), g_gemm_status));
+    return KBN_OK;
+}
+
 }  // namespace kbn
 
 extern "C" {
@@ -35,5 +46,13 @@ extern "C" {
 int kbn_version(void) { return 1; }
 const char* kbn_last_error(void) { return kbn::g_err; }
 int64_t kbn_launch_count(void) { return kbn::g_launches.load(); }
+
+int kbn_gemm_status(int32_t* host_out, kbn_stream_t stream) {
+    using namespace kbn;
+    KBN_REQUIRE(host_out, KBN_ERR_ARG, "kbn_gemm_status: null pointer");
+    KBN_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+    KBN_CUDA(cudaMemcpyFromSymbol(host_out, g_gemm_status, sizeof(int32_t)));
+    return KBN_OK;
+}
 
 }  // extern "C"

@@ -128,5 +128,55 @@ __host__ __device__ constexpr uint32_t umma_idesc_e4m3_f32(uint32_t m, uint32_t 
            | ((m >> 4) << 24);  // M / 16
 }
 
+
+// ---- block-scaled MMA (UE8M0 scale factors held in TMEM) ------------------------------------
+// D[tmem] (+)= (A * 2^(sfa-127)) * (B * 2^(sfb-127)); one scale per row and 32 K-elements, read from
+// the byte of the 32-bit TMEM scale column that the instruction descriptor's sf ids select.
+__device__ __forceinline__ void mma_mxf8f6f4_block_scale(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                         uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+        : "memory");
+}
+
+// Shared memory -> TMEM copy of one 32-row x 16-byte block, broadcast to the four 32-lane quarters:
+// lane l of every quarter receives the 16 bytes of row l as four 32-bit columns.
+__device__ __forceinline__ void tmem_cp_32x128b_warpx4(uint32_t dst_tmem, uint64_t src_desc) {
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(dst_tmem), "l"(src_desc) : "memory");
+}
+
+// Descriptor of an unswizzled K-major block whose rows are 16 bytes: 8-row groups are 128 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc_sf(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3ffffu) >> 4);
+    d |= (uint64_t)(128 >> 4) << 32;                  // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                           // descriptor version of sm_100
+    return d;                                          // layout type 0: no swizzle
+}
+
+// Instruction descriptor, kind::mxf8f6f4 block-scaled: A = B = e4m3 K-major, UE8M0 scale factors,
+// fp32 accumulation; sf ids choose the byte (0..3) of the scale columns used by this instruction.
+__host__ __device__ constexpr uint32_t umma_idesc_mx_e4m3(uint32_t m, uint32_t n, uint32_t a_sf_id, uint32_t b_sf_id) {
+    return (b_sf_id << 4)       // scale-factor byte of B
+           | (0u << 7)          // A format: e4m3
+           | (0u << 10)         // B format: e4m3
+           | (0u << 15)         // A K-major
+           | (0u << 16)         // B K-major
+           | ((n >> 3) << 17)   // N / 8
+           | (1u << 23)         // scale format: UE8M0
+           | ((m >> 4) << 24)   // M / 16
+           | (a_sf_id << 29);   // scale-factor byte of A
+}
+
+// Plain (untiled) bulk copy global -> shared, completion on an mbarrier; 16-byte aligned, size % 16 == 0.
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
 }  // namespace ptx
 }  // namespace kbn
