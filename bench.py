@@ -329,9 +329,11 @@ def wl_gemm_c1(args, rank, world, dev, sampler):
     a_s = torch.empty(k // 128, m, device=dev).t()
     out = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
     ops.per_token_group_quant_fp8(x, a_q, a_s)
+    sfb = ops.packed_weight_scales(w_s, n, k)     # weight scales are powers of two: block-scaled tensor-core path
+    sfa = ops.pack_sf_rows(a_s, k)
     flop = 2.0 * m * n * k
     l0 = _lib.launch_count()
-    ms = Timed(world, 256 << 20, dev).run(lambda i: ops.fp8_gemm_nt(a_q, a_s, w_q, w_s, out), args.steps, args.warmup, sampler)
+    ms = Timed(world, 256 << 20, dev).run(lambda i: ops.fp8_gemm_nt_ue8m0(a_q, sfa, w_q, sfb, out), args.steps, args.warmup, sampler)
     launches = _lib.launch_count() - l0
     hx = x.cpu().pin_memory()
     dx = torch.empty_like(x)
@@ -340,7 +342,7 @@ def wl_gemm_c1(args, rank, world, dev, sampler):
     def e2e_step(i):   # the Fp8Linear call: quant + GEMM on a host activation, result back on the host
         dx.copy_(hx, non_blocking=True)
         ops.per_token_group_quant_fp8(dx, a_q, a_s)
-        ops.fp8_gemm_nt(a_q, a_s, w_q, w_s, out)
+        ops.fp8_gemm_nt_auto(a_q, a_s, w_q, w_s, out)
         hout.copy_(out, non_blocking=True)
 
     ms_e2e = Timed(world, 256 << 20, dev).run(e2e_step, args.steps, 2)
@@ -355,7 +357,7 @@ def wl_gemm_c1(args, rank, world, dev, sampler):
                    "l2": "256 MB flush buffer written between steps", "replicas": world},
         "e2e": {"value": flop / (ms_e2e * 1e-3) / 1e12 * world, "unit": "TFLOP/s", "h2d_bytes_per_step": m * k * 2, "d2h_bytes_per_step": m * n * 2},
         "gpu_launches": launches // (args.steps + args.warmup) * args.steps,
-        "roofline": {"bound": "tensor", "kernel": "fp8_gemm_kernel", "achieved": tf, "peak": fp8_peak, "unit": "TFLOP/s", "frac": tf / fp8_peak,
+        "roofline": {"bound": "tensor", "kernel": "fp8_gemm_mx_kernel", "achieved": tf, "peak": fp8_peak, "unit": "TFLOP/s", "frac": tf / fp8_peak,
                      "traffic": None, "peak_source": peaks["source"] + " bf16 burst x2 (no FP8 entry in MEASURED_PEAKS.json)",
                      "frac_of_nominal_4500": tf / 4500.0, "algorithmic_flop_per_launch": flop},
         "_cpu": lambda: cpu_gemm_c1(512, 3),
@@ -393,16 +395,18 @@ def wl_moe_single(args, rank, world, dev, sampler, name):
     launches = _lib.launch_count() - l0
     # dominant kernel: the two grouped GEMM launches, timed alone with events on the same inputs
     evs = []
+    p13, p2 = ops.packed_weight_scales(w13_s, 2 * i, h), ops.packed_weight_scales(w2_s, h, i)
+    sf1 = ops.pack_sf_rows(sc.a_s_perm, h)
     for _ in range(max(3, min(args.steps, 10))):
-        a, b, c = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+        a, b = (torch.cuda.Event(enable_timing=True) for _ in range(2))
         a.record()
-        ops.m_grouped_fp8_gemm_nt_contiguous(sc.a_perm, sc.a_s_perm, w13_q, w13_s, sc.mm1(i), sc.row_expert)
+        ops.m_grouped_fp8_gemm_nt_contiguous_ue8m0(sc.a_perm, sf1, w13_q, p13, sc.mm1(i), sc.row_expert)
         b.record()
-        ops.silu_mul_quant_fp8(sc.mm1(i), sc.a2_q, sc.a2_s)
-        c.record()
+        ops.silu_mul_quant_fp8_rows(sc.mm1(i), sc.a2_q, sc.a2_s, sc.row_expert)
+        sf2 = ops.pack_sf_rows(sc.a2_s, i)
         d, f = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         d.record()
-        ops.m_grouped_fp8_gemm_nt_contiguous(sc.a2_q, sc.a2_s, w2_q, w2_s, sc.mm2(h), sc.row_expert)
+        ops.m_grouped_fp8_gemm_nt_contiguous_ue8m0(sc.a2_q, sf2, w2_q, p2, sc.mm2(h), sc.row_expert)
         f.record()
         evs.append((a, b, d, f))
     torch.cuda.synchronize()
@@ -430,12 +434,12 @@ def wl_moe_single(args, rank, world, dev, sampler, name):
     hbm_bound = (pairs / e) < 562      # rows per expert below the machine balance: weights dominate
     if hbm_bound:
         ach = (g1 + g2) / 2.0 / (gemm_ms * 1e-3) / 1e9
-        roof = {"bound": "hbm", "kernel": "fp8_gemm_kernel (grouped, 2 launches per layer)", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+        roof = {"bound": "hbm", "kernel": "fp8_gemm_mx_kernel (grouped, 2 launches per layer)", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                 "frac": ach / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"], "algorithmic_bytes_per_launch": (g1 + g2) / 2.0,
                 "tflops": flop / 2.0 / (gemm_ms * 1e-3) / 1e12}
     else:
         ach = flop / 2.0 / (gemm_ms * 1e-3) / 1e12
-        roof = {"bound": "tensor", "kernel": "fp8_gemm_kernel (grouped, 2 launches per layer)", "achieved": ach, "peak": 2.0 * peaks["bf16_tflops_sustained"],
+        roof = {"bound": "tensor", "kernel": "fp8_gemm_mx_kernel (grouped, 2 launches per layer)", "achieved": ach, "peak": 2.0 * peaks["bf16_tflops_sustained"],
                 "unit": "TFLOP/s", "frac": ach / (2.0 * peaks["bf16_tflops_sustained"]), "traffic": None,
                 "peak_source": peaks["source"] + " bf16 sustained x2 (no FP8 entry in MEASURED_PEAKS.json)",
                 "frac_of_nominal_4500": ach / 4500.0, "algorithmic_flop_per_launch": flop / 2.0}
@@ -485,19 +489,20 @@ def wl_ep_moe(args, rank, world, dev, sampler):
     # dominant kernel: the two masked grouped GEMM launches, timed alone on buffers of the same shape and row counts
     masked = local.to(torch.int32).to(dev)
     a1 = torch.empty(e_l, max_m, h, dtype=torch.uint8, device=dev).random_(0, 120).view(FP8)
-    s1 = torch.full((e_l, max_m, h // 128), 2.0 ** -7, device=dev)
+    s1 = ops.pack_sf_rows(torch.full((e_l * max_m, h // 128), 2.0 ** -7, device=dev), h)
     o1 = torch.empty(e_l, max_m, 2 * i, dtype=torch.bfloat16, device=dev)
     a2 = torch.empty(e_l, max_m, i, dtype=torch.uint8, device=dev).random_(0, 120).view(FP8)
-    s2 = torch.full((e_l, max_m, i // 128), 2.0 ** -7, device=dev)
+    s2 = ops.pack_sf_rows(torch.full((e_l * max_m, i // 128), 2.0 ** -7, device=dev), i)
+    p13, p2 = ops.packed_weight_scales(w13_s, 2 * i, h), ops.packed_weight_scales(w2_s, h, i)
     o2 = torch.empty(e_l, max_m, h, dtype=torch.bfloat16, device=dev)
     evs = []
     for k_ in range(3 + max(3, min(args.steps, 10))):
         a, b, c, d = (torch.cuda.Event(enable_timing=True) for _ in range(4))
         a.record()
-        ops.m_grouped_fp8_gemm_nt_masked(a1, s1, w13_q, w13_s, o1, masked)
+        ops.m_grouped_fp8_gemm_nt_masked_ue8m0(a1, s1, w13_q, p13, o1, masked)
         b.record()
         c.record()
-        ops.m_grouped_fp8_gemm_nt_masked(a2, s2, w2_q, w2_s, o2, masked)
+        ops.m_grouped_fp8_gemm_nt_masked_ue8m0(a2, s2, w2_q, p2, o2, masked)
         d.record()
         if k_ >= 3:
             evs.append((a, b, c, d))
@@ -537,7 +542,7 @@ def wl_ep_moe(args, rank, world, dev, sampler):
                    "layer_tflops": flop / world / (ms * 1e-3) / 1e12},
         "e2e": {"value": t * world / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": t * h * 2 + t * topk * 8, "d2h_bytes_per_step": t * h * 2},
         "gpu_launches": launches // (args.steps + args.warmup) * args.steps,
-        "roofline": {"bound": "hbm", "kernel": "fp8_gemm_kernel (masked grouped, 2 launches per layer; rank 0)", "achieved": ach, "peak": peaks["hbm_gbs"],
+        "roofline": {"bound": "hbm", "kernel": "fp8_gemm_mx_kernel (masked grouped, 2 launches per layer; rank 0)", "achieved": ach, "peak": peaks["hbm_gbs"],
                      "unit": "GB/s", "frac": ach / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
                      "algorithmic_bytes_per_launch": (g1 + g2) / 2.0, "gemm_ms_per_launch": gemm_ms},
         "_cpu": lambda: cpu_moe(t, h, i, e, topk, "sigmoid", 8, 1),

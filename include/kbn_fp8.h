@@ -190,8 +190,10 @@ int kbn_moe_unpermute_combine(const void* rows, int64_t ld_rows, const int32_t* 
  *   handles by any host channel -> kbn_ep_attach(all handles, rank order).  world == 1 needs no attach.
  * kbn_ep_moe_forward: x bf16 [T,H] local tokens, topk_ids int32 [T,topk] GLOBAL expert ids,
  *   topk_w fp32 [T,topk]; w13 fp8 [E/R,2I,H] + w13_s fp32 [E/R,2I/128,H/128], w2 fp8 [E/R,H,I] +
- *   w2_s [E/R,H/128,I/128] of the LOCAL experts; out bf16 [T,H].  Every rank must call it the same
- *   number of times (also with T == 0).  An expert can take at most max_m rows per call.
+ *   w2_s [E/R,H/128,I/128] of the LOCAL experts; out bf16 [T,H].  When both w13_sf_packed and
+ *   w2_sf_packed (kbn_pack_sf_weights of the same scales) are given and max_m % 128 == 0, the expert
+ *   GEMMs take the UE8M0 fast path and the fp32 scale pointers may be null.  Every rank must call it
+ *   the same number of times (also with T == 0).  An expert can take at most max_m rows per call.
  * kbn_ep_status: 4 int32 {code, phase, peer, detail}; code 0 = ok, 10 = an expert overflowed max_m
  *   rows (detail = expert), 11 = expert id out of range, 20 = a wait on peer `peer` ran out in
  *   phase 1 (dispatch) or 2 (combine).  Synchronises `stream`.
@@ -204,7 +206,8 @@ int kbn_ep_attach(kbn_ep_ctx* ctx, const void* handles);
 int64_t kbn_ep_symmetric_bytes(kbn_ep_ctx* ctx);
 int kbn_ep_moe_forward(kbn_ep_ctx* ctx, const void* x_bf16, const int32_t* topk_ids,
                        const float* topk_w, int64_t T, const void* w13, const float* w13_s,
-                       const void* w2, const float* w2_s, void* out_bf16, kbn_stream_t stream);
+                       const void* w2, const float* w2_s, const void* w13_sf_packed,
+                       const void* w2_sf_packed, void* out_bf16, kbn_stream_t stream);
 int kbn_ep_status(kbn_ep_ctx* ctx, int32_t* host_out4, kbn_stream_t stream);
 int kbn_ep_destroy(kbn_ep_ctx* ctx);
 

@@ -24,6 +24,11 @@
 extern "C" int kbn_fp8_grouped_gemm_masked(const void*, const float*, int64_t, int64_t, int64_t, const void*, const float*,
                                            void*, const int32_t*, int64_t, int64_t, int64_t, int64_t, kbn_stream_t);
 
+extern "C" int kbn_fp8_grouped_gemm_masked_ue8m0(const void*, const void*, const void*, const void*, void*, const int32_t*, int64_t, int64_t,
+                                                 int64_t, int64_t, kbn_stream_t);
+extern "C" int kbn_pack_sf_rows(const float*, int64_t, int64_t, int64_t, int64_t, void*, kbn_stream_t);
+extern "C" int64_t kbn_packed_sf_rows_bytes(int64_t, int64_t);
+
 namespace kbn {
 int silu_mul_quant_masked(const void* in, int64_t E, int64_t max_m, int64_t N2, void* q, float* scale,
                           const int32_t* masked_m, cudaStream_t st);   // silu_mul_quant.cu
@@ -51,6 +56,7 @@ struct kbn_ep_ctx {
     // local scratch
     uint8_t* a_q; float* a_s;          // quantised local tokens
     __nv_bfloat16* mm1; uint8_t* a2_q; float* a2_s; __nv_bfloat16* mm2;
+    uint8_t* sf1; uint8_t* sf2;        // packed UE8M0 scales of the received rows / of the activation (UE8M0 GEMM path)
     int32_t* identity;                 // [max_tokens*topk] 0,1,2,...
     int32_t* done;                     // [2] block-completion counters
     int32_t* status;                   // [4] code, phase, peer, detail
@@ -215,6 +221,8 @@ extern "C" int kbn_ep_create(int rank, int world, int64_t experts_total, int64_t
     KBN_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->a2_q), (size_t)(rows * inter)));
     KBN_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->a2_s), (size_t)(rows * (inter / 128) * 4)));
     KBN_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->mm2), (size_t)(rows * hidden * 2)));
+    KBN_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->sf1), (size_t)kbn_packed_sf_rows_bytes(rows, hidden)));
+    KBN_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->sf2), (size_t)kbn_packed_sf_rows_bytes(rows, inter)));
     KBN_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->identity), (size_t)(max_tokens * topk * 4)));
     KBN_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->done), 16));
     KBN_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->status), 16));
@@ -259,13 +267,15 @@ extern "C" int kbn_ep_attach(kbn_ep_ctx* c, const void* handles) {
 extern "C" int64_t kbn_ep_symmetric_bytes(kbn_ep_ctx* c) { return c ? c->lay.total : 0; }
 
 extern "C" int kbn_ep_moe_forward(kbn_ep_ctx* c, const void* x_bf16, const int32_t* topk_ids, const float* topk_w, int64_t T,
-                                  const void* w13, const float* w13_s, const void* w2, const float* w2_s, void* out_bf16,
-                                  kbn_stream_t stream) {
+                                  const void* w13, const float* w13_s, const void* w2, const float* w2_s,
+                                  const void* w13_sf_packed, const void* w2_sf_packed, void* out_bf16, kbn_stream_t stream) {
     using namespace kbn;
     KBN_REQUIRE(c, KBN_ERR_ARG, "kbn_ep_moe_forward: null context");
     KBN_REQUIRE(c->attached, KBN_ERR_ARG, "kbn_ep_moe_forward: peers not attached (call kbn_ep_attach)");
     KBN_REQUIRE(T >= 0 && T <= c->max_tokens, KBN_ERR_ARG, "kbn_ep_moe_forward: T=%lld exceeds max_tokens=%lld", (long long)T, (long long)c->max_tokens);
-    KBN_REQUIRE(w13 && w13_s && w2 && w2_s, KBN_ERR_ARG, "kbn_ep_moe_forward: null weight pointer");
+    const bool ue8m0 = w13_sf_packed && w2_sf_packed;
+    KBN_REQUIRE(w13 && w2 && (ue8m0 || (w13_s && w2_s)), KBN_ERR_ARG, "kbn_ep_moe_forward: null weight pointer");
+    KBN_REQUIRE(!ue8m0 || c->max_m % 128 == 0, KBN_ERR_ARG, "kbn_ep_moe_forward: the UE8M0 path needs max_m to be a multiple of 128");
     if (T > 0) KBN_REQUIRE(x_bf16 && topk_ids && topk_w && out_bf16, KBN_ERR_ARG, "kbn_ep_moe_forward: null pointer");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int32_t epoch = ++c->epoch;
@@ -288,12 +298,25 @@ extern "C" int kbn_ep_moe_forward(kbn_ep_ctx* c, const void* x_bf16, const int32
     ep_wait_kernel<<<1, kMaxRanks, 0, st>>>(reinterpret_cast<const int32_t*>(mine + c->lay.flags_dispatch), c->world, epoch, 1, c->status);
     KBN_CHECK_LAUNCH();
     // 4. local experts on the received rows
-    rc = kbn_fp8_grouped_gemm_masked(mine + c->lay.recv_q, reinterpret_cast<const float*>(mine + c->lay.recv_s), c->max_m * G, G, 1, w13, w13_s,
-                                     c->mm1, counters, c->e_local, c->max_m, 2 * I, H, stream);
+    const float* recv_s = reinterpret_cast<const float*>(mine + c->lay.recv_s);
+    const int64_t rows_all = c->e_local * c->max_m;
+    if (ue8m0) {
+        rc = kbn_pack_sf_rows(recv_s, rows_all, H, G, 1, c->sf1, stream);
+        if (rc != KBN_OK) return rc;
+        rc = kbn_fp8_grouped_gemm_masked_ue8m0(mine + c->lay.recv_q, c->sf1, w13, w13_sf_packed, c->mm1, counters, c->e_local, c->max_m, 2 * I, H, stream);
+    } else {
+        rc = kbn_fp8_grouped_gemm_masked(mine + c->lay.recv_q, recv_s, c->max_m * G, G, 1, w13, w13_s, c->mm1, counters, c->e_local, c->max_m, 2 * I, H, stream);
+    }
     if (rc != KBN_OK) return rc;
     rc = silu_mul_quant_masked(c->mm1, c->e_local, c->max_m, I, c->a2_q, c->a2_s, counters, st);
     if (rc != KBN_OK) return rc;
-    rc = kbn_fp8_grouped_gemm_masked(c->a2_q, c->a2_s, c->max_m * (I / 128), I / 128, 1, w2, w2_s, c->mm2, counters, c->e_local, c->max_m, H, I, stream);
+    if (ue8m0) {
+        rc = kbn_pack_sf_rows(c->a2_s, rows_all, I, I / 128, 1, c->sf2, stream);
+        if (rc != KBN_OK) return rc;
+        rc = kbn_fp8_grouped_gemm_masked_ue8m0(c->a2_q, c->sf2, w2, w2_sf_packed, c->mm2, counters, c->e_local, c->max_m, H, I, stream);
+    } else {
+        rc = kbn_fp8_grouped_gemm_masked(c->a2_q, c->a2_s, c->max_m * (I / 128), I / 128, 1, w2, w2_s, c->mm2, counters, c->e_local, c->max_m, H, I, stream);
+    }
     if (rc != KBN_OK) return rc;
     // 5. results back to their sources + signal
     const int64_t rows = c->e_local * c->max_m;
@@ -324,7 +347,7 @@ extern "C" int kbn_ep_destroy(kbn_ep_ctx* c) {
     for (int r = 0; r < c->world; ++r)
         if (r != c->rank && c->peers.base[r]) cudaIpcCloseMemHandle(c->peers.base[r]);
     cudaFree(c->sym); cudaFree(c->a_q); cudaFree(c->a_s); cudaFree(c->mm1); cudaFree(c->a2_q); cudaFree(c->a2_s);
-    cudaFree(c->mm2); cudaFree(c->identity); cudaFree(c->done); cudaFree(c->status);
+    cudaFree(c->mm2); cudaFree(c->sf1); cudaFree(c->sf2); cudaFree(c->identity); cudaFree(c->done); cudaFree(c->status);
     delete c;
     return KBN_OK;
 }

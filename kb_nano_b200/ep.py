@@ -17,6 +17,7 @@ import ctypes
 import torch
 
 from . import _lib
+from . import ops as _ops
 from .ops import _on, _stream
 
 FP8 = torch.float8_e4m3fn
@@ -45,7 +46,8 @@ class EpStatusError(RuntimeError):
 
 class EpMoe:
     def __init__(self, rank: int, world: int, experts_total: int, hidden: int, inter: int, max_tokens: int, topk: int,
-                 max_m: int = 256, group=None, device: torch.device | None = None):
+                 max_m: int = 256, group=None, device: torch.device | None = None, use_ue8m0: bool = True):
+        self.use_ue8m0 = use_ue8m0
         self.rank, self.world = rank, world
         self.experts_total, self.hidden, self.inter = experts_total, hidden, inter
         self.max_tokens, self.topk, self.max_m = max_tokens, topk, max_m
@@ -93,9 +95,17 @@ class EpMoe:
             raise ValueError("topk_ids / topk_w must be [T, topk]")
         if out is None:
             out = torch.empty(t, self.hidden, dtype=torch.bfloat16, device=x.device)
+        # power-of-two weight scales (checked and packed once per tensor) take the UE8M0 GEMM path
+        p13 = p2 = None
+        if self.use_ue8m0 and self.max_m % 128 == 0:
+            p13 = _ops.packed_weight_scales(w13_s, 2 * self.inter, self.hidden)
+            p2 = _ops.packed_weight_scales(w2_s, self.hidden, self.inter)
+        fast = p13 is not None and p2 is not None
         with _on(self.device):
             _lib.check(self._lib.kbn_ep_moe_forward(self._ctx, x.data_ptr(), ids.data_ptr(), w.data_ptr(), t, w13.data_ptr(),
-                                                    w13_s.data_ptr(), w2.data_ptr(), w2_s.data_ptr(), out.data_ptr(), _stream(x)))
+                                                    w13_s.data_ptr(), w2.data_ptr(), w2_s.data_ptr(),
+                                                    p13.data_ptr() if fast else None, p2.data_ptr() if fast else None,
+                                                    out.data_ptr(), _stream(x)))
         return out
 
     def status(self) -> dict:
@@ -111,7 +121,7 @@ class EpMoe:
         if s["code"] != 0:
             raise EpStatusError(f"expert-parallel layer on rank {self.rank}: {s}")
 
-    LAUNCHES_PER_FORWARD = 9   # quant, dispatch, wait, GEMM1, act-quant, GEMM2, send, wait, sum
+    LAUNCHES_PER_FORWARD = 11  # quant, dispatch, wait, pack, GEMM1, act-quant, pack, GEMM2, send, wait, sum
 
     def close(self) -> None:
         if self._ctx:

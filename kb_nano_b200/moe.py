@@ -54,7 +54,8 @@ def get_scratch(t: int, topk: int, e: int, h: int, i: int, device: torch.device)
 
 def fused_experts_fp8(hidden_states: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, topk_weights: torch.Tensor,
                       topk_ids: torch.Tensor, num_experts: int, w13_scale: torch.Tensor, w2_scale: torch.Tensor,
-                      scratch: MoeScratch | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+                      scratch: MoeScratch | None = None, out: torch.Tensor | None = None,
+                      use_ue8m0: bool = True) -> torch.Tensor:
     """hidden bf16 [T,H]; w13 fp8 [E,2I,H] + fp32 scales [E,2I/128,H/128]; w2 fp8 [E,H,I] + scales
     [E,H/128,I/128]; topk_weights [T,topk] (fp32 or bf16), topk_ids [T,topk] int -> bf16 [T,H]."""
     t, h = hidden_states.shape
@@ -74,11 +75,18 @@ def fused_experts_fp8(hidden_states: torch.Tensor, w13: torch.Tensor, w2: torch.
         out = torch.empty(t, h, dtype=torch.bfloat16, device=dev)
     ops.per_token_group_quant_fp8(x, sc.a_q, sc.a_s)
     ops.moe_permute(sc.a_q, sc.a_s, ids, num_experts, sc.a_perm, sc.a_s_perm, sc.row_expert, sc.dest_row, sc.workspace)
-    mm1 = sc.mm1(i)
-    ops.m_grouped_fp8_gemm_nt_contiguous(sc.a_perm, sc.a_s_perm, w13, w13_scale, mm1, sc.row_expert)
-    ops.silu_mul_quant_fp8_rows(mm1, sc.a2_q, sc.a2_s, sc.row_expert)
-    mm2 = sc.mm2(h)
-    ops.m_grouped_fp8_gemm_nt_contiguous(sc.a2_q, sc.a2_s, w2, w2_scale, mm2, sc.row_expert)
+    mm1, mm2 = sc.mm1(i), sc.mm2(h)
+    # power-of-two weight scales (checked and packed once per tensor) take the UE8M0 block-scaled GEMM
+    p13 = ops.packed_weight_scales(w13_scale, n2, h) if use_ue8m0 else None
+    p2 = ops.packed_weight_scales(w2_scale, h, i) if use_ue8m0 else None
+    if p13 is not None and p2 is not None:
+        ops.m_grouped_fp8_gemm_nt_contiguous_ue8m0(sc.a_perm, ops.pack_sf_rows(sc.a_s_perm, h), w13, p13, mm1, sc.row_expert)
+        ops.silu_mul_quant_fp8_rows(mm1, sc.a2_q, sc.a2_s, sc.row_expert)
+        ops.m_grouped_fp8_gemm_nt_contiguous_ue8m0(sc.a2_q, ops.pack_sf_rows(sc.a2_s, i), w2, p2, mm2, sc.row_expert)
+    else:
+        ops.m_grouped_fp8_gemm_nt_contiguous(sc.a_perm, sc.a_s_perm, w13, w13_scale, mm1, sc.row_expert)
+        ops.silu_mul_quant_fp8_rows(mm1, sc.a2_q, sc.a2_s, sc.row_expert)
+        ops.m_grouped_fp8_gemm_nt_contiguous(sc.a2_q, sc.a2_s, w2, w2_scale, mm2, sc.row_expert)
     ops.moe_unpermute_combine(mm2, sc.dest_row, w, out)
     return out
 

@@ -269,3 +269,100 @@ def moe_unpermute_combine(rows: torch.Tensor, dest_row: torch.Tensor, topk_w: to
     with _on(dev):
         _lib.check(_lib.load().kbn_moe_unpermute_combine(rows.data_ptr(), rows.stride(0), dest_row.data_ptr(),
                                                          topk_w.data_ptr(), t, topk, h, out.data_ptr(), _stream(out)))
+
+
+# ---- UE8M0 fast path: packed power-of-two scales, block-scaled tensor-core instruction -------------
+
+def pack_sf_rows(scale: torch.Tensor, k: int) -> torch.Tensor:
+    """fp32 scales [..., rows, ceil(K/128)] (any strides on the last two dims; leading dims contiguous over
+    rows) -> packed uint8 buffer for the *_ue8m0 GEMMs."""
+    s2 = scale if scale.dim() == 2 else scale.reshape(-1, scale.shape[-1])
+    rows = s2.shape[0]
+    if s2.dtype != torch.float32 or s2.shape[1] != (k + 127) // 128:
+        raise ValueError("scale must be float32 [rows, ceil(K/128)]")
+    lib = _lib.load()
+    out = torch.empty(int(lib.kbn_packed_sf_rows_bytes(rows, k)), dtype=torch.uint8, device=scale.device)
+    with _on(scale.device):
+        _lib.check(lib.kbn_pack_sf_rows(s2.data_ptr(), rows, k, s2.stride(0), s2.stride(1), out.data_ptr(), _stream(scale)))
+    return out
+
+
+_WEIGHT_SF_CACHE: dict = {}
+
+
+def packed_weight_scales(b_s: torch.Tensor, n: int, k: int):
+    """(packed buffer or None) for fp32 weight scales [E?, N/128, K/128].  None when some scale is not a
+    power of two, in which case the fp32-scale kernel must be used.  Checked and packed once per tensor
+    (keyed by storage address, shape and version); the check synchronises the stream that one time."""
+    key = (b_s.data_ptr(), tuple(b_s.shape), b_s._version, str(b_s.device))
+    hit = _WEIGHT_SF_CACHE.get(key)
+    if hit is not None:
+        return hit[0]
+    s = b_s if b_s.is_contiguous() else b_s.contiguous()
+    e = s.shape[0] if s.dim() == 3 else 1
+    lib = _lib.load()
+    with _on(s.device):
+        cnt = torch.zeros(1, dtype=torch.int32, device=s.device)
+        _lib.check(lib.kbn_count_non_pow2_scales(s.data_ptr(), s.numel(), cnt.data_ptr(), _stream(s)))
+        packed = None
+        if int(cnt.item()) == 0:
+            packed = torch.empty(int(lib.kbn_packed_sf_weights_bytes(e, n, k)), dtype=torch.uint8, device=s.device)
+            _lib.check(lib.kbn_pack_sf_weights(s.data_ptr(), e, n, k, packed.data_ptr(), _stream(s)))
+    if len(_WEIGHT_SF_CACHE) >= 64:
+        _WEIGHT_SF_CACHE.pop(next(iter(_WEIGHT_SF_CACHE)))
+    _WEIGHT_SF_CACHE[key] = (packed, b_s)      # keep the tensor alive so the address cannot be reused
+    return packed
+
+
+def fp8_gemm_nt_ue8m0(a_q, sfa_packed, b_q, sfb_packed, out) -> None:
+    dev = _cuda(a_q, sfa_packed, b_q, sfb_packed, out)
+    m, k = a_q.shape
+    n = b_q.shape[0]
+    _check_ab(a_q, b_q, k)
+    if out.dtype != torch.bfloat16 or tuple(out.shape) != (m, n) or out.stride(1) != 1:
+        raise ValueError("out must be bf16 [M,N], contiguous along N")
+    with _on(dev):
+        _lib.check(_lib.load().kbn_fp8_gemm_nt_ue8m0(a_q.data_ptr(), sfa_packed.data_ptr(), b_q.data_ptr(), sfb_packed.data_ptr(),
+                                                     out.data_ptr(), out.stride(0) if m > 1 else n, m, n, k, _stream(out)))
+
+
+def m_grouped_fp8_gemm_nt_contiguous_ue8m0(a_q, sfa_packed, b_q, sfb_packed, out, expert_ids) -> None:
+    dev = _cuda(a_q, sfa_packed, b_q, sfb_packed, out, expert_ids)
+    m, k = a_q.shape
+    e, n, _ = b_q.shape
+    _check_ab(a_q, b_q, k)
+    if out.dtype != torch.bfloat16 or tuple(out.shape) != (m, n) or out.stride(1) != 1:
+        raise ValueError("out must be bf16 [M_sum,N], contiguous along N")
+    if expert_ids.dtype != torch.int32 or expert_ids.numel() != m or not expert_ids.is_contiguous():
+        raise ValueError("expert_ids must be contiguous int32 [M_sum]")
+    with _on(dev):
+        _lib.check(_lib.load().kbn_fp8_grouped_gemm_contig_ue8m0(a_q.data_ptr(), sfa_packed.data_ptr(), b_q.data_ptr(),
+                                                                 sfb_packed.data_ptr(), out.data_ptr(), out.stride(0) if m > 1 else n,
+                                                                 expert_ids.data_ptr(), m, n, k, e, _stream(out)))
+
+
+def m_grouped_fp8_gemm_nt_masked_ue8m0(a_q, sfa_packed, b_q, sfb_packed, out, masked_m) -> None:
+    dev = _cuda(a_q, sfa_packed, b_q, sfb_packed, out, masked_m)
+    e, max_m, k = a_q.shape
+    n = b_q.shape[1]
+    _check_ab(a_q, b_q, k)
+    if out.dtype != torch.bfloat16 or tuple(out.shape) != (e, max_m, n) or not out.is_contiguous():
+        raise ValueError("out must be contiguous bf16 [E,max_m,N]")
+    if masked_m.dtype != torch.int32 or masked_m.numel() != e or not masked_m.is_contiguous():
+        raise ValueError("masked_m must be contiguous int32 [E]")
+    with _on(dev):
+        _lib.check(_lib.load().kbn_fp8_grouped_gemm_masked_ue8m0(a_q.data_ptr(), sfa_packed.data_ptr(), b_q.data_ptr(),
+                                                                 sfb_packed.data_ptr(), out.data_ptr(), masked_m.data_ptr(),
+                                                                 e, max_m, n, k, _stream(out)))
+
+
+def fp8_gemm_nt_auto(a_q: torch.Tensor, a_s: torch.Tensor, b_q: torch.Tensor, b_s: torch.Tensor, out: torch.Tensor) -> None:
+    """Dense block-scaled GEMM for activations quantised with power-of-two (UE8M0) scales, which is what
+    per_token_group_quant_fp8 produces by default: takes the block-scaled tensor-core path when the weight
+    scales are powers of two as well (checked once per weight tensor), the fp32-scale kernel otherwise."""
+    n, k = b_q.shape
+    packed = packed_weight_scales(b_s, n, k)
+    if packed is not None:
+        fp8_gemm_nt_ue8m0(a_q, pack_sf_rows(a_s, k), b_q, packed, out)
+    else:
+        fp8_gemm_nt(a_q, a_s, b_q, b_s, out)

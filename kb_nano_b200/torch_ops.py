@@ -27,7 +27,7 @@ def silu_mul_quant_fp8(input: torch.Tensor, output_fp8: torch.Tensor, output_sca
 @torch.library.custom_op("kbn_b200::fp8_gemm_nt", mutates_args=("output",))
 def fp8_gemm_nt(a_fp8: torch.Tensor, a_scale: torch.Tensor, b_fp8: torch.Tensor, b_scale: torch.Tensor,
                 output: torch.Tensor) -> None:
-    ops.fp8_gemm_nt(a_fp8, a_scale, b_fp8, b_scale, output)
+    ops.fp8_gemm_nt_auto(a_fp8, a_scale, b_fp8, b_scale, output)
 
 
 @torch.library.custom_op("kbn_b200::m_grouped_gemm_nt_contiguous", mutates_args=("c_bf16",))

@@ -27,9 +27,15 @@ def test_ep_world1_matches_oracle(cuda_dev):
     t, h, i, e, topk = 96, 512, 256, 16, 4
     xs, routes, (w13_q, w13_s, w2_q, w2_s) = ep_case(1, t, h, i, e, topk, seed=3)
     d = cuda_dev
-    layer = ep.EpMoe(0, 1, e, h, i, max_tokens=128, topk=topk, max_m=64, device=d)
     wd = [w.to(d) for w in (w13_q, w13_s, w2_q, w2_s)]
     ref = to.moe_layer(xs[0], w13_q, w13_s, w2_q, w2_s, routes[0][0], routes[0][1])
+    # max_m = 64 is not a multiple of 128: the expert GEMMs use the fp32-scale kernels
+    slow = ep.EpMoe(0, 1, e, h, i, max_tokens=128, topk=topk, max_m=64, device=d)
+    out = slow.forward(xs[0].to(d), routes[0][1].to(d), routes[0][0].to(d), *wd)
+    slow.check()
+    assert_gemm_close(out.cpu(), ref, "EP world=1, fp32-scale GEMMs")
+    slow.close()
+    layer = ep.EpMoe(0, 1, e, h, i, max_tokens=128, topk=topk, max_m=128, device=d)
     for it in range(3):        # repeated calls reuse buffers, counters and flags
         out = layer.forward(xs[0].to(d), routes[0][1].to(d), routes[0][0].to(d), *[wd[j] for j in (0, 1, 2, 3)])
         layer.check()

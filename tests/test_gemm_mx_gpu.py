@@ -1,0 +1,115 @@
+"""GPU parity of the UE8M0 block-scaled GEMM path (scales packed and applied by the tensor core) against
+the same oracle and tolerance as the fp32-scale kernels, and against the fp32-scale kernels themselves."""
+import pytest
+import torch
+
+from oracle import torch_oracle as to
+from tests.util import assert_gemm_close, bf16_from_bits, fp8_from_bits, golden
+from tests.test_gemm_gpu import make_dense, make_grouped
+
+pytestmark = pytest.mark.gpu
+FP8 = torch.float8_e4m3fn
+
+
+def run_dense_mx(a_q, a_s, w_q, w_s, dev):
+    from kb_nano_b200 import ops
+    m, k = a_q.shape
+    n = w_q.shape[0]
+    sfb = ops.packed_weight_scales(w_s.to(dev), n, k)
+    assert sfb is not None
+    sfa = ops.pack_sf_rows(a_s.to(dev), k)
+    out = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=dev)
+    ops.fp8_gemm_nt_ue8m0(a_q.to(dev), sfa, w_q.to(dev), sfb, out)
+    assert ops.gemm_status(dev) == 0
+    return out.cpu()
+
+
+def test_mx_dense_golden(cuda_dev):
+    g = golden("fp8_linear")
+    out = run_dense_mx(fp8_from_bits(g["a_q"]), torch.from_numpy(g["a_s"]), fp8_from_bits(g["w_q"]), torch.from_numpy(g["w_s"]), cuda_dev)
+    assert_gemm_close(out, bf16_from_bits(g["c"]), "golden fp8_linear (ue8m0 path)")
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 128), (128, 256, 512), (1, 256, 512), (127, 384, 1024), (129, 128, 256), (300, 640, 7168), (64, 2304, 4096), (70, 200, 400)])
+def test_mx_dense_shapes(cuda_dev, m, n, k):
+    a_q, a_s, w_q, w_s = make_dense(m, n, k, seed=m + n + k, dev=cuda_dev)
+    ref = to.gemm_nt_dequant(a_q, a_s, w_q, w_s)
+    assert_gemm_close(run_dense_mx(a_q, a_s, w_q, w_s, cuda_dev), ref, f"dense ue8m0 {m}x{n}x{k}")
+
+
+def test_mx_scales_with_wide_exponent_range(cuda_dev):
+    """Each K-block and each row with a different power-of-two scale: catches any mix-up of the packed order."""
+    m, n, k = 256, 512, 1024
+    a_q, a_s, w_q, w_s = make_dense(m, n, k, seed=77, dev=cuda_dev)
+    gen = torch.Generator().manual_seed(5)
+    a_s = torch.pow(2.0, torch.randint(-12, 4, a_s.shape, generator=gen).float())
+    w_s = torch.pow(2.0, torch.randint(-9, 3, w_s.shape, generator=gen).float())
+    ref = to.gemm_nt_dequant(a_q, a_s, w_q, w_s)
+    got = run_dense_mx(a_q, a_s, w_q, w_s, cuda_dev)
+    g, r = got.float(), ref.float()
+    # values span many octaves: compare relative to each row's own magnitude
+    scale = r.abs().amax(dim=1, keepdim=True).clamp_min(1e-30)
+    assert float(((g - r).abs() / scale).max()) < 1e-2
+    assert float(torch.nn.functional.cosine_similarity(g.flatten().double(), r.flatten().double(), dim=0)) > 0.9999
+
+
+def test_non_pow2_weight_scales_are_detected(cuda_dev):
+    from kb_nano_b200 import ops
+    w_s = torch.tensor([[0.5, 0.25], [0.75, 1.0]], device=cuda_dev)
+    assert ops.packed_weight_scales(w_s, 256, 256) is None
+    assert ops.packed_weight_scales(torch.tensor([[0.5, 0.25], [2.0, 1.0]], device=cuda_dev), 256, 256) is not None
+
+
+@pytest.mark.parametrize("counts", [[128, 256], [1, 0, 127, 129], [300, 5, 0, 0, 77, 128, 1, 640]])
+def test_mx_grouped_contiguous(cuda_dev, counts):
+    from kb_nano_b200 import ops
+    e, n, k = len(counts), 512, 1024
+    a_q, a_s, b_q, b_s, row_expert = make_grouped(e, n, k, counts, seed=sum(counts))
+    ref = to.grouped_gemm_contig(a_q, a_s, b_q, b_s, row_expert)
+    d = cuda_dev
+    out = torch.full((a_q.shape[0], n), 7.0, dtype=torch.bfloat16, device=d)
+    ops.m_grouped_fp8_gemm_nt_contiguous_ue8m0(a_q.to(d), ops.pack_sf_rows(a_s.to(d), k), b_q.to(d), ops.packed_weight_scales(b_s.to(d), n, k),
+                                               out, row_expert.to(d))
+    assert ops.gemm_status(d) == 0
+    out = out.cpu()
+    valid = row_expert >= 0
+    assert_gemm_close(out[valid], ref[valid], f"contiguous ue8m0 {counts}")
+    assert bool((out[~valid] == 7.0).all())
+
+
+@pytest.mark.parametrize("masked", [[0, 1, 128, 129, 256, 77], [256] * 4, [0] * 3, [5, 200]])
+def test_mx_grouped_masked(cuda_dev, masked):
+    from kb_nano_b200 import inputs, ops
+    e, max_m, n, k = len(masked), 256, 384, 512
+    b_q, b_s = inputs.expert_weights(e, n, k, seed=len(masked))
+    a_q, a_s = to.quant_1x128(inputs.activations(e * max_m, k, seed=17))
+    a_q, a_s = a_q.view(e, max_m, k), a_s.view(e, max_m, k // 128)
+    mm = torch.tensor(masked, dtype=torch.int32)
+    ref = to.grouped_gemm_masked(a_q, a_s, b_q, b_s, mm)
+    d = cuda_dev
+    out = torch.full((e, max_m, n), 7.0, dtype=torch.bfloat16, device=d)
+    ops.m_grouped_fp8_gemm_nt_masked_ue8m0(a_q.to(d), ops.pack_sf_rows(a_s.to(d), k), b_q.to(d), ops.packed_weight_scales(b_s.to(d), n, k), out, mm.to(d))
+    assert ops.gemm_status(d) == 0
+    out = out.cpu()
+    for i, c in enumerate(masked):
+        if c:
+            assert_gemm_close(out[i, :c], ref[i, :c], f"masked ue8m0 expert {i}")
+        assert bool((out[i, c:] == 7.0).all())
+
+
+def test_mx_matches_fp32_scale_kernel_on_config1(cuda_dev):
+    from kb_nano_b200 import inputs, ops
+    d = cuda_dev
+    x = inputs.activations(512, 7168, seed=0, device=d)
+    w_q, w_s = inputs.weight(4096, 7168, seed=1, device=d)
+    a_q = torch.empty(512, 7168, dtype=FP8, device=d)
+    a_s = torch.empty(56, 512, device=d).t()
+    ops.per_token_group_quant_fp8(x, a_q, a_s)
+    o1 = torch.empty(512, 4096, dtype=torch.bfloat16, device=d)
+    o2 = torch.empty_like(o1)
+    ops.fp8_gemm_nt(a_q, a_s, w_q, w_s, o1)
+    ops.fp8_gemm_nt_ue8m0(a_q, ops.pack_sf_rows(a_s, 7168), w_q, ops.packed_weight_scales(w_s, 4096, 7168), o2)
+    assert ops.gemm_status(d) == 0
+    assert_gemm_close(o2.cpu(), o1.cpu(), "ue8m0 path vs fp32-scale path")
+    ref = to.gemm_nt_dequant(a_q.cpu(), a_s.cpu(), w_q.cpu(), w_s.cpu())
+    assert_gemm_close(o2.cpu(), ref, "ue8m0 path vs oracle, C1")

@@ -97,8 +97,9 @@ def test_moe_layer_vs_oracle(cuda_dev, t, h, i, e, topk, routing):
     x, w13_q, w13_s, w2_q, w2_s, tw, ti = moe_case(t, h, i, e, topk, seed=t + e, routing=routing)
     ref = to.moe_layer(x, w13_q, w13_s, w2_q, w2_s, tw, ti)
     d = cuda_dev
-    out = moe.fused_experts_fp8(x.to(d), w13_q.to(d), w2_q.to(d), tw.to(d), ti.to(d), e, w13_s.to(d), w2_s.to(d))
-    assert_gemm_close(out.cpu(), ref, f"moe layer t={t} e={e}")
+    for fast in (True, False):      # UE8M0 block-scaled GEMMs, then the fp32-scale kernels
+        out = moe.fused_experts_fp8(x.to(d), w13_q.to(d), w2_q.to(d), tw.to(d), ti.to(d), e, w13_s.to(d), w2_s.to(d), use_ue8m0=fast)
+        assert_gemm_close(out.cpu(), ref, f"moe layer t={t} e={e} ue8m0={fast}")
     # bf16 router weights (as MixtralMoE casts them) and int64 ids go through the same path
     out2 = moe.fused_experts_fp8(x.to(d), w13_q.to(d), w2_q.to(d), tw.to(torch.bfloat16).to(d), ti.long().to(d), e, w13_s.to(d), w2_s.to(d))
     ref2 = to.moe_layer(x, w13_q, w13_s, w2_q, w2_s, tw.to(torch.bfloat16), ti)
