@@ -461,7 +461,7 @@ def wl_ep_moe(args, rank, world, dev, sampler):
     """BASELINE configs[3]: DeepSeek-V3-shaped MoE layer, experts split over the ranks, 128 tokens per rank,
     masked layout with at most 256 rows per expert, dispatch/combine by peer stores over NVLink."""
     from kb_nano_b200 import _lib, ep, inputs, ops
-    t, h, i, e, topk, max_m = 128, 7168, 2048, 256, 8, 256
+    t, h, i, e, topk, max_m = 128, 7168, 2048, args.experts, 8, 256
     lo, hi = ep.expert_range(rank, world, e)
     e_l = hi - lo
     x = inputs.activations(t, h, seed=rank, device=dev)
@@ -535,7 +535,8 @@ def wl_ep_moe(args, rank, world, dev, sampler):
         "metric": "EP FP8 MoE layer throughput", "value": t * world / (ms * 1e-3), "unit": "tokens/s", "ms_per_step": ms,
         "dtype": "e4m3 x e4m3 -> fp32 -> bf16", "scaling": "weak",
         "config": {"workload": "ep_moe: BASELINE configs[3], DeepSeek-V3-shaped FP8 MoE layer (hidden 7168, intermediate 2048, 256 experts, "
-                               "top-8 sigmoid routing), expert-parallel, 128 tokens per rank, masked layout, <=256 rows per expert",
+                               "top-8 sigmoid routing), expert-parallel, 128 tokens per rank, masked layout, <=256 rows per expert"
+                               + ("" if e == 256 else f" [REDUCED to {e} experts: profiling case, not the benchmark configuration]"),
                    "parallelism": f"ep{world}", "experts_per_rank": e_l, "global_tokens": t * world,
                    "l2": f"local expert weights ({e_l * 3 * i * h / 1e9:.2f} GB) exceed the 126 MB L2",
                    "exchange": "peer stores over NVLink (dispatch fp8 rows + scales, combine bf16 rows), release/acquire flags",
@@ -602,6 +603,9 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--experts", type=int, default=256,
+                    help="ep_moe only: total experts (256 = the benchmark configuration; 32 on one GPU reproduces the "
+                         "per-rank load of the 8-GPU run with 1.4 GB of weights, small enough for a profiler capture)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank, local, world = dist_info()
