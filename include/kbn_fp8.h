@@ -172,6 +172,15 @@ int kbn_moe_permute(const void* a_q, const float* a_s, const int32_t* topk_ids, 
                     int64_t topk, int64_t K, int64_t E, void* a_perm, float* a_s_perm,
                     int32_t* row_expert, int32_t* dest_row, int64_t M_cap, void* workspace,
                     int64_t workspace_bytes, kbn_stream_t stream);
+/* kbn_moe_permute for callers that cannot allocate device memory (a plug-in that only receives its
+ * input and output tensors, a host that has frozen its memory map): identical outputs, the scratch is
+ * a ~264 KB device array built into the library.  No counterpart in kb-nano.  Limits: T*topk <= 65536
+ * and E <= 1024 (KBN_ERR_UNSUPPORTED beyond).  Allocates nothing; the first call on a device resolves
+ * the array's address and should come before any stream capture; calls that overlap on one GPU race
+ * on the shared scratch. */
+int kbn_moe_permute_static(const void* a_q, const float* a_s, const int32_t* topk_ids, int64_t T,
+                           int64_t topk, int64_t K, int64_t E, void* a_perm, float* a_s_perm,
+                           int32_t* row_expert, int32_t* dest_row, int64_t M_cap, kbn_stream_t stream);
 int kbn_moe_unpermute_combine(const void* rows, int64_t ld_rows, const int32_t* dest_row,
                               const float* topk_w, int64_t T, int64_t topk, int64_t H, void* out,
                               kbn_stream_t stream);

@@ -213,3 +213,62 @@ extern "C" int kbn_moe_unpermute_combine(const void* rows, int64_t ld_rows, cons
     KBN_CHECK_LAUNCH();
     return KBN_OK;
 }
+
+// ---- permute without any allocation by anyone ---------------------------------------------------
+// Some hosts of this library may not call cudaMalloc at the point where they need a permute: code
+// running inside a framework that owns all device memory and hands out none for scratch, a real-time
+// serving loop that has frozen its memory map, or a plug-in that is only ever given its input and
+// output tensors.  For them the three permute kernels can run on scratch that lives in the library
+// image itself: a file-scope device array, present on every GPU that loads the library until the
+// process exits (about 264 KB).  Limits: T*topk <= 65536 pairs and E <= 1024 experts.
+namespace kbn {
+
+constexpr int64_t kStaticPermutePairs = 65536;
+constexpr int64_t kStaticPermuteExperts = 1024;
+constexpr int64_t kStaticPermuteWords = kStaticPermutePairs + 2 * kStaticPermuteExperts + 2;
+
+static __device__ __align__(256) int32_t g_permute_scratch[kStaticPermuteWords];
+
+// Device address of the array on the current device.  In host code `g_permute_scratch` is only a
+// handle for the symbol, not an address a kernel may use, so the address is looked up once per device
+// (with that device current) and remembered.
+static int static_permute_scratch(int32_t** out) {
+    static int32_t* addr[64] = {nullptr};
+    int dev = 0;
+    KBN_CUDA(cudaGetDevice(&dev));
+    KBN_REQUIRE(dev >= 0 && dev < 64, KBN_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+    if (addr[dev] == nullptr) {
+        int32_t* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_permute_scratch);
+        if (e != cudaSuccess || p == nullptr) {
+            set_error("kbn_moe_permute_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+            return KBN_ERR_CUDA;
+        }
+        addr[dev] = p;
+    }
+    *out = addr[dev];
+    return KBN_OK;
+}
+
+}  // namespace kbn
+
+// Same contract and outputs as kbn_moe_permute, minus the workspace arguments.  Calls no cudaMalloc,
+// cudaFree or allocating library routine.  The first call on a device looks up the scratch address
+// (make that call before any stream capture).  All calls on a device share the one scratch array:
+// every word a call reads it has written itself earlier in the same call, so nothing needs clearing,
+// but two calls whose kernels overlap on the GPU (different streams) would race on it.
+extern "C" int kbn_moe_permute_static(const void* a_q, const float* a_s, const int32_t* topk_ids, int64_t T, int64_t topk,
+                                      int64_t K, int64_t E, void* a_perm, float* a_s_perm, int32_t* row_expert,
+                                      int32_t* dest_row, int64_t M_cap, kbn_stream_t stream) {
+    using namespace kbn;
+    KBN_REQUIRE(T >= 0 && topk > 0 && E > 0, KBN_ERR_ARG, "kbn_moe_permute_static: bad sizes");
+    KBN_REQUIRE(T * topk <= kStaticPermutePairs && E <= kStaticPermuteExperts, KBN_ERR_UNSUPPORTED,
+                "kbn_moe_permute_static: T*topk=%lld (limit %lld) or E=%lld (limit %lld) beyond the built-in scratch; "
+                "use kbn_moe_permute with a caller-provided workspace",
+                (long long)(T * topk), (long long)kStaticPermutePairs, (long long)E, (long long)kStaticPermuteExperts);
+    int32_t* scratch = nullptr;
+    int rc = static_permute_scratch(&scratch);
+    if (rc != KBN_OK) return rc;
+    return kbn_moe_permute(a_q, a_s, topk_ids, T, topk, K, E, a_perm, a_s_perm, row_expert, dest_row, M_cap, scratch,
+                           kStaticPermuteWords * 4, stream);
+}
