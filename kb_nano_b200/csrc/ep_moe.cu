@@ -96,7 +96,7 @@ __device__ __forceinline__ void signal_when_grid_done(int32_t* done, const EpPee
     __threadfence_system();
     __syncthreads();
     __shared__ int last;
-    if (threadIdx.x == 0) last = (atomicAdd(done, 1) == (int)gridDim.x - 1);
+    if (threadIdx.x == 0) last = (atomicAdd(done, 1) == (int)(gridDim.x * gridDim.y) - 1);
     __syncthreads();
     if (!last) return;
     if (counters_to_clear)
@@ -162,24 +162,29 @@ __global__ void ep_wait_kernel(const int32_t* __restrict__ flags, int world, int
     }
 }
 
-// One warp per received row: send the expert output back to the pair's slot on its source rank.
+// Expert outputs back to their sources: blockIdx.y = local expert, whose first counters[le] rows are
+// spread over the warps of its gridDim.x blocks; each lane keeps four 16-byte loads in flight.
 __global__ void __launch_bounds__(256)
 ep_combine_send_kernel(const __nv_bfloat16* __restrict__ mm2, int hidden, int e_local, int max_m, EpPeers peers, EpLayout lay,
                        int rank, int world, int32_t epoch, int32_t* done) {
-    const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int le = blockIdx.y;
     const int lane = threadIdx.x & 31;
     uint8_t* mine = peers.base[rank];
     int32_t* counters = reinterpret_cast<int32_t*>(mine + lay.counters);
-    if (row < (int64_t)e_local * max_m) {
-        const int le = (int)(row / max_m), pos = (int)(row - (int64_t)le * max_m);
-        const int cnt = min(counters[le], max_m);
-        if (pos < cnt) {
-            const int32_t meta = reinterpret_cast<const int32_t*>(mine + lay.recv_meta)[row];
-            const int src = meta >> 20, pair = meta & 0xfffff;
-            const uint4* s = reinterpret_cast<const uint4*>(mm2 + row * hidden);
-            uint4* d = reinterpret_cast<uint4*>(peers.base[src] + lay.comb + (int64_t)pair * hidden * 2);
-            for (int v = lane; v < (hidden >> 3); v += 32) d[v] = s[v];
+    const int cnt = min(counters[le], max_m);
+    const int nvec = hidden >> 3;                       // 16-byte vectors per bf16 row
+    for (int pos = blockIdx.x * 8 + (threadIdx.x >> 5); pos < cnt; pos += gridDim.x * 8) {
+        const int64_t row = (int64_t)le * max_m + pos;
+        const int32_t meta = reinterpret_cast<const int32_t*>(mine + lay.recv_meta)[row];
+        const int src = meta >> 20, pair = meta & 0xfffff;
+        const uint4* s = reinterpret_cast<const uint4*>(mm2 + row * hidden);
+        uint4* d = reinterpret_cast<uint4*>(peers.base[src] + lay.comb + (int64_t)pair * hidden * 2);
+        int v = lane;
+        for (; v + 96 < nvec; v += 128) {
+            const uint4 a0 = s[v], a1 = s[v + 32], a2 = s[v + 64], a3 = s[v + 96];
+            d[v] = a0; d[v + 32] = a1; d[v + 64] = a2; d[v + 96] = a3;
         }
+        for (; v < nvec; v += 32) d[v] = s[v];
     }
     // the last block also zeroes the counters: every block has read them by then, and no peer
     // starts its next dispatch before it has seen this rank's combine signal
@@ -319,8 +324,7 @@ extern "C" int kbn_ep_moe_forward(kbn_ep_ctx* c, const void* x_bf16, const int32
     }
     if (rc != KBN_OK) return rc;
     // 5. results back to their sources + signal
-    const int64_t rows = c->e_local * c->max_m;
-    ep_combine_send_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(c->mm2, H, (int)c->e_local, (int)c->max_m, c->peers, c->lay, c->rank, c->world,
+    ep_combine_send_kernel<<<dim3(8, (unsigned)c->e_local), 256, 0, st>>>(c->mm2, H, (int)c->e_local, (int)c->max_m, c->peers, c->lay, c->rank, c->world,
                                                                         epoch, c->done + 1);
     KBN_CHECK_LAUNCH();
     ep_wait_kernel<<<1, kMaxRanks, 0, st>>>(reinterpret_cast<const int32_t*>(mine + c->lay.flags_combine), c->world, epoch, 2, c->status);

@@ -5,8 +5,9 @@
 // Exact rounding of silu: the reference rounds g/(1+exp(-g)) (fp32, IEEE ops on a correctly
 // rounded exp) to bf16 before the multiply.  There are only 65536 possible gates, so the
 // kernel evaluates a 5-instruction approximation (ex2.approx / rcp.approx, error < 2^-20
-// relative for |g| <= 8) and falls back to a device-resident table of exactly rounded results
-// when the approximation lands within 64 fp32 ulps of a bf16 rounding boundary or |g| > 8.
+// relative for g >= -8) and, one decision per eight values, falls back to a device-resident table
+// of exactly rounded results when any approximation lands within 64 fp32 ulps of a bf16 rounding
+// boundary or any gate is below -8.
 // The table is filled once per device by silu_table_kernel (fp64 exp rounded to fp32, then the
 // reference's fp32 add and divide).
 #include "common.cuh"
@@ -28,25 +29,50 @@ __global__ void silu_table_kernel(uint16_t* __restrict__ table) {
 
 __device__ __forceinline__ float silu_approx(float g) {
     float e, r;
-    asm("ex2.approx.f32 %0, %1;" : "=f"(e) : "f"(g * -1.4426950408889634f));
-    asm("rcp.approx.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(g * -1.4426950408889634f));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
     return g * r;
 }
 
-// true when the fast value cannot be trusted to round to the same bf16 as the exact one
-__device__ __forceinline__ bool silu_needs_table(float g, float s) {
-    uint32_t low = __float_as_uint(s) & 0xffffu;
-    return !(fabsf(g) <= 8.0f) || (low - 0x7fc0u) <= 0x80u;
+__device__ __forceinline__ uint32_t min_bf16x2(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("min.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
 }
 
-// packed bf16x2 gate, up -> packed bf16x2 y = bf16(bf16(silu(g)) * up)
-__device__ __forceinline__ uint32_t silu_mul_pair(uint32_t g2, uint32_t u2, const uint16_t* __restrict__ table) {
-    float g0 = bf16_lo(g2), g1 = bf16_hi(g2);
-    float s0 = silu_approx(g0), s1 = silu_approx(g1);
-    uint32_t sb = pack_bf16x2(s0, s1);
-    if (silu_needs_table(g0, s0)) sb = (sb & 0xffff0000u) | table[g2 & 0xffffu];
-    if (silu_needs_table(g1, s1)) sb = (sb & 0x0000ffffu) | ((uint32_t)table[g2 >> 16] << 16);
-    return mul_bf16x2(sb, u2);
+// Two gates -> packed bf16x2 silu by the fast path; `doubt` collects, for both values at once, whether
+// the fp32 result lies within 64 ulps of a bf16 rounding boundary (low 16 bits within 0x40 of 0x8000).
+__device__ __forceinline__ uint32_t silu_fast_pair(uint32_t g2, uint32_t& doubt) {
+    const float s0 = silu_approx(bf16_lo(g2)), s1 = silu_approx(bf16_hi(g2));
+    // low halves of both results side by side; +0x8040 per half maps the doubtful band onto [0, 0x80]
+    const uint32_t lo = __byte_perm(__float_as_uint(s0), __float_as_uint(s1), 0x5410);
+    const uint32_t z = (lo + 0x80408040u) & 0xff80ff80u;
+    doubt |= (z - 0x00010001u) & ~z & 0x80008000u;          // non-zero iff some 16-bit half of z is zero
+    return pack_bf16x2(s0, s1);
+}
+
+__device__ __forceinline__ uint32_t silu_table_pair(uint32_t g2, const uint16_t* __restrict__ table) {
+    return (uint32_t)table[g2 & 0xffffu] | ((uint32_t)table[g2 >> 16] << 16);
+}
+
+// Eight gates (one 16-byte load) times eight ups -> four packed bf16x2 y = bf16(bf16(silu(g)) * up).
+// One decision per eight values: if any fast result is doubtful, or any gate is below -8 (where the
+// approximation's error grows), all eight come from the exactly rounded table instead.
+__device__ __forceinline__ void silu_mul_8(const uint4& g, const uint4& u, const uint16_t* __restrict__ table, uint32_t (&y)[4]) {
+    uint32_t doubt = 0;
+    uint32_t s0 = silu_fast_pair(g.x, doubt), s1 = silu_fast_pair(g.y, doubt);
+    uint32_t s2 = silu_fast_pair(g.z, doubt), s3 = silu_fast_pair(g.w, doubt);
+    const uint32_t gm = min_bf16x2(min_bf16x2(g.x, g.y), min_bf16x2(g.z, g.w));
+    if (doubt != 0u || !(fminf(bf16_lo(gm), bf16_hi(gm)) >= -8.0f)) {
+        s0 = silu_table_pair(g.x, table);
+        s1 = silu_table_pair(g.y, table);
+        s2 = silu_table_pair(g.z, table);
+        s3 = silu_table_pair(g.w, table);
+    }
+    y[0] = mul_bf16x2(s0, u.x);
+    y[1] = mul_bf16x2(s1, u.y);
+    y[2] = mul_bf16x2(s2, u.z);
+    y[3] = mul_bf16x2(s3, u.w);
 }
 
 __device__ __forceinline__ float halfwarp_absmax4(uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
@@ -72,22 +98,15 @@ __device__ __forceinline__ uint32_t quant_pair_s(uint32_t w, float scale, float 
 // One half-warp per output group, U groups per half-warp (2*U 16-byte loads in flight per lane).
 // ROWS selects which rows are processed: 0 = all; 1 = rows with row_info[m] >= 0 (expert-contiguous
 // layout, -1 marks padding); 2 = rows with (m % max_m) < row_info[m / max_m] (masked layout).
-template <bool UE8M0, int U, int ROWS>
-__global__ void __launch_bounds__(256)
-silu_mul_quant_kernel(const __nv_bfloat16* __restrict__ in, uint32_t N2, int64_t ld_in, uint8_t* __restrict__ q,
-                      int64_t ld_q, float* __restrict__ scale, int64_t s_row, int64_t s_grp, float eps,
-                      const uint16_t* __restrict__ table, const int32_t* __restrict__ row_info, uint32_t max_m,
-                      uint32_t G, uint32_t chunks_per_row, uint32_t n_chunks) {
-    const uint32_t j = threadIdx.x & 15u;
-    const uint32_t chunk = blockIdx.x * 16u + (threadIdx.x >> 4);
-    bool valid = chunk < n_chunks;
-    const uint32_t row = valid ? chunk / chunks_per_row : 0u;
-    const uint32_t g0 = (chunk - row * chunks_per_row) * U;
-    if (ROWS == 1) valid = valid && row_info[row] >= 0;
-    if (ROWS == 2) valid = valid && (int)(row % max_m) < row_info[row / max_m];
+// One chunk = U consecutive groups of one row, handled by a half-warp (both halves of a warp must
+// call this together: the absmax uses full-warp shuffles).
+template <bool UE8M0, int U, bool SMEM = false>
+__device__ __forceinline__ void smq_chunk(bool valid, uint32_t row, uint32_t g0, uint32_t j, const __nv_bfloat16* __restrict__ in,
+                                          uint32_t N2, int64_t ld_in, uint8_t* __restrict__ q, int64_t ld_q,
+                                          float* __restrict__ scale, int64_t s_row, int64_t s_grp, float eps,
+                                          const uint16_t* __restrict__ table, uint32_t G) {
     const __nv_bfloat16* ir = in + (int64_t)row * ld_in;
     uint8_t* qr = q + (int64_t)row * ld_q;
-
     uint4 gv[U], uv[U];
     bool live[U];
 #pragma unroll
@@ -99,11 +118,17 @@ silu_mul_quant_kernel(const __nv_bfloat16* __restrict__ in, uint32_t N2, int64_t
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-        uint32_t y0 = silu_mul_pair(gv[u].x, uv[u].x, table);
-        uint32_t y1 = silu_mul_pair(gv[u].y, uv[u].y, table);
-        uint32_t y2 = silu_mul_pair(gv[u].z, uv[u].z, table);
-        uint32_t y3 = silu_mul_pair(gv[u].w, uv[u].w, table);
-        float a = fmaxf(halfwarp_absmax4(y0, y1, y2, y3), eps);
+        uint32_t y[4];
+        if (SMEM) {
+            // `table` is the block's shared-memory copy: every value comes from the exact table
+            y[0] = mul_bf16x2(silu_table_pair(gv[u].x, table), uv[u].x);
+            y[1] = mul_bf16x2(silu_table_pair(gv[u].y, table), uv[u].y);
+            y[2] = mul_bf16x2(silu_table_pair(gv[u].z, table), uv[u].z);
+            y[3] = mul_bf16x2(silu_table_pair(gv[u].w, table), uv[u].w);
+        } else {
+            silu_mul_8(gv[u], uv[u], table, y);
+        }
+        float a = fmaxf(halfwarp_absmax4(y[0], y[1], y[2], y[3]), eps);
         float sc, inv = 0.0f;
         if (UE8M0) {
             uint32_t f = ue8m0_scale_field(a);
@@ -115,22 +140,90 @@ silu_mul_quant_kernel(const __nv_bfloat16* __restrict__ in, uint32_t N2, int64_t
         if (live[u]) {
             const uint32_t g = g0 + u;
             uint2 o;
-            o.x = quant_pair_s<UE8M0>(y0, sc, inv) | (quant_pair_s<UE8M0>(y1, sc, inv) << 16);
-            o.y = quant_pair_s<UE8M0>(y2, sc, inv) | (quant_pair_s<UE8M0>(y3, sc, inv) << 16);
+            o.x = quant_pair_s<UE8M0>(y[0], sc, inv) | (quant_pair_s<UE8M0>(y[1], sc, inv) << 16);
+            o.y = quant_pair_s<UE8M0>(y[2], sc, inv) | (quant_pair_s<UE8M0>(y[3], sc, inv) << 16);
             *reinterpret_cast<uint2*>(qr + g * 128u + j * 8u) = o;
             if (j == 0) scale[(int64_t)row * s_row + (int64_t)g * s_grp] = sc;
         }
     }
 }
 
-// all 65536 gates through the same device function the main kernel uses (up = 1.0)
+// Flat grid: chunk index -> (row, first group) with one 32-bit division per thread.
+// ROWS: 0 = every row; 1 = rows with row_info[m] >= 0 (expert-contiguous layout, -1 marks padding).
+template <bool UE8M0, int U, int ROWS>
+__global__ void __launch_bounds__(256)
+silu_mul_quant_kernel(const __nv_bfloat16* __restrict__ in, uint32_t N2, int64_t ld_in, uint8_t* __restrict__ q,
+                      int64_t ld_q, float* __restrict__ scale, int64_t s_row, int64_t s_grp, float eps,
+                      const uint16_t* __restrict__ table, const int32_t* __restrict__ row_info, uint32_t G,
+                      uint32_t chunks_per_row, uint32_t n_chunks) {
+    const uint32_t chunk = blockIdx.x * 16u + (threadIdx.x >> 4);
+    bool valid = chunk < n_chunks;
+    const uint32_t row = valid ? chunk / chunks_per_row : 0u;
+    const uint32_t g0 = (chunk - row * chunks_per_row) * U;
+    if (ROWS == 1) valid = valid && row_info[row] >= 0;
+    smq_chunk<UE8M0, U>(valid, row, g0, threadIdx.x & 15u, in, N2, ld_in, q, ld_q, scale, s_row, s_grp, eps, table, G);
+}
+
+// Large inputs: one persistent block of 1024 threads per SM keeps the whole 128 KB exact table in
+// shared memory, so silu costs two shared loads per pair instead of the approximation and its
+// check; the blocks stride over the chunks.  ROWS as in the flat kernel.
+template <bool UE8M0, int U, int ROWS>
+__global__ void __launch_bounds__(1024, 1)
+silu_mul_quant_smem_kernel(const __nv_bfloat16* __restrict__ in, uint32_t N2, int64_t ld_in, uint8_t* __restrict__ q,
+                           int64_t ld_q, float* __restrict__ scale, int64_t s_row, int64_t s_grp, float eps,
+                           const uint16_t* __restrict__ table, const int32_t* __restrict__ row_info, uint32_t G,
+                           uint32_t chunks_per_row, uint32_t n_chunks) {
+    extern __shared__ __align__(16) uint16_t tab[];
+    for (uint32_t i = threadIdx.x; i < 8192u; i += blockDim.x)
+        reinterpret_cast<uint4*>(tab)[i] = __ldg(reinterpret_cast<const uint4*>(table) + i);
+    __syncthreads();
+    const uint32_t half = (threadIdx.x >> 4) & 1u;
+    const uint32_t per_iter = gridDim.x * (blockDim.x >> 4);
+    for (uint32_t base = blockIdx.x * (blockDim.x >> 4) + (threadIdx.x >> 5) * 2u; base < n_chunks; base += per_iter) {
+        const uint32_t chunk = base + half;
+        bool valid = chunk < n_chunks;
+        const uint32_t row = valid ? chunk / chunks_per_row : 0u;
+        const uint32_t g0 = (chunk - row * chunks_per_row) * U;
+        if (ROWS == 1) valid = valid && row_info[row] >= 0;
+        smq_chunk<UE8M0, U, true>(valid, row, g0, threadIdx.x & 15u, in, N2, ld_in, q, ld_q, scale, s_row, s_grp, eps, tab, G);
+    }
+}
+
+// Masked layout: blockIdx.y = expert; the blocks of an expert loop over the chunks of its first
+// masked_m[e] rows only, so an almost empty buffer costs a handful of blocks, not one per row.
+template <bool UE8M0, int U>
+__global__ void __launch_bounds__(256)
+silu_mul_quant_masked_kernel(const __nv_bfloat16* __restrict__ in, uint32_t N2, int64_t ld_in, uint8_t* __restrict__ q,
+                             int64_t ld_q, float* __restrict__ scale, int64_t s_row, int64_t s_grp, float eps,
+                             const uint16_t* __restrict__ table, const int32_t* __restrict__ masked_m, uint32_t max_m,
+                             uint32_t G, uint32_t chunks_per_row) {
+    const uint32_t e = blockIdx.y;
+    const uint32_t cnt = (uint32_t)min(max(masked_m[e], 0), (int)max_m);
+    const uint32_t n = cnt * chunks_per_row;
+    const uint32_t half = (threadIdx.x >> 4) & 1u;
+    // the loop variable is warp-uniform so that both half-warps stay together for the shuffles
+    for (uint32_t base = blockIdx.x * 16u + (threadIdx.x >> 5) * 2u; base < n; base += gridDim.x * 16u) {
+        const uint32_t chunk = base + half;
+        const bool valid = chunk < n;
+        const uint32_t r = valid ? chunk / chunks_per_row : 0u;
+        const uint32_t g0 = (chunk - r * chunks_per_row) * U;
+        smq_chunk<UE8M0, U>(valid, e * max_m + r, g0, threadIdx.x & 15u, in, N2, ld_in, q, ld_q, scale, s_row, s_grp, eps, table, G);
+    }
+}
+
+// Every gate through the same device function the main kernel uses (up = 1.0).  Each gate is tested
+// alone (the eight values of its group are copies of it), so the per-eight decision is exactly the
+// gate's own: whatever neighbours it meets in real data can only send it to the table, never to a
+// fast result this probe has not seen.
 __global__ void silu_probe_kernel(uint16_t* __restrict__ out, const uint16_t* __restrict__ table) {
-    uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= 32768u) return;
-    uint32_t g2 = (2u * i) | ((2u * i + 1u) << 16);
-    uint32_t y = silu_mul_pair(g2, 0x3f803f80u, table);
-    out[2 * i] = (uint16_t)(y & 0xffffu);
-    out[2 * i + 1] = (uint16_t)(y >> 16);
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= 65536u) return;
+    const uint32_t g2 = i | (i << 16);
+    const uint4 g = make_uint4(g2, g2, g2, g2);
+    const uint4 one = make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u);
+    uint32_t y[4];
+    silu_mul_8(g, one, table, y);
+    out[i] = (uint16_t)(y[0] & 0xffffu);
 }
 
 // Table pointer of the current device; the first call per device enqueues the fill on `st`.
@@ -177,7 +270,7 @@ static int launch_silu_mul_quant(const char* who, const void* in, int64_t M, int
     const uint16_t* table = nullptr;
     int rc = silu_table_for_stream(st, &table);
     if (rc != KBN_OK) return rc;
-    constexpr int U = 2;
+    constexpr int U = 4;
     const int64_t G = N2 / 128, cpr = (G + U - 1) / U, n_chunks = M * cpr;
     KBN_REQUIRE(2 * N2 < (1ll << 31) && n_chunks < (1ll << 31) && max_m < (1ll << 31), KBN_ERR_ARG, "%s: more than 2^31 groups", who);
     const auto* ib = static_cast<const __nv_bfloat16*>(in);
@@ -186,13 +279,39 @@ static int launch_silu_mul_quant(const char* who, const void* in, int64_t M, int
     const uint32_t mm = (uint32_t)max_m;
 #define KBN_SMQ(UE, RM)                                                                                                   \
     silu_mul_quant_kernel<UE, U, RM><<<nb, 256, 0, st>>>(ib, (uint32_t)N2, ld_in, qb, ld_q, scale, s_row, s_grp, eps, table, \
-                                                         row_info, mm, (uint32_t)G, (uint32_t)cpr, (uint32_t)n_chunks)
-    if (ue8m0) {
-        if (rows_mode == 0) KBN_SMQ(true, 0); else if (rows_mode == 1) KBN_SMQ(true, 1); else KBN_SMQ(true, 2);
+                                                         row_info, (uint32_t)G, (uint32_t)cpr, (uint32_t)n_chunks)
+#define KBN_SMQ_MASKED(UE)                                                                                                \
+    silu_mul_quant_masked_kernel<UE, U><<<dim3(4, (unsigned)(M / max_m)), 256, 0, st>>>(                                  \
+        ib, (uint32_t)N2, ld_in, qb, ld_q, scale, s_row, s_grp, eps, table, row_info, mm, (uint32_t)G, (uint32_t)cpr)
+    // large flat inputs with power-of-two scales: persistent blocks with the exact table in shared memory
+    if (rows_mode != 2 && ue8m0 && n_chunks * U >= 32768) {
+        constexpr int U2 = 2;
+        const int64_t cpr2 = (G + U2 - 1) / U2, n2c = M * cpr2;
+        static int attr_set[64] = {0};
+        int dev = 0;
+        KBN_CUDA(cudaGetDevice(&dev));
+        if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+            KBN_CUDA(cudaFuncSetAttribute(silu_mul_quant_smem_kernel<true, U2, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 131072));
+            KBN_CUDA(cudaFuncSetAttribute(silu_mul_quant_smem_kernel<true, U2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 131072));
+            attr_set[dev] = 1;
+        }
+        const unsigned grid = (unsigned)sm_count();
+        if (rows_mode == 0)
+            silu_mul_quant_smem_kernel<true, U2, 0><<<grid, 1024, 131072, st>>>(ib, (uint32_t)N2, ld_in, qb, ld_q, scale, s_row, s_grp, eps, table,
+                                                                               row_info, (uint32_t)G, (uint32_t)cpr2, (uint32_t)n2c);
+        else
+            silu_mul_quant_smem_kernel<true, U2, 1><<<grid, 1024, 131072, st>>>(ib, (uint32_t)N2, ld_in, qb, ld_q, scale, s_row, s_grp, eps, table,
+                                                                               row_info, (uint32_t)G, (uint32_t)cpr2, (uint32_t)n2c);
+    } else if (rows_mode == 2) {
+        KBN_REQUIRE(M / max_m <= 65535, KBN_ERR_ARG, "%s: more than 65535 experts", who);
+        if (ue8m0) KBN_SMQ_MASKED(true); else KBN_SMQ_MASKED(false);
+    } else if (ue8m0) {
+        if (rows_mode == 0) KBN_SMQ(true, 0); else KBN_SMQ(true, 1);
     } else {
-        if (rows_mode == 0) KBN_SMQ(false, 0); else if (rows_mode == 1) KBN_SMQ(false, 1); else KBN_SMQ(false, 2);
+        if (rows_mode == 0) KBN_SMQ(false, 0); else KBN_SMQ(false, 1);
     }
 #undef KBN_SMQ
+#undef KBN_SMQ_MASKED
     KBN_CHECK_LAUNCH();
     return KBN_OK;
 }
@@ -233,7 +352,7 @@ extern "C" int kbn_silu_bf16_table(void* out_u16, kbn_stream_t stream) {
     const uint16_t* table = nullptr;
     int rc = silu_table_for_stream(st, &table);
     if (rc != KBN_OK) return rc;
-    silu_probe_kernel<<<128, 256, 0, st>>>(static_cast<uint16_t*>(out_u16), table);
+    silu_probe_kernel<<<256, 256, 0, st>>>(static_cast<uint16_t*>(out_u16), table);
     KBN_CHECK_LAUNCH();
     return KBN_OK;
 }

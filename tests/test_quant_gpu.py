@@ -169,6 +169,22 @@ def test_silu_exhaustive_gate_times_several_ups(cuda_dev):
     assert_quant_equal(q, s, qr, np.ascontiguousarray(sr), "all gates x random ups")
 
 
+def test_silu_every_gate_through_the_shared_memory_table_kernel(cuda_dev):
+    """Inputs of 32768 groups or more run on the persistent kernel that keeps the exact table in shared
+    memory; every finite gate appears in this one, with random ups, checked bit for bit."""
+    rng = np.random.default_rng(1)
+    gates = np.arange(65536, dtype=np.uint16)
+    gf = bf16_from_bits(gates).float().numpy()
+    gates = np.where(np.isfinite(gf) & (np.abs(gf) < 1e30), gates, np.uint16(0x3F80))
+    g = np.tile(gates.reshape(8, 8192), (64, 1))                     # [512, 8192]: 512 * 64 = 32768 groups
+    rng.shuffle(g, axis=1)
+    ups = bits16(torch.from_numpy(rng.standard_normal(g.shape).astype(np.float32) * 2).to(torch.bfloat16))
+    x = np.concatenate([g, ups], axis=1)
+    q, s = run_smq(bf16_from_bits(x), cuda_dev)
+    qr, sr = co.silu_mul_quant_1x128(x)
+    assert_quant_equal(q, s, qr, np.ascontiguousarray(sr), "shared-memory-table kernel, all gates")
+
+
 def test_silu_mul_quant_golden(cuda_dev):
     g = golden("silu_mul_quant")
     q, s = run_smq(bf16_from_bits(g["x"]), cuda_dev)
