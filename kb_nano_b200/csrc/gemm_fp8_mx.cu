@@ -22,18 +22,25 @@
 namespace kbn {
 namespace mx {
 
-constexpr int kBN = 256;
-constexpr int kStages = 4;
+// Tile width BN is 256 (less L2 traffic per flop; the default) or 128 (twice the tiles: used when a
+// dense problem would otherwise leave most SMs without a tile).
+template <int BN>
+struct Cfg {
+    static constexpr int kBN = BN;
+    static constexpr int kStages = BN == 256 ? 4 : 6;
+    static constexpr int kBBytes = BN * kBlockK;
+    static constexpr int kStageBytes = kBlockM * kBlockK + kBBytes;
+    static constexpr int kSfbBytes = 512 * (BN / 128);
+    static constexpr int kSfStage = 512 + kSfbBytes;
+    static constexpr int kTxBytes = kStageBytes + kSfStage;
+    static constexpr size_t kSmemBytes = (size_t)kStages * (kStageBytes + kSfStage) + 1024 + 256;
+};
 constexpr int kABytes = kBlockM * kBlockK;          // 16 KB
-constexpr int kBBytes = kBN * kBlockK;              // 32 KB
-constexpr int kStageBytes = kABytes + kBBytes;      // 48 KB
-constexpr int kSfaBytes = 512, kSfbBytes = 1024, kSfStage = kSfaBytes + kSfbBytes;
-constexpr int kTxBytes = kStageBytes + kSfStage;
+constexpr int kSfaBytes = 512;
 constexpr int kEpiWarps = 8;
 constexpr int kThreads = 32 * (2 + kEpiWarps);
 constexpr int kTmemCols = 512;
 constexpr int kColSfa = 256, kColSfb = 260;         // TMEM columns of the scale factors
-constexpr size_t kSmemBytes = (size_t)kStages * (kStageBytes + kSfStage) + 1024 + 256;
 
 struct MxExtra {
     const uint8_t* sfa;      // packed [row_blocks][KB][512 B]
@@ -41,9 +48,13 @@ struct MxExtra {
     int32_t nb_pad;          // 128-column blocks per expert, rounded up to even
 };
 
+template <int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p,
                    const MxExtra x) {
+    constexpr int kBN = Cfg<BN>::kBN, kStages = Cfg<BN>::kStages, kStageBytes = Cfg<BN>::kStageBytes;
+    constexpr int kSfbBytes = Cfg<BN>::kSfbBytes, kSfStage = Cfg<BN>::kSfStage, kTxBytes = Cfg<BN>::kTxBytes;
+    constexpr int kHalfCols = BN / 2;                // columns each epilogue warp of a lane quarter drains
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~(uintptr_t)1023u);
     uint8_t* sf_smem = smem + (size_t)kStages * kStageBytes;
@@ -92,7 +103,7 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                 if (!tile.compute) continue;
                 const int32_t b_row = tile.expert * p.N + tile.n_blk * kBN;
                 const uint8_t* sfa = x.sfa + (int64_t)(tile.row0 / kBlockM) * KB * kSfaBytes;
-                const uint8_t* sfb = x.sfb + (((int64_t)tile.expert * KB) * x.nb_pad + 2 * tile.n_blk) * (int64_t)kSfaBytes;
+                const uint8_t* sfb = x.sfb + (((int64_t)tile.expert * KB) * x.nb_pad + (BN / 128) * tile.n_blk) * (int64_t)kSfaBytes;
                 for (int kb = 0; kb < KB; ++kb, ++it) {
                     const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
                     if (!wait_bar(bar_empty + 8 * s, ph ^ 1u, w)) { ok = false; break; }
@@ -133,7 +144,8 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                     const uint32_t sf_addr = smem_sf + s * kSfStage;
                     ptx::tmem_cp_32x128b_warpx4(tmem_base + kColSfa, ptx::umma_desc_sf(sf_addr));
                     ptx::tmem_cp_32x128b_warpx4(tmem_base + kColSfb, ptx::umma_desc_sf(sf_addr + kSfaBytes));
-                    ptx::tmem_cp_32x128b_warpx4(tmem_base + kColSfb + 4, ptx::umma_desc_sf(sf_addr + 2 * kSfaBytes));
+                    if (BN == 256)
+                        ptx::tmem_cp_32x128b_warpx4(tmem_base + kColSfb + 4, ptx::umma_desc_sf(sf_addr + 2 * kSfaBytes));
                     const uint64_t a_desc = ptx::umma_desc_k_sw128(a_addr);
                     const uint64_t b_desc = ptx::umma_desc_k_sw128(a_addr + kABytes);
 #pragma unroll
@@ -150,7 +162,7 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     } else {
         // ---------------- epilogue ----------------
         const int quarter = warp & 3;
-        const int half = (warp - 2) >> 2;            // columns 128*half .. 128*half+127
+        const int half = (warp - 2) >> 2;            // which half of the tile's columns this warp drains
         const int r_in_tile = quarter * 32 + lane;
         WaitCtx w{abort_flag, p.status, 6};
         TileWalk walk(p);
@@ -164,12 +176,12 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             if (p.mode == kContig && row_ok) row_ok = p.row_expert[row] >= 0;
             if (!wait_bar(bar_tfull, tile_it & 1u, w)) { ok = false; break; }
             ptx::tc_fence_after();
-            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + half * 128;
-            const int32_t n0 = tile.n_blk * kBN + half * 128;
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + half * kHalfCols;
+            const int32_t n0 = tile.n_blk * kBN + half * kHalfCols;
             __nv_bfloat16* crow = p.C + (int64_t)row * p.ldc + n0;
             const bool vec_ok = (reinterpret_cast<uintptr_t>(crow) & 15u) == 0;
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < kHalfCols / 32; ++c) {
                 uint32_t r[32];
                 ptx::tmem_ld_32x32(taddr + 32 * c, r);
                 ptx::tmem_ld_wait(r);
@@ -288,7 +300,8 @@ static int check_device() {
         int major = 0;
         KBN_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
         KBN_REQUIRE(major == 10, KBN_ERR_UNSUPPORTED, "kbn_fp8 GEMMs need an sm_100 device (found major %d)", major);
-        KBN_CUDA(cudaFuncSetAttribute(fp8_gemm_mx_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+        KBN_CUDA(cudaFuncSetAttribute(fp8_gemm_mx_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<256>::kSmemBytes));
+        KBN_CUDA(cudaFuncSetAttribute(fp8_gemm_mx_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<128>::kSmemBytes));
         ok[dev] = 1;
     }
     return KBN_OK;
@@ -296,18 +309,24 @@ static int check_device() {
 
 static inline int32_t cdiv32(int64_t a, int64_t b) { return (int32_t)((a + b - 1) / b); }
 
+// m_blocks_upper: number of 128-row blocks (an upper bound in the masked form).
 static int launch(const void* A, int64_t a_rows, const void* B, int64_t b_rows, GemmParams& p, const void* sfa, const void* sfb,
-                  int64_t max_tiles, cudaStream_t st) {
+                  int64_t m_blocks_upper, cudaStream_t st) {
     int rc = check_device();
     if (rc != KBN_OK) return rc;
     KBN_REQUIRE(sfa && sfb, KBN_ERR_ARG, "fp8 gemm (ue8m0): null packed scales");
     KBN_REQUIRE(aligned16(A) && aligned16(B) && aligned16(sfa) && aligned16(sfb), KBN_ERR_ARG, "fp8 gemm (ue8m0): pointers must be 16-byte aligned");
     KBN_REQUIRE(p.K % 16 == 0 && p.K > 0 && p.N > 0, KBN_ERR_ARG, "fp8 gemm (ue8m0): K=%d must be a positive multiple of 16", p.K);
     KBN_REQUIRE(a_rows < (1ll << 31) && b_rows < (1ll << 31), KBN_ERR_ARG, "fp8 gemm (ue8m0): more than 2^31 rows");
+    // 256-wide tiles unless that would leave SMs without a tile and 128-wide tiles fill more of them
+    int bn = 256;
+    if (p.mode != kMasked && p.N > 128 && m_blocks_upper * cdiv32(p.N, 256) < sm_count()) bn = 128;
+    p.num_n_blocks = cdiv32(p.N, bn);
+    const int64_t max_tiles = m_blocks_upper * p.num_n_blocks;
     CUtensorMap tmA, tmB;
     rc = make_tmap(&tmA, A, a_rows, p.K, kBlockM, CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
     if (rc != KBN_OK) return rc;
-    rc = make_tmap(&tmB, B, b_rows, p.K, kBN, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+    rc = make_tmap(&tmB, B, b_rows, p.K, bn, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
     if (rc != KBN_OK) return rc;
     rc = gemm_status_ptr(&p.status);
     if (rc != KBN_OK) return rc;
@@ -318,7 +337,10 @@ static int launch(const void* A, int64_t a_rows, const void* B, int64_t b_rows, 
     int64_t grid = sm_count();
     if (max_tiles < grid) grid = max_tiles;
     if (grid <= 0) return KBN_OK;
-    fp8_gemm_mx_kernel<<<(unsigned)grid, kThreads, kSmemBytes, st>>>(tmA, tmB, p, x);
+    if (bn == 256)
+        fp8_gemm_mx_kernel<256><<<(unsigned)grid, kThreads, Cfg<256>::kSmemBytes, st>>>(tmA, tmB, p, x);
+    else
+        fp8_gemm_mx_kernel<128><<<(unsigned)grid, kThreads, Cfg<128>::kSmemBytes, st>>>(tmA, tmB, p, x);
     KBN_CHECK_LAUNCH();
     return KBN_OK;
 }
@@ -328,7 +350,7 @@ static void fill_params(GemmParams& p, void* C, int64_t ldc, int64_t rows, int64
     p.C = static_cast<__nv_bfloat16*>(C); p.ldc = ldc;
     p.rows_total = (int32_t)rows; p.N = (int32_t)N; p.K = (int32_t)K; p.E = (int32_t)E; p.max_m = (int32_t)max_m;
     p.num_m_blocks = mode == kMasked ? 0 : cdiv32(rows, kBlockM);
-    p.num_n_blocks = cdiv32(N, kBN); p.num_k_blocks = cdiv32(K, kBlockK); p.sb_nb = cdiv32(N, 128);
+    p.num_n_blocks = 0 /* set by launch() */; p.num_k_blocks = cdiv32(K, kBlockK); p.sb_nb = cdiv32(N, 128);
     p.mode = mode;
 }
 
@@ -389,7 +411,7 @@ extern "C" int kbn_fp8_gemm_nt_ue8m0(const void* A, const void* sfa_packed, cons
     KBN_REQUIRE(A && B && C && ldc >= N, KBN_ERR_ARG, "kbn_fp8_gemm_nt_ue8m0: null pointer or ldc < N");
     GemmParams p{};
     mx::fill_params(p, C, ldc, M, N, K, 1, 0, kDense);
-    return mx::launch(A, M, B, N, p, sfa_packed, sfb_packed, (int64_t)p.num_m_blocks * p.num_n_blocks, static_cast<cudaStream_t>(stream));
+    return mx::launch(A, M, B, N, p, sfa_packed, sfb_packed, p.num_m_blocks, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int kbn_fp8_grouped_gemm_contig_ue8m0(const void* A, const void* sfa_packed, const void* B, const void* sfb_packed,
@@ -403,7 +425,7 @@ extern "C" int kbn_fp8_grouped_gemm_contig_ue8m0(const void* A, const void* sfa_
     GemmParams p{};
     mx::fill_params(p, C, ldc, M_sum, N, K, E, 0, kContig);
     p.row_expert = row_expert;
-    return mx::launch(A, M_sum, B, E * N, p, sfa_packed, sfb_packed, (int64_t)p.num_m_blocks * p.num_n_blocks, static_cast<cudaStream_t>(stream));
+    return mx::launch(A, M_sum, B, E * N, p, sfa_packed, sfb_packed, p.num_m_blocks, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int kbn_fp8_grouped_gemm_masked_ue8m0(const void* A, const void* sfa_packed, const void* B, const void* sfb_packed,
@@ -418,6 +440,5 @@ extern "C" int kbn_fp8_grouped_gemm_masked_ue8m0(const void* A, const void* sfa_
     GemmParams p{};
     mx::fill_params(p, C, N, E * max_m, N, K, E, max_m, kMasked);
     p.masked_m = masked_m;
-    const int64_t max_tiles = E * (int64_t)((max_m + 127) / 128) * p.num_n_blocks;
-    return mx::launch(A, E * max_m, B, E * N, p, sfa_packed, sfb_packed, max_tiles, static_cast<cudaStream_t>(stream));
+    return mx::launch(A, E * max_m, B, E * N, p, sfa_packed, sfb_packed, E * ((max_m + 127) / 128), static_cast<cudaStream_t>(stream));
 }

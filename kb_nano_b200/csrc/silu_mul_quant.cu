@@ -285,7 +285,7 @@ static int launch_silu_mul_quant(const char* who, const void* in, int64_t M, int
         ib, (uint32_t)N2, ld_in, qb, ld_q, scale, s_row, s_grp, eps, table, row_info, mm, (uint32_t)G, (uint32_t)cpr)
     // large flat inputs with power-of-two scales: persistent blocks with the exact table in shared memory
     if (rows_mode != 2 && ue8m0 && n_chunks * U >= 32768) {
-        constexpr int U2 = 2;
+        constexpr int U2 = 4;
         const int64_t cpr2 = (G + U2 - 1) / U2, n2c = M * cpr2;
         static int attr_set[64] = {0};
         int dev = 0;

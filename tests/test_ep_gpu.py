@@ -76,7 +76,7 @@ def _ep_worker(rank, world, port, t, h, i, e, topk, seed, q):
     try:
         xs, routes, (w13_q, w13_s, w2_q, w2_s) = ep_case(world, t, h, i, e, topk, seed)
         lo, hi = ep.expert_range(rank, world, e)
-        layer = ep.EpMoe(rank, world, e, h, i, max_tokens=t, topk=topk, max_m=128, device=d)
+        layer = ep.EpMoe(rank, world, e, h, i, max_tokens=t, topk=topk, max_m=256, device=d)   # 8 ranks x 64 tokens x 4 slots over 16 experts: 128 rows per expert on average
         loc = [w[lo:hi].contiguous().to(d) for w in (w13_q, w13_s, w2_q, w2_s)]
         ref = to.moe_layer(xs[rank], w13_q, w13_s, w2_q, w2_s, routes[rank][0], routes[rank][1])
         ok, msg = True, ""
