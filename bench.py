@@ -551,7 +551,11 @@ def wl_ep_moe(args, rank, world, dev, sampler):
         "e2e": {"value": t * world / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": t * h * 2 + t * topk * 8, "d2h_bytes_per_step": t * h * 2},
         "gpu_launches": launches // (args.steps + args.warmup) * args.steps,
         "roofline": {"bound": "hbm", "kernel": "fp8_gemm_mx_kernel (masked grouped, 2 launches per layer; rank 0)", "achieved": ach, "peak": peaks["hbm_gbs"],
-                     "unit": "GB/s", "frac": ach / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
+                     "unit": "GB/s", "frac": ach / peaks["hbm_gbs"],
+                     # dram read+write bytes per launch from the ncu capture summarised in
+                     # profiles/fp8_gemm_mx_masked_ep_moe.md (0.76 GB per launch with 32 local experts; proportional
+                     # to the number of experts whose weights are streamed)
+                     "traffic": 0.76e9 / 32.0 * active, "peak_source": peaks["source"],
                      "algorithmic_bytes_per_launch": (g1 + g2) / 2.0, "gemm_ms_per_launch": gemm_ms},
         "_cpu": lambda: cpu_moe(t, h, i, e, topk, "sigmoid", 8, 1),
     }

@@ -26,18 +26,17 @@ extern "C" int kbn_fp8_grouped_gemm_masked(const void*, const float*, int64_t, i
 
 extern "C" int kbn_fp8_grouped_gemm_masked_ue8m0(const void*, const void*, const void*, const void*, void*, const int32_t*, int64_t, int64_t,
                                                  int64_t, int64_t, kbn_stream_t);
-extern "C" int kbn_pack_sf_rows(const float*, int64_t, int64_t, int64_t, int64_t, void*, kbn_stream_t);
 extern "C" int64_t kbn_packed_sf_rows_bytes(int64_t, int64_t);
 
 namespace kbn {
 int silu_mul_quant_masked(const void* in, int64_t E, int64_t max_m, int64_t N2, void* q, float* scale,
-                          const int32_t* masked_m, cudaStream_t st);   // silu_mul_quant.cu
+                          const int32_t* masked_m, cudaStream_t st, void* packed_sf);   // silu_mul_quant.cu
 
 constexpr int kMaxRanks = 16;
 constexpr long long kFlagWaitCycles = 2000000000ll;   // about a second
 
 struct EpLayout {          // byte offsets inside each rank's symmetric buffer (identical on all ranks)
-    int64_t recv_q, recv_s, recv_meta, counters, flags_dispatch, flags_combine, comb, total;
+    int64_t recv_q, recv_s, recv_sf, recv_meta, counters, flags_dispatch, flags_combine, comb, total;
 };
 
 struct EpPeers {
@@ -56,7 +55,7 @@ struct kbn_ep_ctx {
     // local scratch
     uint8_t* a_q; float* a_s;          // quantised local tokens
     __nv_bfloat16* mm1; uint8_t* a2_q; float* a2_s; __nv_bfloat16* mm2;
-    uint8_t* sf1; uint8_t* sf2;        // packed UE8M0 scales of the received rows / of the activation (UE8M0 GEMM path)
+    uint8_t* sf2;                      // packed UE8M0 scales of the activation between the GEMMs (UE8M0 GEMM path)
     int32_t* identity;                 // [max_tokens*topk] 0,1,2,...
     int32_t* done;                     // [2] block-completion counters
     int32_t* status;                   // [4] code, phase, peer, detail
@@ -72,6 +71,7 @@ static EpLayout make_layout(const kbn_ep_ctx& c) {
     int64_t o = 0;
     l.recv_q = o;          o += up256(c.e_local * c.max_m * c.hidden);
     l.recv_s = o;          o += up256(c.e_local * c.max_m * (c.hidden / 128) * 4);
+    l.recv_sf = o;         o += up256(kbn_packed_sf_rows_bytes(c.e_local * c.max_m, c.hidden));
     l.recv_meta = o;       o += up256(c.e_local * c.max_m * 4);
     l.counters = o;        o += up256(c.e_local * 4);
     l.flags_dispatch = o;  o += up256(kMaxRanks * 4);
@@ -131,7 +131,14 @@ ep_dispatch_kernel(const uint8_t* __restrict__ a_q, const float* __restrict__ a_
                 for (int v = lane; v < (hidden >> 4); v += 32) dq[v] = __ldg(src + v);
                 const int g = hidden >> 7;
                 float* ds = reinterpret_cast<float*>(pb + lay.recv_s) + row * g;
-                for (int k = lane; k < g; k += 32) ds[k] = __ldg(a_s + (int64_t)t * g + k);
+                // scales twice: fp32 (general GEMM path) and packed UE8M0 words (block-scaled GEMM path):
+                // word ((row/128)*g + k)*128 + (row%32)*4 + (row%128)/32, exponent byte repeated
+                uint32_t* dp = reinterpret_cast<uint32_t*>(pb + lay.recv_sf) + (size_t)(row >> 7) * g * 128 + (row & 31) * 4 + ((row & 127) >> 5);
+                for (int k = lane; k < g; k += 32) {
+                    const float sv = __ldg(a_s + (int64_t)t * g + k);
+                    ds[k] = sv;
+                    dp[(size_t)k * 128] = ((__float_as_uint(sv) >> 23) & 0xffu) * 0x01010101u;
+                }
                 if (lane == 0) reinterpret_cast<int32_t*>(pb + lay.recv_meta)[row] = (rank << 20) | i;
             } else if (lane == 0) {
                 atomicCAS(status, 0, 10);          // an expert received more than max_m rows
@@ -226,8 +233,8 @@ extern "C" int kbn_ep_create(int rank, int world, int64_t experts_total, int64_t
     KBN_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->a2_q), (size_t)(rows * inter)));
     KBN_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->a2_s), (size_t)(rows * (inter / 128) * 4)));
     KBN_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->mm2), (size_t)(rows * hidden * 2)));
-    KBN_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->sf1), (size_t)kbn_packed_sf_rows_bytes(rows, hidden)));
     KBN_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->sf2), (size_t)kbn_packed_sf_rows_bytes(rows, inter)));
+    KBN_CUDA(cudaMemset(c->sf2, 0x7f, (size_t)kbn_packed_sf_rows_bytes(rows, inter)));
     KBN_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->identity), (size_t)(max_tokens * topk * 4)));
     KBN_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->done), 16));
     KBN_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->status), 16));
@@ -306,18 +313,14 @@ extern "C" int kbn_ep_moe_forward(kbn_ep_ctx* c, const void* x_bf16, const int32
     const float* recv_s = reinterpret_cast<const float*>(mine + c->lay.recv_s);
     const int64_t rows_all = c->e_local * c->max_m;
     if (ue8m0) {
-        rc = kbn_pack_sf_rows(recv_s, rows_all, H, G, 1, c->sf1, stream);
-        if (rc != KBN_OK) return rc;
-        rc = kbn_fp8_grouped_gemm_masked_ue8m0(mine + c->lay.recv_q, c->sf1, w13, w13_sf_packed, c->mm1, counters, c->e_local, c->max_m, 2 * I, H, stream);
+        rc = kbn_fp8_grouped_gemm_masked_ue8m0(mine + c->lay.recv_q, mine + c->lay.recv_sf, w13, w13_sf_packed, c->mm1, counters, c->e_local, c->max_m, 2 * I, H, stream);
     } else {
         rc = kbn_fp8_grouped_gemm_masked(mine + c->lay.recv_q, recv_s, c->max_m * G, G, 1, w13, w13_s, c->mm1, counters, c->e_local, c->max_m, 2 * I, H, stream);
     }
     if (rc != KBN_OK) return rc;
-    rc = silu_mul_quant_masked(c->mm1, c->e_local, c->max_m, I, c->a2_q, c->a2_s, counters, st);
+    rc = silu_mul_quant_masked(c->mm1, c->e_local, c->max_m, I, c->a2_q, c->a2_s, counters, st, ue8m0 ? c->sf2 : nullptr);
     if (rc != KBN_OK) return rc;
     if (ue8m0) {
-        rc = kbn_pack_sf_rows(c->a2_s, rows_all, I, I / 128, 1, c->sf2, stream);
-        if (rc != KBN_OK) return rc;
         rc = kbn_fp8_grouped_gemm_masked_ue8m0(c->a2_q, c->sf2, w2, w2_sf_packed, c->mm2, counters, c->e_local, c->max_m, H, I, stream);
     } else {
         rc = kbn_fp8_grouped_gemm_masked(c->a2_q, c->a2_s, c->max_m * (I / 128), I / 128, 1, w2, w2_s, c->mm2, counters, c->e_local, c->max_m, H, I, stream);
@@ -351,7 +354,7 @@ extern "C" int kbn_ep_destroy(kbn_ep_ctx* c) {
     for (int r = 0; r < c->world; ++r)
         if (r != c->rank && c->peers.base[r]) cudaIpcCloseMemHandle(c->peers.base[r]);
     cudaFree(c->sym); cudaFree(c->a_q); cudaFree(c->a_s); cudaFree(c->mm1); cudaFree(c->a2_q); cudaFree(c->a2_s);
-    cudaFree(c->mm2); cudaFree(c->sf1); cudaFree(c->sf2); cudaFree(c->identity); cudaFree(c->done); cudaFree(c->status);
+    cudaFree(c->mm2); cudaFree(c->sf2); cudaFree(c->identity); cudaFree(c->done); cudaFree(c->status);
     delete c;
     return KBN_OK;
 }

@@ -1,7 +1,7 @@
 // Block-scaled FP8 GEMM, UE8M0 fast path: when every activation and weight scale is a power of two,
 // the scales ride along as UE8M0 bytes in TMEM and the tensor core applies them itself
-// (tcgen05.mma.kind::mxf8f6f4.block_scale), so a whole 128x256 output tile accumulates in TMEM over
-// all of K and is read back once.  Same three forms (dense, expert-contiguous, masked) and the
+// (tcgen05.mma.kind::mxf8f6f4.block_scale), so a whole 128x256 (or 128x128) output tile accumulates in
+// TMEM over all of K and is read back once.  Same three forms (dense, expert-contiguous, masked) and the
 // same tile walk as the fp32-scale kernel.
 //
 //   warp 0      producer: per K-block one TMA box of A (128 B x 128 rows), one of B (128 B x 256

@@ -104,7 +104,7 @@ template <bool UE8M0, int U, bool SMEM = false>
 __device__ __forceinline__ void smq_chunk(bool valid, uint32_t row, uint32_t g0, uint32_t j, const __nv_bfloat16* __restrict__ in,
                                           uint32_t N2, int64_t ld_in, uint8_t* __restrict__ q, int64_t ld_q,
                                           float* __restrict__ scale, int64_t s_row, int64_t s_grp, float eps,
-                                          const uint16_t* __restrict__ table, uint32_t G) {
+                                          const uint16_t* __restrict__ table, uint32_t G, uint32_t* __restrict__ packed = nullptr) {
     const __nv_bfloat16* ir = in + (int64_t)row * ld_in;
     uint8_t* qr = q + (int64_t)row * ld_q;
     uint4 gv[U], uv[U];
@@ -143,7 +143,14 @@ __device__ __forceinline__ void smq_chunk(bool valid, uint32_t row, uint32_t g0,
             o.x = quant_pair_s<UE8M0>(y[0], sc, inv) | (quant_pair_s<UE8M0>(y[1], sc, inv) << 16);
             o.y = quant_pair_s<UE8M0>(y[2], sc, inv) | (quant_pair_s<UE8M0>(y[3], sc, inv) << 16);
             *reinterpret_cast<uint2*>(qr + g * 128u + j * 8u) = o;
-            if (j == 0) scale[(int64_t)row * s_row + (int64_t)g * s_grp] = sc;
+            if (j == 0) {
+                scale[(int64_t)row * s_row + (int64_t)g * s_grp] = sc;
+                // optional second copy of the scale in the packed UE8M0 form the block-scaled GEMM reads:
+                // word ((row/128)*G + g)*128 + (row%32)*4 + (row%128)/32, exponent byte repeated four times
+                if (UE8M0 && packed != nullptr)
+                    packed[((size_t)(row >> 7) * G + g) * 128u + (row & 31u) * 4u + ((row & 127u) >> 5)] =
+                        ((__float_as_uint(sc) >> 23) & 0xffu) * 0x01010101u;
+            }
         }
     }
 }
@@ -174,14 +181,22 @@ silu_mul_quant_smem_kernel(const __nv_bfloat16* __restrict__ in, uint32_t N2, in
                            const uint16_t* __restrict__ table, const int32_t* __restrict__ row_info, uint32_t G,
                            uint32_t chunks_per_row, uint32_t n_chunks) {
     extern __shared__ __align__(16) uint16_t tab[];
-    for (uint32_t i = threadIdx.x; i < 8192u; i += blockDim.x)
-        reinterpret_cast<uint4*>(tab)[i] = __ldg(reinterpret_cast<const uint4*>(table) + i);
+    // every block copies the same 128 KB; each starts at a different offset so that the SMs do not all
+    // ask L2 for the same line at the same time
+    const uint32_t rot = (blockIdx.x * 55u) & 8191u;
+    for (uint32_t i = threadIdx.x; i < 8192u; i += blockDim.x) {
+        const uint32_t k = (i + rot) & 8191u;
+        reinterpret_cast<uint4*>(tab)[k] = __ldg(reinterpret_cast<const uint4*>(table) + k);
+    }
     __syncthreads();
     const uint32_t half = (threadIdx.x >> 4) & 1u;
-    const uint32_t per_iter = gridDim.x * (blockDim.x >> 4);
-    for (uint32_t base = blockIdx.x * (blockDim.x >> 4) + (threadIdx.x >> 5) * 2u; base < n_chunks; base += per_iter) {
+    // each block takes one contiguous, equally sized range of chunks (a grid-stride loop would leave
+    // most blocks idle during the last, partly filled round)
+    const uint32_t lo = (uint32_t)(((uint64_t)n_chunks * blockIdx.x) / gridDim.x);
+    const uint32_t hi = (uint32_t)(((uint64_t)n_chunks * (blockIdx.x + 1)) / gridDim.x);
+    for (uint32_t base = lo + (threadIdx.x >> 5) * 2u; base < hi; base += (blockDim.x >> 4)) {
         const uint32_t chunk = base + half;
-        bool valid = chunk < n_chunks;
+        bool valid = chunk < hi;
         const uint32_t row = valid ? chunk / chunks_per_row : 0u;
         const uint32_t g0 = (chunk - row * chunks_per_row) * U;
         if (ROWS == 1) valid = valid && row_info[row] >= 0;
@@ -196,7 +211,7 @@ __global__ void __launch_bounds__(256)
 silu_mul_quant_masked_kernel(const __nv_bfloat16* __restrict__ in, uint32_t N2, int64_t ld_in, uint8_t* __restrict__ q,
                              int64_t ld_q, float* __restrict__ scale, int64_t s_row, int64_t s_grp, float eps,
                              const uint16_t* __restrict__ table, const int32_t* __restrict__ masked_m, uint32_t max_m,
-                             uint32_t G, uint32_t chunks_per_row) {
+                             uint32_t G, uint32_t chunks_per_row, uint32_t* __restrict__ packed) {
     const uint32_t e = blockIdx.y;
     const uint32_t cnt = (uint32_t)min(max(masked_m[e], 0), (int)max_m);
     const uint32_t n = cnt * chunks_per_row;
@@ -207,7 +222,7 @@ silu_mul_quant_masked_kernel(const __nv_bfloat16* __restrict__ in, uint32_t N2, 
         const bool valid = chunk < n;
         const uint32_t r = valid ? chunk / chunks_per_row : 0u;
         const uint32_t g0 = (chunk - r * chunks_per_row) * U;
-        smq_chunk<UE8M0, U>(valid, e * max_m + r, g0, threadIdx.x & 15u, in, N2, ld_in, q, ld_q, scale, s_row, s_grp, eps, table, G);
+        smq_chunk<UE8M0, U>(valid, e * max_m + r, g0, threadIdx.x & 15u, in, N2, ld_in, q, ld_q, scale, s_row, s_grp, eps, table, G, packed);
     }
 }
 
@@ -257,7 +272,7 @@ namespace kbn {
 
 static int launch_silu_mul_quant(const char* who, const void* in, int64_t M, int64_t N2, int64_t ld_in, void* q, int64_t ld_q,
                                  float* scale, int64_t s_row, int64_t s_grp, float eps, int ue8m0, int rows_mode,
-                                 const int32_t* row_info, int64_t max_m, cudaStream_t st) {
+                                 const int32_t* row_info, int64_t max_m, cudaStream_t st, uint32_t* packed = nullptr) {
     KBN_REQUIRE(M >= 0 && N2 >= 0, KBN_ERR_ARG, "%s: negative size", who);
     if (M == 0 || N2 == 0) return KBN_OK;
     KBN_REQUIRE(in && q && scale, KBN_ERR_ARG, "%s: null pointer", who);
@@ -282,7 +297,7 @@ static int launch_silu_mul_quant(const char* who, const void* in, int64_t M, int
                                                          row_info, (uint32_t)G, (uint32_t)cpr, (uint32_t)n_chunks)
 #define KBN_SMQ_MASKED(UE)                                                                                                \
     silu_mul_quant_masked_kernel<UE, U><<<dim3(4, (unsigned)(M / max_m)), 256, 0, st>>>(                                  \
-        ib, (uint32_t)N2, ld_in, qb, ld_q, scale, s_row, s_grp, eps, table, row_info, mm, (uint32_t)G, (uint32_t)cpr)
+        ib, (uint32_t)N2, ld_in, qb, ld_q, scale, s_row, s_grp, eps, table, row_info, mm, (uint32_t)G, (uint32_t)cpr, packed)
     // large flat inputs with power-of-two scales: persistent blocks with the exact table in shared memory
     if (rows_mode != 2 && ue8m0 && n_chunks * U >= 32768) {
         constexpr int U2 = 4;
@@ -318,9 +333,9 @@ static int launch_silu_mul_quant(const char* who, const void* in, int64_t M, int
 
 // masked layout [E, max_m, 2*N2] -> q [E, max_m, N2], row-major scales [E, max_m, N2/128]
 int silu_mul_quant_masked(const void* in, int64_t E, int64_t max_m, int64_t N2, void* q, float* scale,
-                          const int32_t* masked_m, cudaStream_t st) {
+                          const int32_t* masked_m, cudaStream_t st, void* packed_sf) {
     return launch_silu_mul_quant("silu_mul_quant_masked", in, E * max_m, N2, 2 * N2, q, N2, scale, N2 / 128, 1, 1e-10f, 1, 2,
-                                 masked_m, max_m, st);
+                                 masked_m, max_m, st, static_cast<uint32_t*>(packed_sf));
 }
 
 }  // namespace kbn
@@ -342,7 +357,7 @@ extern "C" int kbn_silu_mul_quant_1x128_rows(const void* in, int64_t M, int64_t 
 extern "C" int kbn_silu_mul_quant_1x128_masked(const void* in, int64_t E, int64_t max_m, int64_t N2, void* q, float* scale,
                                                const int32_t* masked_m, kbn_stream_t stream) {
     KBN_REQUIRE(E >= 0 && max_m > 0, KBN_ERR_ARG, "kbn_silu_mul_quant_1x128_masked: bad sizes");
-    return kbn::silu_mul_quant_masked(in, E, max_m, N2, q, scale, masked_m, static_cast<cudaStream_t>(stream));
+    return kbn::silu_mul_quant_masked(in, E, max_m, N2, q, scale, masked_m, static_cast<cudaStream_t>(stream), nullptr);
 }
 
 extern "C" int kbn_silu_bf16_table(void* out_u16, kbn_stream_t stream) {

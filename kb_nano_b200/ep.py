@@ -121,7 +121,7 @@ class EpMoe:
         if s["code"] != 0:
             raise EpStatusError(f"expert-parallel layer on rank {self.rank}: {s}")
 
-    LAUNCHES_PER_FORWARD = 11  # quant, dispatch, wait, pack, GEMM1, act-quant, pack, GEMM2, send, wait, sum
+    LAUNCHES_PER_FORWARD = 9   # quant, dispatch, wait, GEMM1, act-quant, GEMM2, send, wait, sum
 
     def close(self) -> None:
         if self._ctx:
