@@ -106,6 +106,49 @@ def test_moe_layer_vs_oracle(cuda_dev, t, h, i, e, topk, routing):
     assert_gemm_close(out2.cpu(), ref2, "moe layer, bf16 weights")
 
 
+def test_moe_grouped_gemm_candidate_golden(cuda_dev):
+    """The MoeGroupedGemm drop-in (sorted-token layout of kb-nano's Triton path) on the fixture produced by
+    the reference's MoeGroupedGemm, with and without the routed-weight multiply, and in the one-row-per-block
+    form (sorted_token_ids=None)."""
+    import importlib.util, os, sys
+    from kb_nano_b200 import candidate_dir
+    spec = importlib.util.spec_from_file_location("_candidate_impl_L1_moe_grouped_gemm", os.path.join(candidate_dir(), "L1", "moe_grouped_gemm.py"))
+    mod = importlib.util.module_from_spec(spec); sys.modules[spec.name] = mod; spec.loader.exec_module(mod)
+    g = golden("grouped_gemm")
+    d = cuda_dev
+    a_q, a_s = fp8_from_bits(g["a_q"]).to(d), torch.from_numpy(g["a_s"]).to(d)
+    b_q, b_s = fp8_from_bits(g["b_q"]).to(d), torch.from_numpy(g["b_s"]).to(d)
+    tw = torch.from_numpy(g["topk_w"]).to(d)
+    sorted_ids, blk = torch.from_numpy(g["sorted_ids"]).to(d), torch.from_numpy(g["blk_experts"]).to(d)
+    t, topk = g["topk_ids"].shape
+    ntpp = torch.tensor([sorted_ids.numel()], dtype=torch.int32, device=d)
+    ref = bf16_from_bits(g["c"])
+    gg = mod.MoeGroupedGemm()
+    c = torch.full((t * topk, b_q.shape[1]), 3.0, dtype=torch.bfloat16, device=d)
+    a0 = a_q.clone()
+    gg(a_q, b_q, c, tw, sorted_ids, blk, ntpp, False, topk, config={"BLOCK_SIZE_M": 16}, a_scale=a_s, b_scale=b_s,
+       use_fp8_w8a8=True, block_shape=[128, 128])
+    assert_gemm_close(c.cpu(), ref, "MoeGroupedGemm golden")
+    assert bool((a_q.view(torch.uint8) == a0.view(torch.uint8)).all())
+    c2 = torch.zeros_like(c)
+    gg(a_q, b_q, c2, tw, sorted_ids, blk, ntpp, True, topk, config={"BLOCK_SIZE_M": 16}, a_scale=a_s, b_scale=b_s,
+       use_fp8_w8a8=True, block_shape=[128, 128])
+    assert_gemm_close(c2.cpu(), (ref.float() * torch.from_numpy(g["topk_w"]).reshape(-1, 1)).to(torch.bfloat16), "MoeGroupedGemm x routed weight")
+    # naive block assignment: block i = row i, expert_ids has one entry per row
+    c3 = torch.zeros_like(c)
+    gg(a_q, b_q, c3, tw, None, torch.from_numpy(g["topk_ids"]).reshape(-1).to(d), ntpp, False, topk, config={"BLOCK_SIZE_M": 16},
+       a_scale=a_s, b_scale=b_s, use_fp8_w8a8=True, block_shape=[128, 128])
+    assert_gemm_close(c3.cpu(), ref, "MoeGroupedGemm naive")
+    # weight scales that are not powers of two take the fp32-scale kernels
+    b_s2 = b_s * 1.3
+    c4 = torch.zeros_like(c)
+    gg(a_q, b_q, c4, tw, sorted_ids, blk, ntpp, False, topk, config={"BLOCK_SIZE_M": 16}, a_scale=a_s, b_scale=b_s2,
+       use_fp8_w8a8=True, block_shape=[128, 128])
+    assert_gemm_close(c4.cpu(), (ref.float() * 1.3).to(torch.bfloat16), "MoeGroupedGemm, arbitrary weight scales")
+    with pytest.raises(NotImplementedError):
+        gg(a_q.float(), b_q, c, tw, sorted_ids, blk, ntpp, False, topk)
+
+
 def test_fused_experts_candidate_golden(cuda_dev):
     """The FusedExperts drop-in class on the reference-generated fixture."""
     import importlib.util, os, sys
