@@ -72,6 +72,24 @@ int kbn_silu_mul_quant_1x128_rows(const void* in, int64_t M, int64_t N2, int64_t
 int kbn_silu_mul_quant_1x128_masked(const void* in, int64_t E, int64_t max_m, int64_t N2, void* q,
                                     float* scale, const int32_t* masked_m, kbn_stream_t stream);
 
+/*
+ * Fused RMSNorm + 1x128 quantisation, and its residual-add form: the producer of the activations the FP8
+ * linears consume.  Stand behind torch.ops.kb_nano_norm.rmsnorm_fp8_quant / fused_add_rmsnorm_fp8_quant
+ * (tasks/baseline/L1/rmsnorm_quant.py:25-57,63-132; kernels tasks/baseline/L1/csrc/rmsnorm_quant.cu:22-97,125-204).
+ *   x [M,H] bf16, weight [H] bf16; q [M,H] fp8; scale element (m,g) at scale[m*s_row + g*s_grp], UE8M0,
+ *   absmax clamp 1e-10.  H % 8 == 0, H <= 16384.
+ *   add form: residual <- bf16(residual + x) (fp32 sum), the norm is taken of that rounded row, and
+ *   x <- bf16(normalised row); both are modified in place like the reference.
+ * Floating-point kernel: results match the reference's arithmetic up to the summation order of the
+ * squares (tolerance: the harness's FP8 pair rule, bench/kernels/runner.py:265-291).
+ */
+int kbn_rmsnorm_quant_1x128(const void* x, const void* weight, int64_t M, int64_t H, int64_t ld_x,
+                            void* q, int64_t ld_q, float* scale, int64_t s_row, int64_t s_grp,
+                            float eps, kbn_stream_t stream);
+int kbn_add_rmsnorm_quant_1x128(void* x, void* residual, const void* weight, int64_t M, int64_t H,
+                                int64_t ld_x, int64_t ld_res, void* q, int64_t ld_q, float* scale,
+                                int64_t s_row, int64_t s_grp, float eps, kbn_stream_t stream);
+
 /* silu(gate)->bf16 for all 65536 gate bit patterns, as the kernel above computes it
  * (out: 65536 x uint16 on the device).  Used by the exhaustive parity test. */
 int kbn_silu_bf16_table(void* out_u16, kbn_stream_t stream);

@@ -21,6 +21,8 @@ SIGNATURES = {
     "kbn_quant_1x128": (_i32, [_ptr, _i64, _i64, _i64, _ptr, _i64, _ptr, _i64, _i64, _f32, _i32, _ptr]),
     "kbn_silu_mul_quant_1x128": (_i32, [_ptr, _i64, _i64, _i64, _ptr, _i64, _ptr, _i64, _i64, _f32, _i32, _ptr]),
     "kbn_silu_bf16_table": (_i32, [_ptr, _ptr]),
+    "kbn_rmsnorm_quant_1x128": (_i32, [_ptr, _ptr, _i64, _i64, _i64, _ptr, _i64, _ptr, _i64, _i64, _f32, _ptr]),
+    "kbn_add_rmsnorm_quant_1x128": (_i32, [_ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _ptr, _i64, _ptr, _i64, _i64, _f32, _ptr]),
     "kbn_silu_mul_quant_1x128_rows": (_i32, [_ptr, _i64, _i64, _i64, _ptr, _i64, _ptr, _i64, _i64, _f32, _i32, _ptr, _ptr]),
     "kbn_silu_mul_quant_1x128_masked": (_i32, [_ptr, _i64, _i64, _i64, _ptr, _ptr, _ptr, _ptr]),
     "kbn_fp8_gemm_nt": (_i32, [_ptr, _ptr, _i64, _i64, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _ptr]),

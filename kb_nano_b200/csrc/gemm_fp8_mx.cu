@@ -104,14 +104,8 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                 const int32_t b_row = tile.expert * p.N + tile.n_blk * kBN;
                 const uint8_t* sfa = x.sfa + (int64_t)(tile.row0 / kBlockM) * KB * kSfaBytes;
                 const uint8_t* sfb = x.sfb + (((int64_t)tile.expert * KB) * x.nb_pad + (BN / 128) * tile.n_blk) * (int64_t)kSfaBytes;
-                // The shared-memory ring holds kStages K-blocks; the weights of the next kPrefetch K-blocks
-                // beyond it are asked into L2 early, so that HBM latency is covered by more than the ring.
-                constexpr int kPrefetch = 8;
-                for (int pf = kStages; pf < kStages + kPrefetch && pf < KB; ++pf)
-                    ptx::tma_prefetch_l2_2d(&tmB, pf * kBlockK, b_row);
                 for (int kb = 0; kb < KB; ++kb, ++it) {
                     const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
-                    if (kb + kStages + kPrefetch < KB) ptx::tma_prefetch_l2_2d(&tmB, (kb + kStages + kPrefetch) * kBlockK, b_row);
                     if (!wait_bar(bar_empty + 8 * s, ph ^ 1u, w)) { ok = false; break; }
                     const uint32_t bar = bar_full + 8 * s;
                     ptx::mbar_arrive_expect_tx(bar, kTxBytes);

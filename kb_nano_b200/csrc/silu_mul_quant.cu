@@ -199,7 +199,10 @@ silu_mul_quant_smem_kernel(const __nv_bfloat16* __restrict__ in, uint32_t N2, in
         bool valid = chunk < hi;
         const uint32_t row = valid ? chunk / chunks_per_row : 0u;
         const uint32_t g0 = (chunk - row * chunks_per_row) * U;
-        if (ROWS == 1) valid = valid && row_info[row] >= 0;
+        if (ROWS == 1) {
+            valid = valid && row_info[row] >= 0;
+            if (!__any_sync(0xffffffffu, valid)) continue;      // both chunks of this warp are padding rows
+        }
         smq_chunk<UE8M0, U, true>(valid, row, g0, threadIdx.x & 15u, in, N2, ld_in, q, ld_q, scale, s_row, s_grp, eps, tab, G);
     }
 }

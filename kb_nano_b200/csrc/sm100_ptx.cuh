@@ -46,12 +46,6 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int3
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(x), "r"(y)
         : "memory");
 }
-// Hint: bring one box of the tensor from HBM into L2 (no shared-memory destination, no barrier).
-__device__ __forceinline__ void tma_prefetch_l2_2d(const void* tmap, int32_t x, int32_t y) {
-    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
-                 ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(x), "r"(y)
-                 : "memory");
-}
 __device__ __forceinline__ void prefetch_tensormap(const void* tmap) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");
 }

@@ -366,3 +366,31 @@ def fp8_gemm_nt_auto(a_q: torch.Tensor, a_s: torch.Tensor, b_q: torch.Tensor, b_
         fp8_gemm_nt_ue8m0(a_q, pack_sf_rows(a_s, k), b_q, packed, out)
     else:
         fp8_gemm_nt(a_q, a_s, b_q, b_s, out)
+
+
+def rmsnorm_quant_fp8(x: torch.Tensor, weight: torch.Tensor, out_fp8: torch.Tensor, out_scale: torch.Tensor, eps: float = 1e-6,
+                      residual: torch.Tensor | None = None) -> None:
+    """RMSNorm(x) * weight quantised 1x128 (UE8M0) into out_fp8 / out_scale.  With `residual`: residual += x
+    (rounded to bf16) first, the norm is taken of the new residual, and x is overwritten with the normalised row."""
+    tensors = [x, weight, out_fp8, out_scale] + ([residual] if residual is not None else [])
+    dev = _cuda(*tensors)
+    if x.dim() != 2 or x.dtype != torch.bfloat16 or x.stride(1) != 1:
+        raise ValueError("x must be bf16 [M,H], contiguous along H")
+    m, h = x.shape
+    if weight.dtype != torch.bfloat16 or weight.numel() != h or not weight.is_contiguous():
+        raise ValueError("weight must be contiguous bf16 [H]")
+    if out_fp8.dtype != FP8 or tuple(out_fp8.shape) != (m, h) or out_fp8.stride(1) != 1:
+        raise ValueError("out_fp8 must be float8_e4m3fn [M,H], contiguous along H")
+    s_row, s_grp = _scale_strides(out_scale, m, (h + GROUP - 1) // GROUP)
+    lib = _lib.load()
+    with _on(dev):
+        if residual is None:
+            _lib.check(lib.kbn_rmsnorm_quant_1x128(x.data_ptr(), weight.data_ptr(), m, h, x.stride(0) if m > 1 else h, out_fp8.data_ptr(),
+                                                   out_fp8.stride(0) if m > 1 else h, out_scale.data_ptr(), s_row, s_grp, eps, _stream(x)))
+        else:
+            if residual.dtype != torch.bfloat16 or tuple(residual.shape) != (m, h) or residual.stride(1) != 1:
+                raise ValueError("residual must be bf16 [M,H], contiguous along H")
+            _lib.check(lib.kbn_add_rmsnorm_quant_1x128(x.data_ptr(), residual.data_ptr(), weight.data_ptr(), m, h,
+                                                       x.stride(0) if m > 1 else h, residual.stride(0) if m > 1 else h,
+                                                       out_fp8.data_ptr(), out_fp8.stride(0) if m > 1 else h, out_scale.data_ptr(),
+                                                       s_row, s_grp, eps, _stream(x)))

@@ -16,6 +16,8 @@ Reference lines each function follows (paths relative to the kb-nano tree):
   grouped_gemm_masked   same arithmetic in the [E, max_m, K] layout (no reference call site)
   route_sigmoid_topk    tasks/baseline/L1/grouped_topk.py:119-174 with n_group=1, no bias
   route_softmax_topk    tasks/reference/L1/topk_softmax.py:46-52
+  rmsnorm_quant         tasks/baseline/L1/csrc/rmsnorm_quant.cu:22-97,125-204 (fp32 arithmetic of the CUDA
+                        kernel; there is no torch reference of the fused op in the tree)
   moe_layer             tasks/baseline/L2/fused_experts.py:246-283,119-136
                         (quant -> GEMM1 -> silu*up+quant -> GEMM2 -> weighted sum over top-k
                         in the activation dtype)
@@ -167,3 +169,20 @@ def moe_layer(x, w13_q, w13_s, w2_q, w2_s, topk_w, topk_ids, experts=None) -> to
         acc[tok, slot] = h2
     # dtype promotion as in the reference: bf16 rows times the router's weights (fp32 or bf16)
     return (acc * topk_w.unsqueeze(-1)).sum(dim=1).to(x.dtype)
+
+
+def rmsnorm_quant(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6, residual: torch.Tensor | None = None):
+    """(q, scale[, new_residual, normalised_x]) of the fused (add +) RMSNorm + 1x128 quant."""
+    if residual is not None:
+        s = residual.float() + x.float()
+        row = s.to(torch.bfloat16)
+        sum_sq = (s * s).sum(dim=-1, keepdim=True)
+    else:
+        row = x
+        sum_sq = (x.float() * x.float()).sum(dim=-1, keepdim=True)
+    rms_inv = torch.rsqrt(sum_sq / x.shape[-1] + eps)
+    v = (row.float() * rms_inv) * weight.float()
+    q, sc = quant_1x128(v)
+    if residual is not None:
+        return q, sc, row, v.to(torch.bfloat16)
+    return q, sc
