@@ -63,12 +63,18 @@ int kbn_silu_mul_quant_1x128(const void* in, int64_t M, int64_t N2, int64_t ld_i
 /* Same kernel restricted to the rows that hold data, for the two grouped-GEMM layouts (the rows it
  * skips are neither read nor written):
  *   _rows:   expert-contiguous layout, row m is processed iff row_expert[m] >= 0;
+ *   _list:   only the rows named in row_list[0..n_list) (entries < 0 skipped); each listed row is read and
+ *            written at its own index.  The MoE layer passes the destination rows of its (token, slot) pairs,
+ *            which spreads the work evenly however the rows are grouped;
  *   _masked: in [E, max_m, 2*N2] -> q [E, max_m, N2], row-major scales [E, max_m, N2/128], UE8M0,
  *            eps 1e-10; row (e, m) is processed iff m < masked_m[e].
  * kb-nano runs its kernel over every row of the padded buffer (tasks/baseline/L2/fused_experts.py:269-274). */
 int kbn_silu_mul_quant_1x128_rows(const void* in, int64_t M, int64_t N2, int64_t ld_in, void* q,
                                   int64_t ld_q, float* scale, int64_t s_row, int64_t s_grp, float eps,
                                   int ue8m0, const int32_t* row_expert, kbn_stream_t stream);
+int kbn_silu_mul_quant_1x128_list(const void* in, int64_t N2, int64_t ld_in, void* q, int64_t ld_q,
+                                  float* scale, int64_t s_row, int64_t s_grp, float eps, int ue8m0,
+                                  const int32_t* row_list, int64_t n_list, kbn_stream_t stream);
 int kbn_silu_mul_quant_1x128_masked(const void* in, int64_t E, int64_t max_m, int64_t N2, void* q,
                                     float* scale, const int32_t* masked_m, kbn_stream_t stream);
 
@@ -162,6 +168,18 @@ int kbn_fp8_grouped_gemm_masked_ue8m0(const void* A, const void* sfa_packed, con
                                       const void* sfb_packed, void* C, const int32_t* masked_m,
                                       int64_t E, int64_t max_m, int64_t N, int64_t K,
                                       kbn_stream_t stream);
+
+/*
+ * Load-time re-quantisation of block-scaled FP8 weights to power-of-two scales, in place:
+ * per 128x128 block  w = fp32(w_fp8) * scale,  scale <- 2^ceil(log2(max(max|w|, eps) / 448)),
+ * w_fp8 <- e4m3(w / scale).  w_fp8 [E,N,K] (E = 1 for a dense weight), scale fp32 [E, ceil(N/128), ceil(K/128)].
+ * Stands behind the dequantise -> deep_gemm.per_block_cast_to_fp8(use_ue8m0=True) step of
+ * postprocess_fp8_weights / postprocess_fp8_weights_batched (tasks/baseline/L1/fp8_linear.py:453-554);
+ * DeepGEMM (v2.1.1.post3, not in the kb-nano tree) clamps the block maximum at 1e-4: pass that as eps
+ * to follow it.  After this call kbn_pack_sf_weights gives the layout the UE8M0 GEMMs read.
+ */
+int kbn_requant_weights_ue8m0(void* w_fp8, float* scale, int64_t E, int64_t N, int64_t K, float eps,
+                              kbn_stream_t stream);
 
 /* Device status word of the GEMM kernels' bounded waits: 0 = no wait ever ran out in this
  * process.  Host pointer out; synchronises `stream` first. */

@@ -24,11 +24,13 @@ SIGNATURES = {
     "kbn_rmsnorm_quant_1x128": (_i32, [_ptr, _ptr, _i64, _i64, _i64, _ptr, _i64, _ptr, _i64, _i64, _f32, _ptr]),
     "kbn_add_rmsnorm_quant_1x128": (_i32, [_ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _ptr, _i64, _ptr, _i64, _i64, _f32, _ptr]),
     "kbn_silu_mul_quant_1x128_rows": (_i32, [_ptr, _i64, _i64, _i64, _ptr, _i64, _ptr, _i64, _i64, _f32, _i32, _ptr, _ptr]),
+    "kbn_silu_mul_quant_1x128_list": (_i32, [_ptr, _i64, _i64, _ptr, _i64, _ptr, _i64, _i64, _f32, _i32, _ptr, _i64, _ptr]),
     "kbn_silu_mul_quant_1x128_masked": (_i32, [_ptr, _i64, _i64, _i64, _ptr, _ptr, _ptr, _ptr]),
     "kbn_fp8_gemm_nt": (_i32, [_ptr, _ptr, _i64, _i64, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _ptr]),
     "kbn_fp8_grouped_gemm_contig": (_i32, [_ptr, _ptr, _i64, _i64, _ptr, _ptr, _ptr, _i64, _ptr, _i64, _i64, _i64, _i64, _ptr]),
     "kbn_fp8_grouped_gemm_masked": (_i32, [_ptr, _ptr, _i64, _i64, _i64, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _ptr]),
     "kbn_gemm_status": (_i32, [_ptr, _ptr]),
+    "kbn_requant_weights_ue8m0": (_i32, [_ptr, _ptr, _i64, _i64, _i64, _f32, _ptr]),
     "kbn_packed_sf_rows_bytes": (_i64, [_i64, _i64]),
     "kbn_packed_sf_weights_bytes": (_i64, [_i64, _i64, _i64]),
     "kbn_pack_sf_rows": (_i32, [_ptr, _i64, _i64, _i64, _i64, _ptr, _ptr]),

@@ -42,6 +42,32 @@ def unpack_ue8m0_packed_scales(sf: torch.Tensor, N: int, K: int) -> torch.Tensor
     return torch.pow(2.0, (exps - 127).float())
 
 
+def postprocess_fp8_weights(weight_fp8: torch.Tensor, scale_inv: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """Load-time step of the same name in the baseline (tasks/baseline/L1/fp8_linear.py:453-512): re-quantise
+    a checkpoint's block-scaled FP8 weight to power-of-two scales.  Returns (new weight, fp32 scales
+    [ceil(N/128), ceil(K/128)]) -- the layout this file's Fp8Linear reads; no DeepGEMM layout transform is
+    needed (the packed form the tensor core reads is built once per weight inside the GEMM call path)."""
+    N, K = weight_fp8.shape
+    w = weight_fp8.clone() if weight_fp8.is_contiguous() else weight_fp8.contiguous()
+    s = scale_inv[: math.ceil(N / _GROUP), : math.ceil(K / _GROUP)].to(torch.float32).contiguous().clone()
+    ops.requant_weights_ue8m0(w, s)
+    return w, s
+
+
+def postprocess_fp8_weights_batched(weight_fp8: torch.Tensor, scale_inv: torch.Tensor) -> None:
+    """In-place form for 3-D MoE weights [E,N,K] (tasks/baseline/L1/fp8_linear.py:515-554)."""
+    assert weight_fp8.ndim == 3
+    E, N, K = weight_fp8.shape
+    s = scale_inv[:, : math.ceil(N / _GROUP), : math.ceil(K / _GROUP)]
+    if s.is_contiguous() and s.dtype == torch.float32 and weight_fp8.is_contiguous():
+        ops.requant_weights_ue8m0(weight_fp8, s)
+    else:
+        w, s2 = weight_fp8.contiguous(), s.to(torch.float32).contiguous()
+        ops.requant_weights_ue8m0(w, s2)
+        weight_fp8.copy_(w)
+        s.copy_(s2)
+
+
 class _Fp8PrefillBufs:
     __slots__ = ("a", "s", "o")
 

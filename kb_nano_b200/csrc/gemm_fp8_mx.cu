@@ -180,32 +180,38 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             const int32_t n0 = tile.n_blk * kBN + half * kHalfCols;
             __nv_bfloat16* crow = p.C + (int64_t)row * p.ldc + n0;
             const bool vec_ok = (reinterpret_cast<uintptr_t>(crow) & 15u) == 0;
+            // Drain first, convert later: all of this warp's columns go to registers with back-to-back TMEM
+            // loads, the accumulator is handed back to the MMA warp at once, and the bf16 conversion and the
+            // global stores overlap the next tile's MMAs.
+            constexpr int kChunks = kHalfCols / 32;
+            uint32_t r[kChunks][32];
 #pragma unroll
-            for (int c = 0; c < kHalfCols / 32; ++c) {
-                uint32_t r[32];
-                ptx::tmem_ld_32x32(taddr + 32 * c, r);
-                ptx::tmem_ld_wait(r);
-                if (row_ok) {
+            for (int c = 0; c < kChunks; ++c) ptx::tmem_ld_32x32(taddr + 32 * c, r[c]);
+#pragma unroll
+            for (int c = 0; c < kChunks; ++c) ptx::tmem_ld_wait(r[c]);
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(bar_tempty);
+            if (row_ok) {
+#pragma unroll
+                for (int c = 0; c < kChunks; ++c) {
                     if (n0 + 32 * c + 32 <= p.N && vec_ok) {
 #pragma unroll
                         for (int j = 0; j < 32; j += 8) {
                             uint4 v;
-                            v.x = pack_bf16x2(__uint_as_float(r[j + 0]), __uint_as_float(r[j + 1]));
-                            v.y = pack_bf16x2(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-                            v.z = pack_bf16x2(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
-                            v.w = pack_bf16x2(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
+                            v.x = pack_bf16x2(__uint_as_float(r[c][j + 0]), __uint_as_float(r[c][j + 1]));
+                            v.y = pack_bf16x2(__uint_as_float(r[c][j + 2]), __uint_as_float(r[c][j + 3]));
+                            v.z = pack_bf16x2(__uint_as_float(r[c][j + 4]), __uint_as_float(r[c][j + 5]));
+                            v.w = pack_bf16x2(__uint_as_float(r[c][j + 6]), __uint_as_float(r[c][j + 7]));
                             *reinterpret_cast<uint4*>(crow + 32 * c + j) = v;
                         }
                     } else {
 #pragma unroll
                         for (int j = 0; j < 32; ++j)
-                            if (n0 + 32 * c + j < p.N) crow[32 * c + j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+                            if (n0 + 32 * c + j < p.N) crow[32 * c + j] = __float2bfloat16_rn(__uint_as_float(r[c][j]));
                     }
                 }
             }
-            ptx::tc_fence_before();
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(bar_tempty);
             ++tile_it;
         }
     }

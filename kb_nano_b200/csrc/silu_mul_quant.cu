@@ -156,7 +156,8 @@ __device__ __forceinline__ void smq_chunk(bool valid, uint32_t row, uint32_t g0,
 }
 
 // Flat grid: chunk index -> (row, first group) with one 32-bit division per thread.
-// ROWS: 0 = every row; 1 = rows with row_info[m] >= 0 (expert-contiguous layout, -1 marks padding).
+// ROWS: 0 = every row; 1 = rows with row_info[m] >= 0 (expert-contiguous layout, -1 marks padding);
+// 3 = the rows listed in row_info[0..M) (entries < 0 skipped).
 template <bool UE8M0, int U, int ROWS>
 __global__ void __launch_bounds__(256)
 silu_mul_quant_kernel(const __nv_bfloat16* __restrict__ in, uint32_t N2, int64_t ld_in, uint8_t* __restrict__ q,
@@ -167,8 +168,14 @@ silu_mul_quant_kernel(const __nv_bfloat16* __restrict__ in, uint32_t N2, int64_t
     bool valid = chunk < n_chunks;
     const uint32_t row = valid ? chunk / chunks_per_row : 0u;
     const uint32_t g0 = (chunk - row * chunks_per_row) * U;
+    uint32_t out_row = row;
     if (ROWS == 1) valid = valid && row_info[row] >= 0;
-    smq_chunk<UE8M0, U>(valid, row, g0, threadIdx.x & 15u, in, N2, ld_in, q, ld_q, scale, s_row, s_grp, eps, table, G);
+    if (ROWS == 3) {                      // `row` indexes a list of rows to process
+        const int32_t r = valid ? row_info[row] : -1;
+        valid = r >= 0;
+        out_row = valid ? (uint32_t)r : 0u;
+    }
+    smq_chunk<UE8M0, U>(valid, out_row, g0, threadIdx.x & 15u, in, N2, ld_in, q, ld_q, scale, s_row, s_grp, eps, table, G);
 }
 
 // Large inputs: one persistent block of 1024 threads per SM keeps the whole 128 KB exact table in
@@ -194,14 +201,23 @@ silu_mul_quant_smem_kernel(const __nv_bfloat16* __restrict__ in, uint32_t N2, in
     // most blocks idle during the last, partly filled round)
     const uint32_t lo = (uint32_t)(((uint64_t)n_chunks * blockIdx.x) / gridDim.x);
     const uint32_t hi = (uint32_t)(((uint64_t)n_chunks * (blockIdx.x + 1)) / gridDim.x);
-    for (uint32_t base = lo + (threadIdx.x >> 5) * 2u; base < hi; base += (blockDim.x >> 4)) {
+    // the row's validity word is fetched one iteration ahead, so its latency is not added to the data loads
+    const uint32_t step = blockDim.x >> 4;
+    uint32_t base = lo + (threadIdx.x >> 5) * 2u;
+    int32_t info_next = 0;
+    if (ROWS != 0) info_next = (base + half < hi) ? row_info[(base + half) / chunks_per_row] : -1;
+    for (; base < hi; base += step) {
         const uint32_t chunk = base + half;
         bool valid = chunk < hi;
-        const uint32_t row = valid ? chunk / chunks_per_row : 0u;
+        uint32_t row = valid ? chunk / chunks_per_row : 0u;
         const uint32_t g0 = (chunk - row * chunks_per_row) * U;
-        if (ROWS == 1) {
-            valid = valid && row_info[row] >= 0;
-            if (!__any_sync(0xffffffffu, valid)) continue;      // both chunks of this warp are padding rows
+        if (ROWS != 0) {
+            const int32_t info = info_next;
+            const uint32_t nc = chunk + step;
+            info_next = nc < hi ? row_info[nc / chunks_per_row] : -1;
+            valid = valid && info >= 0;
+            if (ROWS == 3) row = valid ? (uint32_t)info : 0u;   // list entry = the row to process
+            if (!__any_sync(0xffffffffu, valid)) continue;      // nothing to do for either chunk of this warp
         }
         smq_chunk<UE8M0, U, true>(valid, row, g0, threadIdx.x & 15u, in, N2, ld_in, q, ld_q, scale, s_row, s_grp, eps, tab, G);
     }
@@ -311,22 +327,26 @@ static int launch_silu_mul_quant(const char* who, const void* in, int64_t M, int
         if (dev >= 0 && dev < 64 && !attr_set[dev]) {
             KBN_CUDA(cudaFuncSetAttribute(silu_mul_quant_smem_kernel<true, U2, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 131072));
             KBN_CUDA(cudaFuncSetAttribute(silu_mul_quant_smem_kernel<true, U2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 131072));
+            KBN_CUDA(cudaFuncSetAttribute(silu_mul_quant_smem_kernel<true, U2, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 131072));
             attr_set[dev] = 1;
         }
         const unsigned grid = (unsigned)sm_count();
         if (rows_mode == 0)
             silu_mul_quant_smem_kernel<true, U2, 0><<<grid, 1024, 131072, st>>>(ib, (uint32_t)N2, ld_in, qb, ld_q, scale, s_row, s_grp, eps, table,
                                                                                row_info, (uint32_t)G, (uint32_t)cpr2, (uint32_t)n2c);
-        else
+        else if (rows_mode == 1)
             silu_mul_quant_smem_kernel<true, U2, 1><<<grid, 1024, 131072, st>>>(ib, (uint32_t)N2, ld_in, qb, ld_q, scale, s_row, s_grp, eps, table,
+                                                                               row_info, (uint32_t)G, (uint32_t)cpr2, (uint32_t)n2c);
+        else
+            silu_mul_quant_smem_kernel<true, U2, 3><<<grid, 1024, 131072, st>>>(ib, (uint32_t)N2, ld_in, qb, ld_q, scale, s_row, s_grp, eps, table,
                                                                                row_info, (uint32_t)G, (uint32_t)cpr2, (uint32_t)n2c);
     } else if (rows_mode == 2) {
         KBN_REQUIRE(M / max_m <= 65535, KBN_ERR_ARG, "%s: more than 65535 experts", who);
         if (ue8m0) KBN_SMQ_MASKED(true); else KBN_SMQ_MASKED(false);
     } else if (ue8m0) {
-        if (rows_mode == 0) KBN_SMQ(true, 0); else KBN_SMQ(true, 1);
+        if (rows_mode == 0) KBN_SMQ(true, 0); else if (rows_mode == 1) KBN_SMQ(true, 1); else KBN_SMQ(true, 3);
     } else {
-        if (rows_mode == 0) KBN_SMQ(false, 0); else KBN_SMQ(false, 1);
+        if (rows_mode == 0) KBN_SMQ(false, 0); else if (rows_mode == 1) KBN_SMQ(false, 1); else KBN_SMQ(false, 3);
     }
 #undef KBN_SMQ
 #undef KBN_SMQ_MASKED
@@ -355,6 +375,13 @@ extern "C" int kbn_silu_mul_quant_1x128_rows(const void* in, int64_t M, int64_t 
                                              int ue8m0, const int32_t* row_expert, kbn_stream_t stream) {
     return kbn::launch_silu_mul_quant("kbn_silu_mul_quant_1x128_rows", in, M, N2, ld_in, q, ld_q, scale, s_row, s_grp, eps, ue8m0, 1,
                                       row_expert, 1, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int kbn_silu_mul_quant_1x128_list(const void* in, int64_t N2, int64_t ld_in, void* q, int64_t ld_q, float* scale,
+                                             int64_t s_row, int64_t s_grp, float eps, int ue8m0, const int32_t* row_list,
+                                             int64_t n_list, kbn_stream_t stream) {
+    return kbn::launch_silu_mul_quant("kbn_silu_mul_quant_1x128_list", in, n_list, N2, ld_in, q, ld_q, scale, s_row, s_grp, eps, ue8m0, 3,
+                                      row_list, 1, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int kbn_silu_mul_quant_1x128_masked(const void* in, int64_t E, int64_t max_m, int64_t N2, void* q, float* scale,

@@ -81,11 +81,11 @@ def fused_experts_fp8(hidden_states: torch.Tensor, w13: torch.Tensor, w2: torch.
     p2 = ops.packed_weight_scales(w2_scale, h, i) if use_ue8m0 else None
     if p13 is not None and p2 is not None:
         ops.m_grouped_fp8_gemm_nt_contiguous_ue8m0(sc.a_perm, ops.pack_sf_rows(sc.a_s_perm, h), w13, p13, mm1, sc.row_expert)
-        ops.silu_mul_quant_fp8_rows(mm1, sc.a2_q, sc.a2_s, sc.row_expert)
+        ops.silu_mul_quant_fp8_list(mm1, sc.a2_q, sc.a2_s, sc.dest_row.view(-1))
         ops.m_grouped_fp8_gemm_nt_contiguous_ue8m0(sc.a2_q, ops.pack_sf_rows(sc.a2_s, i), w2, p2, mm2, sc.row_expert)
     else:
         ops.m_grouped_fp8_gemm_nt_contiguous(sc.a_perm, sc.a_s_perm, w13, w13_scale, mm1, sc.row_expert)
-        ops.silu_mul_quant_fp8_rows(mm1, sc.a2_q, sc.a2_s, sc.row_expert)
+        ops.silu_mul_quant_fp8_list(mm1, sc.a2_q, sc.a2_s, sc.dest_row.view(-1))
         ops.m_grouped_fp8_gemm_nt_contiguous(sc.a2_q, sc.a2_s, w2, w2_scale, mm2, sc.row_expert)
     ops.moe_unpermute_combine(mm2, sc.dest_row, w, out)
     return out

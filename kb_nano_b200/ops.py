@@ -109,6 +109,25 @@ def silu_mul_quant_fp8_rows(inp: torch.Tensor, out_fp8: torch.Tensor, out_scale:
                                                              row_expert.data_ptr(), _stream(inp)))
 
 
+def silu_mul_quant_fp8_list(inp: torch.Tensor, out_fp8: torch.Tensor, out_scale: torch.Tensor, row_list: torch.Tensor,
+                            use_ue8m0: bool = True, eps: float = 1e-10) -> None:
+    """As silu_mul_quant_fp8, but only the rows listed in row_list (int32, entries < 0 skipped) are processed."""
+    dev = _cuda(inp, out_fp8, out_scale, row_list)
+    m, n = inp.shape
+    n2 = n // 2
+    if inp.dtype != torch.bfloat16 or inp.stride(1) != 1 or n % 2 or n2 % GROUP:
+        raise ValueError("inp must be bf16 [M, 2*N2] with N2 a multiple of 128, contiguous along the last dim")
+    if out_fp8.dtype != FP8 or tuple(out_fp8.shape) != (m, n2) or out_fp8.stride(1) != 1:
+        raise ValueError("out_fp8 must be float8_e4m3fn [M, N2], contiguous along the last dim")
+    if row_list.dtype != torch.int32 or not row_list.is_contiguous():
+        raise ValueError("row_list must be contiguous int32")
+    s_row, s_grp = _scale_strides(out_scale, m, n2 // GROUP)
+    with _on(dev):
+        _lib.check(_lib.load().kbn_silu_mul_quant_1x128_list(inp.data_ptr(), n2, inp.stride(0) if m > 1 else n, out_fp8.data_ptr(),
+                                                             out_fp8.stride(0) if m > 1 else n2, out_scale.data_ptr(), s_row, s_grp,
+                                                             eps, int(use_ue8m0), row_list.data_ptr(), row_list.numel(), _stream(inp)))
+
+
 def silu_mul_quant_fp8_masked(inp: torch.Tensor, out_fp8: torch.Tensor, out_scale: torch.Tensor, masked_m: torch.Tensor) -> None:
     """Masked layout: inp bf16 [E,max_m,2*N2] -> out_fp8 [E,max_m,N2], out_scale fp32 [E,max_m,N2/128]
     (all contiguous); only rows m < masked_m[e] are processed."""
@@ -394,3 +413,21 @@ def rmsnorm_quant_fp8(x: torch.Tensor, weight: torch.Tensor, out_fp8: torch.Tens
                                                        x.stride(0) if m > 1 else h, residual.stride(0) if m > 1 else h,
                                                        out_fp8.data_ptr(), out_fp8.stride(0) if m > 1 else h, out_scale.data_ptr(),
                                                        s_row, s_grp, eps, _stream(x)))
+
+
+def requant_weights_ue8m0(w_fp8: torch.Tensor, scale: torch.Tensor, eps: float = 1e-4) -> None:
+    """In place: block-scaled FP8 weights [N,K] or [E,N,K] with fp32 128x128 scales -> the same weights
+    re-quantised to power-of-two scales (load-time step; afterwards the UE8M0 GEMM path applies)."""
+    dev = _cuda(w_fp8, scale)
+    if w_fp8.dtype != FP8 or not w_fp8.is_contiguous() or w_fp8.dim() not in (2, 3):
+        raise ValueError("w_fp8 must be contiguous float8_e4m3fn [N,K] or [E,N,K]")
+    e = w_fp8.shape[0] if w_fp8.dim() == 3 else 1
+    n, k = w_fp8.shape[-2], w_fp8.shape[-1]
+    want = ((e,) if w_fp8.dim() == 3 else ()) + ((n + 127) // 128, (k + 127) // 128)
+    if scale.dtype != torch.float32 or tuple(scale.shape) != want or not scale.is_contiguous():
+        raise ValueError(f"scale must be contiguous float32 {want}")
+    with _on(dev):
+        _lib.check(_lib.load().kbn_requant_weights_ue8m0(w_fp8.data_ptr(), scale.data_ptr(), e, n, k, eps, _stream(w_fp8)))
+    # the scales changed behind torch's version counter: forget any packed copy made from the old values
+    for key in [k_ for k_ in _WEIGHT_SF_CACHE if k_[0] == scale.data_ptr()]:
+        _WEIGHT_SF_CACHE.pop(key, None)

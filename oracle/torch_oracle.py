@@ -16,6 +16,8 @@ Reference lines each function follows (paths relative to the kb-nano tree):
   grouped_gemm_masked   same arithmetic in the [E, max_m, K] layout (no reference call site)
   route_sigmoid_topk    tasks/baseline/L1/grouped_topk.py:119-174 with n_group=1, no bias
   route_softmax_topk    tasks/reference/L1/topk_softmax.py:46-52
+  requant_weights_ue8m0 tasks/baseline/L1/fp8_linear.py:453-512 with DeepGEMM's published per_block_cast_to_fp8
+                        (v2.1.1.post3: block max clamped at 1e-4, scale = 2^ceil(log2(max/448)), x * (1/scale))
   rmsnorm_quant         tasks/baseline/L1/csrc/rmsnorm_quant.cu:22-97,125-204 (fp32 arithmetic of the CUDA
                         kernel; there is no torch reference of the fused op in the tree)
   moe_layer             tasks/baseline/L2/fused_experts.py:246-283,119-136
@@ -186,3 +188,9 @@ def rmsnorm_quant(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6, resi
     if residual is not None:
         return q, sc, row, v.to(torch.bfloat16)
     return q, sc
+
+
+def requant_weights_ue8m0(w_q: torch.Tensor, s: torch.Tensor, eps: float = 1e-4):
+    """(new e4m3 weights, new power-of-two fp32 scales) of block-scaled weights [..., N, K]."""
+    w = dequant_blocks(w_q, s)
+    return block_quant_128x128(w, eps=eps, ue8m0=True)

@@ -113,3 +113,41 @@ def test_mx_matches_fp32_scale_kernel_on_config1(cuda_dev):
     assert_gemm_close(o2.cpu(), o1.cpu(), "ue8m0 path vs fp32-scale path")
     ref = to.gemm_nt_dequant(a_q.cpu(), a_s.cpu(), w_q.cpu(), w_s.cpu())
     assert_gemm_close(o2.cpu(), ref, "ue8m0 path vs oracle, C1")
+
+
+@pytest.mark.parametrize("shape", [(256, 384), (3, 256, 256), (200, 328)])
+def test_weight_requant_to_power_of_two_scales(cuda_dev, shape):
+    """Checkpoint-style weights (plain fp32 block scales) re-quantised on the GPU to UE8M0 scales: bytes and
+    scales identical to the oracle's dequantise -> per-block cast, and the result takes the UE8M0 GEMM path."""
+    from kb_nano_b200 import ops
+    gen = torch.Generator().manual_seed(sum(shape))
+    w = (0.02 * torch.randn(*shape, generator=gen)).to(torch.bfloat16)
+    w_q, w_s = to.block_quant_128x128(w, ue8m0=False)            # arbitrary fp32 scales, as a checkpoint holds them
+    ref_q, ref_s = to.requant_weights_ue8m0(w_q, w_s, eps=1e-4)
+    d = cuda_dev
+    gq, gs = w_q.to(d).contiguous(), w_s.to(d).contiguous()
+    assert ops.packed_weight_scales(gs, shape[-2], shape[-1]) is None          # not powers of two yet
+    ops.requant_weights_ue8m0(gq, gs, eps=1e-4)
+    assert bool((gq.cpu().view(torch.uint8) == ref_q.view(torch.uint8)).all()), "re-quantised bytes differ"
+    assert bool((gs.cpu() == ref_s).all()), "re-quantised scales differ"
+    assert ops.packed_weight_scales(gs, shape[-2], shape[-1]) is not None
+
+
+def test_postprocess_then_fp8_linear(cuda_dev):
+    """The load-time helper of the Fp8Linear drop-in, then the layer itself, against the oracle."""
+    import importlib.util, os, sys
+    from kb_nano_b200 import candidate_dir, inputs
+    spec = importlib.util.spec_from_file_location("_candidate_impl_L1_fp8_linear_pp", os.path.join(candidate_dir(), "L1", "fp8_linear.py"))
+    mod = importlib.util.module_from_spec(spec); sys.modules[spec.name] = mod; spec.loader.exec_module(mod)
+    w = (0.02 * torch.randn(512, 1024, generator=torch.Generator().manual_seed(4))).to(torch.bfloat16)
+    w_q, w_s = to.block_quant_128x128(w, ue8m0=False)
+    d = cuda_dev
+    nw, ns = mod.postprocess_fp8_weights(w_q.to(d), w_s.to(d))
+    assert bool(((ns.view(torch.int32) & 0x7FFFFF) == 0).all())
+    x = inputs.activations(96, 1024, seed=6)
+    out = mod.Fp8Linear()(x.to(d), nw, ns)
+    ref_q, ref_s = to.requant_weights_ue8m0(w_q, w_s)
+    assert_gemm_close(out.cpu(), to.fp8_linear(x, ref_q, ref_s), "Fp8Linear after postprocess_fp8_weights")
+    w3_q, w3_s = torch.stack([w_q, w_q]).to(d), torch.stack([w_s, w_s]).to(d)
+    mod.postprocess_fp8_weights_batched(w3_q, w3_s)
+    assert bool((w3_q[1].view(torch.uint8) == nw.view(torch.uint8)).all()) and bool((w3_s[0] == ns).all())

@@ -266,3 +266,22 @@ def test_silu_mul_quant_row_skipping_variants(cuda_dev):
     v = np.concatenate([np.arange(128) < int(c) for c in masked])
     assert_quant_equal(q3[v], s3[v], qr[v], np.ascontiguousarray(sr)[v], "masked variant")
     assert (q3[~v] == 0x55).all() and (s3[~v] == 7.0).all()
+
+
+@pytest.mark.parametrize("m,n2", [(512, 512), (4096, 2048)])
+def test_silu_mul_quant_row_list(cuda_dev, m, n2):
+    """Only the listed rows are processed (small inputs: flat kernel; 32768 groups or more: the persistent one)."""
+    from kb_nano_b200 import inputs, ops
+    x = inputs.activations(m, 2 * n2, seed=m)
+    gen = torch.Generator().manual_seed(n2)
+    rows = torch.randperm(m, generator=gen)[: m // 2].to(torch.int32)
+    rows[::7] = -1                                           # skipped entries
+    q = torch.full((m, n2), 0x55, dtype=torch.uint8, device=cuda_dev).view(FP8)
+    s = torch.full((n2 // 128, m), 7.0, device=cuda_dev).t()
+    pad = torch.cat([rows, torch.full((m * 8,), -1, dtype=torch.int32)]) if m == 4096 else rows   # long list -> persistent kernel
+    ops.silu_mul_quant_fp8_list(x.to(cuda_dev), q, s, pad.to(cuda_dev))
+    qr, sr = co.silu_mul_quant_1x128(bits16(x))
+    done = np.zeros(m, bool)
+    done[rows[rows >= 0].numpy()] = True
+    assert_quant_equal(q.cpu().view(torch.uint8).numpy()[done], s.cpu().numpy()[done], qr[done], np.ascontiguousarray(sr)[done], "row list")
+    assert (q.cpu().view(torch.uint8).numpy()[~done] == 0x55).all() and (s.cpu().numpy()[~done] == 7.0).all()
