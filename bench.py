@@ -464,15 +464,32 @@ def wl_moe_single(args, rank, world, dev, sampler, name):
     }
 
 
-def wl_ep_moe(args, rank, world, dev, sampler):
-    """BASELINE configs[3]: DeepSeek-V3-shaped MoE layer, experts split over the ranks, 128 tokens per rank,
-    masked layout with at most 256 rows per expert, dispatch/combine by peer stores over NVLink."""
+EP_SHAPES = {
+    # name: (hidden, inter, experts, topk, routing, tokens(world) per rank, max_m, scaling, description)
+    "ep_moe": (7168, 2048, None, 8, "sigmoid", lambda w: 128, 256, "weak",
+               "ep_moe: BASELINE configs[3], DeepSeek-V3-shaped FP8 MoE layer (hidden 7168, intermediate 2048, 256 experts, "
+               "top-8 sigmoid routing), expert-parallel, 128 tokens per rank, masked layout, <=256 rows per expert"),
+    "ep_moe_1024": (7168, 2048, None, 8, "sigmoid", lambda w: 1024 // w, 256, "strong",
+                    "ep_moe_1024: BASELINE configs[3] at a FIXED global batch of 1024 tokens (1024/N per rank), masked layout, "
+                    "<=256 rows per expert"),
+    "ep_c5": (4096, 14336, 8, 2, "softmax", lambda w: 16384 // w, 5120, "strong",
+              "ep_c5: BASELINE configs[4] expert-parallel, Mixtral-8x7B-shaped FP8 MoE layer (hidden 4096, intermediate 14336, "
+              "8 experts, top-2 softmax routing), 16384 tokens in total (16384/N per rank), masked layout, <=5120 rows per expert"),
+}
+
+
+def wl_ep_moe(args, rank, world, dev, sampler, name="ep_moe"):
+    """Expert-parallel MoE layer: experts split over the ranks, masked layout, dispatch/combine by peer stores
+    over NVLink.  `name` picks the shape (BASELINE configs[3], its fixed-global-batch form, or configs[4])."""
     from kb_nano_b200 import _lib, ep, inputs, ops
-    t, h, i, e, topk, max_m = 128, 7168, 2048, args.experts, 8, 256
+    h, i, e_fixed, topk, routing, t_of, max_m, scaling, desc = EP_SHAPES[name]
+    e = e_fixed if e_fixed is not None else args.experts
+    t = t_of(world)
+    route = inputs.route_sigmoid_topk if routing == "sigmoid" else inputs.route_softmax_topk
     lo, hi = ep.expert_range(rank, world, e)
     e_l = hi - lo
     x = inputs.activations(t, h, seed=rank, device=dev)
-    tw, ti = inputs.route_sigmoid_topk(inputs.router_logits(t, e, seed=rank, device=dev), topk)
+    tw, ti = route(inputs.router_logits(t, e, seed=rank, device=dev), topk)
     tw, ti = tw.contiguous(), ti.contiguous()
     w13_q, w13_s = inputs.expert_weights(e_l, 2 * i, h, seed=1, device=dev, first=lo)
     w2_q, w2_s = inputs.expert_weights(e_l, h, i, seed=2, device=dev, first=lo)
@@ -489,7 +506,7 @@ def wl_ep_moe(args, rank, world, dev, sampler):
     # rows every local expert receives (routing of all ranks is reproducible from the seeds)
     counts = torch.zeros(e, dtype=torch.long)
     for r in range(world):
-        _, ti_r = inputs.route_sigmoid_topk(inputs.router_logits(t, e, seed=r), topk)
+        _, ti_r = route(inputs.router_logits(t, e, seed=r), topk)
         counts += torch.bincount(ti_r.reshape(-1).long(), minlength=e)
     local = counts[lo:hi]
     assert int(local.max()) <= max_m
@@ -521,6 +538,7 @@ def wl_ep_moe(args, rank, world, dev, sampler):
     g2 = active * h * i + rows * i + rows * h * 2 + 4 * rows * (i // 128)
     peaks = measured_peaks()
     ach = (g1 + g2) / 2.0 / (gemm_ms * 1e-3) / 1e9
+    gemm_tflops = 2.0 * rows * 3 * i * h / 2.0 / (gemm_ms * 1e-3) / 1e12
     assert ops.gemm_status(dev) == 0
     # e2e: pinned host activations and routing in, result back to the host
     hx, htw, hti = x.cpu().pin_memory(), tw.cpu().pin_memory(), ti.cpu().pin_memory()
@@ -538,26 +556,35 @@ def wl_ep_moe(args, rank, world, dev, sampler):
     layer.check()
     layer.close()
     flop = 2.0 * t * topk * world * 3 * i * h
+    # rows per streamed expert decide the bound: below ~560 rows per weight pass the weights' HBM traffic dominates
+    tensor_bound = rows / max(active, 1) >= 560
+    if tensor_bound:
+        fp8_peak = 2.0 * peaks["bf16_tflops_sustained"]
+        roof = {"bound": "tensor", "kernel": "fp8_gemm_mx_kernel (masked grouped, 2 launches per layer; rank 0)", "achieved": gemm_tflops,
+                "peak": fp8_peak, "unit": "TFLOP/s", "frac": gemm_tflops / fp8_peak, "traffic": None,
+                "peak_source": peaks["source"] + " (2 x sustained bf16 cuBLAS figure; no FP8 figure is measured)",
+                "algorithmic_flop_per_launch": 2.0 * rows * 3 * i * h / 2.0, "gemm_ms_per_launch": gemm_ms}
+    else:
+        roof = {"bound": "hbm", "kernel": "fp8_gemm_mx_kernel (masked grouped, 2 launches per layer; rank 0)", "achieved": ach,
+                "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"],
+                # dram read+write bytes per launch from the ncu capture summarised in
+                # profiles/fp8_gemm_mx_masked_ep_moe.md (0.76 GB per launch with 32 local DeepSeek-V3-shaped experts;
+                # proportional to the bytes of the experts whose weights are streamed)
+                "traffic": 0.76e9 / 32.0 * active * (3.0 * i * h) / (3.0 * 2048 * 7168), "peak_source": peaks["source"],
+                "algorithmic_bytes_per_launch": (g1 + g2) / 2.0, "gemm_ms_per_launch": gemm_ms}
     return {
         "metric": "EP FP8 MoE layer throughput", "value": t * world / (ms * 1e-3), "unit": "tokens/s", "ms_per_step": ms,
-        "dtype": "e4m3 x e4m3 -> fp32 -> bf16", "scaling": "weak",
-        "config": {"workload": "ep_moe: BASELINE configs[3], DeepSeek-V3-shaped FP8 MoE layer (hidden 7168, intermediate 2048, 256 experts, "
-                               "top-8 sigmoid routing), expert-parallel, 128 tokens per rank, masked layout, <=256 rows per expert"
-                               + ("" if e == 256 else f" [REDUCED to {e} experts: profiling case, not the benchmark configuration]"),
-                   "parallelism": f"ep{world}", "experts_per_rank": e_l, "global_tokens": t * world,
+        "dtype": "e4m3 x e4m3 -> fp32 -> bf16", "scaling": scaling,
+        "config": {"workload": desc + ("" if e_fixed is not None or e == 256 else
+                                       f" [REDUCED to {e} experts: profiling case, not the benchmark configuration]"),
+                   "parallelism": f"ep{world}", "experts_per_rank": e_l, "tokens_per_rank": t, "global_tokens": t * world,
                    "l2": f"local expert weights ({e_l * 3 * i * h / 1e9:.2f} GB) exceed the 126 MB L2",
                    "exchange": "peer stores over NVLink (dispatch fp8 rows + scales, combine bf16 rows), release/acquire flags",
                    "layer_tflops": flop / world / (ms * 1e-3) / 1e12},
         "e2e": {"value": t * world / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": t * h * 2 + t * topk * 8, "d2h_bytes_per_step": t * h * 2},
         "gpu_launches": launches // (args.steps + args.warmup) * args.steps,
-        "roofline": {"bound": "hbm", "kernel": "fp8_gemm_mx_kernel (masked grouped, 2 launches per layer; rank 0)", "achieved": ach, "peak": peaks["hbm_gbs"],
-                     "unit": "GB/s", "frac": ach / peaks["hbm_gbs"],
-                     # dram read+write bytes per launch from the ncu capture summarised in
-                     # profiles/fp8_gemm_mx_masked_ep_moe.md (0.76 GB per launch with 32 local experts; proportional
-                     # to the number of experts whose weights are streamed)
-                     "traffic": 0.76e9 / 32.0 * active, "peak_source": peaks["source"],
-                     "algorithmic_bytes_per_launch": (g1 + g2) / 2.0, "gemm_ms_per_launch": gemm_ms},
-        "_cpu": lambda: cpu_moe(t, h, i, e, topk, "sigmoid", 8, 1),
+        "roofline": roof,
+        "_cpu": lambda: cpu_moe(t, h, i, e, topk, routing, 8 if routing == "sigmoid" else 1, 1),
     }
 
 
@@ -569,6 +596,8 @@ WORKLOADS = {
     "quant_c3": lambda *a: wl_quant_c1(*a, m=4096, k=7168),
     "moe_c3": lambda *a: wl_moe_single(*a, "moe_c3"),
     "moe_c5": lambda *a: wl_moe_single(*a, "moe_c5"),
+    "ep_moe_1024": lambda *a: wl_ep_moe(*a, name="ep_moe_1024"),
+    "ep_c5": lambda *a: wl_ep_moe(*a, name="ep_c5"),
 }
 DEFAULT_WORKLOAD = "ep_moe"
 
@@ -596,11 +625,14 @@ def reference_arm(args, rank, world):
         v, dt, sample = cpu_moe(4096, 7168, 2048, 256, 8, "sigmoid", 8, 1)
         metric, unit = "FP8 MoE layer throughput", "tokens/s"
     else:
-        v, dt, sample = cpu_moe(128 * world, 7168, 2048, 256, 8, "sigmoid", 8, 1)
-        metric, unit = "FP8 MoE layer throughput", "tokens/s"
+        h, i, e_fixed, topk, routing, t_of, _, _, desc = EP_SHAPES[wl]
+        e = e_fixed if e_fixed is not None else args.experts
+        v, dt, sample = cpu_moe(t_of(world) * world, h, i, e, topk, routing, 8 if routing == "sigmoid" else 1, 1)
+        metric, unit = "EP FP8 MoE layer throughput", "tokens/s"
+        wl = desc
     line = {"impl": "reference", "metric": metric, "value": v, "unit": unit, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32 (torch CPU)", "data": "synthetic",
-            "config": {"workload": wl},
+            "config": {"workload": wl, "parallelism": "host cores of rank 0"},
             "cpu_baseline": {"value": v, "unit": unit, "cores": cpu_threads(), "kind": "port", "sample": sample},
             "e2e": {"value": v, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
     print(json.dumps(line), flush=True)

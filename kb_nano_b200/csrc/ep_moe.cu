@@ -17,6 +17,7 @@
 // (tasks/baseline/L1/allreduce.py:37-48 behind tasks/baseline/L2/deepseek_moe.py:301-302).
 // Per rank and step the NVLink traffic is at most T*topk*(H + 4*H/128 + 4) bytes out for the
 // dispatch and T*topk*2*H bytes in for the combine.
+#include <algorithm>
 #include <new>
 
 #include "common.cuh"
@@ -327,7 +328,9 @@ extern "C" int kbn_ep_moe_forward(kbn_ep_ctx* c, const void* x_bf16, const int32
     }
     if (rc != KBN_OK) return rc;
     // 5. results back to their sources + signal
-    ep_combine_send_kernel<<<dim3(8, (unsigned)c->e_local), 256, 0, st>>>(c->mm2, H, (int)c->e_local, (int)c->max_m, c->peers, c->lay, c->rank, c->world,
+    // blocks per expert: enough to fill the GPU when a rank owns few experts with many rows, never more than the rows need
+    const unsigned cs_x = (unsigned)std::min<int64_t>((c->max_m + 7) / 8, std::max<int64_t>(8, (4 * (int64_t)sm_count() + c->e_local - 1) / c->e_local));
+    ep_combine_send_kernel<<<dim3(cs_x, (unsigned)c->e_local), 256, 0, st>>>(c->mm2, H, (int)c->e_local, (int)c->max_m, c->peers, c->lay, c->rank, c->world,
                                                                         epoch, c->done + 1);
     KBN_CHECK_LAUNCH();
     ep_wait_kernel<<<1, kMaxRanks, 0, st>>>(reinterpret_cast<const int32_t*>(mine + c->lay.flags_combine), c->world, epoch, 2, c->status);

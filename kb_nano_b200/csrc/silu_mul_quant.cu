@@ -10,6 +10,8 @@
 // boundary or any gate is below -8.
 // The table is filled once per device by silu_table_kernel (fp64 exp rounded to fp32, then the
 // reference's fp32 add and divide).
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace kbn {
@@ -315,8 +317,11 @@ static int launch_silu_mul_quant(const char* who, const void* in, int64_t M, int
     silu_mul_quant_kernel<UE, U, RM><<<nb, 256, 0, st>>>(ib, (uint32_t)N2, ld_in, qb, ld_q, scale, s_row, s_grp, eps, table, \
                                                          row_info, (uint32_t)G, (uint32_t)cpr, (uint32_t)n_chunks)
 #define KBN_SMQ_MASKED(UE)                                                                                                \
-    silu_mul_quant_masked_kernel<UE, U><<<dim3(4, (unsigned)(M / max_m)), 256, 0, st>>>(                                  \
+    silu_mul_quant_masked_kernel<UE, U><<<dim3(masked_x, (unsigned)(M / max_m)), 256, 0, st>>>(                                  \
         ib, (uint32_t)N2, ld_in, qb, ld_q, scale, s_row, s_grp, eps, table, row_info, mm, (uint32_t)G, (uint32_t)cpr, packed)
+    // masked layout, blocks per expert: enough to fill the GPU when there are few experts with many rows
+    const int64_t n_exp = rows_mode == 2 ? M / max_m : 1;
+    const unsigned masked_x = (unsigned)std::min<int64_t>((max_m * cpr + 15) / 16, std::max<int64_t>(4, (8 * (int64_t)sm_count() + n_exp - 1) / std::max<int64_t>(n_exp, 1)));
     // large flat inputs with power-of-two scales: persistent blocks with the exact table in shared memory
     if (rows_mode != 2 && ue8m0 && n_chunks * U >= 32768) {
         constexpr int U2 = 4;
