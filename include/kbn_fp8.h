@@ -68,13 +68,16 @@ int kbn_silu_mul_quant_1x128(const void* in, int64_t M, int64_t N2, int64_t ld_i
  *            which spreads the work evenly however the rows are grouped;
  *   _masked: in [E, max_m, 2*N2] -> q [E, max_m, N2], row-major scales [E, max_m, N2/128], UE8M0,
  *            eps 1e-10; row (e, m) is processed iff m < masked_m[e].
+ *   sf_packed (_list; may be null, needs ue8m0): also receives the scales of the listed rows in the packed
+ *            form of the *_ue8m0 GEMMs, kbn_packed_sf_rows_bytes(rows of q, N2) bytes, rows indexed as in q.
  * kb-nano runs its kernel over every row of the padded buffer (tasks/baseline/L2/fused_experts.py:269-274). */
 int kbn_silu_mul_quant_1x128_rows(const void* in, int64_t M, int64_t N2, int64_t ld_in, void* q,
                                   int64_t ld_q, float* scale, int64_t s_row, int64_t s_grp, float eps,
                                   int ue8m0, const int32_t* row_expert, kbn_stream_t stream);
 int kbn_silu_mul_quant_1x128_list(const void* in, int64_t N2, int64_t ld_in, void* q, int64_t ld_q,
                                   float* scale, int64_t s_row, int64_t s_grp, float eps, int ue8m0,
-                                  const int32_t* row_list, int64_t n_list, kbn_stream_t stream);
+                                  const int32_t* row_list, int64_t n_list, void* sf_packed,
+                                  kbn_stream_t stream);
 int kbn_silu_mul_quant_1x128_masked(const void* in, int64_t E, int64_t max_m, int64_t N2, void* q,
                                     float* scale, const int32_t* masked_m, kbn_stream_t stream);
 
@@ -199,6 +202,9 @@ int kbn_gemm_status(int32_t* host_out, kbn_stream_t stream);
  *   row_expert int32 [M_cap]: expert of each row, -1 for padding;
  *   dest_row int32 [T,topk]: row each (token, slot) went to (-1 if its expert id is out of range).
  *   workspace: kbn_moe_permute_workspace_bytes(T, topk, E) bytes of device scratch.
+ * kbn_moe_permute_sf: the same, and a_sf_packed (kbn_packed_sf_rows_bytes(M_cap, K) bytes; may be null)
+ *   also receives the moved rows' scales in the packed form of the *_ue8m0 GEMMs (scales must be powers
+ *   of two); words of padding rows are left unwritten.
  * kbn_moe_unpermute_combine: out[t,:] = sum_s topk_w[t,s] * rows[dest_row[t,s],:], fp32
  *   accumulation in slot order, bf16 [T,H] out; rows is bf16 with row stride ld_rows.
  */
@@ -214,6 +220,10 @@ int kbn_moe_permute(const void* a_q, const float* a_s, const int32_t* topk_ids, 
  * and E <= 1024 (KBN_ERR_UNSUPPORTED beyond).  Allocates nothing; the first call on a device resolves
  * the array's address and should come before any stream capture; calls that overlap on one GPU race
  * on the shared scratch. */
+int kbn_moe_permute_sf(const void* a_q, const float* a_s, const int32_t* topk_ids, int64_t T,
+                       int64_t topk, int64_t K, int64_t E, void* a_perm, float* a_s_perm,
+                       int32_t* row_expert, int32_t* dest_row, int64_t M_cap, void* workspace,
+                       int64_t workspace_bytes, void* a_sf_packed, kbn_stream_t stream);
 int kbn_moe_permute_static(const void* a_q, const float* a_s, const int32_t* topk_ids, int64_t T,
                            int64_t topk, int64_t K, int64_t E, void* a_perm, float* a_s_perm,
                            int32_t* row_expert, int32_t* dest_row, int64_t M_cap, kbn_stream_t stream);

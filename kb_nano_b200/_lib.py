@@ -24,7 +24,7 @@ SIGNATURES = {
     "kbn_rmsnorm_quant_1x128": (_i32, [_ptr, _ptr, _i64, _i64, _i64, _ptr, _i64, _ptr, _i64, _i64, _f32, _ptr]),
     "kbn_add_rmsnorm_quant_1x128": (_i32, [_ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _ptr, _i64, _ptr, _i64, _i64, _f32, _ptr]),
     "kbn_silu_mul_quant_1x128_rows": (_i32, [_ptr, _i64, _i64, _i64, _ptr, _i64, _ptr, _i64, _i64, _f32, _i32, _ptr, _ptr]),
-    "kbn_silu_mul_quant_1x128_list": (_i32, [_ptr, _i64, _i64, _ptr, _i64, _ptr, _i64, _i64, _f32, _i32, _ptr, _i64, _ptr]),
+    "kbn_silu_mul_quant_1x128_list": (_i32, [_ptr, _i64, _i64, _ptr, _i64, _ptr, _i64, _i64, _f32, _i32, _ptr, _i64, _ptr, _ptr]),
     "kbn_silu_mul_quant_1x128_masked": (_i32, [_ptr, _i64, _i64, _i64, _ptr, _ptr, _ptr, _ptr]),
     "kbn_fp8_gemm_nt": (_i32, [_ptr, _ptr, _i64, _i64, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _ptr]),
     "kbn_fp8_grouped_gemm_contig": (_i32, [_ptr, _ptr, _i64, _i64, _ptr, _ptr, _ptr, _i64, _ptr, _i64, _i64, _i64, _i64, _ptr]),
@@ -42,6 +42,7 @@ SIGNATURES = {
     "kbn_moe_aligned_rows": (_i64, [_i64, _i64, _i64]),
     "kbn_moe_permute_workspace_bytes": (_i64, [_i64, _i64, _i64]),
     "kbn_moe_permute": (_i32, [_ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _ptr, _ptr, _ptr, _ptr, _i64, _ptr, _i64, _ptr]),
+    "kbn_moe_permute_sf": (_i32, [_ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _ptr, _ptr, _ptr, _ptr, _i64, _ptr, _i64, _ptr, _ptr]),
     "kbn_ep_create": (_i32, [_i32, _i32, _i64, _i64, _i64, _i64, _i64, _i64, ctypes.POINTER(_ptr)]),
     "kbn_ep_ipc_handle": (_i32, [_ptr, _ptr]),
     "kbn_ep_attach": (_i32, [_ptr, _ptr]),

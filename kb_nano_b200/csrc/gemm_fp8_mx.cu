@@ -50,7 +50,8 @@ struct MxExtra {
 
 template <int BN>
 __global__ void __launch_bounds__(kThreads, 1)
-fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p,
+fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmA64,
+                   const __grid_constant__ CUtensorMap tmA32, const __grid_constant__ CUtensorMap tmB, const GemmParams p,
                    const MxExtra x) {
     constexpr int kBN = Cfg<BN>::kBN, kStages = Cfg<BN>::kStages, kStageBytes = Cfg<BN>::kStageBytes;
     constexpr int kSfbBytes = Cfg<BN>::kSfbBytes, kSfStage = Cfg<BN>::kSfStage, kTxBytes = Cfg<BN>::kTxBytes;
@@ -91,36 +92,58 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 
     if (warp == 0) {
         // ---------------- producer ----------------
+        // The whole warp walks the tiles (so that it can look at a block's 128 row ids with one load per
+        // lane); lane 0 alone waits on the ring and issues the copies.
         if (lane == 0) {
             ptx::prefetch_tensormap(&tmA);
+            ptx::prefetch_tensormap(&tmA64);
+            ptx::prefetch_tensormap(&tmA32);
             ptx::prefetch_tensormap(&tmB);
-            WaitCtx w{abort_flag, p.status, 4};
-            TileWalk walk(p);
-            Tile tile;
-            uint32_t it = 0;
-            bool ok = true;
-            for (int64_t t = blockIdx.x; ok && walk.get(t, tile); t += gridDim.x) {
-                if (!tile.compute) continue;
+        }
+        WaitCtx w{abort_flag, p.status, 4};
+        TileWalk walk(p);
+        Tile tile;
+        uint32_t it = 0;
+        bool ok = true;
+        for (int64_t t = blockIdx.x; ok && walk.get(t, tile); t += gridDim.x) {
+            if (!tile.compute) continue;
+            // Rows of the block that hold data: a block with few of them (decode batches, the last block
+            // of an expert) fetches a 32- or 64-row box of A instead of 128 rows.  The rest of the stage
+            // keeps whatever an earlier tile left there; those accumulator rows are never used.
+            int32_t live = min(tile.row_end - tile.row0, kBlockM);
+            if (p.mode == kContig) {
+                int32_t last = -1;                  // last row of the block with a valid expert id
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int32_t r = 4 * lane + j;
+                    if (r < live && p.row_expert[tile.row0 + r] >= 0) last = r;
+                }
+                live = __reduce_max_sync(0xffffffffu, last) + 1;
+            }
+            if (lane == 0) {
                 const int32_t b_row = tile.expert * p.N + tile.n_blk * kBN;
                 const uint8_t* sfa = x.sfa + (int64_t)(tile.row0 / kBlockM) * KB * kSfaBytes;
                 const uint8_t* sfb = x.sfb + (((int64_t)tile.expert * KB) * x.nb_pad + (BN / 128) * tile.n_blk) * (int64_t)kSfaBytes;
+                const CUtensorMap* tma = live <= 32 ? &tmA32 : (live <= 64 ? &tmA64 : &tmA);
+                const uint32_t tx = (uint32_t)(kTxBytes - kABytes) + (live <= 32 ? 32u : (live <= 64 ? 64u : 128u)) * (uint32_t)kBlockK;
                 for (int kb = 0; kb < KB; ++kb, ++it) {
                     const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
                     if (!wait_bar(bar_empty + 8 * s, ph ^ 1u, w)) { ok = false; break; }
                     const uint32_t bar = bar_full + 8 * s;
-                    ptx::mbar_arrive_expect_tx(bar, kTxBytes);
+                    ptx::mbar_arrive_expect_tx(bar, tx);
                     const uint32_t dst = smem_tiles + s * kStageBytes;
-                    ptx::tma_load_2d(dst, &tmA, kb * kBlockK, tile.row0, bar);
+                    ptx::tma_load_2d(dst, tma, kb * kBlockK, tile.row0, bar);
                     ptx::tma_load_2d(dst + kABytes, &tmB, kb * kBlockK, b_row, bar);
                     const uint32_t sdst = smem_sf + s * kSfStage;
                     ptx::bulk_load(sdst, sfa + (int64_t)kb * kSfaBytes, kSfaBytes, bar);
                     ptx::bulk_load(sdst + kSfaBytes, sfb + (int64_t)kb * x.nb_pad * kSfaBytes, kSfbBytes, bar);
                 }
             }
-            if (!ok) {
-                const long long t0 = clock64();
-                while (clock64() - t0 < 400000ll) __nanosleep(1000);
-            }
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        }
+        if (!ok && lane == 0) {
+            const long long t0 = clock64();
+            while (clock64() - t0 < 400000ll) __nanosleep(1000);
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
@@ -224,6 +247,195 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     }
 }
 
+// ---- split-K over a thread-block cluster (dense form, few output tiles) ---------------------------
+//
+// A dense problem with fewer 128x256 tiles than SMs (decode-sized M, a single linear layer) would
+// leave most of the GPU idle and stream the weights through a handful of SMs.  Here the S CTAs of a
+// cluster share one output tile: CTA r accumulates K-blocks [r*KB/S, (r+1)*KB/S) in its own TMEM,
+// then the partial tiles are exchanged through distributed shared memory -- CTA o owns columns
+// [o*BN/S, (o+1)*BN/S) of the tile and receives every CTA's partial of that slice in the (by then
+// idle) pipeline stages -- and each owner adds the S partials in rank order and stores bf16.  No
+// workspace, no atomics, and the result does not depend on timing.  One tile per cluster.
+constexpr int kSplitPad = 16;     // bytes added to a staged row so that 16-byte stores of a warp spread over the banks
+
+template <int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+fp8_gemm_mx_splitk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmA64,
+                          const __grid_constant__ CUtensorMap tmA32, const __grid_constant__ CUtensorMap tmB,
+                          const GemmParams p, const MxExtra x, const int S) {
+    constexpr int kBN = Cfg<BN>::kBN, kStages = Cfg<BN>::kStages, kStageBytes = Cfg<BN>::kStageBytes;
+    constexpr int kSfbBytes = Cfg<BN>::kSfbBytes, kSfStage = Cfg<BN>::kSfStage, kTxBytes = Cfg<BN>::kTxBytes;
+    constexpr int kHalfCols = BN / 2;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~(uintptr_t)1023u);
+    uint8_t* sf_smem = smem + (size_t)kStages * kStageBytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sf_smem + (size_t)kStages * kSfStage);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t bar_full = ptx::smem_u32(bars), bar_empty = ptx::smem_u32(bars + kStages);
+    const uint32_t bar_tfull = ptx::smem_u32(bars + 2 * kStages);
+    const uint32_t smem_tiles = ptx::smem_u32(smem), smem_sf = ptx::smem_u32(sf_smem);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            ptx::mbar_init(bar_full + 8 * s, 1);
+            ptx::mbar_init(bar_empty + 8 * s, 1);
+        }
+        ptx::mbar_init(bar_tfull, 1);
+        *abort_flag = 0;
+        ptx::fence_barrier_init();
+        ptx::fence_proxy_async();
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(ptx::smem_u32(tmem_slot), kTmemCols);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const uint32_t rank = ptx::cluster_ctarank();
+    const int32_t cid = (int32_t)(blockIdx.x / (uint32_t)S);
+    const int32_t m_blk = cid % p.num_m_blocks, n_blk = cid / p.num_m_blocks;
+    const int32_t row0 = m_blk * kBlockM;
+    const int32_t live = min(p.rows_total - row0, kBlockM);
+    const int32_t kbs = (p.num_k_blocks + S - 1) / S;
+    const int32_t kb0 = (int32_t)rank * kbs, kb1 = min(p.num_k_blocks, kb0 + kbs);     // host guarantees kb0 < kb1
+
+    if (warp == 0) {
+        if (lane == 0) {
+            ptx::prefetch_tensormap(&tmA);
+            ptx::prefetch_tensormap(&tmA64);
+            ptx::prefetch_tensormap(&tmA32);
+            ptx::prefetch_tensormap(&tmB);
+            WaitCtx w{abort_flag, p.status, 4};
+            const uint8_t* sfa = x.sfa + (int64_t)m_blk * p.num_k_blocks * kSfaBytes;
+            const uint8_t* sfb = x.sfb + (int64_t)(BN / 128) * n_blk * kSfaBytes;
+            const CUtensorMap* tma = live <= 32 ? &tmA32 : (live <= 64 ? &tmA64 : &tmA);
+            const uint32_t tx = (uint32_t)(kTxBytes - kABytes) + (live <= 32 ? 32u : (live <= 64 ? 64u : 128u)) * (uint32_t)kBlockK;
+            uint32_t it = 0;
+            for (int kb = kb0; kb < kb1; ++kb, ++it) {
+                const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+                if (!wait_bar(bar_empty + 8 * s, ph ^ 1u, w)) break;
+                const uint32_t bar = bar_full + 8 * s;
+                ptx::mbar_arrive_expect_tx(bar, tx);
+                const uint32_t dst = smem_tiles + s * kStageBytes;
+                ptx::tma_load_2d(dst, tma, kb * kBlockK, row0, bar);
+                ptx::tma_load_2d(dst + kABytes, &tmB, kb * kBlockK, n_blk * kBN, bar);
+                const uint32_t sdst = smem_sf + s * kSfStage;
+                ptx::bulk_load(sdst, sfa + (int64_t)kb * kSfaBytes, kSfaBytes, bar);
+                ptx::bulk_load(sdst + kSfaBytes, sfb + (int64_t)kb * x.nb_pad * kSfaBytes, kSfbBytes, bar);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            WaitCtx w{abort_flag, p.status, 5};
+            constexpr uint32_t idesc = ptx::umma_idesc_mx_e4m3(kBlockM, kBN, 0, 0);
+            uint32_t it = 0;
+            bool ok = true;
+            for (int kb = kb0; kb < kb1; ++kb, ++it) {
+                const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+                if (!wait_bar(bar_full + 8 * s, ph, w)) { ok = false; break; }
+                ptx::tc_fence_after();
+                const uint32_t a_addr = smem_tiles + s * kStageBytes;
+                const uint32_t sf_addr = smem_sf + s * kSfStage;
+                ptx::tmem_cp_32x128b_warpx4(tmem_base + kColSfa, ptx::umma_desc_sf(sf_addr));
+                ptx::tmem_cp_32x128b_warpx4(tmem_base + kColSfb, ptx::umma_desc_sf(sf_addr + kSfaBytes));
+                if (BN == 256)
+                    ptx::tmem_cp_32x128b_warpx4(tmem_base + kColSfb + 4, ptx::umma_desc_sf(sf_addr + 2 * kSfaBytes));
+                const uint64_t a_desc = ptx::umma_desc_k_sw128(a_addr);
+                const uint64_t b_desc = ptx::umma_desc_k_sw128(a_addr + kABytes);
+#pragma unroll
+                for (int k = 0; k < kBlockK / 32; ++k)
+                    ptx::mma_mxf8f6f4_block_scale(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc, tmem_base + kColSfa,
+                                                  tmem_base + kColSfb, (kb > kb0 || k > 0) ? 1u : 0u);
+                ptx::mma_commit(bar_empty + 8 * s);
+            }
+            if (ok) ptx::mma_commit(bar_tfull);
+        }
+    } else {
+        // all MMAs of this CTA have finished (and with them every read of the pipeline stages)
+        WaitCtx w{abort_flag, p.status, 6};
+        wait_bar(bar_tfull, 0u, w);
+        ptx::tc_fence_after();
+    }
+    __syncwarp();
+    ptx::cluster_sync();          // every CTA of the cluster is done with its stages: they may now be overwritten
+
+    // ---- exchange: this CTA's partial of slice o goes to CTA o, slot [rank] ----
+    const int W = kBN / S;                                  // columns per owner (a multiple of 32)
+    const uint32_t pitch = (uint32_t)W * 4u + kSplitPad;    // bytes per staged row
+    if (warp >= 2) {
+        const int quarter = warp & 3;
+        const int half = (warp - 2) >> 2;
+        const int r_in_tile = quarter * 32 + lane;
+        if (quarter * 32 < live) {                           // warp-uniform: some row of this quarter holds data
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + half * kHalfCols;
+            constexpr int kChunks = kHalfCols / 32;
+#pragma unroll
+            for (int c = 0; c < kChunks; ++c) {
+                uint32_t r[32];
+                ptx::tmem_ld_32x32(taddr + 32 * c, r);
+                ptx::tmem_ld_wait(r);
+                const int col = half * kHalfCols + 32 * c;   // first column of the chunk within the tile
+                const uint32_t owner = (uint32_t)(col / W);
+                const uint32_t local = smem_tiles + (rank * (uint32_t)kBlockM + (uint32_t)r_in_tile) * pitch + (uint32_t)(col % W) * 4u;
+                const uint32_t remote = ptx::mapa(local, owner);
+                if (r_in_tile < live) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4) ptx::st_cluster_v4(remote + 4u * j, r[j], r[j + 1], r[j + 2], r[j + 3]);
+                }
+            }
+        }
+        ptx::tc_fence_before();
+    }
+    __syncwarp();
+    ptx::cluster_sync();          // all partials have arrived
+
+    // ---- reduce this CTA's slice in rank order and store ----
+    if (warp >= 2) {
+        const int e = (int)threadIdx.x - 64;                 // 0..255
+        const int row = e & 127, hsel = e >> 7;
+        const int cols = W / 2;                              // columns per thread (a multiple of 16)
+        const int c_in = hsel * cols;
+        const int32_t n0 = n_blk * kBN + (int32_t)rank * W + c_in;
+        if (row < live && *abort_flag == 0) {
+            __nv_bfloat16* crow = p.C + (int64_t)(row0 + row) * p.ldc + n0;
+            const bool vec_ok = (reinterpret_cast<uintptr_t>(crow) & 15u) == 0;
+            for (int j = 0; j < cols; j += 8) {
+                float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0;
+                for (int s = 0; s < S; ++s) {
+                    const uint32_t src = smem_tiles + ((uint32_t)s * (uint32_t)kBlockM + (uint32_t)row) * pitch + (uint32_t)(c_in + j) * 4u;
+                    const float4 v0 = ptx::ld_shared_v4(src), v1 = ptx::ld_shared_v4(src + 16u);
+                    a0.x += v0.x; a0.y += v0.y; a0.z += v0.z; a0.w += v0.w;
+                    a1.x += v1.x; a1.y += v1.y; a1.z += v1.z; a1.w += v1.w;
+                }
+                if (n0 + j + 8 <= p.N && vec_ok) {
+                    uint4 v;
+                    v.x = pack_bf16x2(a0.x, a0.y); v.y = pack_bf16x2(a0.z, a0.w);
+                    v.z = pack_bf16x2(a1.x, a1.y); v.w = pack_bf16x2(a1.z, a1.w);
+                    *reinterpret_cast<uint4*>(crow + j) = v;
+                } else {
+                    const float f[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+#pragma unroll
+                    for (int q = 0; q < 8; ++q)
+                        if (n0 + j + q < p.N) crow[j + q] = __float2bfloat16_rn(f[q]);
+                }
+            }
+        }
+    }
+
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
 // ---- scale packing -----------------------------------------------------------------------------
 
 __device__ __forceinline__ uint32_t ue8m0_word(float s) {
@@ -308,12 +520,62 @@ static int check_device() {
         KBN_REQUIRE(major == 10, KBN_ERR_UNSUPPORTED, "kbn_fp8 GEMMs need an sm_100 device (found major %d)", major);
         KBN_CUDA(cudaFuncSetAttribute(fp8_gemm_mx_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<256>::kSmemBytes));
         KBN_CUDA(cudaFuncSetAttribute(fp8_gemm_mx_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<128>::kSmemBytes));
+        KBN_CUDA(cudaFuncSetAttribute(fp8_gemm_mx_splitk_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<256>::kSmemBytes));
+        KBN_CUDA(cudaFuncSetAttribute(fp8_gemm_mx_splitk_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<128>::kSmemBytes));
         ok[dev] = 1;
     }
     return KBN_OK;
 }
 
 static inline int32_t cdiv32(int64_t a, int64_t b) { return (int32_t)((a + b - 1) / b); }
+
+// Clusters of `split` CTAs of the split-K kernel that can be resident at once (cached per device).
+template <int BN>
+static int max_active_clusters(int split) {
+    static int cache[64][9] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || split < 2 || split > 8) return 0;
+    if (cache[dev][split] == 0) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)(split * 64));
+        cfg.blockDim = dim3(kThreads);
+        cfg.dynamicSmemBytes = Cfg<BN>::kSmemBytes;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = (unsigned)split;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, fp8_gemm_mx_splitk_kernel<BN>, &cfg) != cudaSuccess) {
+            cudaGetLastError();
+            n = -1;
+        }
+        cache[dev][split] = n > 0 ? n : -1;
+    }
+    return cache[dev][split] > 0 ? cache[dev][split] : 0;
+}
+
+template <int BN>
+static int launch_splitk(const CUtensorMap& tmA, const CUtensorMap& tmA64, const CUtensorMap& tmA32, const CUtensorMap& tmB,
+                         const GemmParams& p, const MxExtra& x, int split, int64_t tiles, cudaStream_t st) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(tiles * split));
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = Cfg<BN>::kSmemBytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)split;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    KBN_CUDA(cudaLaunchKernelEx(&cfg, fp8_gemm_mx_splitk_kernel<BN>, tmA, tmA64, tmA32, tmB, p, x, split));
+    KBN_CHECK_LAUNCH();
+    return KBN_OK;
+}
 
 // m_blocks_upper: number of 128-row blocks (an upper bound in the masked form).
 static int launch(const void* A, int64_t a_rows, const void* B, int64_t b_rows, GemmParams& p, const void* sfa, const void* sfb,
@@ -327,10 +589,30 @@ static int launch(const void* A, int64_t a_rows, const void* B, int64_t b_rows, 
     // 256-wide tiles unless that would leave SMs without a tile and 128-wide tiles fill more of them
     int bn = 256;
     if (p.mode != kMasked && p.N > 128 && m_blocks_upper * cdiv32(p.N, 256) < sm_count()) bn = 128;
+    // Dense problems with so few tiles that at least half of the SMs would idle: split K over a cluster
+    // (the widest split whose clusters are all resident at once and leave every CTA some K-blocks).
+    int split = 1;
+    if (p.mode == kDense) {
+        const int bn_s = p.N > 128 ? 256 : 128;
+        const int64_t tiles_s = m_blocks_upper * cdiv32(p.N, bn_s);
+        for (int s2 = bn_s == 256 ? 8 : 4; s2 >= 2; s2 /= 2) {
+            const int kbs = (p.num_k_blocks + s2 - 1) / s2;
+            if (tiles_s * s2 > sm_count() || (s2 - 1) * kbs >= p.num_k_blocks || p.num_k_blocks < 2 * s2) continue;
+            const int resident = bn_s == 256 ? max_active_clusters<256>(s2) : max_active_clusters<128>(s2);
+            if (tiles_s > resident) continue;
+            split = s2;
+            bn = bn_s;
+            break;
+        }
+    }
     p.num_n_blocks = cdiv32(p.N, bn);
     const int64_t max_tiles = m_blocks_upper * p.num_n_blocks;
-    CUtensorMap tmA, tmB;
+    CUtensorMap tmA, tmA64, tmA32, tmB;
     rc = make_tmap(&tmA, A, a_rows, p.K, kBlockM, CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
+    if (rc != KBN_OK) return rc;
+    rc = make_tmap(&tmA64, A, a_rows, p.K, 64, CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
+    if (rc != KBN_OK) return rc;
+    rc = make_tmap(&tmA32, A, a_rows, p.K, 32, CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
     if (rc != KBN_OK) return rc;
     rc = make_tmap(&tmB, B, b_rows, p.K, bn, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
     if (rc != KBN_OK) return rc;
@@ -343,10 +625,13 @@ static int launch(const void* A, int64_t a_rows, const void* B, int64_t b_rows, 
     int64_t grid = sm_count();
     if (max_tiles < grid) grid = max_tiles;
     if (grid <= 0) return KBN_OK;
+    if (split > 1)
+        return bn == 256 ? launch_splitk<256>(tmA, tmA64, tmA32, tmB, p, x, split, max_tiles, st)
+                         : launch_splitk<128>(tmA, tmA64, tmA32, tmB, p, x, split, max_tiles, st);
     if (bn == 256)
-        fp8_gemm_mx_kernel<256><<<(unsigned)grid, kThreads, Cfg<256>::kSmemBytes, st>>>(tmA, tmB, p, x);
+        fp8_gemm_mx_kernel<256><<<(unsigned)grid, kThreads, Cfg<256>::kSmemBytes, st>>>(tmA, tmA64, tmA32, tmB, p, x);
     else
-        fp8_gemm_mx_kernel<128><<<(unsigned)grid, kThreads, Cfg<128>::kSmemBytes, st>>>(tmA, tmB, p, x);
+        fp8_gemm_mx_kernel<128><<<(unsigned)grid, kThreads, Cfg<128>::kSmemBytes, st>>>(tmA, tmA64, tmA32, tmB, p, x);
     KBN_CHECK_LAUNCH();
     return KBN_OK;
 }

@@ -16,34 +16,49 @@ namespace kbn {
 
 constexpr int kAlign = 128;
 
-// Block e ranks, in flat (token, slot) order, the pairs routed to expert e.
+// Block e ranks, in flat (token, slot) order, the pairs routed to expert e: every thread counts the
+// hits in its own contiguous slice of the pairs, one block-wide exclusive scan turns the counts into
+// starting ranks, and a second pass over the slice (still in L1) hands the ranks out.
 __global__ void __launch_bounds__(256)
 moe_rank_kernel(const int32_t* __restrict__ ids, int64_t n_pairs, int32_t* __restrict__ rank,
                 int32_t* __restrict__ counts) {
     const int e = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     __shared__ int warp_tot[8];
-    __shared__ int base_s;
-    if (threadIdx.x == 0) base_s = 0;
-    __syncthreads();
-    for (int64_t i0 = 0; i0 < n_pairs; i0 += 256) {
-        const int64_t i = i0 + threadIdx.x;
-        const bool hit = i < n_pairs && ids[i] == e;
-        const unsigned bal = __ballot_sync(0xffffffffu, hit);
-        if (lane == 0) warp_tot[warp] = __popc(bal);
-        __syncthreads();
-        int before = base_s;
-        for (int w = 0; w < warp; ++w) before += warp_tot[w];
-        if (hit) rank[i] = before + __popc(bal & ((1u << lane) - 1u));
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            int tot = 0;
-            for (int w = 0; w < 8; ++w) tot += warp_tot[w];
-            base_s += tot;
+    const int64_t slice = (((n_pairs + 255) >> 8) + 3) & ~int64_t(3);      // multiple of 4: slices start 16-byte aligned
+    const int64_t lo = min((int64_t)threadIdx.x * slice, n_pairs), hi = min(lo + slice, n_pairs);
+    const bool vec = (reinterpret_cast<uintptr_t>(ids) & 15u) == 0;
+    int cnt = 0;
+    int64_t i = lo;
+    if (vec)
+        for (; i + 4 <= hi; i += 4) {
+            const int4 v = *reinterpret_cast<const int4*>(ids + i);
+            cnt += (v.x == e) + (v.y == e) + (v.z == e) + (v.w == e);
         }
-        __syncthreads();
+    for (; i < hi; ++i) cnt += ids[i] == e;
+    int incl = cnt;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
     }
-    if (threadIdx.x == 0) counts[e] = base_s;
+    if (lane == 31) warp_tot[warp] = incl;
+    __syncthreads();
+    int next = incl - cnt;
+    for (int w = 0; w < warp; ++w) next += warp_tot[w];
+    if (threadIdx.x == 255) counts[e] = next + cnt;
+    if (cnt == 0) return;
+    i = lo;
+    if (vec)
+        for (; i + 4 <= hi; i += 4) {
+            const int4 v = *reinterpret_cast<const int4*>(ids + i);
+            if (v.x == e) rank[i] = next++;
+            if (v.y == e) rank[i + 1] = next++;
+            if (v.z == e) rank[i + 2] = next++;
+            if (v.w == e) rank[i + 3] = next++;
+        }
+    for (; i < hi; ++i)
+        if (ids[i] == e) rank[i] = next++;
 }
 
 // Aligned exclusive scan of the counts (recomputed by every block: E is small) and the per-row
@@ -86,7 +101,7 @@ __global__ void __launch_bounds__(256)
 moe_scatter_kernel(const uint8_t* __restrict__ a_q, const float* __restrict__ a_s, const int32_t* __restrict__ ids,
                    const int32_t* __restrict__ rank, const int32_t* __restrict__ offsets, int64_t n_pairs, int topk,
                    int64_t K, int G, int E, uint8_t* __restrict__ a_perm, float* __restrict__ s_perm,
-                   int32_t* __restrict__ dest) {
+                   int32_t* __restrict__ dest, uint32_t* __restrict__ sf_packed) {
     const int64_t i = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
     if (i >= n_pairs) return;
     const int lane = threadIdx.x & 31;
@@ -100,7 +115,15 @@ moe_scatter_kernel(const uint8_t* __restrict__ a_q, const float* __restrict__ a_
     const uint4* src = reinterpret_cast<const uint4*>(a_q + t * K);
     uint4* dst = reinterpret_cast<uint4*>(a_perm + d * K);
     for (int v = lane; v < (int)(K >> 4); v += 32) dst[v] = __ldg(src + v);
-    for (int g = lane; g < G; g += 32) s_perm[d * G + g] = __ldg(a_s + t * G + g);
+    for (int g = lane; g < G; g += 32) {
+        const float sc = __ldg(a_s + t * G + g);
+        s_perm[d * G + g] = sc;
+        // optional second copy in the packed UE8M0 form the block-scaled GEMM reads: word
+        // ((row/128)*G + g)*128 + (row%32)*4 + (row%128)/32 holds the exponent byte four times
+        if (sf_packed != nullptr)
+            sf_packed[((size_t)(d >> 7) * G + g) * 128u + (size_t)(d & 31) * 4u + (size_t)((d & 127) >> 5)] =
+                ((__float_as_uint(sc) >> 23) & 0xffu) * 0x01010101u;
+    }
     if (lane == 0) dest[i] = (int32_t)d;
 }
 
@@ -140,6 +163,9 @@ moe_combine_kernel(const __nv_bfloat16* __restrict__ rows, int64_t ld_rows, cons
 
 }  // namespace kbn
 
+extern "C" int kbn_moe_permute_sf(const void*, const float*, const int32_t*, int64_t, int64_t, int64_t, int64_t, void*, float*, int32_t*,
+                                  int32_t*, int64_t, void*, int64_t, void*, kbn_stream_t);
+
 extern "C" int64_t kbn_moe_aligned_rows(int64_t T, int64_t topk, int64_t E) {
     int64_t m = T * topk + E * (kbn::kAlign - 1);
     return (m + kbn::kAlign - 1) / kbn::kAlign * kbn::kAlign;
@@ -153,6 +179,14 @@ extern "C" int kbn_moe_permute(const void* a_q, const float* a_s, const int32_t*
                                int64_t K, int64_t E, void* a_perm, float* a_s_perm, int32_t* row_expert,
                                int32_t* dest_row, int64_t M_cap, void* workspace, int64_t workspace_bytes,
                                kbn_stream_t stream) {
+    return kbn_moe_permute_sf(a_q, a_s, topk_ids, T, topk, K, E, a_perm, a_s_perm, row_expert, dest_row, M_cap, workspace,
+                              workspace_bytes, nullptr, stream);
+}
+
+extern "C" int kbn_moe_permute_sf(const void* a_q, const float* a_s, const int32_t* topk_ids, int64_t T, int64_t topk,
+                                  int64_t K, int64_t E, void* a_perm, float* a_s_perm, int32_t* row_expert,
+                                  int32_t* dest_row, int64_t M_cap, void* workspace, int64_t workspace_bytes,
+                                  void* a_sf_packed, kbn_stream_t stream) {
     using namespace kbn;
     KBN_REQUIRE(T >= 0 && topk > 0 && K > 0 && E > 0, KBN_ERR_ARG, "kbn_moe_permute: bad sizes");
     KBN_REQUIRE(K % 128 == 0, KBN_ERR_ARG, "kbn_moe_permute: K=%lld must be a multiple of 128", (long long)K);
@@ -177,7 +211,7 @@ extern "C" int kbn_moe_permute(const void* a_q, const float* a_s, const int32_t*
     if (n_pairs > 0) {
         moe_scatter_kernel<<<(unsigned)((n_pairs + 7) / 8), 256, 0, st>>>(
             static_cast<const uint8_t*>(a_q), a_s, topk_ids, rank, offsets, n_pairs, (int)topk, K, (int)(K / 128), (int)E,
-            static_cast<uint8_t*>(a_perm), a_s_perm, dest_row);
+            static_cast<uint8_t*>(a_perm), a_s_perm, dest_row, static_cast<uint32_t*>(a_sf_packed));
         KBN_CHECK_LAUNCH();
     }
     return KBN_OK;

@@ -165,7 +165,7 @@ __global__ void __launch_bounds__(256)
 silu_mul_quant_kernel(const __nv_bfloat16* __restrict__ in, uint32_t N2, int64_t ld_in, uint8_t* __restrict__ q,
                       int64_t ld_q, float* __restrict__ scale, int64_t s_row, int64_t s_grp, float eps,
                       const uint16_t* __restrict__ table, const int32_t* __restrict__ row_info, uint32_t G,
-                      uint32_t chunks_per_row, uint32_t n_chunks) {
+                      uint32_t chunks_per_row, uint32_t n_chunks, uint32_t* __restrict__ packed) {
     const uint32_t chunk = blockIdx.x * 16u + (threadIdx.x >> 4);
     bool valid = chunk < n_chunks;
     const uint32_t row = valid ? chunk / chunks_per_row : 0u;
@@ -177,7 +177,7 @@ silu_mul_quant_kernel(const __nv_bfloat16* __restrict__ in, uint32_t N2, int64_t
         valid = r >= 0;
         out_row = valid ? (uint32_t)r : 0u;
     }
-    smq_chunk<UE8M0, U>(valid, out_row, g0, threadIdx.x & 15u, in, N2, ld_in, q, ld_q, scale, s_row, s_grp, eps, table, G);
+    smq_chunk<UE8M0, U>(valid, out_row, g0, threadIdx.x & 15u, in, N2, ld_in, q, ld_q, scale, s_row, s_grp, eps, table, G, packed);
 }
 
 // Large inputs: one persistent block of 1024 threads per SM keeps the whole 128 KB exact table in
@@ -188,7 +188,7 @@ __global__ void __launch_bounds__(1024, 1)
 silu_mul_quant_smem_kernel(const __nv_bfloat16* __restrict__ in, uint32_t N2, int64_t ld_in, uint8_t* __restrict__ q,
                            int64_t ld_q, float* __restrict__ scale, int64_t s_row, int64_t s_grp, float eps,
                            const uint16_t* __restrict__ table, const int32_t* __restrict__ row_info, uint32_t G,
-                           uint32_t chunks_per_row, uint32_t n_chunks) {
+                           uint32_t chunks_per_row, uint32_t n_chunks, uint32_t* __restrict__ packed) {
     extern __shared__ __align__(16) uint16_t tab[];
     // every block copies the same 128 KB; each starts at a different offset so that the SMs do not all
     // ask L2 for the same line at the same time
@@ -221,7 +221,7 @@ silu_mul_quant_smem_kernel(const __nv_bfloat16* __restrict__ in, uint32_t N2, in
             if (ROWS == 3) row = valid ? (uint32_t)info : 0u;   // list entry = the row to process
             if (!__any_sync(0xffffffffu, valid)) continue;      // nothing to do for either chunk of this warp
         }
-        smq_chunk<UE8M0, U, true>(valid, row, g0, threadIdx.x & 15u, in, N2, ld_in, q, ld_q, scale, s_row, s_grp, eps, tab, G);
+        smq_chunk<UE8M0, U, true>(valid, row, g0, threadIdx.x & 15u, in, N2, ld_in, q, ld_q, scale, s_row, s_grp, eps, tab, G, packed);
     }
 }
 
@@ -315,7 +315,7 @@ static int launch_silu_mul_quant(const char* who, const void* in, int64_t M, int
     const uint32_t mm = (uint32_t)max_m;
 #define KBN_SMQ(UE, RM)                                                                                                   \
     silu_mul_quant_kernel<UE, U, RM><<<nb, 256, 0, st>>>(ib, (uint32_t)N2, ld_in, qb, ld_q, scale, s_row, s_grp, eps, table, \
-                                                         row_info, (uint32_t)G, (uint32_t)cpr, (uint32_t)n_chunks)
+                                                         row_info, (uint32_t)G, (uint32_t)cpr, (uint32_t)n_chunks, packed)
 #define KBN_SMQ_MASKED(UE)                                                                                                \
     silu_mul_quant_masked_kernel<UE, U><<<dim3(masked_x, (unsigned)(M / max_m)), 256, 0, st>>>(                                  \
         ib, (uint32_t)N2, ld_in, qb, ld_q, scale, s_row, s_grp, eps, table, row_info, mm, (uint32_t)G, (uint32_t)cpr, packed)
@@ -338,13 +338,13 @@ static int launch_silu_mul_quant(const char* who, const void* in, int64_t M, int
         const unsigned grid = (unsigned)sm_count();
         if (rows_mode == 0)
             silu_mul_quant_smem_kernel<true, U2, 0><<<grid, 1024, 131072, st>>>(ib, (uint32_t)N2, ld_in, qb, ld_q, scale, s_row, s_grp, eps, table,
-                                                                               row_info, (uint32_t)G, (uint32_t)cpr2, (uint32_t)n2c);
+                                                                               row_info, (uint32_t)G, (uint32_t)cpr2, (uint32_t)n2c, packed);
         else if (rows_mode == 1)
             silu_mul_quant_smem_kernel<true, U2, 1><<<grid, 1024, 131072, st>>>(ib, (uint32_t)N2, ld_in, qb, ld_q, scale, s_row, s_grp, eps, table,
-                                                                               row_info, (uint32_t)G, (uint32_t)cpr2, (uint32_t)n2c);
+                                                                               row_info, (uint32_t)G, (uint32_t)cpr2, (uint32_t)n2c, packed);
         else
             silu_mul_quant_smem_kernel<true, U2, 3><<<grid, 1024, 131072, st>>>(ib, (uint32_t)N2, ld_in, qb, ld_q, scale, s_row, s_grp, eps, table,
-                                                                               row_info, (uint32_t)G, (uint32_t)cpr2, (uint32_t)n2c);
+                                                                               row_info, (uint32_t)G, (uint32_t)cpr2, (uint32_t)n2c, packed);
     } else if (rows_mode == 2) {
         KBN_REQUIRE(M / max_m <= 65535, KBN_ERR_ARG, "%s: more than 65535 experts", who);
         if (ue8m0) KBN_SMQ_MASKED(true); else KBN_SMQ_MASKED(false);
@@ -384,9 +384,10 @@ extern "C" int kbn_silu_mul_quant_1x128_rows(const void* in, int64_t M, int64_t 
 
 extern "C" int kbn_silu_mul_quant_1x128_list(const void* in, int64_t N2, int64_t ld_in, void* q, int64_t ld_q, float* scale,
                                              int64_t s_row, int64_t s_grp, float eps, int ue8m0, const int32_t* row_list,
-                                             int64_t n_list, kbn_stream_t stream) {
+                                             int64_t n_list, void* sf_packed, kbn_stream_t stream) {
+    KBN_REQUIRE(!sf_packed || ue8m0, KBN_ERR_ARG, "kbn_silu_mul_quant_1x128_list: packed scales need ue8m0");
     return kbn::launch_silu_mul_quant("kbn_silu_mul_quant_1x128_list", in, n_list, N2, ld_in, q, ld_q, scale, s_row, s_grp, eps, ue8m0, 3,
-                                      row_list, 1, static_cast<cudaStream_t>(stream));
+                                      row_list, 1, static_cast<cudaStream_t>(stream), static_cast<uint32_t*>(sf_packed));
 }
 
 extern "C" int kbn_silu_mul_quant_1x128_masked(const void* in, int64_t E, int64_t max_m, int64_t N2, void* q, float* scale,

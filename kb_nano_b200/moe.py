@@ -31,6 +31,9 @@ class MoeScratch:
         self.mm = torch.empty(m_cap * max(2 * i, h), dtype=torch.bfloat16, device=device)
         self.a2_q = torch.empty(m_cap, i, dtype=FP8, device=device)
         self.a2_s = torch.empty(i // 128, m_cap, dtype=torch.float32, device=device).t()
+        # the same scales in the packed form of the UE8M0 GEMMs, written by the permute and the activation kernel
+        self.sf1 = torch.empty(ops.packed_sf_rows_bytes(m_cap, h), dtype=torch.uint8, device=device)
+        self.sf2 = torch.empty(ops.packed_sf_rows_bytes(m_cap, i), dtype=torch.uint8, device=device)
 
     def mm1(self, i: int) -> torch.Tensor:
         return self.mm[: self.m_cap * 2 * i].view(self.m_cap, 2 * i)
@@ -74,16 +77,18 @@ def fused_experts_fp8(hidden_states: torch.Tensor, w13: torch.Tensor, w2: torch.
     if out is None:
         out = torch.empty(t, h, dtype=torch.bfloat16, device=dev)
     ops.per_token_group_quant_fp8(x, sc.a_q, sc.a_s)
-    ops.moe_permute(sc.a_q, sc.a_s, ids, num_experts, sc.a_perm, sc.a_s_perm, sc.row_expert, sc.dest_row, sc.workspace)
     mm1, mm2 = sc.mm1(i), sc.mm2(h)
     # power-of-two weight scales (checked and packed once per tensor) take the UE8M0 block-scaled GEMM
     p13 = ops.packed_weight_scales(w13_scale, n2, h) if use_ue8m0 else None
     p2 = ops.packed_weight_scales(w2_scale, h, i) if use_ue8m0 else None
     if p13 is not None and p2 is not None:
-        ops.m_grouped_fp8_gemm_nt_contiguous_ue8m0(sc.a_perm, ops.pack_sf_rows(sc.a_s_perm, h), w13, p13, mm1, sc.row_expert)
-        ops.silu_mul_quant_fp8_list(mm1, sc.a2_q, sc.a2_s, sc.dest_row.view(-1))
-        ops.m_grouped_fp8_gemm_nt_contiguous_ue8m0(sc.a2_q, ops.pack_sf_rows(sc.a2_s, i), w2, p2, mm2, sc.row_expert)
+        # the permute and the activation kernel emit the packed activation scales themselves
+        ops.moe_permute(sc.a_q, sc.a_s, ids, num_experts, sc.a_perm, sc.a_s_perm, sc.row_expert, sc.dest_row, sc.workspace, sc.sf1)
+        ops.m_grouped_fp8_gemm_nt_contiguous_ue8m0(sc.a_perm, sc.sf1, w13, p13, mm1, sc.row_expert)
+        ops.silu_mul_quant_fp8_list(mm1, sc.a2_q, sc.a2_s, sc.dest_row.view(-1), packed_sf=sc.sf2)
+        ops.m_grouped_fp8_gemm_nt_contiguous_ue8m0(sc.a2_q, sc.sf2, w2, p2, mm2, sc.row_expert)
     else:
+        ops.moe_permute(sc.a_q, sc.a_s, ids, num_experts, sc.a_perm, sc.a_s_perm, sc.row_expert, sc.dest_row, sc.workspace)
         ops.m_grouped_fp8_gemm_nt_contiguous(sc.a_perm, sc.a_s_perm, w13, w13_scale, mm1, sc.row_expert)
         ops.silu_mul_quant_fp8_list(mm1, sc.a2_q, sc.a2_s, sc.dest_row.view(-1))
         ops.m_grouped_fp8_gemm_nt_contiguous(sc.a2_q, sc.a2_s, w2, w2_scale, mm2, sc.row_expert)

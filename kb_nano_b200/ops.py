@@ -110,8 +110,10 @@ def silu_mul_quant_fp8_rows(inp: torch.Tensor, out_fp8: torch.Tensor, out_scale:
 
 
 def silu_mul_quant_fp8_list(inp: torch.Tensor, out_fp8: torch.Tensor, out_scale: torch.Tensor, row_list: torch.Tensor,
-                            use_ue8m0: bool = True, eps: float = 1e-10) -> None:
-    """As silu_mul_quant_fp8, but only the rows listed in row_list (int32, entries < 0 skipped) are processed."""
+                            use_ue8m0: bool = True, eps: float = 1e-10, packed_sf: torch.Tensor | None = None) -> None:
+    """As silu_mul_quant_fp8, but only the rows listed in row_list (int32, entries < 0 skipped) are processed.
+    packed_sf (uint8, packed_sf_rows_bytes(M, N2) bytes) also receives the listed rows' scales in the packed
+    form the *_ue8m0 GEMMs read."""
     dev = _cuda(inp, out_fp8, out_scale, row_list)
     m, n = inp.shape
     n2 = n // 2
@@ -122,10 +124,15 @@ def silu_mul_quant_fp8_list(inp: torch.Tensor, out_fp8: torch.Tensor, out_scale:
     if row_list.dtype != torch.int32 or not row_list.is_contiguous():
         raise ValueError("row_list must be contiguous int32")
     s_row, s_grp = _scale_strides(out_scale, m, n2 // GROUP)
+    sf_ptr = None
+    if packed_sf is not None:
+        _check_packed(packed_sf, m, n2, dev)
+        sf_ptr = packed_sf.data_ptr()
     with _on(dev):
         _lib.check(_lib.load().kbn_silu_mul_quant_1x128_list(inp.data_ptr(), n2, inp.stride(0) if m > 1 else n, out_fp8.data_ptr(),
                                                              out_fp8.stride(0) if m > 1 else n2, out_scale.data_ptr(), s_row, s_grp,
-                                                             eps, int(use_ue8m0), row_list.data_ptr(), row_list.numel(), _stream(inp)))
+                                                             eps, int(use_ue8m0), row_list.data_ptr(), row_list.numel(), sf_ptr,
+                                                             _stream(inp)))
 
 
 def silu_mul_quant_fp8_masked(inp: torch.Tensor, out_fp8: torch.Tensor, out_scale: torch.Tensor, masked_m: torch.Tensor) -> None:
@@ -242,8 +249,10 @@ def moe_aligned_rows(t: int, topk: int, e: int) -> int:
 
 def moe_permute(a_q: torch.Tensor, a_s: torch.Tensor, topk_ids: torch.Tensor, num_experts: int,
                 a_perm: torch.Tensor, a_s_perm: torch.Tensor, row_expert: torch.Tensor, dest_row: torch.Tensor,
-                workspace: torch.Tensor) -> None:
-    """Group quantised rows by expert into 128-aligned segments (all outputs caller-allocated)."""
+                workspace: torch.Tensor, packed_sf: torch.Tensor | None = None) -> None:
+    """Group quantised rows by expert into 128-aligned segments (all outputs caller-allocated).  packed_sf
+    (uint8, packed_sf_rows_bytes(M_cap, K) bytes) also receives the moved rows' scales in the packed form
+    the *_ue8m0 GEMMs read."""
     dev = _cuda(a_q, a_s, topk_ids, a_perm, a_s_perm, row_expert, dest_row, workspace)
     t, k = a_q.shape
     topk = topk_ids.shape[1]
@@ -262,10 +271,14 @@ def moe_permute(a_q: torch.Tensor, a_s: torch.Tensor, topk_ids: torch.Tensor, nu
     if dest_row.dtype != torch.int32 or tuple(dest_row.shape) != (t, topk) or not dest_row.is_contiguous():
         raise ValueError("dest_row must be contiguous int32 [T, topk]")
     ws_bytes = workspace.numel() * workspace.element_size()
+    sf_ptr = None
+    if packed_sf is not None:
+        _check_packed(packed_sf, m_cap, k, dev)
+        sf_ptr = packed_sf.data_ptr()
     with _on(dev):
-        _lib.check(_lib.load().kbn_moe_permute(a_q.data_ptr(), a_s.data_ptr(), topk_ids.data_ptr(), t, topk, k, num_experts,
-                                               a_perm.data_ptr(), a_s_perm.data_ptr(), row_expert.data_ptr(),
-                                               dest_row.data_ptr(), m_cap, workspace.data_ptr(), ws_bytes, _stream(a_q)))
+        _lib.check(_lib.load().kbn_moe_permute_sf(a_q.data_ptr(), a_s.data_ptr(), topk_ids.data_ptr(), t, topk, k, num_experts,
+                                                  a_perm.data_ptr(), a_s_perm.data_ptr(), row_expert.data_ptr(),
+                                                  dest_row.data_ptr(), m_cap, workspace.data_ptr(), ws_bytes, sf_ptr, _stream(a_q)))
 
 
 def moe_permute_workspace_bytes(t: int, topk: int, e: int) -> int:
@@ -291,6 +304,17 @@ def moe_unpermute_combine(rows: torch.Tensor, dest_row: torch.Tensor, topk_w: to
 
 
 # ---- UE8M0 fast path: packed power-of-two scales, block-scaled tensor-core instruction -------------
+
+def packed_sf_rows_bytes(rows: int, k: int) -> int:
+    return int(_lib.load().kbn_packed_sf_rows_bytes(rows, k))
+
+
+def _check_packed(buf: torch.Tensor, rows: int, k: int, dev) -> None:
+    if buf.dtype != torch.uint8 or not buf.is_contiguous() or buf.device != dev or buf.numel() < packed_sf_rows_bytes(rows, k):
+        raise ValueError(f"packed scale buffer must be contiguous uint8 on {dev} with at least {packed_sf_rows_bytes(rows, k)} bytes")
+    if buf.data_ptr() % 16:
+        raise ValueError("packed scale buffer must be 16-byte aligned")
+
 
 def pack_sf_rows(scale: torch.Tensor, k: int) -> torch.Tensor:
     """fp32 scales [..., rows, ceil(K/128)] (any strides on the last two dims; leading dims contiguous over

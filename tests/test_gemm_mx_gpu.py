@@ -37,6 +37,20 @@ def test_mx_dense_shapes(cuda_dev, m, n, k):
     assert_gemm_close(run_dense_mx(a_q, a_s, w_q, w_s, cuda_dev), ref, f"dense ue8m0 {m}x{n}x{k}")
 
 
+@pytest.mark.parametrize("m,n,k", [(1, 4096, 7168), (16, 4096, 7168), (33, 7168, 2048), (100, 1000, 1040), (128, 128, 1024), (96, 384, 2048),
+                                   (200, 512, 4096)])
+def test_mx_dense_few_tiles_split_k(cuda_dev, m, n, k):
+    """Decode-sized problems: K is split over a thread-block cluster and the partial tiles are summed through
+    distributed shared memory (splits of 8, 8, 4, 2, 4, 8, 8 CTAs here; ragged N and K in the fourth case).
+    Two runs must agree bit for bit (the partials are added in a fixed order)."""
+    a_q, a_s, w_q, w_s = make_dense(m, n, k, seed=m + n + k, dev=cuda_dev)
+    ref = to.gemm_nt_dequant(a_q, a_s, w_q, w_s)
+    out1 = run_dense_mx(a_q, a_s, w_q, w_s, cuda_dev)
+    assert_gemm_close(out1, ref, f"dense ue8m0 split-K {m}x{n}x{k}")
+    out2 = run_dense_mx(a_q, a_s, w_q, w_s, cuda_dev)
+    assert torch.equal(out1.view(torch.int16), out2.view(torch.int16))
+
+
 def test_mx_scales_with_wide_exponent_range(cuda_dev):
     """Each K-block and each row with a different power-of-two scale: catches any mix-up of the packed order."""
     m, n, k = 256, 512, 1024

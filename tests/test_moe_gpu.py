@@ -38,6 +38,34 @@ def test_permute_matches_reference_layout(cuda_dev):
     assert (s_perm.numpy()[valid] == g["as_perm"][valid]).all()
 
 
+@pytest.mark.parametrize("t,topk,e,k", [(37, 3, 5, 256), (700, 8, 64, 512), (1, 2, 4, 128)])
+def test_permute_emits_packed_scales(cuda_dev, t, topk, e, k):
+    """The packed UE8M0 copy of the scales written by the permute equals packing the permuted fp32 scales
+    afterwards; the id tensor starts 12 bytes into an allocation in the first case (unaligned ranking path)."""
+    from kb_nano_b200 import ops
+    gen = torch.Generator().manual_seed(t + k)
+    a_q = torch.randint(0, 255, (t, k), dtype=torch.uint8, generator=gen).view(FP8).to(cuda_dev)
+    a_s = torch.exp2(torch.randint(-20, 10, (t, k // 128), generator=gen).float()).to(cuda_dev)
+    ids_all = torch.randint(0, e, (t + 1, topk), dtype=torch.int32, generator=gen).to(cuda_dev)
+    ids = ids_all[1:]
+    m_cap = ops.moe_aligned_rows(t, topk, e)
+    outs = []
+    for fused in (False, True):
+        a_perm = torch.zeros(m_cap, k, dtype=torch.uint8, device=cuda_dev).view(FP8)
+        s_perm = torch.zeros(m_cap, k // 128, device=cuda_dev)
+        row_expert = torch.empty(m_cap, dtype=torch.int32, device=cuda_dev)
+        dest = torch.empty(t, topk, dtype=torch.int32, device=cuda_dev)
+        ws = torch.empty(ops.moe_permute_workspace_bytes(t, topk, e), dtype=torch.uint8, device=cuda_dev)
+        sf = torch.zeros(ops.packed_sf_rows_bytes(m_cap, k), dtype=torch.uint8, device=cuda_dev)
+        ops.moe_permute(a_q, a_s, ids, e, a_perm, s_perm, row_expert, dest, ws, sf if fused else None)
+        outs.append((a_perm.view(torch.uint8).cpu(), s_perm.cpu(), row_expert.cpu(), dest.cpu(), sf.cpu(), ops.pack_sf_rows(s_perm, k).cpu()))
+    for x, y in zip(outs[0][:4], outs[1][:4]):
+        assert torch.equal(x, y)
+    assert not outs[0][4].any()                        # not requested: untouched
+    assert torch.equal(outs[1][4], outs[1][5])         # padding rows: scale 0.0 packs to exponent byte 0 = the pre-zeroed buffer
+    assert outs[1][4].any()
+
+
 def test_combine_matches_reference(cuda_dev):
     from kb_nano_b200 import ops
     g = golden("permute")
@@ -50,7 +78,7 @@ def test_combine_matches_reference(cuda_dev):
     assert_gemm_close(out.cpu(), ref, "combine")
 
 
-@pytest.mark.parametrize("t,topk,e", [(1, 1, 1), (7, 2, 3), (300, 8, 64), (128, 8, 256), (64, 4, 5)])
+@pytest.mark.parametrize("t,topk,e", [(1, 1, 1), (7, 2, 3), (300, 8, 64), (128, 8, 256), (64, 4, 5), (1000, 3, 17), (2048, 8, 256)])
 def test_permute_properties(cuda_dev, t, topk, e):
     """Stable grouping with 128-aligned segments, for shapes with empty experts and every token on one expert."""
     gen = torch.Generator().manual_seed(t * 31 + e)

@@ -279,7 +279,11 @@ def test_silu_mul_quant_row_list(cuda_dev, m, n2):
     q = torch.full((m, n2), 0x55, dtype=torch.uint8, device=cuda_dev).view(FP8)
     s = torch.full((n2 // 128, m), 7.0, device=cuda_dev).t()
     pad = torch.cat([rows, torch.full((m * 8,), -1, dtype=torch.int32)]) if m == 4096 else rows   # long list -> persistent kernel
-    ops.silu_mul_quant_fp8_list(x.to(cuda_dev), q, s, pad.to(cuda_dev))
+    sf = torch.zeros(ops.packed_sf_rows_bytes(m, n2), dtype=torch.uint8, device=cuda_dev)
+    ops.silu_mul_quant_fp8_list(x.to(cuda_dev), q, s, pad.to(cuda_dev), packed_sf=sf)
+    # the packed copy of the scales equals packing the fp32 scales of the processed rows afterwards
+    s_done = torch.where(s == 7.0, torch.zeros_like(s), s)
+    assert torch.equal(sf.cpu(), ops.pack_sf_rows(s_done, n2).cpu())
     qr, sr = co.silu_mul_quant_1x128(bits16(x))
     done = np.zeros(m, bool)
     done[rows[rows >= 0].numpy()] = True
