@@ -172,6 +172,25 @@ int kbn_fp8_grouped_gemm_masked_ue8m0(const void* A, const void* sfa_packed, con
                                       int64_t E, int64_t max_m, int64_t N, int64_t K,
                                       kbn_stream_t stream);
 
+/* Grouped GEMM1 of the MoE expert MLP with the activation applied in its epilogue (UE8M0 path):
+ * W13 is [E, 2*I, K] with an expert's I gate rows followed by its I up rows
+ * (tasks/baseline/L2/fused_experts.py:263-274 runs m_grouped_fp8_gemm_nt_contiguous, stores bf16
+ * [M, 2*I] and then SiluMulQuantFp8); sfb_packed is kbn_pack_sf_weights of its [E, 2*I/128, K/128] scales.
+ * Output: q e4m3 [rows, I] (row stride ld_q), scale fp32 with element strides (s_row, s_grp), and, when
+ * sf_packed is not null, the same scales in the packed form (kbn_packed_sf_rows_bytes(rows, I) bytes) that
+ * GEMM2 reads.  Bit-identical to kbn_fp8_grouped_gemm_*_ue8m0 into a bf16 buffer followed by
+ * kbn_silu_mul_quant_1x128 (ue8m0, eps 1e-10) on it; rows that hold no data are not written.
+ * I must be a multiple of 128.  The masked form writes q [E, max_m, I] and row-major scales [E, max_m, I/128]. */
+int kbn_fp8_grouped_gemm_contig_ue8m0_silu(const void* A, const void* sfa_packed, const void* W13,
+                                           const void* sfb_packed, void* q, int64_t ld_q, float* scale,
+                                           int64_t s_row, int64_t s_grp, void* sf_packed,
+                                           const int32_t* row_expert, int64_t M_sum, int64_t I, int64_t K,
+                                           int64_t E, kbn_stream_t stream);
+int kbn_fp8_grouped_gemm_masked_ue8m0_silu(const void* A, const void* sfa_packed, const void* W13,
+                                           const void* sfb_packed, void* q, float* scale, void* sf_packed,
+                                           const int32_t* masked_m, int64_t E, int64_t max_m, int64_t I,
+                                           int64_t K, kbn_stream_t stream);
+
 /*
  * Load-time re-quantisation of block-scaled FP8 weights to power-of-two scales, in place:
  * per 128x128 block  w = fp32(w_fp8) * scale,  scale <- 2^ceil(log2(max(max|w|, eps) / 448)),

@@ -39,6 +39,8 @@ SIGNATURES = {
     "kbn_fp8_gemm_nt_ue8m0": (_i32, [_ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _ptr]),
     "kbn_fp8_grouped_gemm_contig_ue8m0": (_i32, [_ptr, _ptr, _ptr, _ptr, _ptr, _i64, _ptr, _i64, _i64, _i64, _i64, _ptr]),
     "kbn_fp8_grouped_gemm_masked_ue8m0": (_i32, [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _ptr]),
+    "kbn_fp8_grouped_gemm_contig_ue8m0_silu": (_i32, [_ptr, _ptr, _ptr, _ptr, _ptr, _i64, _ptr, _i64, _i64, _ptr, _ptr, _i64, _i64, _i64, _i64, _ptr]),
+    "kbn_fp8_grouped_gemm_masked_ue8m0_silu": (_i32, [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _ptr]),
     "kbn_moe_aligned_rows": (_i64, [_i64, _i64, _i64]),
     "kbn_moe_permute_workspace_bytes": (_i64, [_i64, _i64, _i64]),
     "kbn_moe_permute": (_i32, [_ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _ptr, _ptr, _ptr, _ptr, _i64, _ptr, _i64, _ptr]),

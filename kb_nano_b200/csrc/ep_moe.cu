@@ -208,6 +208,8 @@ __global__ void ep_iota_kernel(int32_t* p, int n) {
 
 extern "C" int kbn_moe_unpermute_combine(const void*, int64_t, const int32_t*, const float*, int64_t, int64_t, int64_t, void*, kbn_stream_t);
 extern "C" int kbn_quant_1x128(const void*, int64_t, int64_t, int64_t, void*, int64_t, float*, int64_t, int64_t, float, int, kbn_stream_t);
+extern "C" int kbn_fp8_grouped_gemm_masked_ue8m0_silu(const void*, const void*, const void*, const void*, void*, float*, void*, const int32_t*,
+                                                      int64_t, int64_t, int64_t, int64_t, kbn_stream_t);
 
 extern "C" int kbn_ep_create(int rank, int world, int64_t experts_total, int64_t max_m, int64_t hidden, int64_t inter,
                              int64_t max_tokens, int64_t topk, kbn_ep_ctx** out) {
@@ -314,13 +316,16 @@ extern "C" int kbn_ep_moe_forward(kbn_ep_ctx* c, const void* x_bf16, const int32
     const float* recv_s = reinterpret_cast<const float*>(mine + c->lay.recv_s);
     const int64_t rows_all = c->e_local * c->max_m;
     if (ue8m0) {
-        rc = kbn_fp8_grouped_gemm_masked_ue8m0(mine + c->lay.recv_q, mine + c->lay.recv_sf, w13, w13_sf_packed, c->mm1, counters, c->e_local, c->max_m, 2 * I, H, stream);
+        // GEMM1 with SiLU(gate)*up and the 1x128 quantisation in its epilogue
+        rc = kbn_fp8_grouped_gemm_masked_ue8m0_silu(mine + c->lay.recv_q, mine + c->lay.recv_sf, w13, w13_sf_packed, c->a2_q, c->a2_s, c->sf2,
+                                                    counters, c->e_local, c->max_m, I, H, stream);
+        if (rc != KBN_OK) return rc;
     } else {
         rc = kbn_fp8_grouped_gemm_masked(mine + c->lay.recv_q, recv_s, c->max_m * G, G, 1, w13, w13_s, c->mm1, counters, c->e_local, c->max_m, 2 * I, H, stream);
+        if (rc != KBN_OK) return rc;
+        rc = silu_mul_quant_masked(c->mm1, c->e_local, c->max_m, I, c->a2_q, c->a2_s, counters, st, nullptr);
+        if (rc != KBN_OK) return rc;
     }
-    if (rc != KBN_OK) return rc;
-    rc = silu_mul_quant_masked(c->mm1, c->e_local, c->max_m, I, c->a2_q, c->a2_s, counters, st, ue8m0 ? c->sf2 : nullptr);
-    if (rc != KBN_OK) return rc;
     if (ue8m0) {
         rc = kbn_fp8_grouped_gemm_masked_ue8m0(c->a2_q, c->sf2, w2, w2_sf_packed, c->mm2, counters, c->e_local, c->max_m, H, I, stream);
     } else {

@@ -25,6 +25,14 @@ struct GemmParams {
     int32_t N, K, E, max_m;
     int32_t num_m_blocks, num_n_blocks, num_k_blocks, sb_nb;
     int32_t mode;
+    // fused activation epilogue (UE8M0 kernel only): N counts output columns, B holds 2*N rows per expert
+    // (gate rows, then up rows); the tile's 128 outputs per row are quantised as one 1x128 group
+    uint8_t* act_q;            // e4m3 [rows, N], row stride act_ld
+    int64_t act_ld;
+    float* act_scale;          // fp32 scales, element strides (act_s_row, act_s_grp)
+    int64_t act_s_row, act_s_grp;
+    uint32_t* act_packed;      // optional packed UE8M0 copy of the scales
+    const uint16_t* act_table; // exactly rounded bf16 SiLU table
 };
 
 struct Tile {

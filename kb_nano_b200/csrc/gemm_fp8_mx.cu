@@ -18,6 +18,7 @@
 #include <cuda.h>
 
 #include "gemm_common.cuh"
+#include "silu_exact.cuh"
 
 namespace kbn {
 namespace mx {
@@ -33,7 +34,7 @@ struct Cfg {
     static constexpr int kSfbBytes = 512 * (BN / 128);
     static constexpr int kSfStage = 512 + kSfbBytes;
     static constexpr int kTxBytes = kStageBytes + kSfStage;
-    static constexpr size_t kSmemBytes = (size_t)kStages * (kStageBytes + kSfStage) + 1024 + 256;
+    static constexpr size_t kSmemBytes = (size_t)kStages * (kStageBytes + kSfStage) + 1024 + 256 + 2048;
 };
 constexpr int kABytes = kBlockM * kBlockK;          // 16 KB
 constexpr int kSfaBytes = 512;
@@ -48,7 +49,11 @@ struct MxExtra {
     int32_t nb_pad;          // 128-column blocks per expert, rounded up to even
 };
 
-template <int BN>
+// ACT: the tile's B operand is 128 gate rows and the matching 128 up rows of a [2N, K] weight, and the
+// epilogue computes y = bf16(bf16(silu(gate)) * up) on the bf16-rounded accumulators and quantises the
+// 128 outputs of each row as one 1x128 group (UE8M0 scale, eps 1e-10) -- the same bits as storing the
+// bf16 GEMM result and running the stand-alone activation kernel on it, without the round trip.
+template <int BN, bool ACT>
 __global__ void __launch_bounds__(kThreads, 1)
 fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmA64,
                    const __grid_constant__ CUtensorMap tmA32, const __grid_constant__ CUtensorMap tmB, const GemmParams p,
@@ -60,13 +65,15 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~(uintptr_t)1023u);
     uint8_t* sf_smem = smem + (size_t)kStages * kStageBytes;
     uint64_t* bars = reinterpret_cast<uint64_t*>(sf_smem + (size_t)kStages * kSfStage);
-    // bars: full[kStages], empty[kStages], tmem_full, tmem_empty
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 2);
+    // bars: full[kStages], empty[kStages], tmem_full, tmem_empty, pair[4] (the two epilogue warps of a lane quarter)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 6);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    float* xch = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + 256);     // [parity][half][128 rows]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t bar_full = ptx::smem_u32(bars), bar_empty = ptx::smem_u32(bars + kStages);
     const uint32_t bar_tfull = ptx::smem_u32(bars + 2 * kStages), bar_tempty = ptx::smem_u32(bars + 2 * kStages + 1);
+    const uint32_t bar_pair = ptx::smem_u32(bars + 2 * kStages + 2);
     const uint32_t smem_tiles = ptx::smem_u32(smem), smem_sf = ptx::smem_u32(sf_smem);
 
     if (threadIdx.x == 0) {
@@ -76,6 +83,7 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         }
         ptx::mbar_init(bar_tfull, 1);
         ptx::mbar_init(bar_tempty, kEpiWarps);
+        for (int q = 0; q < 4; ++q) ptx::mbar_init(bar_pair + 8 * q, 2);
         *abort_flag = 0;
         ptx::fence_barrier_init();
         ptx::fence_proxy_async();
@@ -121,9 +129,10 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                 live = __reduce_max_sync(0xffffffffu, last) + 1;
             }
             if (lane == 0) {
-                const int32_t b_row = tile.expert * p.N + tile.n_blk * kBN;
+                // ACT: n_blk counts 128 output columns; gate rows of the expert come first, up rows N later
+                const int32_t b_row = ACT ? tile.expert * 2 * p.N + tile.n_blk * 128 : tile.expert * p.N + tile.n_blk * kBN;
                 const uint8_t* sfa = x.sfa + (int64_t)(tile.row0 / kBlockM) * KB * kSfaBytes;
-                const uint8_t* sfb = x.sfb + (((int64_t)tile.expert * KB) * x.nb_pad + (BN / 128) * tile.n_blk) * (int64_t)kSfaBytes;
+                const uint8_t* sfb = x.sfb + (((int64_t)tile.expert * KB) * x.nb_pad + (ACT ? 1 : BN / 128) * tile.n_blk) * (int64_t)kSfaBytes;
                 const CUtensorMap* tma = live <= 32 ? &tmA32 : (live <= 64 ? &tmA64 : &tmA);
                 const uint32_t tx = (uint32_t)(kTxBytes - kABytes) + (live <= 32 ? 32u : (live <= 64 ? 64u : 128u)) * (uint32_t)kBlockK;
                 for (int kb = 0; kb < KB; ++kb, ++it) {
@@ -133,10 +142,19 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                     ptx::mbar_arrive_expect_tx(bar, tx);
                     const uint32_t dst = smem_tiles + s * kStageBytes;
                     ptx::tma_load_2d(dst, tma, kb * kBlockK, tile.row0, bar);
-                    ptx::tma_load_2d(dst + kABytes, &tmB, kb * kBlockK, b_row, bar);
                     const uint32_t sdst = smem_sf + s * kSfStage;
                     ptx::bulk_load(sdst, sfa + (int64_t)kb * kSfaBytes, kSfaBytes, bar);
-                    ptx::bulk_load(sdst + kSfaBytes, sfb + (int64_t)kb * x.nb_pad * kSfaBytes, kSfbBytes, bar);
+                    if (ACT) {
+                        // tmB's box is 128 rows here: gate rows fill the first half of the B tile, up rows the second
+                        ptx::tma_load_2d(dst + kABytes, &tmB, kb * kBlockK, b_row, bar);
+                        ptx::tma_load_2d(dst + kABytes + 128 * kBlockK, &tmB, kb * kBlockK, b_row + p.N, bar);
+                        const uint8_t* sg = sfb + (int64_t)kb * x.nb_pad * kSfaBytes;
+                        ptx::bulk_load(sdst + kSfaBytes, sg, kSfaBytes, bar);
+                        ptx::bulk_load(sdst + 2 * kSfaBytes, sg + (int64_t)(p.N / 128) * kSfaBytes, kSfaBytes, bar);
+                    } else {
+                        ptx::tma_load_2d(dst + kABytes, &tmB, kb * kBlockK, b_row, bar);
+                        ptx::bulk_load(sdst + kSfaBytes, sfb + (int64_t)kb * x.nb_pad * kSfaBytes, kSfbBytes, bar);
+                    }
                 }
             }
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
@@ -208,14 +226,75 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             // global stores overlap the next tile's MMAs.
             constexpr int kChunks = kHalfCols / 32;
             uint32_t r[kChunks][32];
+            if (ACT) {
+                // gate columns [64*half, +64) into r[0..1], the matching up columns (128 further) into r[2..3]
+                const uint32_t tq = tmem_base + ((uint32_t)(quarter * 32) << 16) + half * 64;
 #pragma unroll
-            for (int c = 0; c < kChunks; ++c) ptx::tmem_ld_32x32(taddr + 32 * c, r[c]);
+                for (int c = 0; c < kChunks; ++c) ptx::tmem_ld_32x32(tq + (c >> 1) * 128 + (c & 1) * 32, r[c]);
+            } else {
+#pragma unroll
+                for (int c = 0; c < kChunks; ++c) ptx::tmem_ld_32x32(taddr + 32 * c, r[c]);
+            }
 #pragma unroll
             for (int c = 0; c < kChunks; ++c) ptx::tmem_ld_wait(r[c]);
             ptx::tc_fence_before();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(bar_tempty);
-            if (row_ok) {
+            if (ACT) {
+                // y = bf16(bf16(silu(bf16(gate))) * bf16(up)) for this thread's 64 outputs, packed two per word
+                uint32_t y[32];
+#pragma unroll
+                for (int c = 0; c < 2; ++c)
+#pragma unroll
+                    for (int j = 0; j < 32; j += 8) {
+                        uint4 g, u;
+                        g.x = pack_bf16x2(__uint_as_float(r[c][j + 0]), __uint_as_float(r[c][j + 1]));
+                        g.y = pack_bf16x2(__uint_as_float(r[c][j + 2]), __uint_as_float(r[c][j + 3]));
+                        g.z = pack_bf16x2(__uint_as_float(r[c][j + 4]), __uint_as_float(r[c][j + 5]));
+                        g.w = pack_bf16x2(__uint_as_float(r[c][j + 6]), __uint_as_float(r[c][j + 7]));
+                        u.x = pack_bf16x2(__uint_as_float(r[2 + c][j + 0]), __uint_as_float(r[2 + c][j + 1]));
+                        u.y = pack_bf16x2(__uint_as_float(r[2 + c][j + 2]), __uint_as_float(r[2 + c][j + 3]));
+                        u.z = pack_bf16x2(__uint_as_float(r[2 + c][j + 4]), __uint_as_float(r[2 + c][j + 5]));
+                        u.w = pack_bf16x2(__uint_as_float(r[2 + c][j + 6]), __uint_as_float(r[2 + c][j + 7]));
+                        uint32_t y4[4];
+                        silu_mul_8(g, u, p.act_table, y4);
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) y[(c * 32 + j) / 2 + q] = y4[q];
+                    }
+                uint32_t m2 = abs_bf16x2(y[0]);
+#pragma unroll
+                for (int i = 1; i < 32; ++i) m2 = max_bf16x2(m2, abs_bf16x2(y[i]));
+                float amax = fmaxf(bf16_lo(m2), bf16_hi(m2));
+                // the other half of the row's 128 outputs sits in the partner warp of this lane quarter
+                const uint32_t par = tile_it & 1u;
+                xch[(par * 2u + (uint32_t)half) * 128u + (uint32_t)r_in_tile] = amax;
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(bar_pair + 8 * quarter);
+                if (!wait_bar(bar_pair + 8 * quarter, par, w)) { ok = false; break; }
+                amax = fmaxf(fmaxf(amax, xch[(par * 2u + (uint32_t)(half ^ 1)) * 128u + (uint32_t)r_in_tile]), 1e-10f);
+                const uint32_t f = ue8m0_scale_field(amax);
+                const float inv = __uint_as_float((254u - f) << 23);
+                if (row_ok) {
+                    uint8_t* qrow = p.act_q + (int64_t)row * p.act_ld + tile.n_blk * 128 + half * 64;
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        uint32_t o[4];
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const uint32_t w0 = y[i + 2 * q], w1 = y[i + 2 * q + 1];
+                            o[q] = pack_e4m3x2(__fmul_rn(bf16_lo(w0), inv), __fmul_rn(bf16_hi(w0), inv)) |
+                                   (pack_e4m3x2(__fmul_rn(bf16_lo(w1), inv), __fmul_rn(bf16_hi(w1), inv)) << 16);
+                        }
+                        *reinterpret_cast<uint4*>(qrow + 2 * i) = make_uint4(o[0], o[1], o[2], o[3]);
+                    }
+                    if (half == 0) {
+                        p.act_scale[(int64_t)row * p.act_s_row + (int64_t)tile.n_blk * p.act_s_grp] = __uint_as_float(f << 23);
+                        if (p.act_packed != nullptr)
+                            p.act_packed[((size_t)(row >> 7) * p.num_n_blocks + tile.n_blk) * 128u + (row & 31) * 4 + ((row & 127) >> 5)] =
+                                f * 0x01010101u;
+                    }
+                }
+            } else if (row_ok) {
 #pragma unroll
                 for (int c = 0; c < kChunks; ++c) {
                     if (n0 + 32 * c + 32 <= p.N && vec_ok) {
@@ -518,8 +597,9 @@ static int check_device() {
         int major = 0;
         KBN_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
         KBN_REQUIRE(major == 10, KBN_ERR_UNSUPPORTED, "kbn_fp8 GEMMs need an sm_100 device (found major %d)", major);
-        KBN_CUDA(cudaFuncSetAttribute(fp8_gemm_mx_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<256>::kSmemBytes));
-        KBN_CUDA(cudaFuncSetAttribute(fp8_gemm_mx_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<128>::kSmemBytes));
+        KBN_CUDA(cudaFuncSetAttribute(fp8_gemm_mx_kernel<256, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<256>::kSmemBytes));
+        KBN_CUDA(cudaFuncSetAttribute(fp8_gemm_mx_kernel<256, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<256>::kSmemBytes));
+        KBN_CUDA(cudaFuncSetAttribute(fp8_gemm_mx_kernel<128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<128>::kSmemBytes));
         KBN_CUDA(cudaFuncSetAttribute(fp8_gemm_mx_splitk_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<256>::kSmemBytes));
         KBN_CUDA(cudaFuncSetAttribute(fp8_gemm_mx_splitk_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<128>::kSmemBytes));
         ok[dev] = 1;
@@ -578,8 +658,9 @@ static int launch_splitk(const CUtensorMap& tmA, const CUtensorMap& tmA64, const
 }
 
 // m_blocks_upper: number of 128-row blocks (an upper bound in the masked form).
+// act: fused activation epilogue (p.act_* filled in, p.N = output columns, B has 2*p.N rows per expert).
 static int launch(const void* A, int64_t a_rows, const void* B, int64_t b_rows, GemmParams& p, const void* sfa, const void* sfb,
-                  int64_t m_blocks_upper, cudaStream_t st) {
+                  int64_t m_blocks_upper, cudaStream_t st, bool act = false) {
     int rc = check_device();
     if (rc != KBN_OK) return rc;
     KBN_REQUIRE(sfa && sfb, KBN_ERR_ARG, "fp8 gemm (ue8m0): null packed scales");
@@ -605,7 +686,11 @@ static int launch(const void* A, int64_t a_rows, const void* B, int64_t b_rows, 
             break;
         }
     }
-    p.num_n_blocks = cdiv32(p.N, bn);
+    if (act) {           // 128 output columns (= 256 weight rows) per tile
+        bn = 256;
+        split = 1;
+    }
+    p.num_n_blocks = act ? cdiv32(p.N, 128) : cdiv32(p.N, bn);
     const int64_t max_tiles = m_blocks_upper * p.num_n_blocks;
     CUtensorMap tmA, tmA64, tmA32, tmB;
     rc = make_tmap(&tmA, A, a_rows, p.K, kBlockM, CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
@@ -614,24 +699,26 @@ static int launch(const void* A, int64_t a_rows, const void* B, int64_t b_rows, 
     if (rc != KBN_OK) return rc;
     rc = make_tmap(&tmA32, A, a_rows, p.K, 32, CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
     if (rc != KBN_OK) return rc;
-    rc = make_tmap(&tmB, B, b_rows, p.K, bn, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+    rc = make_tmap(&tmB, B, b_rows, p.K, act ? 128 : bn, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
     if (rc != KBN_OK) return rc;
     rc = gemm_status_ptr(&p.status);
     if (rc != KBN_OK) return rc;
     MxExtra x;
     x.sfa = static_cast<const uint8_t*>(sfa);
     x.sfb = static_cast<const uint8_t*>(sfb);
-    x.nb_pad = (cdiv32(p.N, 128) + 1) / 2 * 2;
+    x.nb_pad = (cdiv32(act ? 2 * (int64_t)p.N : p.N, 128) + 1) / 2 * 2;
     int64_t grid = sm_count();
     if (max_tiles < grid) grid = max_tiles;
     if (grid <= 0) return KBN_OK;
     if (split > 1)
         return bn == 256 ? launch_splitk<256>(tmA, tmA64, tmA32, tmB, p, x, split, max_tiles, st)
                          : launch_splitk<128>(tmA, tmA64, tmA32, tmB, p, x, split, max_tiles, st);
-    if (bn == 256)
-        fp8_gemm_mx_kernel<256><<<(unsigned)grid, kThreads, Cfg<256>::kSmemBytes, st>>>(tmA, tmA64, tmA32, tmB, p, x);
+    if (act)
+        fp8_gemm_mx_kernel<256, true><<<(unsigned)grid, kThreads, Cfg<256>::kSmemBytes, st>>>(tmA, tmA64, tmA32, tmB, p, x);
+    else if (bn == 256)
+        fp8_gemm_mx_kernel<256, false><<<(unsigned)grid, kThreads, Cfg<256>::kSmemBytes, st>>>(tmA, tmA64, tmA32, tmB, p, x);
     else
-        fp8_gemm_mx_kernel<128><<<(unsigned)grid, kThreads, Cfg<128>::kSmemBytes, st>>>(tmA, tmA64, tmA32, tmB, p, x);
+        fp8_gemm_mx_kernel<128, false><<<(unsigned)grid, kThreads, Cfg<128>::kSmemBytes, st>>>(tmA, tmA64, tmA32, tmB, p, x);
     KBN_CHECK_LAUNCH();
     return KBN_OK;
 }
@@ -732,4 +819,65 @@ extern "C" int kbn_fp8_grouped_gemm_masked_ue8m0(const void* A, const void* sfa_
     mx::fill_params(p, C, N, E * max_m, N, K, E, max_m, kMasked);
     p.masked_m = masked_m;
     return mx::launch(A, E * max_m, B, E * N, p, sfa_packed, sfb_packed, E * ((max_m + 127) / 128), static_cast<cudaStream_t>(stream));
+}
+
+// ---- grouped GEMM1 with the activation in the epilogue ------------------------------------------
+
+namespace kbn {
+namespace mx {
+
+static int fill_act(GemmParams& p, const char* who, void* q, int64_t ld_q, float* scale, int64_t s_row, int64_t s_grp, void* sf_packed,
+                    int64_t I, cudaStream_t st) {
+    KBN_REQUIRE(q && scale, KBN_ERR_ARG, "%s: null output pointer", who);
+    KBN_REQUIRE(I % 128 == 0, KBN_ERR_ARG, "%s: I=%lld must be a multiple of 128", who, (long long)I);
+    KBN_REQUIRE(ld_q >= I && ld_q % 16 == 0 && aligned16(q), KBN_ERR_ARG, "%s: q must be 16-byte aligned with a row stride that is a multiple of 16", who);
+    KBN_REQUIRE(!sf_packed || aligned16(sf_packed), KBN_ERR_ARG, "%s: packed scales must be 16-byte aligned", who);
+    p.act_q = static_cast<uint8_t*>(q);
+    p.act_ld = ld_q;
+    p.act_scale = scale;
+    p.act_s_row = s_row;
+    p.act_s_grp = s_grp;
+    p.act_packed = static_cast<uint32_t*>(sf_packed);
+    return silu_table_for_stream(st, &p.act_table);
+}
+
+}  // namespace mx
+}  // namespace kbn
+
+extern "C" int kbn_fp8_grouped_gemm_contig_ue8m0_silu(const void* A, const void* sfa_packed, const void* W13, const void* sfb_packed,
+                                                      void* q, int64_t ld_q, float* scale, int64_t s_row, int64_t s_grp, void* sf_packed,
+                                                      const int32_t* row_expert, int64_t M_sum, int64_t I, int64_t K, int64_t E,
+                                                      kbn_stream_t stream) {
+    using namespace kbn;
+    const char* who = "kbn_fp8_grouped_gemm_contig_ue8m0_silu";
+    KBN_REQUIRE(M_sum >= 0 && I >= 0 && K >= 0 && E >= 0, KBN_ERR_ARG, "%s: negative size", who);
+    if (M_sum == 0 || I == 0 || E == 0) return KBN_OK;
+    KBN_REQUIRE(A && W13 && row_expert, KBN_ERR_ARG, "%s: null pointer", who);
+    KBN_REQUIRE(E * 2 * I < (1ll << 31), KBN_ERR_ARG, "%s: E*2*I too large", who);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    GemmParams p{};
+    mx::fill_params(p, nullptr, 0, M_sum, I, K, E, 0, kContig);
+    p.row_expert = row_expert;
+    int rc = mx::fill_act(p, who, q, ld_q, scale, s_row, s_grp, sf_packed, I, st);
+    if (rc != KBN_OK) return rc;
+    return mx::launch(A, M_sum, W13, E * 2 * I, p, sfa_packed, sfb_packed, p.num_m_blocks, st, true);
+}
+
+extern "C" int kbn_fp8_grouped_gemm_masked_ue8m0_silu(const void* A, const void* sfa_packed, const void* W13, const void* sfb_packed,
+                                                      void* q, float* scale, void* sf_packed, const int32_t* masked_m, int64_t E,
+                                                      int64_t max_m, int64_t I, int64_t K, kbn_stream_t stream) {
+    using namespace kbn;
+    const char* who = "kbn_fp8_grouped_gemm_masked_ue8m0_silu";
+    KBN_REQUIRE(E >= 0 && max_m >= 0 && I >= 0 && K >= 0, KBN_ERR_ARG, "%s: negative size", who);
+    if (E == 0 || max_m == 0 || I == 0) return KBN_OK;
+    KBN_REQUIRE(A && W13 && masked_m, KBN_ERR_ARG, "%s: null pointer", who);
+    KBN_REQUIRE(max_m % 128 == 0, KBN_ERR_ARG, "%s: max_m=%lld must be a multiple of 128", who, (long long)max_m);
+    KBN_REQUIRE(E * 2 * I < (1ll << 31) && E * max_m < (1ll << 31), KBN_ERR_ARG, "%s: too large", who);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    GemmParams p{};
+    mx::fill_params(p, nullptr, 0, E * max_m, I, K, E, max_m, kMasked);
+    p.masked_m = masked_m;
+    int rc = mx::fill_act(p, who, q, I, scale, I / 128, 1, sf_packed, I, st);
+    if (rc != KBN_OK) return rc;
+    return mx::launch(A, E * max_m, W13, E * 2 * I, p, sfa_packed, sfb_packed, E * (max_m / 128), st, true);
 }

@@ -1,7 +1,8 @@
 """FP8 MoE expert pipeline on one GPU: quant -> permute -> grouped GEMM1 -> fused SiLU*up+quant ->
 grouped GEMM2 -> weighted combine.  Mirrors FusedExperts._forward_deep_gemm
 (tasks/baseline/L2/fused_experts.py:246-283) step for step, with every step a kernel of this library:
-seven launches per layer, no host synchronisation, scratch buffers reused across calls.
+seven launches per layer (GEMM1 applies the activation and its quantisation in its epilogue when the weight
+scales are powers of two), no host synchronisation, scratch buffers reused across calls.
 """
 from __future__ import annotations
 
@@ -58,7 +59,7 @@ def get_scratch(t: int, topk: int, e: int, h: int, i: int, device: torch.device)
 def fused_experts_fp8(hidden_states: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, topk_weights: torch.Tensor,
                       topk_ids: torch.Tensor, num_experts: int, w13_scale: torch.Tensor, w2_scale: torch.Tensor,
                       scratch: MoeScratch | None = None, out: torch.Tensor | None = None,
-                      use_ue8m0: bool = True) -> torch.Tensor:
+                      use_ue8m0: bool = True, fuse_activation: bool = True) -> torch.Tensor:
     """hidden bf16 [T,H]; w13 fp8 [E,2I,H] + fp32 scales [E,2I/128,H/128]; w2 fp8 [E,H,I] + scales
     [E,H/128,I/128]; topk_weights [T,topk] (fp32 or bf16), topk_ids [T,topk] int -> bf16 [T,H]."""
     t, h = hidden_states.shape
@@ -84,8 +85,12 @@ def fused_experts_fp8(hidden_states: torch.Tensor, w13: torch.Tensor, w2: torch.
     if p13 is not None and p2 is not None:
         # the permute and the activation kernel emit the packed activation scales themselves
         ops.moe_permute(sc.a_q, sc.a_s, ids, num_experts, sc.a_perm, sc.a_s_perm, sc.row_expert, sc.dest_row, sc.workspace, sc.sf1)
-        ops.m_grouped_fp8_gemm_nt_contiguous_ue8m0(sc.a_perm, sc.sf1, w13, p13, mm1, sc.row_expert)
-        ops.silu_mul_quant_fp8_list(mm1, sc.a2_q, sc.a2_s, sc.dest_row.view(-1), packed_sf=sc.sf2)
+        if fuse_activation:
+            # GEMM1 applies SiLU(gate)*up and the 1x128 quantisation in its epilogue: no bf16 [M, 2I] round trip
+            ops.m_grouped_gemm1_silu_quant_contiguous_ue8m0(sc.a_perm, sc.sf1, w13, p13, sc.a2_q, sc.a2_s, sc.row_expert, sc.sf2)
+        else:
+            ops.m_grouped_fp8_gemm_nt_contiguous_ue8m0(sc.a_perm, sc.sf1, w13, p13, mm1, sc.row_expert)
+            ops.silu_mul_quant_fp8_list(mm1, sc.a2_q, sc.a2_s, sc.dest_row.view(-1), packed_sf=sc.sf2)
         ops.m_grouped_fp8_gemm_nt_contiguous_ue8m0(sc.a2_q, sc.sf2, w2, p2, mm2, sc.row_expert)
     else:
         ops.moe_permute(sc.a_q, sc.a_s, ids, num_experts, sc.a_perm, sc.a_s_perm, sc.row_expert, sc.dest_row, sc.workspace)
@@ -96,4 +101,4 @@ def fused_experts_fp8(hidden_states: torch.Tensor, w13: torch.Tensor, w2: torch.
     return out
 
 
-LAUNCHES_PER_LAYER = 8   # quant, rank, offsets, scatter, GEMM1, silu-mul-quant, GEMM2, combine
+LAUNCHES_PER_LAYER = 7   # quant, rank, offsets, scatter, GEMM1 (+activation), GEMM2, combine

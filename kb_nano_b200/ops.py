@@ -399,6 +399,60 @@ def m_grouped_fp8_gemm_nt_masked_ue8m0(a_q, sfa_packed, b_q, sfb_packed, out, ma
                                                                  e, max_m, n, k, _stream(out)))
 
 
+def m_grouped_gemm1_silu_quant_contiguous_ue8m0(a_q, sfa_packed, w13_q, sfb_packed, out_fp8, out_scale, expert_ids,
+                                                packed_sf: torch.Tensor | None = None) -> None:
+    """GEMM1 of the expert MLP with SiLU(gate)*up + 1x128 quantisation in its epilogue: a_q [M_sum,K] x
+    w13_q [E,2I,K] -> out_fp8 [M_sum,I], out_scale fp32 [M_sum,I/128] (any strides) and, optionally, the packed
+    copy of the scales.  Same bits as the bf16 GEMM followed by silu_mul_quant_fp8."""
+    dev = _cuda(a_q, sfa_packed, w13_q, sfb_packed, out_fp8, out_scale, expert_ids)
+    m, k = a_q.shape
+    e, n2, _ = w13_q.shape
+    i = n2 // 2
+    _check_ab(a_q, w13_q, k)
+    if n2 % 2 or i % GROUP:
+        raise ValueError("w13 must have 2*I rows per expert with I a multiple of 128")
+    if out_fp8.dtype != FP8 or tuple(out_fp8.shape) != (m, i) or out_fp8.stride(1) != 1:
+        raise ValueError("out_fp8 must be float8_e4m3fn [M_sum, I], contiguous along the last dim")
+    if expert_ids.dtype != torch.int32 or expert_ids.numel() != m or not expert_ids.is_contiguous():
+        raise ValueError("expert_ids must be contiguous int32 [M_sum]")
+    s_row, s_grp = _scale_strides(out_scale, m, i // GROUP)
+    sf_ptr = None
+    if packed_sf is not None:
+        _check_packed(packed_sf, m, i, dev)
+        sf_ptr = packed_sf.data_ptr()
+    with _on(dev):
+        _lib.check(_lib.load().kbn_fp8_grouped_gemm_contig_ue8m0_silu(
+            a_q.data_ptr(), sfa_packed.data_ptr(), w13_q.data_ptr(), sfb_packed.data_ptr(), out_fp8.data_ptr(),
+            out_fp8.stride(0) if m > 1 else i, out_scale.data_ptr(), s_row, s_grp, sf_ptr, expert_ids.data_ptr(), m, i, k, e,
+            _stream(out_fp8)))
+
+
+def m_grouped_gemm1_silu_quant_masked_ue8m0(a_q, sfa_packed, w13_q, sfb_packed, out_fp8, out_scale, masked_m,
+                                            packed_sf: torch.Tensor | None = None) -> None:
+    """Masked-layout form: a_q [E,max_m,K] x w13_q [E,2I,K] -> out_fp8 [E,max_m,I], out_scale fp32 [E,max_m,I/128]
+    (both contiguous); rows m >= masked_m[e] are not written."""
+    dev = _cuda(a_q, sfa_packed, w13_q, sfb_packed, out_fp8, out_scale, masked_m)
+    e, max_m, k = a_q.shape
+    i = w13_q.shape[1] // 2
+    _check_ab(a_q, w13_q, k)
+    if w13_q.shape[1] % 2 or i % GROUP:
+        raise ValueError("w13 must have 2*I rows per expert with I a multiple of 128")
+    if out_fp8.dtype != FP8 or tuple(out_fp8.shape) != (e, max_m, i) or not out_fp8.is_contiguous():
+        raise ValueError("out_fp8 must be contiguous float8_e4m3fn [E,max_m,I]")
+    if out_scale.dtype != torch.float32 or tuple(out_scale.shape) != (e, max_m, i // GROUP) or not out_scale.is_contiguous():
+        raise ValueError("out_scale must be contiguous float32 [E,max_m,I/128]")
+    if masked_m.dtype != torch.int32 or masked_m.numel() != e or not masked_m.is_contiguous():
+        raise ValueError("masked_m must be contiguous int32 [E]")
+    sf_ptr = None
+    if packed_sf is not None:
+        _check_packed(packed_sf, e * max_m, i, dev)
+        sf_ptr = packed_sf.data_ptr()
+    with _on(dev):
+        _lib.check(_lib.load().kbn_fp8_grouped_gemm_masked_ue8m0_silu(
+            a_q.data_ptr(), sfa_packed.data_ptr(), w13_q.data_ptr(), sfb_packed.data_ptr(), out_fp8.data_ptr(),
+            out_scale.data_ptr(), sf_ptr, masked_m.data_ptr(), e, max_m, i, k, _stream(out_fp8)))
+
+
 def fp8_gemm_nt_auto(a_q: torch.Tensor, a_s: torch.Tensor, b_q: torch.Tensor, b_s: torch.Tensor, out: torch.Tensor) -> None:
     """Dense block-scaled GEMM for activations quantised with power-of-two (UE8M0) scales, which is what
     per_token_group_quant_fp8 produces by default: takes the block-scaled tensor-core path when the weight

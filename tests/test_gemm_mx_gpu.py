@@ -111,6 +111,59 @@ def test_mx_grouped_masked(cuda_dev, masked):
         assert bool((out[i, c:] == 7.0).all())
 
 
+@pytest.mark.parametrize("counts,i_sz,k", [([128, 256], 256, 512), ([1, 0, 127, 129], 384, 1024), ([300, 5, 0, 0, 77, 128, 1, 640], 128, 256)])
+def test_gemm1_with_fused_activation_contiguous(cuda_dev, counts, i_sz, k):
+    """GEMM1 with SiLU(gate)*up + quantisation in its epilogue gives the bits of the bf16 GEMM followed by the
+    stand-alone activation kernel (bytes, fp32 scales, packed scales); padding rows stay untouched."""
+    from kb_nano_b200 import ops
+    e, d = len(counts), cuda_dev
+    a_q, a_s, b_q, b_s, row_expert = make_grouped(e, 2 * i_sz, k, counts, seed=sum(counts) + i_sz)
+    m = a_q.shape[0]
+    a_q, row_expert, b_q = a_q.to(d), row_expert.to(d), b_q.to(d)
+    sfa, sfb = ops.pack_sf_rows(a_s.to(d), k), ops.packed_weight_scales(b_s.to(d), 2 * i_sz, k)
+    mm1 = torch.zeros(m, 2 * i_sz, dtype=torch.bfloat16, device=d)
+    ops.m_grouped_fp8_gemm_nt_contiguous_ue8m0(a_q, sfa, b_q, sfb, mm1, row_expert)
+    q_ref = torch.full((m, i_sz), 0x55, dtype=torch.uint8, device=d).view(FP8)
+    s_ref = torch.full((i_sz // 128, m), 7.0, device=d).t()
+    ops.silu_mul_quant_fp8_rows(mm1, q_ref, s_ref, row_expert)
+    q = torch.full((m, i_sz), 0x55, dtype=torch.uint8, device=d).view(FP8)
+    s = torch.full((i_sz // 128, m), 7.0, device=d).t()
+    sf = torch.zeros(ops.packed_sf_rows_bytes(m, i_sz), dtype=torch.uint8, device=d)
+    ops.m_grouped_gemm1_silu_quant_contiguous_ue8m0(a_q, sfa, b_q, sfb, q, s, row_expert, sf)
+    assert ops.gemm_status(d) == 0
+    assert torch.equal(q.view(torch.uint8), q_ref.view(torch.uint8))
+    assert torch.equal(s.view(torch.int32), s_ref.view(torch.int32))
+    s_valid = torch.where(s == 7.0, torch.zeros_like(s), s)
+    assert torch.equal(sf, ops.pack_sf_rows(s_valid, i_sz))
+    valid = (row_expert >= 0).cpu()
+    assert bool((q.view(torch.uint8).cpu()[valid] != 0x55).any()) and bool((s.cpu()[~valid] == 7.0).all())
+
+
+@pytest.mark.parametrize("masked", [[0, 1, 128, 129, 256, 77], [256] * 3, [5, 200]])
+def test_gemm1_with_fused_activation_masked(cuda_dev, masked):
+    from kb_nano_b200 import inputs, ops
+    e, max_m, i_sz, k, d = len(masked), 256, 256, 512, cuda_dev
+    b_q, b_s = inputs.expert_weights(e, 2 * i_sz, k, seed=len(masked) + 9)
+    a_q, a_s = to.quant_1x128(inputs.activations(e * max_m, k, seed=23))
+    a_q, mm = a_q.view(e, max_m, k).to(d), torch.tensor(masked, dtype=torch.int32, device=d)
+    b_q = b_q.to(d)
+    sfa, sfb = ops.pack_sf_rows(a_s.to(d), k), ops.packed_weight_scales(b_s.to(d), 2 * i_sz, k)
+    mm1 = torch.zeros(e, max_m, 2 * i_sz, dtype=torch.bfloat16, device=d)
+    ops.m_grouped_fp8_gemm_nt_masked_ue8m0(a_q, sfa, b_q, sfb, mm1, mm)
+    q_ref = torch.full((e, max_m, i_sz), 0x55, dtype=torch.uint8, device=d).view(FP8)
+    s_ref = torch.full((e, max_m, i_sz // 128), 7.0, device=d)
+    ops.silu_mul_quant_fp8_masked(mm1, q_ref, s_ref, mm)
+    q = torch.full((e, max_m, i_sz), 0x55, dtype=torch.uint8, device=d).view(FP8)
+    s = torch.full((e, max_m, i_sz // 128), 7.0, device=d)
+    sf = torch.zeros(ops.packed_sf_rows_bytes(e * max_m, i_sz), dtype=torch.uint8, device=d)
+    ops.m_grouped_gemm1_silu_quant_masked_ue8m0(a_q, sfa, b_q, sfb, q, s, mm, sf)
+    assert ops.gemm_status(d) == 0
+    assert torch.equal(q.view(torch.uint8), q_ref.view(torch.uint8))
+    assert torch.equal(s.view(torch.int32), s_ref.view(torch.int32))
+    s_valid = torch.where(s == 7.0, torch.zeros_like(s), s)
+    assert torch.equal(sf, ops.pack_sf_rows(s_valid.view(e * max_m, -1), i_sz))
+
+
 def test_mx_matches_fp32_scale_kernel_on_config1(cuda_dev):
     from kb_nano_b200 import inputs, ops
     d = cuda_dev

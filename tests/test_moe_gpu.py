@@ -134,6 +134,21 @@ def test_moe_layer_vs_oracle(cuda_dev, t, h, i, e, topk, routing):
     assert_gemm_close(out2.cpu(), ref2, "moe layer, bf16 weights")
 
 
+def test_moe_layer_fused_activation_matches_unfused(cuda_dev):
+    """The layer with the activation inside GEMM1's epilogue returns the bits of the layer with the
+    stand-alone activation kernel."""
+    from kb_nano_b200 import inputs, moe
+    t, h, i, e, topk, d = 300, 1024, 512, 16, 4, cuda_dev
+    x = inputs.activations(t, h, seed=5, device=d)
+    tw, ti = inputs.route_sigmoid_topk(inputs.router_logits(t, e, seed=5, device=d), topk)
+    w13_q, w13_s = inputs.expert_weights(e, 2 * i, h, seed=6, device=d)
+    w2_q, w2_s = inputs.expert_weights(e, h, i, seed=7, device=d)
+    a = moe.fused_experts_fp8(x, w13_q, w2_q, tw, ti, e, w13_s, w2_s, fuse_activation=True).clone()
+    b = moe.fused_experts_fp8(x, w13_q, w2_q, tw, ti, e, w13_s, w2_s, fuse_activation=False).clone()
+    assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+    assert bool(a.float().abs().sum() > 0)
+
+
 def test_moe_grouped_gemm_candidate_golden(cuda_dev):
     """The MoeGroupedGemm drop-in (sorted-token layout of kb-nano's Triton path) on the fixture produced by
     the reference's MoeGroupedGemm, with and without the routed-weight multiply, and in the one-row-per-block
