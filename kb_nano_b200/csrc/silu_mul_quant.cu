@@ -49,18 +49,56 @@ __device__ __forceinline__ uint32_t quant_pair_s(uint32_t w, float scale, float 
     return pack_e4m3x2(lo, hi);
 }
 
-// One half-warp per output group, U groups per half-warp (2*U 16-byte loads in flight per lane).
-// ROWS selects which rows are processed: 0 = all; 1 = rows with row_info[m] >= 0 (expert-contiguous
-// layout, -1 marks padding); 2 = rows with (m % max_m) < row_info[m / max_m] (masked layout).
-// One chunk = U consecutive groups of one row, handled by a half-warp (both halves of a warp must
-// call this together: the absmax uses full-warp shuffles).
+// One group of 128 outputs held by a half-warp (8 gates + 8 ups per lane): activation, absmax over the
+// half-warp, scale, quantise, store.  Both halves of a warp must call this together (full-warp shuffles).
+// SMEM: `table` is a shared-memory copy of the exact table and every value is looked up there.
+template <bool UE8M0, bool SMEM>
+__device__ __forceinline__ void smq_group(bool live, uint32_t row, uint32_t g, uint32_t j, const uint4& gv, const uint4& uv,
+                                          uint8_t* __restrict__ q, int64_t ld_q, float* __restrict__ scale, int64_t s_row,
+                                          int64_t s_grp, float eps, const uint16_t* __restrict__ table, uint32_t G,
+                                          uint32_t* __restrict__ packed) {
+    uint32_t y[4];
+    if (SMEM) {
+        y[0] = mul_bf16x2(silu_table_pair(gv.x, table), uv.x);
+        y[1] = mul_bf16x2(silu_table_pair(gv.y, table), uv.y);
+        y[2] = mul_bf16x2(silu_table_pair(gv.z, table), uv.z);
+        y[3] = mul_bf16x2(silu_table_pair(gv.w, table), uv.w);
+    } else {
+        silu_mul_8(gv, uv, table, y);
+    }
+    float a = fmaxf(halfwarp_absmax4(y[0], y[1], y[2], y[3]), eps);
+    float sc, inv = 0.0f;
+    if (UE8M0) {
+        uint32_t f = ue8m0_scale_field(a);
+        sc = __uint_as_float(f << 23);
+        inv = __uint_as_float((254u - f) << 23);
+    } else {
+        sc = __fdiv_rn(a, kFp8MaxS);
+    }
+    if (live) {
+        uint2 o;
+        o.x = quant_pair_s<UE8M0>(y[0], sc, inv) | (quant_pair_s<UE8M0>(y[1], sc, inv) << 16);
+        o.y = quant_pair_s<UE8M0>(y[2], sc, inv) | (quant_pair_s<UE8M0>(y[3], sc, inv) << 16);
+        *reinterpret_cast<uint2*>(q + (int64_t)row * ld_q + g * 128u + j * 8u) = o;
+        if (j == 0) {
+            scale[(int64_t)row * s_row + (int64_t)g * s_grp] = sc;
+            // optional second copy of the scale in the packed UE8M0 form the block-scaled GEMM reads:
+            // word ((row/128)*G + g)*128 + (row%32)*4 + (row%128)/32, exponent byte repeated four times
+            if (UE8M0 && packed != nullptr)
+                packed[((size_t)(row >> 7) * G + g) * 128u + (row & 31u) * 4u + ((row & 127u) >> 5)] =
+                    ((__float_as_uint(sc) >> 23) & 0xffu) * 0x01010101u;
+        }
+    }
+}
+
+// One chunk = U consecutive groups of one row, handled by a half-warp: all 2*U 16-byte loads are issued
+// before the first group is processed.
 template <bool UE8M0, int U, bool SMEM = false>
 __device__ __forceinline__ void smq_chunk(bool valid, uint32_t row, uint32_t g0, uint32_t j, const __nv_bfloat16* __restrict__ in,
                                           uint32_t N2, int64_t ld_in, uint8_t* __restrict__ q, int64_t ld_q,
                                           float* __restrict__ scale, int64_t s_row, int64_t s_grp, float eps,
                                           const uint16_t* __restrict__ table, uint32_t G, uint32_t* __restrict__ packed = nullptr) {
     const __nv_bfloat16* ir = in + (int64_t)row * ld_in;
-    uint8_t* qr = q + (int64_t)row * ld_q;
     uint4 gv[U], uv[U];
     bool live[U];
 #pragma unroll
@@ -71,42 +109,8 @@ __device__ __forceinline__ void smq_chunk(bool valid, uint32_t row, uint32_t g0,
         uv[u] = live[u] ? __ldcs(reinterpret_cast<const uint4*>(ir + N2 + col)) : make_uint4(0, 0, 0, 0);
     }
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-        uint32_t y[4];
-        if (SMEM) {
-            // `table` is the block's shared-memory copy: every value comes from the exact table
-            y[0] = mul_bf16x2(silu_table_pair(gv[u].x, table), uv[u].x);
-            y[1] = mul_bf16x2(silu_table_pair(gv[u].y, table), uv[u].y);
-            y[2] = mul_bf16x2(silu_table_pair(gv[u].z, table), uv[u].z);
-            y[3] = mul_bf16x2(silu_table_pair(gv[u].w, table), uv[u].w);
-        } else {
-            silu_mul_8(gv[u], uv[u], table, y);
-        }
-        float a = fmaxf(halfwarp_absmax4(y[0], y[1], y[2], y[3]), eps);
-        float sc, inv = 0.0f;
-        if (UE8M0) {
-            uint32_t f = ue8m0_scale_field(a);
-            sc = __uint_as_float(f << 23);
-            inv = __uint_as_float((254u - f) << 23);
-        } else {
-            sc = __fdiv_rn(a, kFp8MaxS);
-        }
-        if (live[u]) {
-            const uint32_t g = g0 + u;
-            uint2 o;
-            o.x = quant_pair_s<UE8M0>(y[0], sc, inv) | (quant_pair_s<UE8M0>(y[1], sc, inv) << 16);
-            o.y = quant_pair_s<UE8M0>(y[2], sc, inv) | (quant_pair_s<UE8M0>(y[3], sc, inv) << 16);
-            *reinterpret_cast<uint2*>(qr + g * 128u + j * 8u) = o;
-            if (j == 0) {
-                scale[(int64_t)row * s_row + (int64_t)g * s_grp] = sc;
-                // optional second copy of the scale in the packed UE8M0 form the block-scaled GEMM reads:
-                // word ((row/128)*G + g)*128 + (row%32)*4 + (row%128)/32, exponent byte repeated four times
-                if (UE8M0 && packed != nullptr)
-                    packed[((size_t)(row >> 7) * G + g) * 128u + (row & 31u) * 4u + ((row & 127u) >> 5)] =
-                        ((__float_as_uint(sc) >> 23) & 0xffu) * 0x01010101u;
-            }
-        }
-    }
+    for (int u = 0; u < U; ++u)
+        smq_group<UE8M0, SMEM>(live[u], row, g0 + u, j, gv[u], uv[u], q, ld_q, scale, s_row, s_grp, eps, table, G, packed);
 }
 
 // Flat grid: chunk index -> (row, first group) with one 32-bit division per thread.
@@ -142,6 +146,41 @@ silu_mul_quant_smem_kernel(const __nv_bfloat16* __restrict__ in, uint32_t N2, in
                            const uint16_t* __restrict__ table, const int32_t* __restrict__ row_info, uint32_t G,
                            uint32_t chunks_per_row, uint32_t n_chunks, uint32_t* __restrict__ packed) {
     extern __shared__ __align__(16) uint16_t tab[];
+    const uint32_t half = (threadIdx.x >> 4) & 1u, j = threadIdx.x & 15u;
+    // each block takes one contiguous, equally sized range of chunks (a grid-stride loop would leave
+    // most blocks idle during the last, partly filled round)
+    const uint32_t lo = (uint32_t)(((uint64_t)n_chunks * blockIdx.x) / gridDim.x);
+    const uint32_t hi = (uint32_t)(((uint64_t)n_chunks * (blockIdx.x + 1)) / gridDim.x);
+    const uint32_t step = blockDim.x >> 4;
+    // Rolling prefetch: the U groups of a chunk sit in registers; as soon as group u of the current chunk
+    // has been processed, group u of the warp's next chunk is requested into the same registers, so about
+    // (U-1)/U of the register buffer is in flight at any time instead of the buffer draining once per chunk.
+    struct Ref { bool valid; uint32_t row, g0; };
+    auto ref_of = [&](uint32_t base) -> Ref {
+        const uint32_t chunk = base + half;
+        Ref r;
+        r.valid = base < hi && chunk < hi;
+        r.row = r.valid ? chunk / chunks_per_row : 0u;
+        r.g0 = (chunk - r.row * chunks_per_row) * U;
+        if (ROWS != 0) {
+            const int32_t info = r.valid ? row_info[r.row] : -1;
+            r.valid = r.valid && info >= 0;
+            if (ROWS == 3) r.row = r.valid ? (uint32_t)info : 0u;      // list entry = the row to process
+        }
+        return r;
+    };
+    uint4 gv[U], uv[U];
+    auto fetch = [&](const Ref& r, int u) {
+        const bool live = r.valid && (r.g0 + u) < G;
+        const __nv_bfloat16* src = in + (int64_t)r.row * ld_in + (r.g0 + u) * 128u + j * 8u;
+        gv[u] = live ? __ldcs(reinterpret_cast<const uint4*>(src)) : make_uint4(0, 0, 0, 0);
+        uv[u] = live ? __ldcs(reinterpret_cast<const uint4*>(src + N2)) : make_uint4(0, 0, 0, 0);
+    };
+    uint32_t base = lo + (threadIdx.x >> 5) * 2u;
+    Ref cur = ref_of(base);
+#pragma unroll
+    for (int u = 0; u < U; ++u) fetch(cur, u);
+    // the first chunk's loads are in flight while the table is copied
     // every block copies the same 128 KB; each starts at a different offset so that the SMs do not all
     // ask L2 for the same line at the same time
     const uint32_t rot = (blockIdx.x * 55u) & 8191u;
@@ -150,30 +189,17 @@ silu_mul_quant_smem_kernel(const __nv_bfloat16* __restrict__ in, uint32_t N2, in
         reinterpret_cast<uint4*>(tab)[k] = __ldg(reinterpret_cast<const uint4*>(table) + k);
     }
     __syncthreads();
-    const uint32_t half = (threadIdx.x >> 4) & 1u;
-    // each block takes one contiguous, equally sized range of chunks (a grid-stride loop would leave
-    // most blocks idle during the last, partly filled round)
-    const uint32_t lo = (uint32_t)(((uint64_t)n_chunks * blockIdx.x) / gridDim.x);
-    const uint32_t hi = (uint32_t)(((uint64_t)n_chunks * (blockIdx.x + 1)) / gridDim.x);
-    // the row's validity word is fetched one iteration ahead, so its latency is not added to the data loads
-    const uint32_t step = blockDim.x >> 4;
-    uint32_t base = lo + (threadIdx.x >> 5) * 2u;
-    int32_t info_next = 0;
-    if (ROWS != 0) info_next = (base + half < hi) ? row_info[(base + half) / chunks_per_row] : -1;
     for (; base < hi; base += step) {
-        const uint32_t chunk = base + half;
-        bool valid = chunk < hi;
-        uint32_t row = valid ? chunk / chunks_per_row : 0u;
-        const uint32_t g0 = (chunk - row * chunks_per_row) * U;
-        if (ROWS != 0) {
-            const int32_t info = info_next;
-            const uint32_t nc = chunk + step;
-            info_next = nc < hi ? row_info[nc / chunks_per_row] : -1;
-            valid = valid && info >= 0;
-            if (ROWS == 3) row = valid ? (uint32_t)info : 0u;   // list entry = the row to process
-            if (!__any_sync(0xffffffffu, valid)) continue;      // nothing to do for either chunk of this warp
+        const Ref nxt = ref_of(base + step);
+        const bool any_cur = __any_sync(0xffffffffu, cur.valid);       // warp-uniform: something to do in this chunk pair
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if (any_cur)
+                smq_group<UE8M0, true>(cur.valid && (cur.g0 + u) < G, cur.row, cur.g0 + u, j, gv[u], uv[u], q, ld_q, scale, s_row, s_grp,
+                                       eps, tab, G, packed);
+            fetch(nxt, u);
         }
-        smq_chunk<UE8M0, U, true>(valid, row, g0, threadIdx.x & 15u, in, N2, ld_in, q, ld_q, scale, s_row, s_grp, eps, tab, G, packed);
+        cur = nxt;
     }
 }
 
