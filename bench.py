@@ -618,9 +618,9 @@ def wl_ep_moe(args, rank, world, dev, sampler, name="ep_moe"):
         roof = {"bound": "hbm", "kernel": "fp8_gemm_mx_kernel (masked grouped; GEMM1 with the activation epilogue and GEMM2, 2 launches per layer; rank 0)", "achieved": ach,
                 "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"],
                 # dram read+write bytes per launch from the ncu capture summarised in
-                # profiles/fp8_gemm_mx_masked_ep_moe.md (0.76 GB per launch with 32 local DeepSeek-V3-shaped experts;
+                # profiles/fp8_gemm_mx_masked_ep_moe.md (0.745 GB per launch with 32 local DeepSeek-V3-shaped experts;
                 # proportional to the bytes of the experts whose weights are streamed)
-                "traffic": 0.76e9 / 32.0 * active * (3.0 * i * h) / (3.0 * 2048 * 7168), "peak_source": peaks["source"],
+                "traffic": 0.745e9 / 32.0 * active * (3.0 * i * h) / (3.0 * 2048 * 7168), "peak_source": peaks["source"],
                 "algorithmic_bytes_per_launch": (g1 + g2) / 2.0, "gemm_ms_per_launch": gemm_ms}
     return {
         "metric": "EP FP8 MoE layer throughput", "value": t * world / (ms * 1e-3), "unit": "tokens/s", "ms_per_step": ms,
