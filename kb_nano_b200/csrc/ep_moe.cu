@@ -20,7 +20,7 @@
 #include <algorithm>
 #include <new>
 
-#include "common.cuh"
+#include "gemm_common.cuh"
 
 extern "C" int kbn_fp8_grouped_gemm_masked(const void*, const float*, int64_t, int64_t, int64_t, const void*, const float*,
                                            void*, const int32_t*, int64_t, int64_t, int64_t, int64_t, kbn_stream_t);
@@ -33,7 +33,12 @@ namespace kbn {
 int silu_mul_quant_masked(const void* in, int64_t E, int64_t max_m, int64_t N2, void* q, float* scale,
                           const int32_t* masked_m, cudaStream_t st, void* packed_sf);   // silu_mul_quant.cu
 
-constexpr int kMaxRanks = 16;
+namespace mx {
+int gemm_masked_ue8m0_combine(const void* A, const void* sfa_packed, const void* B, const void* sfb_packed, const int32_t* masked_m,
+                              int64_t E, int64_t max_m, int64_t N, int64_t K, const CombineEpilogue& cb, cudaStream_t st);   // gemm_fp8_mx.cu
+}
+
+constexpr int kMaxRanks = kMaxPeerRanks;
 constexpr long long kFlagWaitCycles = 2000000000ll;   // about a second
 
 struct EpLayout {          // byte offsets inside each rank's symmetric buffer (identical on all ranks)
@@ -327,17 +332,31 @@ extern "C" int kbn_ep_moe_forward(kbn_ep_ctx* c, const void* x_bf16, const int32
         if (rc != KBN_OK) return rc;
     }
     if (ue8m0) {
-        rc = kbn_fp8_grouped_gemm_masked_ue8m0(c->a2_q, c->sf2, w2, w2_sf_packed, c->mm2, counters, c->e_local, c->max_m, H, I, stream);
+        // 5. GEMM2 whose epilogue writes every result row straight into its source rank's staging buffer (peer
+        //    stores issued tile by tile while the weights of the next tiles stream in) and signals when the grid is done
+        CombineEpilogue cb{};
+        for (int r = 0; r < c->world; ++r) {
+            cb.peer_comb[r] = c->peers.base[r] + c->lay.comb;
+            cb.peer_flag[r] = reinterpret_cast<int32_t*>(c->peers.base[r] + c->lay.flags_combine) + c->rank;
+        }
+        cb.meta = reinterpret_cast<const int32_t*>(mine + c->lay.recv_meta);
+        cb.done = c->done + 1;
+        cb.counters = counters;
+        cb.n_counters = (int32_t)c->e_local;
+        cb.world = c->world;
+        cb.epoch = epoch;
+        rc = mx::gemm_masked_ue8m0_combine(c->a2_q, c->sf2, w2, w2_sf_packed, counters, c->e_local, c->max_m, H, I, cb, st);
+        if (rc != KBN_OK) return rc;
     } else {
         rc = kbn_fp8_grouped_gemm_masked(c->a2_q, c->a2_s, c->max_m * (I / 128), I / 128, 1, w2, w2_s, c->mm2, counters, c->e_local, c->max_m, H, I, stream);
+        if (rc != KBN_OK) return rc;
+        // 5. results back to their sources + signal; blocks per expert: enough to fill the GPU when a rank owns few
+        //    experts with many rows, never more than the rows need
+        const unsigned cs_x = (unsigned)std::min<int64_t>((c->max_m + 7) / 8, std::max<int64_t>(8, (4 * (int64_t)sm_count() + c->e_local - 1) / c->e_local));
+        ep_combine_send_kernel<<<dim3(cs_x, (unsigned)c->e_local), 256, 0, st>>>(c->mm2, H, (int)c->e_local, (int)c->max_m, c->peers, c->lay, c->rank,
+                                                                                c->world, epoch, c->done + 1);
+        KBN_CHECK_LAUNCH();
     }
-    if (rc != KBN_OK) return rc;
-    // 5. results back to their sources + signal
-    // blocks per expert: enough to fill the GPU when a rank owns few experts with many rows, never more than the rows need
-    const unsigned cs_x = (unsigned)std::min<int64_t>((c->max_m + 7) / 8, std::max<int64_t>(8, (4 * (int64_t)sm_count() + c->e_local - 1) / c->e_local));
-    ep_combine_send_kernel<<<dim3(cs_x, (unsigned)c->e_local), 256, 0, st>>>(c->mm2, H, (int)c->e_local, (int)c->max_m, c->peers, c->lay, c->rank, c->world,
-                                                                        epoch, c->done + 1);
-    KBN_CHECK_LAUNCH();
     ep_wait_kernel<<<1, kMaxRanks, 0, st>>>(reinterpret_cast<const int32_t*>(mine + c->lay.flags_combine), c->world, epoch, 2, c->status);
     KBN_CHECK_LAUNCH();
     // 6. weighted sum over the topk slots of each local token, in slot order

@@ -35,6 +35,22 @@ struct GemmParams {
     const uint16_t* act_table; // exactly rounded bf16 SiLU table
 };
 
+// Epilogue that returns result rows to the ranks they came from (expert-parallel MoE layer, masked
+// layout): row r of the 2-D view goes to row (meta[r] & 0xfffff) of the [pairs, N] bf16 staging buffer of
+// rank meta[r] >> 20, written with plain stores through peer mappings.  When every CTA of the grid has
+// finished, the last one clears `counters` and publishes `epoch` in this rank's flag slot on every rank.
+constexpr int kMaxPeerRanks = 16;
+struct CombineEpilogue {
+    uint8_t* peer_comb[kMaxPeerRanks];
+    int32_t* peer_flag[kMaxPeerRanks];
+    const int32_t* meta;
+    int32_t* done;
+    int32_t* counters;
+    int32_t n_counters, world, epoch;
+};
+
+enum GemmEpilogue : int { kEpiStore = 0, kEpiAct = 1, kEpiCombine = 2 };
+
 struct Tile {
     int32_t row0;      // first row in the 2-D view of A and C
     int32_t row_end;   // rows >= row_end are not written

@@ -25,6 +25,9 @@ namespace mx {
 
 // Tile width BN is 256 (less L2 traffic per flop; the default) or 128 (twice the tiles: used when a
 // dense problem would otherwise leave most SMs without a tile).
+constexpr int kStgPitch = 80;                        // bytes per staged row of a 32x32 bf16 chunk (64 B + padding)
+constexpr int kEpiScratch = 8 * 32 * kStgPitch;      // 20,480 B: one 32-row staging area per epilogue warp
+
 template <int BN>
 struct Cfg {
     static constexpr int kBN = BN;
@@ -34,7 +37,8 @@ struct Cfg {
     static constexpr int kSfbBytes = 512 * (BN / 128);
     static constexpr int kSfStage = 512 + kSfbBytes;
     static constexpr int kTxBytes = kStageBytes + kSfStage;
-    static constexpr size_t kSmemBytes = (size_t)kStages * (kStageBytes + kSfStage) + 1024 + 256 + 2048;
+    // 1024: alignment slack; 256: barriers; kEpiScratch: epilogue scratch (absmax exchange or per-warp transposes)
+    static constexpr size_t kSmemBytes = (size_t)kStages * (kStageBytes + kSfStage) + 1024 + 256 + kEpiScratch;
 };
 constexpr int kABytes = kBlockM * kBlockK;          // 16 KB
 constexpr int kSfaBytes = 512;
@@ -53,11 +57,15 @@ struct MxExtra {
 // epilogue computes y = bf16(bf16(silu(gate)) * up) on the bf16-rounded accumulators and quantises the
 // 128 outputs of each row as one 1x128 group (UE8M0 scale, eps 1e-10) -- the same bits as storing the
 // bf16 GEMM result and running the stand-alone activation kernel on it, without the round trip.
-template <int BN, bool ACT>
+// EPI == kEpiCombine: instead of storing to C, every result row is written to the rank it came from (see
+// CombineEpilogue); 32x32 chunks are transposed through shared memory so that four lanes write 64 contiguous
+// bytes of one row, and the grid signals the peers when its last CTA is done.
+template <int BN, int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmA64,
                    const __grid_constant__ CUtensorMap tmA32, const __grid_constant__ CUtensorMap tmB, const GemmParams p,
-                   const MxExtra x) {
+                   const MxExtra x, const CombineEpilogue cb) {
+    constexpr bool ACT = EPI == kEpiAct;
     constexpr int kBN = Cfg<BN>::kBN, kStages = Cfg<BN>::kStages, kStageBytes = Cfg<BN>::kStageBytes;
     constexpr int kSfbBytes = Cfg<BN>::kSfbBytes, kSfStage = Cfg<BN>::kSfStage, kTxBytes = Cfg<BN>::kTxBytes;
     constexpr int kHalfCols = BN / 2;                // columns each epilogue warp of a lane quarter drains
@@ -294,6 +302,36 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                                 f * 0x01010101u;
                     }
                 }
+            } else if (EPI == kEpiCombine) {
+                uint8_t* dst_row = nullptr;
+                if (row_ok) {
+                    const int32_t meta = cb.meta[row];
+                    dst_row = cb.peer_comb[meta >> 20] + (int64_t)(meta & 0xfffff) * p.N * 2;
+                }
+                uint8_t* stg = reinterpret_cast<uint8_t*>(xch) + (warp - 2) * (32 * kStgPitch);
+#pragma unroll
+                for (int c = 0; c < kChunks; ++c) {
+                    const int32_t col0 = n0 + 32 * c;
+                    if (col0 >= p.N) break;                            // warp-uniform (N is a multiple of 32 here)
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        uint4 v;
+                        v.x = pack_bf16x2(__uint_as_float(r[c][8 * k + 0]), __uint_as_float(r[c][8 * k + 1]));
+                        v.y = pack_bf16x2(__uint_as_float(r[c][8 * k + 2]), __uint_as_float(r[c][8 * k + 3]));
+                        v.z = pack_bf16x2(__uint_as_float(r[c][8 * k + 4]), __uint_as_float(r[c][8 * k + 5]));
+                        v.w = pack_bf16x2(__uint_as_float(r[c][8 * k + 6]), __uint_as_float(r[c][8 * k + 7]));
+                        *reinterpret_cast<uint4*>(stg + lane * kStgPitch + 16 * k) = v;
+                    }
+                    __syncwarp();
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const int rr = (lane >> 2) + 8 * k, seg = lane & 3;
+                        const uint4 v = *reinterpret_cast<const uint4*>(stg + rr * kStgPitch + 16 * seg);
+                        const uint64_t d = __shfl_sync(0xffffffffu, reinterpret_cast<uint64_t>(dst_row), rr);
+                        if (d != 0) *reinterpret_cast<uint4*>(d + (uint64_t)(col0 + 8 * seg) * 2u) = v;
+                    }
+                    __syncwarp();
+                }
             } else if (row_ok) {
 #pragma unroll
                 for (int c = 0; c < kChunks; ++c) {
@@ -318,11 +356,25 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         }
     }
 
+    if (EPI == kEpiCombine) __threadfence_system();     // this thread's rows are on their way to the peers
     ptx::tc_fence_before();
     __syncthreads();
     if (warp == 1) {
         ptx::tc_fence_after();
         ptx::tmem_dealloc(tmem_base, kTmemCols);
+    }
+    if (EPI == kEpiCombine) {
+        // last CTA of the grid: every CTA has read the row counts and sent its rows
+        __shared__ int last;
+        if (threadIdx.x == 0) last = (atomicAdd(cb.done, 1) == (int)gridDim.x - 1);
+        __syncthreads();
+        if (!last) return;
+        for (int i = threadIdx.x; i < cb.n_counters; i += blockDim.x) cb.counters[i] = 0;
+        __threadfence_system();
+        __syncthreads();
+        if ((int)threadIdx.x < cb.world)
+            asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(cb.peer_flag[threadIdx.x]), "r"(cb.epoch) : "memory");
+        if (threadIdx.x == 0) *cb.done = 0;
     }
 }
 
@@ -597,9 +649,10 @@ static int check_device() {
         int major = 0;
         KBN_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
         KBN_REQUIRE(major == 10, KBN_ERR_UNSUPPORTED, "kbn_fp8 GEMMs need an sm_100 device (found major %d)", major);
-        KBN_CUDA(cudaFuncSetAttribute(fp8_gemm_mx_kernel<256, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<256>::kSmemBytes));
-        KBN_CUDA(cudaFuncSetAttribute(fp8_gemm_mx_kernel<256, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<256>::kSmemBytes));
-        KBN_CUDA(cudaFuncSetAttribute(fp8_gemm_mx_kernel<128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<128>::kSmemBytes));
+        KBN_CUDA(cudaFuncSetAttribute(fp8_gemm_mx_kernel<256, kEpiStore>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<256>::kSmemBytes));
+        KBN_CUDA(cudaFuncSetAttribute(fp8_gemm_mx_kernel<256, kEpiAct>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<256>::kSmemBytes));
+        KBN_CUDA(cudaFuncSetAttribute(fp8_gemm_mx_kernel<256, kEpiCombine>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<256>::kSmemBytes));
+        KBN_CUDA(cudaFuncSetAttribute(fp8_gemm_mx_kernel<128, kEpiStore>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<128>::kSmemBytes));
         KBN_CUDA(cudaFuncSetAttribute(fp8_gemm_mx_splitk_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<256>::kSmemBytes));
         KBN_CUDA(cudaFuncSetAttribute(fp8_gemm_mx_splitk_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<128>::kSmemBytes));
         ok[dev] = 1;
@@ -659,8 +712,9 @@ static int launch_splitk(const CUtensorMap& tmA, const CUtensorMap& tmA64, const
 
 // m_blocks_upper: number of 128-row blocks (an upper bound in the masked form).
 // act: fused activation epilogue (p.act_* filled in, p.N = output columns, B has 2*p.N rows per expert).
+// combine: epilogue that sends the rows to their source ranks (masked form, 256-wide tiles).
 static int launch(const void* A, int64_t a_rows, const void* B, int64_t b_rows, GemmParams& p, const void* sfa, const void* sfb,
-                  int64_t m_blocks_upper, cudaStream_t st, bool act = false) {
+                  int64_t m_blocks_upper, cudaStream_t st, bool act = false, const CombineEpilogue* combine = nullptr) {
     int rc = check_device();
     if (rc != KBN_OK) return rc;
     KBN_REQUIRE(sfa && sfb, KBN_ERR_ARG, "fp8 gemm (ue8m0): null packed scales");
@@ -686,7 +740,7 @@ static int launch(const void* A, int64_t a_rows, const void* B, int64_t b_rows, 
             break;
         }
     }
-    if (act) {           // 128 output columns (= 256 weight rows) per tile
+    if (act || combine) {           // act: 128 output columns (= 256 weight rows) per tile
         bn = 256;
         split = 1;
     }
@@ -710,15 +764,19 @@ static int launch(const void* A, int64_t a_rows, const void* B, int64_t b_rows, 
     int64_t grid = sm_count();
     if (max_tiles < grid) grid = max_tiles;
     if (grid <= 0) return KBN_OK;
+    CombineEpilogue cb{};
+    if (combine) cb = *combine;
     if (split > 1)
         return bn == 256 ? launch_splitk<256>(tmA, tmA64, tmA32, tmB, p, x, split, max_tiles, st)
                          : launch_splitk<128>(tmA, tmA64, tmA32, tmB, p, x, split, max_tiles, st);
-    if (act)
-        fp8_gemm_mx_kernel<256, true><<<(unsigned)grid, kThreads, Cfg<256>::kSmemBytes, st>>>(tmA, tmA64, tmA32, tmB, p, x);
+    if (combine)
+        fp8_gemm_mx_kernel<256, kEpiCombine><<<(unsigned)grid, kThreads, Cfg<256>::kSmemBytes, st>>>(tmA, tmA64, tmA32, tmB, p, x, cb);
+    else if (act)
+        fp8_gemm_mx_kernel<256, kEpiAct><<<(unsigned)grid, kThreads, Cfg<256>::kSmemBytes, st>>>(tmA, tmA64, tmA32, tmB, p, x, cb);
     else if (bn == 256)
-        fp8_gemm_mx_kernel<256, false><<<(unsigned)grid, kThreads, Cfg<256>::kSmemBytes, st>>>(tmA, tmA64, tmA32, tmB, p, x);
+        fp8_gemm_mx_kernel<256, kEpiStore><<<(unsigned)grid, kThreads, Cfg<256>::kSmemBytes, st>>>(tmA, tmA64, tmA32, tmB, p, x, cb);
     else
-        fp8_gemm_mx_kernel<128, false><<<(unsigned)grid, kThreads, Cfg<128>::kSmemBytes, st>>>(tmA, tmA64, tmA32, tmB, p, x);
+        fp8_gemm_mx_kernel<128, kEpiStore><<<(unsigned)grid, kThreads, Cfg<128>::kSmemBytes, st>>>(tmA, tmA64, tmA32, tmB, p, x, cb);
     KBN_CHECK_LAUNCH();
     return KBN_OK;
 }
@@ -820,6 +878,29 @@ extern "C" int kbn_fp8_grouped_gemm_masked_ue8m0(const void* A, const void* sfa_
     p.masked_m = masked_m;
     return mx::launch(A, E * max_m, B, E * N, p, sfa_packed, sfb_packed, E * ((max_m + 127) / 128), static_cast<cudaStream_t>(stream));
 }
+
+// ---- masked grouped GEMM2 whose epilogue returns the rows to their source ranks -------------------
+
+namespace kbn {
+namespace mx {
+
+// Not part of the C ABI: called by the expert-parallel layer, which owns the peer mappings.
+int gemm_masked_ue8m0_combine(const void* A, const void* sfa_packed, const void* B, const void* sfb_packed, const int32_t* masked_m,
+                              int64_t E, int64_t max_m, int64_t N, int64_t K, const CombineEpilogue& cb, cudaStream_t st) {
+    const char* who = "fp8 gemm (ue8m0, combine epilogue)";
+    KBN_REQUIRE(E > 0 && max_m > 0 && N > 0 && K > 0 && A && B && masked_m, KBN_ERR_ARG, "%s: bad arguments", who);
+    KBN_REQUIRE(max_m % 128 == 0 && N % 32 == 0, KBN_ERR_ARG, "%s: max_m must be a multiple of 128 and N of 32", who);
+    KBN_REQUIRE(E * N < (1ll << 31) && E * max_m < (1ll << 31), KBN_ERR_ARG, "%s: too large", who);
+    KBN_REQUIRE(cb.world >= 1 && cb.world <= kMaxPeerRanks && cb.meta && cb.done, KBN_ERR_ARG, "%s: bad peer description", who);
+    GemmParams p{};
+    fill_params(p, nullptr, N, E * max_m, N, K, E, max_m, kMasked);
+    p.masked_m = masked_m;
+    // the grid is never empty here: the last CTA must signal the peers even when no expert has rows
+    return launch(A, E * max_m, B, E * N, p, sfa_packed, sfb_packed, E * (max_m / 128), st, false, &cb);
+}
+
+}  // namespace mx
+}  // namespace kbn
 
 // ---- grouped GEMM1 with the activation in the epilogue ------------------------------------------
 
