@@ -262,6 +262,8 @@ int kbn_moe_unpermute_combine(const void* rows, int64_t ld_rows, const int32_t* 
  * Bootstrap (not the hot path; allocates with cudaMalloc and maps peers with CUDA IPC):
  *   kbn_ep_create on every rank (its GPU current) -> kbn_ep_ipc_handle -> exchange the 64-byte
  *   handles by any host channel -> kbn_ep_attach(all handles, rank order).  world == 1 needs no attach.
+ *   An all-zero handle maps that rank onto the caller's own buffer: a rank that never runs, whose
+ *   signals never arrive (the bounded waits for it end with status 20 after about a second each).
  * kbn_ep_moe_forward: x bf16 [T,H] local tokens, topk_ids int32 [T,topk] GLOBAL expert ids,
  *   topk_w fp32 [T,topk]; w13 fp8 [E/R,2I,H] + w13_s fp32 [E/R,2I/128,H/128], w2 fp8 [E/R,H,I] +
  *   w2_s [E/R,H/128,I/128] of the LOCAL experts; out bf16 [T,H].  When both w13_sf_packed and

@@ -276,6 +276,14 @@ extern "C" int kbn_ep_attach(kbn_ep_ctx* c, const void* handles) {
         if (r == c->rank) continue;
         cudaIpcMemHandle_t h;
         memcpy(&h, static_cast<const uint8_t*>(handles) + 64 * r, 64);
+        // An all-zero handle maps that rank onto this rank's own buffer: a rank that never runs, for
+        // exercising the bounded waits (its flag is never published) inside one process.
+        bool zero = true;
+        for (int i = 0; i < 64; ++i) zero = zero && static_cast<const uint8_t*>(handles)[64 * r + i] == 0;
+        if (zero) {
+            c->peers.base[r] = c->sym;
+            continue;
+        }
         void* p = nullptr;
         KBN_CUDA(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
         c->peers.base[r] = static_cast<uint8_t*>(p);
@@ -379,9 +387,10 @@ extern "C" int kbn_ep_destroy(kbn_ep_ctx* c) {
     if (!c) return KBN_OK;
     cudaDeviceSynchronize();
     for (int r = 0; r < c->world; ++r)
-        if (r != c->rank && c->peers.base[r]) cudaIpcCloseMemHandle(c->peers.base[r]);
+        if (r != c->rank && c->peers.base[r] && c->peers.base[r] != c->sym) cudaIpcCloseMemHandle(c->peers.base[r]);
     cudaFree(c->sym); cudaFree(c->a_q); cudaFree(c->a_s); cudaFree(c->mm1); cudaFree(c->a2_q); cudaFree(c->a2_s);
     cudaFree(c->mm2); cudaFree(c->sf2); cudaFree(c->identity); cudaFree(c->done); cudaFree(c->status);
     delete c;
+    cudaGetLastError();        // a failed release must not surface as the next launch's error
     return KBN_OK;
 }

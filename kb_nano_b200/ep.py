@@ -46,7 +46,11 @@ class EpStatusError(RuntimeError):
 
 class EpMoe:
     def __init__(self, rank: int, world: int, experts_total: int, hidden: int, inter: int, max_tokens: int, topk: int,
-                 max_m: int = 256, group=None, device: torch.device | None = None, use_ue8m0: bool = True):
+                 max_m: int = 256, group=None, device: torch.device | None = None, use_ue8m0: bool = True,
+                 handles: bytes | None = None):
+        """`handles`: the world's 64-byte IPC handles concatenated in rank order, when the caller has exchanged
+        them itself (default: all_gather over `group`).  An all-zero handle stands for a rank that never runs
+        and is mapped onto this rank's own buffer: waits for it run into their time limit."""
         self.use_ue8m0 = use_ue8m0
         self.rank, self.world = rank, world
         self.experts_total, self.hidden, self.inter = experts_total, hidden, inter
@@ -58,7 +62,11 @@ class EpMoe:
         with _on(self.device):
             _lib.check(self._lib.kbn_ep_create(rank, world, experts_total, max_m, hidden, inter, max_tokens, topk,
                                                ctypes.byref(self._ctx)))
-            if world > 1:
+            if world > 1 and handles is not None:
+                if len(handles) != 64 * world:
+                    raise ValueError("handles must hold 64 bytes per rank")
+                _lib.check(self._lib.kbn_ep_attach(self._ctx, handles))
+            elif world > 1:
                 import torch.distributed as dist
                 buf = ctypes.create_string_buffer(64)
                 _lib.check(self._lib.kbn_ep_ipc_handle(self._ctx, buf))
@@ -121,7 +129,7 @@ class EpMoe:
         if s["code"] != 0:
             raise EpStatusError(f"expert-parallel layer on rank {self.rank}: {s}")
 
-    LAUNCHES_PER_FORWARD = 9   # quant, dispatch, wait, GEMM1, act-quant, GEMM2, send, wait, sum
+    LAUNCHES_PER_FORWARD = 7   # quant, dispatch, wait, GEMM1 (+activation), GEMM2 (+combine stores), wait, sum
 
     def close(self) -> None:
         if self._ctx:

@@ -66,6 +66,29 @@ def test_ep_overflow_is_reported_not_fatal(cuda_dev):
     layer.close()
 
 
+def test_ep_wait_for_a_silent_rank_times_out(cuda_dev):
+    """A world of two in which rank 1 never runs (its handle is all zero, so its slots alias this rank's own
+    buffer): the waits for its dispatch and combine signals give up after their time limit and record
+    {code 20, phase, peer 1}; nothing faults and the context and the GPU stay usable."""
+    import time
+    from kb_nano_b200 import ep
+    t, h, i, e, topk = 16, 256, 128, 8, 2
+    xs, routes, (w13_q, w13_s, w2_q, w2_s) = ep_case(1, t, h, i, e, topk, seed=9)
+    d = cuda_dev
+    layer = ep.EpMoe(0, 2, e, h, i, max_tokens=t, topk=topk, max_m=128, device=d, handles=b"\x01" * 64 + b"\x00" * 64)
+    tw, ti = routes[0]
+    t0 = time.time()
+    layer.forward(xs[0].to(d), ti.to(d), tw.to(d), w13_q[: e // 2].to(d), w13_s[: e // 2].to(d), w2_q[: e // 2].to(d), w2_s[: e // 2].to(d))
+    st = layer.status()
+    assert st["code"] == 20 and st["phase"] == 1 and st["peer"] == 1, st
+    assert time.time() - t0 < 30
+    with pytest.raises(ep.EpStatusError):
+        layer.check()
+    layer.close()
+    # the device still works
+    assert float(torch.ones(8, device=d).sum()) == 8.0
+
+
 def _ep_worker(rank, world, port, t, h, i, e, topk, seed, q):
     import torch.distributed as dist
     from kb_nano_b200 import ep, ops

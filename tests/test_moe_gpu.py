@@ -209,3 +209,23 @@ def test_fused_experts_candidate_golden(cuda_dev):
     assert bool((x == x0).all())
     with pytest.raises(NotImplementedError):
         mod.FusedExperts()(x, x, x, x, x, 4)
+
+
+def test_vllm_fused_experts_candidate_golden(cuda_dev):
+    """The VllmFusedExperts drop-in class (DeepSeek's expert path) on the reference-generated fixture, whose
+    operation order (routed weight applied at GEMM2, sum over the slots) is that class's."""
+    import importlib.util, os, sys
+    from kb_nano_b200 import candidate_dir
+    spec = importlib.util.spec_from_file_location("_candidate_impl_L2_vllm_fused_experts", os.path.join(candidate_dir(), "L2", "vllm_fused_experts.py"))
+    mod = importlib.util.module_from_spec(spec); sys.modules[spec.name] = mod; spec.loader.exec_module(mod)
+    g = golden("fused_experts")
+    d = cuda_dev
+    x = bf16_from_bits(g["x"]).to(d)
+    x0 = x.clone()
+    args = (fp8_from_bits(g["w13_q"]).to(d), fp8_from_bits(g["w2_q"]).to(d), torch.from_numpy(g["topk_w"]).to(d),
+            torch.from_numpy(g["topk_ids"]).to(d), 4, torch.from_numpy(g["w13_s"]).to(d), torch.from_numpy(g["w2_s"]).to(d))
+    out = mod.VllmFusedExperts()(x, *args, [128, 128])
+    assert_gemm_close(out.cpu(), bf16_from_bits(g["out"]), "VllmFusedExperts golden")
+    assert bool((x == x0).all())
+    with pytest.raises(NotImplementedError):
+        mod.VllmFusedExperts()(x, *args, [64, 64])
