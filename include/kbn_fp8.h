@@ -251,6 +251,25 @@ int kbn_moe_unpermute_combine(const void* rows, int64_t ld_rows, const int32_t* 
                               kbn_stream_t stream);
 
 /*
+ * Expert routing in front of the MoE pipeline, one kernel per token batch: stands behind TopKSoftmax
+ * (tasks/baseline/L1/topk_softmax.py:37-60) and GroupedTopK (tasks/baseline/L1/grouped_topk.py:75-174).
+ *   logits [T, E] fp32 or bf16 (logits_bf16), row stride ld; E <= 1024, topk <= 32;
+ *   softmax != 0: scores = softmax(logits), else sigmoid(logits); fp32 arithmetic, or, with round_bf16,
+ *     rounded to bf16 step by step (GroupedTopK scores in the logits' dtype);
+ *   bias (may be null) fp32 [E]: added to the scores for the selection only (e_score_correction_bias);
+ *   n_group / topk_group: the experts form n_group contiguous groups (n_group divides E, <= 32); only the
+ *     topk_group groups with the best score (sum of their two largest biased scores, or their largest score
+ *     without a bias) take part; n_group = topk_group = 1 switches this off;
+ *   out_w fp32 [T, topk]: unbiased scores of the chosen experts, divided by max(their sum, renorm_floor) when
+ *     renormalize != 0, times scale; out_ids int32 [T, topk]; both in descending order of the selection value,
+ *     ties to the lower expert id.
+ */
+int kbn_moe_route_topk(const void* logits, int logits_bf16, int64_t ld, int64_t T, int64_t E, int softmax,
+                       const float* bias, int64_t n_group, int64_t topk_group, int64_t topk,
+                       int renormalize, float renorm_floor, float scale, int round_bf16, float* out_w,
+                       int32_t* out_ids, kbn_stream_t stream);
+
+/*
  * Expert-parallel FP8 MoE layer over the GPUs of one NVLink/NVSwitch box, one process per GPU.
  * Experts are split in contiguous blocks (rank r owns experts [r*E/R, (r+1)*E/R)); tokens stay on
  * their source rank.  Dispatch and combine are peer stores over NVLink issued by this library's

@@ -52,6 +52,7 @@ SIGNATURES = {
     "kbn_ep_moe_forward": (_i32, [_ptr, _ptr, _ptr, _ptr, _i64, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr]),
     "kbn_ep_status": (_i32, [_ptr, _ptr, _ptr]),
     "kbn_ep_destroy": (_i32, [_ptr]),
+    "kbn_moe_route_topk": (_i32, [_ptr, _i32, _i64, _i64, _i64, _i32, _ptr, _i64, _i64, _i64, _i32, _f32, _f32, _i32, _ptr, _ptr, _ptr]),
     "kbn_moe_permute_static": (_i32, [_ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _ptr, _ptr, _ptr, _ptr, _i64, _ptr]),
     "kbn_moe_unpermute_combine": (_i32, [_ptr, _i64, _ptr, _ptr, _i64, _i64, _i64, _ptr, _ptr]),
 }

@@ -281,6 +281,36 @@ def moe_permute(a_q: torch.Tensor, a_s: torch.Tensor, topk_ids: torch.Tensor, nu
                                                   dest_row.data_ptr(), m_cap, workspace.data_ptr(), ws_bytes, sf_ptr, _stream(a_q)))
 
 
+def moe_route_topk(logits: torch.Tensor, topk: int, scoring: str = "softmax", bias: torch.Tensor | None = None, n_group: int = 1,
+                   topk_group: int = 1, renormalize: bool = True, renorm_floor: float = 0.0, scale: float = 1.0,
+                   round_bf16: bool = False, out_w: torch.Tensor | None = None, out_ids: torch.Tensor | None = None):
+    """Router logits [T, E] (fp32 or bf16) -> (weights fp32 [T, topk], expert ids int32 [T, topk]) in one kernel:
+    softmax or sigmoid scores, optional selection bias and group-limited selection, top-k, renormalisation, scaling."""
+    if scoring not in ("softmax", "sigmoid"):
+        raise ValueError(f"unsupported scoring function {scoring!r}")
+    if logits.dim() != 2 or logits.dtype not in (torch.float32, torch.bfloat16) or logits.stride(1) != 1:
+        raise ValueError("logits must be fp32 or bf16 [T, E], contiguous along E")
+    t, e = logits.shape
+    tensors = [logits] + ([bias] if bias is not None else [])
+    if out_w is None:
+        out_w = torch.empty(t, topk, dtype=torch.float32, device=logits.device)
+    if out_ids is None:
+        out_ids = torch.empty(t, topk, dtype=torch.int32, device=logits.device)
+    dev = _cuda(*tensors, out_w, out_ids)
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != e or not bias.is_contiguous()):
+        raise ValueError("bias must be contiguous float32 [E]")
+    if out_w.dtype != torch.float32 or tuple(out_w.shape) != (t, topk) or not out_w.is_contiguous():
+        raise ValueError("out_w must be contiguous float32 [T, topk]")
+    if out_ids.dtype != torch.int32 or tuple(out_ids.shape) != (t, topk) or not out_ids.is_contiguous():
+        raise ValueError("out_ids must be contiguous int32 [T, topk]")
+    with _on(dev):
+        _lib.check(_lib.load().kbn_moe_route_topk(logits.data_ptr(), int(logits.dtype == torch.bfloat16), logits.stride(0) if t > 1 else e,
+                                                  t, e, int(scoring == "softmax"), bias.data_ptr() if bias is not None else None,
+                                                  n_group, topk_group, topk, int(renormalize), renorm_floor, scale, int(round_bf16),
+                                                  out_w.data_ptr(), out_ids.data_ptr(), _stream(logits)))
+    return out_w, out_ids
+
+
 def moe_permute_workspace_bytes(t: int, topk: int, e: int) -> int:
     return int(_lib.load().kbn_moe_permute_workspace_bytes(t, topk, e))
 

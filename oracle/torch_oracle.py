@@ -194,3 +194,32 @@ def requant_weights_ue8m0(w_q: torch.Tensor, s: torch.Tensor, eps: float = 1e-4)
     """(new e4m3 weights, new power-of-two fp32 scales) of block-scaled weights [..., N, K]."""
     w = dequant_blocks(w_q, s)
     return block_quant_128x128(w, eps=eps, ue8m0=True)
+
+
+def route_topk(logits: torch.Tensor, topk: int, scoring: str = "softmax", bias: torch.Tensor | None = None, n_group: int = 1,
+               topk_group: int = 1, renormalize: bool = True, renorm_floor: float = 0.0, scale: float = 1.0,
+               score_in_input_dtype: bool = False):
+    """Expert routing.  TopKSoftmax (tasks/reference/L1/topk_softmax.py:46-52): softmax in fp32, top-k, division by
+    the clamped sum (renorm_floor = 1e-20).  GroupedTopK's eager path (tasks/baseline/L1/grouped_topk.py:117-174):
+    scores in the logits' dtype (score_in_input_dtype), biased scores for the selection, a group's score = sum of its
+    top-2 biased scores (max of the scores without a bias), the topk_group best groups kept, top-k among them,
+    weights = unbiased scores of the chosen experts, / sum, * scale, returned as fp32.  Returns (weights fp32, ids int32)."""
+    x = logits if score_in_input_dtype else logits.float()
+    scores = torch.softmax(x, dim=-1) if scoring == "softmax" else x.sigmoid()
+    t, e = scores.shape
+    choice = scores if bias is None else scores + bias.unsqueeze(0)
+    if n_group > 1 and topk_group < n_group:
+        grouped = choice.view(t, n_group, e // n_group)
+        gscore = grouped.topk(2, dim=-1)[0].sum(dim=-1) if bias is not None else grouped.max(dim=-1).values
+        gidx = torch.topk(gscore, k=topk_group, dim=-1)[1]
+        gmask = torch.zeros_like(gscore).scatter_(1, gidx, 1)
+        mask = gmask.unsqueeze(-1).expand(t, n_group, e // n_group).reshape(t, e)
+        choice = choice.masked_fill(~mask.bool(), float("-inf"))
+    ids = torch.topk(choice, k=topk, dim=-1)[1]
+    w = scores.gather(1, ids)
+    if renormalize:
+        den = w.sum(dim=-1, keepdim=True)
+        w = w / (den.clamp_min(renorm_floor) if renorm_floor > 0 else den)
+    if scale != 1.0:
+        w = w * scale
+    return w.to(torch.float32), ids.to(torch.int32)

@@ -16,6 +16,7 @@ Every array is produced by reference code, imported from the tree as it lies:
   permute.npz         tasks/reference/L2/fused_experts.py _deepgemm_permute / _deepgemm_unpermute_and_reduce
   fused_experts.npz   the op sequence of tasks/reference/L2/fused_experts.py FusedExperts._forward_triton, run
                       with that file's own MoeAlign / MoeGroupedGemm / SiluAndMul / PerTokenGroupQuantFp8 / MoeSum
+  routing.npz         tasks/reference/L1/topk_softmax.py TopKSoftmax.forward (renormalised and raw weights)
 Inputs are seeded; bf16 tensors are stored as uint16 bit patterns, fp8 as uint8.
 """
 from __future__ import annotations
@@ -194,6 +195,19 @@ def main() -> None:
     np.savez_compressed(os.path.join(HERE, "fused_experts.npz"), x=bits(hs), w13_q=bits(w13q), w13_s=bits(w13s),
                         w2_q=bits(w2q), w2_s=bits(w2s), topk_w=bits(tw), topk_ids=bits(ti), inter1=bits(inter1),
                         a2_q=bits(a2q), a2_s=bits(a2s), out=bits(out))
+    # routing: the reference TopKSoftmax on fp32 logits (Mixtral-like 8 experts / top-2 and 256 experts / top-8)
+    ref_tk = _load("tasks/reference/L1/topk_softmax.py", "_ref_topk_softmax")
+    router = ref_tk.TopKSoftmax()
+    lg8 = torch.randn(64, 8, generator=gen)
+    lg256 = torch.randn(48, 256, generator=gen)
+    w8, i8 = router(lg8, 2, True)
+    w8, i8 = w8.clone(), i8.clone()
+    router = ref_tk.TopKSoftmax()             # its output buffers keep the first call's top_k: one instance per top_k
+    w256, i256 = router(lg256, 8, True)
+    w256, i256 = w256.clone(), i256.clone()
+    w256n, i256n = router(lg256, 8, False)
+    np.savez_compressed(os.path.join(HERE, "routing.npz"), logits8=bits(lg8), w8=bits(w8), ids8=bits(i8), logits256=bits(lg256),
+                        w256=bits(w256), ids256=bits(i256), w256_raw=bits(w256n.clone()), ids256_raw=bits(i256n.clone()))
     for f in sorted(os.listdir(HERE)):
         if f.endswith(".npz"):
             print(f, os.path.getsize(os.path.join(HERE, f)))

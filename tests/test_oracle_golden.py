@@ -150,3 +150,19 @@ def test_routing_oracles():
     assert (torch.sigmoid(logits).gather(1, ids.long()) >= torch.sigmoid(logits).topk(4).values[:, -1:]).all()
     w2, ids2 = to.route_softmax_topk(logits, 2)
     assert torch.allclose(w2.sum(-1), torch.ones(32)) and (ids2[:, 0] == logits.argmax(-1)).all()
+
+
+def test_routing_oracle_matches_reference_fixture():
+    """The oracle's routing restatement reproduces kb-nano's TopKSoftmax bit for bit on CPU."""
+    g = golden("routing")
+    for name, k in (("8", 2), ("256", 8)):
+        w, ids = to.route_topk(torch.from_numpy(g["logits" + name]), k, "softmax", renorm_floor=1e-20)
+        assert (ids.numpy() == g["ids" + name]).all()
+        assert (w.numpy() == g["w" + name]).all()
+    w, ids = to.route_topk(torch.from_numpy(g["logits256"]), 8, "softmax", renormalize=False)
+    assert (ids.numpy() == g["ids256_raw"]).all() and (w.numpy() == g["w256_raw"]).all()
+    # group-limited selection keeps only experts of the best groups
+    lg = torch.randn(16, 64, generator=torch.Generator().manual_seed(1))
+    w, ids = to.route_topk(lg, 4, "sigmoid", None, 8, 2, True)
+    assert all(len(set((ids[r] // 8).tolist())) <= 2 for r in range(16))
+    assert torch.allclose(w.sum(dim=1), torch.ones(16))
