@@ -283,6 +283,11 @@ static inline int32_t cdiv32(int64_t a, int64_t b) { return (int32_t)((a + b - 1
 
 }  // namespace kbn
 
+namespace kbn {
+int fp8_gemm_small_m(const void* A, const float* sa, int64_t sa_row, int64_t sa_grp, const void* B, const float* sb, void* C,
+                     int64_t ldc, int64_t M, int64_t N, int64_t K, cudaStream_t st);   // gemm_fp8_small_m.cu
+}
+
 extern "C" int kbn_fp8_gemm_nt(const void* A, const float* sa, int64_t sa_row, int64_t sa_grp, const void* B,
                                const float* sb, void* C, int64_t ldc, int64_t M, int64_t N, int64_t K,
                                kbn_stream_t stream) {
@@ -291,6 +296,9 @@ extern "C" int kbn_fp8_gemm_nt(const void* A, const float* sa, int64_t sa_row, i
     if (M == 0 || N == 0) return KBN_OK;
     KBN_REQUIRE(A && sa && B && sb && C, KBN_ERR_ARG, "kbn_fp8_gemm_nt: null pointer");
     KBN_REQUIRE(ldc >= N, KBN_ERR_ARG, "kbn_fp8_gemm_nt: ldc < N");
+    // decode-sized batches: a weight-streaming kernel instead of 128-row tiles
+    if (M <= 16 && K >= 16 && K % 16 == 0 && aligned16(A) && aligned16(B))
+        return fp8_gemm_small_m(A, sa, sa_row, sa_grp, B, sb, C, ldc, M, N, K, static_cast<cudaStream_t>(stream));
     GemmParams p{};
     p.sa = sa; p.sa_exp = 0; p.sa_row = sa_row; p.sa_grp = sa_grp; p.sb = sb;
     p.C = static_cast<__nv_bfloat16*>(C); p.ldc = ldc;

@@ -488,6 +488,11 @@ def fp8_gemm_nt_auto(a_q: torch.Tensor, a_s: torch.Tensor, b_q: torch.Tensor, b_
     per_token_group_quant_fp8 produces by default: takes the block-scaled tensor-core path when the weight
     scales are powers of two as well (checked once per weight tensor), the fp32-scale kernel otherwise."""
     n, k = b_q.shape
+    if a_q.shape[0] <= 8:
+        # decode-sized batch: the fp32-scale entry point streams the weights with a kernel of its own, as fast as the
+        # block-scaled path at this size and without the scale-packing launch
+        fp8_gemm_nt(a_q, a_s, b_q, b_s, out)
+        return
     packed = packed_weight_scales(b_s, n, k)
     if packed is not None:
         fp8_gemm_nt_ue8m0(a_q, pack_sf_rows(a_s, k), b_q, packed, out)

@@ -40,6 +40,19 @@ def test_dense_golden(cuda_dev):
     assert_gemm_close(out, bf16_from_bits(g["c"]), "golden fp8_linear")
 
 
+@pytest.mark.parametrize("m,n,k", [(1, 4096, 7168), (5, 1000, 400), (8, 256, 512), (9, 2304, 4096), (16, 7168, 2048), (13, 24, 144)])
+@pytest.mark.parametrize("arbitrary", [False, True])
+def test_dense_decode_sizes(cuda_dev, m, n, k, arbitrary):
+    """M <= 16 takes the weight-streaming kernel (tokens as the N dimension of mma.sync, any fp32 scales): ragged N
+    and K, one to sixteen tokens, row- and column-major activation scales; two runs agree bit for bit."""
+    a_q, a_s, w_q, w_s = make_dense(m, n, k, seed=m * 7 + n + k, dev=cuda_dev, arbitrary_scales=arbitrary)
+    ref = to.gemm_nt_dequant(a_q, a_s, w_q, w_s)
+    outs = [run_dense(a_q, a_s, w_q, w_s, cuda_dev, colmajor=cm) for cm in (True, False, True)]
+    assert_gemm_close(outs[0], ref, f"decode-size dense {m}x{n}x{k}")
+    assert torch.equal(outs[0].view(torch.int16), outs[1].view(torch.int16))
+    assert torch.equal(outs[0].view(torch.int16), outs[2].view(torch.int16))
+
+
 @pytest.mark.parametrize("m,n,k", [(128, 128, 128), (1, 256, 512), (127, 384, 1024), (129, 128, 256), (300, 640, 7168), (64, 2304, 4096)])
 def test_dense_shapes(cuda_dev, m, n, k):
     a_q, a_s, w_q, w_s = make_dense(m, n, k, seed=m + n + k, dev=cuda_dev)
