@@ -41,6 +41,11 @@ def test_ep_world1_matches_oracle(cuda_dev):
         layer.check()
         assert ops.gemm_status(d) == 0
         assert_gemm_close(out.cpu(), ref, f"EP world=1, call {it}")
+    # BASELINE configs[3]: "output is checked against the single-GPU result" -- the expert-contiguous pipeline on one
+    # GPU gives the same bits (same per-row arithmetic, same slot order in the weighted sum)
+    from kb_nano_b200 import moe
+    single = moe.fused_experts_fp8(xs[0].to(d), wd[0], wd[2], routes[0][0].to(d), routes[0][1].to(d), e, wd[1], wd[3])
+    assert torch.equal(out.view(torch.int16), single.view(torch.int16))
     # fewer tokens than max_tokens, then none at all
     out = layer.forward(xs[0][:5].to(d), routes[0][1][:5].to(d), routes[0][0][:5].to(d), *wd)
     assert_gemm_close(out.cpu(), ref[:5], "EP world=1, 5 tokens")
@@ -114,6 +119,13 @@ def _ep_worker(rank, world, port, t, h, i, e, topk, seed, q):
             except AssertionError as ex:
                 ok, msg = False, str(ex)
                 break
+        if ok:
+            # the same tokens through the one-GPU pipeline with all experts on this GPU: identical bits
+            from kb_nano_b200 import moe
+            allw = [w.to(d) for w in (w13_q, w13_s, w2_q, w2_s)]
+            single = moe.fused_experts_fp8(xs[rank].to(d), allw[0], allw[2], routes[rank][0].to(d), routes[rank][1].to(d), e, allw[1], allw[3])
+            if not torch.equal(out.view(torch.int16), single.view(torch.int16)):
+                ok, msg = False, f"rank {rank}: expert-parallel result differs from the single-GPU result in {int((out != single).sum())} elements"
         dist.barrier()
         layer.close()
         q.put((rank, ok, msg))
