@@ -70,6 +70,13 @@ __device__ __forceinline__ uint32_t max_bf16x2(uint32_t a, uint32_t b) {
     return d;
 }
 
+// Per half: the larger of |a| and |b| with the sign of a*b -- absmax chains need no separate abs until the end.
+__device__ __forceinline__ uint32_t absmax_bf16x2(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("max.xorsign.abs.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+
 __device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
     uint32_t d;
     asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));

@@ -269,9 +269,10 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 #pragma unroll
                         for (int q = 0; q < 4; ++q) y[(c * 32 + j) / 2 + q] = y4[q];
                     }
-                uint32_t m2 = abs_bf16x2(y[0]);
+                uint32_t m2 = y[0];
 #pragma unroll
-                for (int i = 1; i < 32; ++i) m2 = max_bf16x2(m2, abs_bf16x2(y[i]));
+                for (int i = 1; i < 32; ++i) m2 = absmax_bf16x2(m2, y[i]);
+                m2 = abs_bf16x2(m2);
                 float amax = fmaxf(bf16_lo(m2), bf16_hi(m2));
                 // the other half of the row's 128 outputs sits in the partner warp of this lane quarter
                 const uint32_t par = tile_it & 1u;

@@ -44,10 +44,10 @@ __device__ __forceinline__ uint32_t quant_pair(uint32_t w, const GroupScale& s) 
 }
 
 __device__ __forceinline__ float halfwarp_absmax(uint4 v) {
-    uint32_t m = max_bf16x2(max_bf16x2(abs_bf16x2(v.x), abs_bf16x2(v.y)),
-                            max_bf16x2(abs_bf16x2(v.z), abs_bf16x2(v.w)));
+    uint32_t m = absmax_bf16x2(absmax_bf16x2(v.x, v.y), absmax_bf16x2(v.z, v.w));
 #pragma unroll
-    for (int o = 8; o >= 1; o >>= 1) m = max_bf16x2(m, __shfl_xor_sync(0xffffffffu, m, o));
+    for (int o = 8; o >= 1; o >>= 1) m = absmax_bf16x2(m, __shfl_xor_sync(0xffffffffu, m, o));
+    m = abs_bf16x2(m);
     return fmaxf(bf16_lo(m), bf16_hi(m));
 }
 

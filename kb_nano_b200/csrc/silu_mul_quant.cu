@@ -30,9 +30,10 @@ __global__ void silu_table_kernel(uint16_t* __restrict__ table) {
 }
 
 __device__ __forceinline__ float halfwarp_absmax4(uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-    uint32_t m = max_bf16x2(max_bf16x2(abs_bf16x2(a), abs_bf16x2(b)), max_bf16x2(abs_bf16x2(c), abs_bf16x2(d)));
+    uint32_t m = absmax_bf16x2(absmax_bf16x2(a, b), absmax_bf16x2(c, d));
 #pragma unroll
-    for (int o = 8; o >= 1; o >>= 1) m = max_bf16x2(m, __shfl_xor_sync(0xffffffffu, m, o));
+    for (int o = 8; o >= 1; o >>= 1) m = absmax_bf16x2(m, __shfl_xor_sync(0xffffffffu, m, o));
+    m = abs_bf16x2(m);
     return fmaxf(bf16_lo(m), bf16_hi(m));
 }
 
@@ -136,28 +137,70 @@ silu_mul_quant_kernel(const __nv_bfloat16* __restrict__ in, uint32_t N2, int64_t
     smq_chunk<UE8M0, U>(valid, out_row, g0, threadIdx.x & 15u, in, N2, ld_in, q, ld_q, scale, s_row, s_grp, eps, table, G, packed);
 }
 
-// Large inputs: one persistent block of 1024 threads per SM keeps the whole 128 KB exact table in
-// shared memory, so silu costs two shared loads per pair instead of the approximation and its
-// check; the blocks stride over the chunks.  ROWS as in the flat kernel.
-template <bool UE8M0, int U, int ROWS>
+// One group of 128 outputs held by a QUARTER-warp: lane j owns elements [8j, 8j+8) and [64+8j, 64+8j+8), i.e. two
+// 16-byte vectors of gate and two of up (each load instruction of the quarter-warp still covers 128 contiguous
+// bytes).  Compared with a half-warp per group, the per-group work -- absmax shuffles, scale arithmetic, scale
+// store -- is shared by 16 elements per lane instead of 8.  All values come from the shared-memory table.
+// The four quarter-warps of a warp must call this together (full-warp shuffles).
+__device__ __forceinline__ void smq_group16(bool live, uint32_t row, uint32_t g, uint32_t j, const uint4 (&gv)[2], const uint4 (&uv)[2],
+                                            uint8_t* __restrict__ q, int64_t ld_q, float* __restrict__ scale, int64_t s_row,
+                                            int64_t s_grp, float eps, const uint16_t* __restrict__ tab, uint32_t G,
+                                            uint32_t* __restrict__ packed) {
+    uint32_t y[8];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        y[4 * h + 0] = mul_bf16x2(silu_table_pair(gv[h].x, tab), uv[h].x);
+        y[4 * h + 1] = mul_bf16x2(silu_table_pair(gv[h].y, tab), uv[h].y);
+        y[4 * h + 2] = mul_bf16x2(silu_table_pair(gv[h].z, tab), uv[h].z);
+        y[4 * h + 3] = mul_bf16x2(silu_table_pair(gv[h].w, tab), uv[h].w);
+    }
+    uint32_t m = absmax_bf16x2(absmax_bf16x2(absmax_bf16x2(y[0], y[1]), absmax_bf16x2(y[2], y[3])),
+                               absmax_bf16x2(absmax_bf16x2(y[4], y[5]), absmax_bf16x2(y[6], y[7])));
+#pragma unroll
+    for (int o = 4; o >= 1; o >>= 1) m = absmax_bf16x2(m, __shfl_xor_sync(0xffffffffu, m, o));
+    m = abs_bf16x2(m);
+    const float a = fmaxf(fmaxf(bf16_lo(m), bf16_hi(m)), eps);
+    const uint32_t f = ue8m0_scale_field(a);
+    const float sc = __uint_as_float(f << 23), inv = __uint_as_float((254u - f) << 23);
+    if (live) {
+        uint8_t* qrow = q + (int64_t)row * ld_q + g * 128u + j * 8u;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            uint2 o;
+            o.x = quant_pair_s<true>(y[4 * h + 0], sc, inv) | (quant_pair_s<true>(y[4 * h + 1], sc, inv) << 16);
+            o.y = quant_pair_s<true>(y[4 * h + 2], sc, inv) | (quant_pair_s<true>(y[4 * h + 3], sc, inv) << 16);
+            *reinterpret_cast<uint2*>(qrow + 64 * h) = o;
+        }
+        if (j == 0) {
+            scale[(int64_t)row * s_row + (int64_t)g * s_grp] = sc;
+            if (packed != nullptr)
+                packed[((size_t)(row >> 7) * G + g) * 128u + (row & 31u) * 4u + ((row & 127u) >> 5)] = f * 0x01010101u;
+        }
+    }
+}
+
+// Large inputs (UE8M0 scales): one persistent block of 1024 threads per SM keeps the whole 128 KB exact table in
+// shared memory, so silu costs two shared loads per pair instead of the approximation and its check.  A chunk is
+// U consecutive groups of one row and belongs to a quarter-warp.  ROWS as in the flat kernel.
+template <int U, int ROWS>
 __global__ void __launch_bounds__(1024, 1)
 silu_mul_quant_smem_kernel(const __nv_bfloat16* __restrict__ in, uint32_t N2, int64_t ld_in, uint8_t* __restrict__ q,
                            int64_t ld_q, float* __restrict__ scale, int64_t s_row, int64_t s_grp, float eps,
                            const uint16_t* __restrict__ table, const int32_t* __restrict__ row_info, uint32_t G,
                            uint32_t chunks_per_row, uint32_t n_chunks, uint32_t* __restrict__ packed) {
     extern __shared__ __align__(16) uint16_t tab[];
-    const uint32_t half = (threadIdx.x >> 4) & 1u, j = threadIdx.x & 15u;
+    const uint32_t quarter = (threadIdx.x >> 3) & 3u, j = threadIdx.x & 7u;
     // each block takes one contiguous, equally sized range of chunks (a grid-stride loop would leave
     // most blocks idle during the last, partly filled round)
     const uint32_t lo = (uint32_t)(((uint64_t)n_chunks * blockIdx.x) / gridDim.x);
     const uint32_t hi = (uint32_t)(((uint64_t)n_chunks * (blockIdx.x + 1)) / gridDim.x);
-    const uint32_t step = blockDim.x >> 4;
+    const uint32_t step = blockDim.x >> 3;
     // Rolling prefetch: the U groups of a chunk sit in registers; as soon as group u of the current chunk
     // has been processed, group u of the warp's next chunk is requested into the same registers, so about
     // (U-1)/U of the register buffer is in flight at any time instead of the buffer draining once per chunk.
     struct Ref { bool valid; uint32_t row, g0; };
     auto ref_of = [&](uint32_t base) -> Ref {
-        const uint32_t chunk = base + half;
+        const uint32_t chunk = base + quarter;
         Ref r;
         r.valid = base < hi && chunk < hi;
         r.row = r.valid ? chunk / chunks_per_row : 0u;
@@ -169,14 +212,17 @@ silu_mul_quant_smem_kernel(const __nv_bfloat16* __restrict__ in, uint32_t N2, in
         }
         return r;
     };
-    uint4 gv[U], uv[U];
+    uint4 gv[U][2], uv[U][2];
     auto fetch = [&](const Ref& r, int u) {
         const bool live = r.valid && (r.g0 + u) < G;
         const __nv_bfloat16* src = in + (int64_t)r.row * ld_in + (r.g0 + u) * 128u + j * 8u;
-        gv[u] = live ? __ldcs(reinterpret_cast<const uint4*>(src)) : make_uint4(0, 0, 0, 0);
-        uv[u] = live ? __ldcs(reinterpret_cast<const uint4*>(src + N2)) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            gv[u][h] = live ? __ldcs(reinterpret_cast<const uint4*>(src + 64 * h)) : make_uint4(0, 0, 0, 0);
+            uv[u][h] = live ? __ldcs(reinterpret_cast<const uint4*>(src + 64 * h + N2)) : make_uint4(0, 0, 0, 0);
+        }
     };
-    uint32_t base = lo + (threadIdx.x >> 5) * 2u;
+    uint32_t base = lo + (threadIdx.x >> 5) * 4u;
     Ref cur = ref_of(base);
 #pragma unroll
     for (int u = 0; u < U; ++u) fetch(cur, u);
@@ -191,12 +237,12 @@ silu_mul_quant_smem_kernel(const __nv_bfloat16* __restrict__ in, uint32_t N2, in
     __syncthreads();
     for (; base < hi; base += step) {
         const Ref nxt = ref_of(base + step);
-        const bool any_cur = __any_sync(0xffffffffu, cur.valid);       // warp-uniform: something to do in this chunk pair
+        const bool any_cur = __any_sync(0xffffffffu, cur.valid);       // warp-uniform: something to do in these four chunks
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             if (any_cur)
-                smq_group<UE8M0, true>(cur.valid && (cur.g0 + u) < G, cur.row, cur.g0 + u, j, gv[u], uv[u], q, ld_q, scale, s_row, s_grp,
-                                       eps, tab, G, packed);
+                smq_group16(cur.valid && (cur.g0 + u) < G, cur.row, cur.g0 + u, j, gv[u], uv[u], q, ld_q, scale, s_row, s_grp, eps, tab, G,
+                            packed);
             fetch(nxt, u);
         }
         cur = nxt;
@@ -302,27 +348,28 @@ static int launch_silu_mul_quant(const char* who, const void* in, int64_t M, int
     const unsigned masked_x = (unsigned)std::min<int64_t>((max_m * cpr + 15) / 16, std::max<int64_t>(4, (8 * (int64_t)sm_count() + n_exp - 1) / std::max<int64_t>(n_exp, 1)));
     // large flat inputs with power-of-two scales: persistent blocks with the exact table in shared memory
     if (rows_mode != 2 && ue8m0 && n_chunks * U >= 32768) {
-        constexpr int U2 = 4;
+        constexpr int U2 = 2;                 // groups per quarter-warp: 128 bytes per lane in flight
         const int64_t cpr2 = (G + U2 - 1) / U2, n2c = M * cpr2;
+        KBN_REQUIRE(n2c < (1ll << 31), KBN_ERR_ARG, "%s: more than 2^31 groups", who);
         static int attr_set[64] = {0};
         int dev = 0;
         KBN_CUDA(cudaGetDevice(&dev));
         if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-            KBN_CUDA(cudaFuncSetAttribute(silu_mul_quant_smem_kernel<true, U2, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 131072));
-            KBN_CUDA(cudaFuncSetAttribute(silu_mul_quant_smem_kernel<true, U2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 131072));
-            KBN_CUDA(cudaFuncSetAttribute(silu_mul_quant_smem_kernel<true, U2, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 131072));
+            KBN_CUDA(cudaFuncSetAttribute(silu_mul_quant_smem_kernel<U2, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 131072));
+            KBN_CUDA(cudaFuncSetAttribute(silu_mul_quant_smem_kernel<U2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 131072));
+            KBN_CUDA(cudaFuncSetAttribute(silu_mul_quant_smem_kernel<U2, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 131072));
             attr_set[dev] = 1;
         }
         const unsigned grid = (unsigned)sm_count();
         if (rows_mode == 0)
-            silu_mul_quant_smem_kernel<true, U2, 0><<<grid, 1024, 131072, st>>>(ib, (uint32_t)N2, ld_in, qb, ld_q, scale, s_row, s_grp, eps, table,
-                                                                               row_info, (uint32_t)G, (uint32_t)cpr2, (uint32_t)n2c, packed);
+            silu_mul_quant_smem_kernel<U2, 0><<<grid, 1024, 131072, st>>>(ib, (uint32_t)N2, ld_in, qb, ld_q, scale, s_row, s_grp, eps, table,
+                                                                         row_info, (uint32_t)G, (uint32_t)cpr2, (uint32_t)n2c, packed);
         else if (rows_mode == 1)
-            silu_mul_quant_smem_kernel<true, U2, 1><<<grid, 1024, 131072, st>>>(ib, (uint32_t)N2, ld_in, qb, ld_q, scale, s_row, s_grp, eps, table,
-                                                                               row_info, (uint32_t)G, (uint32_t)cpr2, (uint32_t)n2c, packed);
+            silu_mul_quant_smem_kernel<U2, 1><<<grid, 1024, 131072, st>>>(ib, (uint32_t)N2, ld_in, qb, ld_q, scale, s_row, s_grp, eps, table,
+                                                                         row_info, (uint32_t)G, (uint32_t)cpr2, (uint32_t)n2c, packed);
         else
-            silu_mul_quant_smem_kernel<true, U2, 3><<<grid, 1024, 131072, st>>>(ib, (uint32_t)N2, ld_in, qb, ld_q, scale, s_row, s_grp, eps, table,
-                                                                               row_info, (uint32_t)G, (uint32_t)cpr2, (uint32_t)n2c, packed);
+            silu_mul_quant_smem_kernel<U2, 3><<<grid, 1024, 131072, st>>>(ib, (uint32_t)N2, ld_in, qb, ld_q, scale, s_row, s_grp, eps, table,
+                                                                         row_info, (uint32_t)G, (uint32_t)cpr2, (uint32_t)n2c, packed);
     } else if (rows_mode == 2) {
         KBN_REQUIRE(M / max_m <= 65535, KBN_ERR_ARG, "%s: more than 65535 experts", who);
         if (ue8m0) KBN_SMQ_MASKED(true); else KBN_SMQ_MASKED(false);
