@@ -590,15 +590,21 @@ def wl_ep_moe(args, rank, world, dev, sampler, name="ep_moe"):
     ach = (g1 + g2) / 2.0 / (gemm_ms * 1e-3) / 1e9
     gemm_tflops = 2.0 * rows * 3 * i * h / 2.0 / (gemm_ms * 1e-3) / 1e12
     assert ops.gemm_status(dev) == 0
-    # e2e: pinned host activations and routing in, result back to the host
-    hx, htw, hti = x.cpu().pin_memory(), tw.cpu().pin_memory(), ti.cpu().pin_memory()
-    dx, dtw, dti = torch.empty_like(x), torch.empty_like(tw), torch.empty_like(ti)
+    # e2e: pinned host activations and routing in, result back to the host.  The three inputs travel as one staged
+    # buffer (one H2D copy per step); the device tensors the layer sees are views of its device twin.
+    nx, nw = t * h * 2, t * topk * 4
+    hblob = torch.empty(nx + 2 * nw, dtype=torch.uint8).pin_memory()
+    hblob[:nx].view(torch.bfloat16).view(t, h).copy_(x.cpu())
+    hblob[nx:nx + nw].view(torch.float32).view(t, topk).copy_(tw.cpu())
+    hblob[nx + nw:].view(torch.int32).view(t, topk).copy_(ti.cpu())
+    dblob = torch.empty(nx + 2 * nw, dtype=torch.uint8, device=dev)
+    dx = dblob[:nx].view(torch.bfloat16).view(t, h)
+    dtw = dblob[nx:nx + nw].view(torch.float32).view(t, topk)
+    dti = dblob[nx + nw:].view(torch.int32).view(t, topk)
     hout = torch.empty(t, h, dtype=torch.bfloat16).pin_memory()
 
     def e2e_step(_):
-        dx.copy_(hx, non_blocking=True)
-        dtw.copy_(htw, non_blocking=True)
-        dti.copy_(hti, non_blocking=True)
+        dblob.copy_(hblob, non_blocking=True)
         layer.forward(dx, dti, dtw, w13_q, w13_s, w2_q, w2_s, out=out)
         hout.copy_(out, non_blocking=True)
 
