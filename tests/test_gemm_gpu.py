@@ -1,6 +1,5 @@
 """GPU parity, through the C ABI, of the block-scaled FP8 GEMMs against the oracle's
 dequantise-then-fp32-matmul: max relative error 1e-2 (|d| <= 1e-2 + 1e-2*|ref|), cosine > 0.9999."""
-import numpy as np
 import pytest
 import torch
 

@@ -1,6 +1,5 @@
 """GPU parity of the MoE permutation kernels (bit-exact against kb-nano's own permute, from the
 golden fixture) and of the whole FP8 expert pipeline (tolerance rule of the GEMMs)."""
-import numpy as np
 import pytest
 import torch
 

@@ -5,7 +5,7 @@ import torch
 
 from oracle import c_oracle as co
 from oracle import torch_oracle as to
-from tests.util import (assert_gemm_close, assert_quant_equal, bf16_from_bits, bits16, bits8, fp8_from_bits, golden)
+from tests.util import (assert_gemm_close, assert_quant_equal, bf16_from_bits, bits16, fp8_from_bits, golden)
 
 
 def test_quant_1x128_matches_reference():

@@ -6,7 +6,7 @@ import torch
 
 from oracle import c_oracle as co
 from oracle import torch_oracle as to
-from tests.util import assert_quant_equal, bf16_from_bits, bits16, bits8, golden
+from tests.util import assert_quant_equal, bf16_from_bits, bits16, golden
 
 pytestmark = pytest.mark.gpu
 FP8 = torch.float8_e4m3fn

@@ -2,7 +2,6 @@
 A floating-point kernel (the sum of squares is order-dependent), so the comparison uses kb-nano's own rule
 for (fp8, scale) pairs: |dequant(got) - dequant(ref)| <= 0.5*scale + 0.125*|ref| (bench/kernels/runner.py:265-291),
 plus: scales identical and bytes identical on all but a sliver of groups/elements."""
-import numpy as np
 import pytest
 import torch
 

@@ -1,7 +1,6 @@
 """GPU parity of the routing kernel against kb-nano's TopKSoftmax (reference-generated fixture) and against the
 oracle's restatement of GroupedTopK.  Expert ids must agree wherever the selection values are not tied to within
 rounding; weights within 2e-6 relative (fp32 exp on the GPU and on the host differ in the last place)."""
-import numpy as np
 import pytest
 import torch
 
