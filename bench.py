@@ -608,7 +608,9 @@ def wl_ep_moe(args, rank, world, dev, sampler, name="ep_moe"):
         layer.forward(dx, dti, dtw, w13_q, w13_s, w2_q, w2_s, out=out)
         hout.copy_(out, non_blocking=True)
 
-    ms_e2e = Timed(world, 0, dev).run(e2e_step, args.steps, 3)
+    # the K steps (copy in, layer, copy out) are captured in one CUDA graph, the way a serving loop replays a decode
+    # step: the layer keeps its step counter on the device, so a captured step can be replayed
+    ms_e2e = run_graph(world, e2e_step, args.steps, 3)
     layer.check()
     layer.close()
     flop = 2.0 * t * topk * world * 3 * i * h
@@ -636,6 +638,8 @@ def wl_ep_moe(args, rank, world, dev, sampler, name="ep_moe"):
                    "parallelism": f"ep{world}", "experts_per_rank": e_l, "tokens_per_rank": t, "global_tokens": t * world,
                    "l2": f"local expert weights ({e_l * 3 * i * h / 1e9:.2f} GB) exceed the 126 MB L2",
                    "exchange": "peer stores over NVLink (dispatch fp8 rows + scales, combine bf16 rows), release/acquire flags",
+                   "e2e": "per step one pinned-host -> device copy of the inputs, the layer, one device -> host copy of the result; "
+                          "the K steps are captured in one CUDA graph and timed with one CUDA-event pair",
                    "layer_tflops": flop / world / (ms * 1e-3) / 1e12},
         "e2e": {"value": t * world / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": t * h * 2 + t * topk * 8, "d2h_bytes_per_step": t * h * 2},
         "gpu_launches": launches // (args.steps + args.warmup) * args.steps,

@@ -5,7 +5,10 @@
 //   dispatch  one warp per (token, slot): a remote atomicAdd on the owner's per-expert counter
 //             gives the row slot, then the fp8 row, its 1x128 scales and a (source, pair) tag are
 //             stored straight into the owner's masked-layout buffers [E_local, max_m, H].
-//   signal    the last block of a sender publishes `epoch` into a per-(source) flag on every peer
+//   signal    the last block of a sender publishes the step number into a per-(source) flag on every peer.
+//             The step number lives in device memory (`epoch`, the number of completed steps; the running step is
+//             *epoch + 1 and the step's last wait kernel advances it), so a step takes no argument that changes
+//             from call to call and a captured CUDA graph of it can be replayed
 //             (st.release.sys after a system fence); a one-block kernel on the receiver polls its
 //             flags (ld.acquire.sys) with a one-second bound and records {phase, peer} on expiry.
 //   experts   masked grouped GEMM1 -> fused SiLU*up+quant (valid rows only) -> masked grouped GEMM2.
@@ -63,9 +66,9 @@ struct kbn_ep_ctx {
     __nv_bfloat16* mm1; uint8_t* a2_q; float* a2_s; __nv_bfloat16* mm2;
     uint8_t* sf2;                      // packed UE8M0 scales of the activation between the GEMMs (UE8M0 GEMM path)
     int32_t* identity;                 // [max_tokens*topk] 0,1,2,...
-    int32_t* done;                     // [2] block-completion counters
+    int32_t* done;                     // [4] block-completion counters of dispatch and combine, the step counter, spare
     int32_t* status;                   // [4] code, phase, peer, detail
-    int32_t epoch;
+    int32_t* epoch;                    // device word: completed steps
 };
 
 namespace kbn {
@@ -98,7 +101,7 @@ __device__ __forceinline__ int32_t ld_acquire_sys(const int32_t* p) {
 
 // Publishes `epoch` to flag slot `rank` of every peer once every block of the grid has passed here.
 __device__ __forceinline__ void signal_when_grid_done(int32_t* done, const EpPeers& peers, int64_t flags_off, int rank,
-                                                      int world, int32_t epoch, int32_t* counters_to_clear, int n_clear) {
+                                                      int world, const int32_t* epoch, int32_t* counters_to_clear, int n_clear) {
     __threadfence_system();
     __syncthreads();
     __shared__ int last;
@@ -110,7 +113,7 @@ __device__ __forceinline__ void signal_when_grid_done(int32_t* done, const EpPee
     __threadfence_system();
     __syncthreads();
     if (threadIdx.x < world)
-        st_release_sys(reinterpret_cast<int32_t*>(peers.base[threadIdx.x] + flags_off) + rank, epoch);
+        st_release_sys(reinterpret_cast<int32_t*>(peers.base[threadIdx.x] + flags_off) + rank, *epoch + 1);
     if (threadIdx.x == 0) *done = 0;
 }
 
@@ -118,7 +121,7 @@ __device__ __forceinline__ void signal_when_grid_done(int32_t* done, const EpPee
 __global__ void __launch_bounds__(256)
 ep_dispatch_kernel(const uint8_t* __restrict__ a_q, const float* __restrict__ a_s, const int32_t* __restrict__ ids,
                    int n_pairs, int topk, int hidden, int e_local, int max_m, int experts_total, EpPeers peers, EpLayout lay,
-                   int rank, int world, int32_t epoch, int32_t* done, int32_t* status) {
+                   int rank, int world, const int32_t* epoch, int32_t* done, int32_t* status) {
     const int i = blockIdx.x * 8 + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (i < n_pairs) {
@@ -159,27 +162,33 @@ ep_dispatch_kernel(const uint8_t* __restrict__ a_q, const float* __restrict__ a_
 }
 
 // One block; thread r waits until source r has published `epoch` (or the bound runs out).
-__global__ void ep_wait_kernel(const int32_t* __restrict__ flags, int world, int32_t epoch, int phase, int32_t* status) {
+// advance != 0 (the step's last wait): once every thread is done, the step counter moves on.
+__global__ void ep_wait_kernel(const int32_t* __restrict__ flags, int world, int32_t* epoch_word, int phase, int32_t* status,
+                               int advance) {
     const int r = threadIdx.x;
-    if (r >= world) return;
-    const long long t0 = clock64();
-    while (ld_acquire_sys(flags + r) != epoch) {
-        if (clock64() - t0 > kFlagWaitCycles) {
-            if (atomicCAS(status, 0, 20) == 0) {   // timed out waiting for a peer's signal
-                status[1] = phase;
-                status[2] = r;
+    const int32_t epoch = *epoch_word + 1;
+    if (r < world) {
+        const long long t0 = clock64();
+        while (ld_acquire_sys(flags + r) != epoch) {
+            if (clock64() - t0 > kFlagWaitCycles) {
+                if (atomicCAS(status, 0, 20) == 0) {   // timed out waiting for a peer's signal
+                    status[1] = phase;
+                    status[2] = r;
+                }
+                break;
             }
-            return;
+            __nanosleep(64);
         }
-        __nanosleep(64);
     }
+    __syncthreads();
+    if (advance && threadIdx.x == 0) *epoch_word = epoch;
 }
 
 // Expert outputs back to their sources: blockIdx.y = local expert, whose first counters[le] rows are
 // spread over the warps of its gridDim.x blocks; each lane keeps four 16-byte loads in flight.
 __global__ void __launch_bounds__(256)
 ep_combine_send_kernel(const __nv_bfloat16* __restrict__ mm2, int hidden, int e_local, int max_m, EpPeers peers, EpLayout lay,
-                       int rank, int world, int32_t epoch, int32_t* done) {
+                       int rank, int world, const int32_t* epoch, int32_t* done) {
     const int le = blockIdx.y;
     const int lane = threadIdx.x & 31;
     uint8_t* mine = peers.base[rank];
@@ -229,7 +238,7 @@ extern "C" int kbn_ep_create(int rank, int world, int64_t experts_total, int64_t
     KBN_REQUIRE(c, KBN_ERR_CUDA, "kbn_ep_create: out of host memory");
     c->rank = rank; c->world = world;
     c->experts_total = experts_total; c->e_local = experts_total / world; c->max_m = max_m; c->hidden = hidden; c->inter = inter;
-    c->max_tokens = max_tokens; c->topk = topk; c->attached = false; c->epoch = 0;
+    c->max_tokens = max_tokens; c->topk = topk; c->attached = false;
     KBN_CUDA(cudaGetDevice(&c->device));
     c->lay = make_layout(*c);
     KBN_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->sym), (size_t)c->lay.total));
@@ -247,6 +256,7 @@ extern "C" int kbn_ep_create(int rank, int world, int64_t experts_total, int64_t
     KBN_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->done), 16));
     KBN_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->status), 16));
     KBN_CUDA(cudaMemset(c->done, 0, 16));
+    c->epoch = c->done + 2;            // words 0 and 1: block-completion counters; word 2: completed steps
     KBN_CUDA(cudaMemset(c->status, 0, 16));
     const int n = (int)(max_tokens * topk);
     ep_iota_kernel<<<(n + 255) / 256, 256>>>(c->identity, n);
@@ -306,7 +316,7 @@ extern "C" int kbn_ep_moe_forward(kbn_ep_ctx* c, const void* x_bf16, const int32
     KBN_REQUIRE(!ue8m0 || c->max_m % 128 == 0, KBN_ERR_ARG, "kbn_ep_moe_forward: the UE8M0 path needs max_m to be a multiple of 128");
     if (T > 0) KBN_REQUIRE(x_bf16 && topk_ids && topk_w && out_bf16, KBN_ERR_ARG, "kbn_ep_moe_forward: null pointer");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const int32_t epoch = ++c->epoch;
+    int32_t* epoch = c->epoch;
     const int H = (int)c->hidden, I = (int)c->inter, G = H / 128;
     uint8_t* mine = c->sym;
     int32_t* counters = reinterpret_cast<int32_t*>(mine + c->lay.counters);
@@ -323,7 +333,7 @@ extern "C" int kbn_ep_moe_forward(kbn_ep_ctx* c, const void* x_bf16, const int32
                                                  (int)c->experts_total, c->peers, c->lay, c->rank, c->world, epoch, c->done, c->status);
     KBN_CHECK_LAUNCH();
     // 3. wait for every source's rows
-    ep_wait_kernel<<<1, kMaxRanks, 0, st>>>(reinterpret_cast<const int32_t*>(mine + c->lay.flags_dispatch), c->world, epoch, 1, c->status);
+    ep_wait_kernel<<<1, kMaxRanks, 0, st>>>(reinterpret_cast<const int32_t*>(mine + c->lay.flags_dispatch), c->world, epoch, 1, c->status, 0);
     KBN_CHECK_LAUNCH();
     // 4. local experts on the received rows
     const float* recv_s = reinterpret_cast<const float*>(mine + c->lay.recv_s);
@@ -352,7 +362,7 @@ extern "C" int kbn_ep_moe_forward(kbn_ep_ctx* c, const void* x_bf16, const int32
         cb.counters = counters;
         cb.n_counters = (int32_t)c->e_local;
         cb.world = c->world;
-        cb.epoch = epoch;
+        cb.epoch = epoch;              // the device word
         rc = mx::gemm_masked_ue8m0_combine(c->a2_q, c->sf2, w2, w2_sf_packed, counters, c->e_local, c->max_m, H, I, cb, st);
         if (rc != KBN_OK) return rc;
     } else {
@@ -365,7 +375,7 @@ extern "C" int kbn_ep_moe_forward(kbn_ep_ctx* c, const void* x_bf16, const int32
                                                                                 c->world, epoch, c->done + 1);
         KBN_CHECK_LAUNCH();
     }
-    ep_wait_kernel<<<1, kMaxRanks, 0, st>>>(reinterpret_cast<const int32_t*>(mine + c->lay.flags_combine), c->world, epoch, 2, c->status);
+    ep_wait_kernel<<<1, kMaxRanks, 0, st>>>(reinterpret_cast<const int32_t*>(mine + c->lay.flags_combine), c->world, epoch, 2, c->status, 1);
     KBN_CHECK_LAUNCH();
     // 6. weighted sum over the topk slots of each local token, in slot order
     if (T > 0) {

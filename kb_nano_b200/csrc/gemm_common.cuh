@@ -46,7 +46,8 @@ struct CombineEpilogue {
     const int32_t* meta;
     int32_t* done;
     int32_t* counters;
-    int32_t n_counters, world, epoch;
+    const int32_t* epoch;     // device word: the step that is running is *epoch + 1 (see ep_moe.cu)
+    int32_t n_counters, world;
 };
 
 enum GemmEpilogue : int { kEpiStore = 0, kEpiAct = 1, kEpiCombine = 2 };

@@ -374,7 +374,7 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         __threadfence_system();
         __syncthreads();
         if ((int)threadIdx.x < cb.world)
-            asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(cb.peer_flag[threadIdx.x]), "r"(cb.epoch) : "memory");
+            asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(cb.peer_flag[threadIdx.x]), "r"(*cb.epoch + 1) : "memory");
         if (threadIdx.x == 0) *cb.done = 0;
     }
 }
@@ -892,7 +892,7 @@ int gemm_masked_ue8m0_combine(const void* A, const void* sfa_packed, const void*
     KBN_REQUIRE(E > 0 && max_m > 0 && N > 0 && K > 0 && A && B && masked_m, KBN_ERR_ARG, "%s: bad arguments", who);
     KBN_REQUIRE(max_m % 128 == 0 && N % 32 == 0, KBN_ERR_ARG, "%s: max_m must be a multiple of 128 and N of 32", who);
     KBN_REQUIRE(E * N < (1ll << 31) && E * max_m < (1ll << 31), KBN_ERR_ARG, "%s: too large", who);
-    KBN_REQUIRE(cb.world >= 1 && cb.world <= kMaxPeerRanks && cb.meta && cb.done, KBN_ERR_ARG, "%s: bad peer description", who);
+    KBN_REQUIRE(cb.world >= 1 && cb.world <= kMaxPeerRanks && cb.meta && cb.done && cb.epoch, KBN_ERR_ARG, "%s: bad peer description", who);
     GemmParams p{};
     fill_params(p, nullptr, N, E * max_m, N, K, E, max_m, kMasked);
     p.masked_m = masked_m;

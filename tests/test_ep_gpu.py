@@ -55,6 +55,36 @@ def test_ep_world1_matches_oracle(cuda_dev):
     layer.close()
 
 
+def test_ep_forward_replays_from_a_cuda_graph(cuda_dev):
+    """kb-nano runs decode steps from CUDA graphs (infra/engine.py:2410-2427): the layer's step counter lives on the
+    device, so a captured forward can be replayed with new inputs in the same buffers."""
+    from kb_nano_b200 import ep
+    t, h, i, e, topk = 32, 512, 256, 16, 4
+    xs, routes, (w13_q, w13_s, w2_q, w2_s) = ep_case(3, t, h, i, e, topk, seed=21)
+    d = cuda_dev
+    wd = [w.to(d) for w in (w13_q, w13_s, w2_q, w2_s)]
+    layer = ep.EpMoe(0, 1, e, h, i, max_tokens=t, topk=topk, max_m=128, device=d)
+    x, tw, ti = xs[0].to(d), routes[0][0].to(d).contiguous(), routes[0][1].to(d).contiguous()
+    out = torch.empty(t, h, dtype=torch.bfloat16, device=d)
+    layer.forward(x, ti, tw, *wd, out=out)                 # warm-up outside the capture (table, attributes, packed scales)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        layer.forward(x, ti, tw, *wd, out=out)
+    for r in range(3):
+        x.copy_(xs[r].to(d))
+        tw.copy_(routes[r][0].to(d))
+        ti.copy_(routes[r][1].to(d))
+        graph.replay()
+        layer.check()
+        ref = to.moe_layer(xs[r], w13_q, w13_s, w2_q, w2_s, routes[r][0], routes[r][1])
+        assert_gemm_close(out.cpu(), ref, f"graph replay {r}")
+    eager = layer.forward(x, ti, tw, *wd).clone()          # eager calls and replays interleave
+    graph.replay()
+    assert torch.equal(out.view(torch.int16), eager.view(torch.int16))
+    layer.close()
+
+
 def test_ep_overflow_is_reported_not_fatal(cuda_dev):
     """More rows for one expert than max_m: the status word says so and the context stays usable."""
     from kb_nano_b200 import ep
