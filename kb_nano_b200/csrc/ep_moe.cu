@@ -246,10 +246,10 @@ extern "C" int kbn_ep_create(int rank, int world, int64_t experts_total, int64_t
     const int64_t rows = c->e_local * max_m;
     KBN_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->a_q), (size_t)(max_tokens * hidden)));
     KBN_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->a_s), (size_t)(max_tokens * (hidden / 128) * 4)));
-    KBN_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->mm1), (size_t)(rows * 2 * inter * 2)));
+    c->mm1 = nullptr;      // bf16 GEMM outputs of the fp32-scale path only: allocated by the first call that takes it
+    c->mm2 = nullptr;
     KBN_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->a2_q), (size_t)(rows * inter)));
     KBN_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->a2_s), (size_t)(rows * (inter / 128) * 4)));
-    KBN_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->mm2), (size_t)(rows * hidden * 2)));
     KBN_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->sf2), (size_t)kbn_packed_sf_rows_bytes(rows, inter)));
     KBN_CUDA(cudaMemset(c->sf2, 0x7f, (size_t)kbn_packed_sf_rows_bytes(rows, inter)));
     KBN_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->identity), (size_t)(max_tokens * topk * 4)));
@@ -337,13 +337,24 @@ extern "C" int kbn_ep_moe_forward(kbn_ep_ctx* c, const void* x_bf16, const int32
     KBN_CHECK_LAUNCH();
     // 4. local experts on the received rows
     const float* recv_s = reinterpret_cast<const float*>(mine + c->lay.recv_s);
-    const int64_t rows_all = c->e_local * c->max_m;
     if (ue8m0) {
         // GEMM1 with SiLU(gate)*up and the 1x128 quantisation in its epilogue
         rc = kbn_fp8_grouped_gemm_masked_ue8m0_silu(mine + c->lay.recv_q, mine + c->lay.recv_sf, w13, w13_sf_packed, c->a2_q, c->a2_s, c->sf2,
                                                     counters, c->e_local, c->max_m, I, H, stream);
         if (rc != KBN_OK) return rc;
     } else {
+        if (!c->mm1) {
+            // Weight scales that are not powers of two (or max_m not a multiple of 128): the GEMMs store bf16 and the
+            // activation and the combine are kernels of their own.  Their two scratch buffers are the size of the
+            // receive buffers times 2I and H bf16 and are allocated here, once; not inside a stream capture.
+            cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+            KBN_CUDA(cudaStreamIsCapturing(st, &cap));
+            KBN_REQUIRE(cap == cudaStreamCaptureStatusNone, KBN_ERR_UNSUPPORTED,
+                        "kbn_ep_moe_forward: the first call on the fp32-scale path allocates scratch and cannot be captured");
+            const int64_t rows = c->e_local * c->max_m;
+            KBN_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->mm1), (size_t)(rows * 2 * I * 2)));
+            KBN_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->mm2), (size_t)(rows * H * 2)));
+        }
         rc = kbn_fp8_grouped_gemm_masked(mine + c->lay.recv_q, recv_s, c->max_m * G, G, 1, w13, w13_s, c->mm1, counters, c->e_local, c->max_m, 2 * I, H, stream);
         if (rc != KBN_OK) return rc;
         rc = silu_mul_quant_masked(c->mm1, c->e_local, c->max_m, I, c->a2_q, c->a2_s, counters, st, nullptr);
