@@ -436,6 +436,9 @@ def wl_moe_single(args, rank, world, dev, sampler, name):
     if name == "moe_c3":
         t, h, i, e, topk, routing = 4096, 7168, 2048, 256, 8, "sigmoid"
         desc = "moe_c3: BASELINE configs[2], DeepSeek-V3-shaped FP8 MoE layer, 4096 tokens, 256 experts, top-8, contiguous layout"
+        if args.experts != 256:          # same rows per expert with fewer experts and tokens: small enough for a profiler capture
+            e, t = args.experts, 16 * args.experts
+            desc += f" [REDUCED to {e} experts and {t} tokens: profiling case, not the benchmark configuration]"
     else:
         t, h, i, e, topk, routing = 16384, 4096, 14336, 8, 2, "softmax"
         desc = "moe_c5: BASELINE configs[4], Mixtral-8x7B-shaped FP8 MoE layer, 16384 tokens, 8 experts, top-2, contiguous layout"
@@ -709,8 +712,9 @@ def main():
     ap.add_argument("--no-components", action="store_true",
                     help="default workload at N=1 only: skip the GEMM / quantiser figures reported beside the headline number")
     ap.add_argument("--experts", type=int, default=256,
-                    help="ep_moe only: total experts (256 = the benchmark configuration; 32 on one GPU reproduces the "
-                         "per-rank load of the 8-GPU run with 1.4 GB of weights, small enough for a profiler capture)")
+                    help="ep_moe and moe_c3: total experts (256 = the benchmark configuration; 32 on one GPU reproduces the "
+                         "per-rank load of the 8-GPU run with 1.4 GB of weights, small enough for a profiler capture; moe_c3 "
+                         "scales its tokens along, 16 per expert)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank, local, world = dist_info()
