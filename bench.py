@@ -155,8 +155,9 @@ def run_graph(world: int, step, steps: int, warmup: int, sampler: ClockSampler |
     """For kernels of a few microseconds to a few tens of microseconds: the K steps are captured in ONE CUDA
     graph (so the launches are back to back on the device and the host's launch cadence is not what is timed)
     and that graph is timed with one pair of CUDA events.  The caller's step(i) must rotate through inputs and
-    outputs whose total size exceeds L2, so that no step finds its data cached.  Warm-up: `warmup` eager steps
-    and one untimed replay; the clock sampler watches a quarter of a second of further replays and the timed one."""
+    outputs whose total size exceeds L2, so that no step finds its data cached.  Warm-up: `warmup` eager steps,
+    one untimed replay and a quarter of a second of further untimed replays (watched by the clock sampler, as is the
+    timed one)."""
     for i in range(warmup):
         step(i)
     torch.cuda.synchronize()
@@ -171,10 +172,10 @@ def run_graph(world: int, step, steps: int, warmup: int, sampler: ClockSampler |
     torch.cuda.synchronize()
     if sampler is not None:
         sampler.active = True
-        t0 = time.perf_counter()
-        while time.perf_counter() - t0 < 0.25:
-            graph.replay()
-            torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    while time.perf_counter() - t0 < 0.25:       # a quarter of a second of untimed replays: clocks and caches as in a running loop
+        graph.replay()
+        torch.cuda.synchronize()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     a.record()
     graph.replay()
