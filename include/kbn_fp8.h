@@ -46,6 +46,13 @@ int64_t kbn_launch_count(void);
 int kbn_quant_1x128(const void* x, int64_t M, int64_t K, int64_t ld_x, void* q, int64_t ld_q,
                     float* scale, int64_t s_row, int64_t s_grp, float eps, int ue8m0,
                     kbn_stream_t stream);
+/* The same with UE8M0 scales, and sf_packed (kbn_packed_sf_rows_bytes(M, K) bytes, 16-byte aligned) also receives
+ * the scales in the packed form the *_ue8m0 GEMMs read, so that a linear layer is two launches (this and the GEMM).
+ * Needs K, ld_x and ld_q to be multiples of 8 and x 16-byte aligned.  Words of rows past M in the last 128-row
+ * block are left unwritten (the GEMM never stores those rows). */
+int kbn_quant_1x128_sf(const void* x, int64_t M, int64_t K, int64_t ld_x, void* q, int64_t ld_q,
+                       float* scale, int64_t s_row, int64_t s_grp, float eps, void* sf_packed,
+                       kbn_stream_t stream);
 
 /*
  * Fused SiLU(gate)*up + 1x128 quantisation.

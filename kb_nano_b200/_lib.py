@@ -19,6 +19,7 @@ SIGNATURES = {
     "kbn_last_error": (ctypes.c_char_p, []),
     "kbn_launch_count": (_i64, []),
     "kbn_quant_1x128": (_i32, [_ptr, _i64, _i64, _i64, _ptr, _i64, _ptr, _i64, _i64, _f32, _i32, _ptr]),
+    "kbn_quant_1x128_sf": (_i32, [_ptr, _i64, _i64, _i64, _ptr, _i64, _ptr, _i64, _i64, _f32, _ptr, _ptr]),
     "kbn_silu_mul_quant_1x128": (_i32, [_ptr, _i64, _i64, _i64, _ptr, _i64, _ptr, _i64, _i64, _f32, _i32, _ptr]),
     "kbn_silu_bf16_table": (_i32, [_ptr, _ptr]),
     "kbn_rmsnorm_quant_1x128": (_i32, [_ptr, _ptr, _i64, _i64, _i64, _ptr, _i64, _ptr, _i64, _i64, _f32, _ptr]),

@@ -141,8 +141,7 @@ class Fp8Linear(nn.Module):
             torch.ops.kbn_b200.per_token_group_quant_fp8(input_2d, q_input, input_scale)
             torch.ops.kbn_b200.fp8_gemm_nt(q_input, input_scale, weight_fp8, w_scale, output)
         else:
-            ops.per_token_group_quant_fp8(input_2d, q_input, input_scale)
-            ops.fp8_gemm_nt_auto(q_input, input_scale, weight_fp8, w_scale, output)
+            ops.fp8_linear(input_2d, q_input, input_scale, weight_fp8, w_scale, output)
         if bias is not None:
             output = output + bias
         return output.view(*input_bf16.shape[:-1], N)

@@ -57,7 +57,7 @@ template <bool UE8M0, int U>
 __global__ void __launch_bounds__(256)
 quant_1x128_kernel(const __nv_bfloat16* __restrict__ x, uint32_t K, int64_t ld_x, uint8_t* __restrict__ q,
                    int64_t ld_q, float* __restrict__ scale, int64_t s_row, int64_t s_grp, float eps,
-                   uint32_t G, uint32_t chunks_per_row, uint32_t n_chunks) {
+                   uint32_t G, uint32_t chunks_per_row, uint32_t n_chunks, uint32_t* __restrict__ packed) {
     const uint32_t j = threadIdx.x & 15u;
     const uint32_t chunk = blockIdx.x * 16u + (threadIdx.x >> 4);
     const bool valid = chunk < n_chunks;
@@ -83,7 +83,14 @@ quant_1x128_kernel(const __nv_bfloat16* __restrict__ x, uint32_t K, int64_t ld_x
             o.x = quant_pair<UE8M0>(v[u].x, s) | (quant_pair<UE8M0>(v[u].y, s) << 16);
             o.y = quant_pair<UE8M0>(v[u].z, s) | (quant_pair<UE8M0>(v[u].w, s) << 16);
             *reinterpret_cast<uint2*>(qr + g * 128u + j * 8u) = o;
-            if (j == 0) scale[(int64_t)row * s_row + (int64_t)g * s_grp] = s.scale;
+            if (j == 0) {
+                scale[(int64_t)row * s_row + (int64_t)g * s_grp] = s.scale;
+                // optional second copy of the scale in the packed UE8M0 form the block-scaled GEMM reads:
+                // word ((row/128)*G + g)*128 + (row%32)*4 + (row%128)/32, exponent byte repeated four times
+                if (UE8M0 && packed != nullptr)
+                    packed[((size_t)(row >> 7) * G + g) * 128u + (row & 31u) * 4u + ((row & 127u) >> 5)] =
+                        ((__float_as_uint(s.scale) >> 23) & 0xffu) * 0x01010101u;
+            }
         }
     }
 }
@@ -126,10 +133,29 @@ quant_1x128_generic_kernel(const __nv_bfloat16* __restrict__ x, int64_t M, int64
 
 }  // namespace kbn
 
+namespace kbn {
+static int quant_1x128_impl(const void* x, int64_t M, int64_t K, int64_t ld_x, void* q, int64_t ld_q, float* scale, int64_t s_row,
+                            int64_t s_grp, float eps, int ue8m0, void* sf_packed, kbn_stream_t stream);
+}
+
 extern "C" int kbn_quant_1x128(const void* x, int64_t M, int64_t K, int64_t ld_x, void* q, int64_t ld_q,
                                float* scale, int64_t s_row, int64_t s_grp, float eps, int ue8m0,
                                kbn_stream_t stream) {
+    return kbn::quant_1x128_impl(x, M, K, ld_x, q, ld_q, scale, s_row, s_grp, eps, ue8m0, nullptr, stream);
+}
+
+extern "C" int kbn_quant_1x128_sf(const void* x, int64_t M, int64_t K, int64_t ld_x, void* q, int64_t ld_q,
+                                  float* scale, int64_t s_row, int64_t s_grp, float eps, void* sf_packed,
+                                  kbn_stream_t stream) {
     using namespace kbn;
+    KBN_REQUIRE(sf_packed && aligned16(sf_packed), KBN_ERR_ARG, "kbn_quant_1x128_sf: the packed scale buffer must be 16-byte aligned");
+    return quant_1x128_impl(x, M, K, ld_x, q, ld_q, scale, s_row, s_grp, eps, 1, sf_packed, stream);
+}
+
+static int kbn::quant_1x128_impl(const void* x, int64_t M, int64_t K, int64_t ld_x, void* q, int64_t ld_q, float* scale, int64_t s_row,
+                                 int64_t s_grp, float eps, int ue8m0, void* sf_packed, kbn_stream_t stream) {
+    using namespace kbn;
+    uint32_t* packed = static_cast<uint32_t*>(sf_packed);
     KBN_REQUIRE(M >= 0 && K >= 0, KBN_ERR_ARG, "kbn_quant_1x128: negative size (M=%lld K=%lld)", (long long)M, (long long)K);
     if (M == 0 || K == 0) return KBN_OK;
     KBN_REQUIRE(x && q && scale, KBN_ERR_ARG, "kbn_quant_1x128: null pointer");
@@ -147,11 +173,12 @@ extern "C" int kbn_quant_1x128(const void* x, int64_t M, int64_t K, int64_t ld_x
         const unsigned blocks = (unsigned)((n_chunks + 15) / 16);
         if (ue8m0)
             quant_1x128_kernel<true, U><<<blocks, 256, 0, st>>>(xb, (uint32_t)K, ld_x, qb, ld_q, scale, s_row, s_grp, eps,
-                                                                 (uint32_t)G, (uint32_t)cpr, (uint32_t)n_chunks);
+                                                                 (uint32_t)G, (uint32_t)cpr, (uint32_t)n_chunks, packed);
         else
             quant_1x128_kernel<false, U><<<blocks, 256, 0, st>>>(xb, (uint32_t)K, ld_x, qb, ld_q, scale, s_row, s_grp, eps,
-                                                                  (uint32_t)G, (uint32_t)cpr, (uint32_t)n_chunks);
+                                                                  (uint32_t)G, (uint32_t)cpr, (uint32_t)n_chunks, nullptr);
     } else {
+        KBN_REQUIRE(!packed, KBN_ERR_ARG, "kbn_quant_1x128_sf: K, the row strides and the pointers must allow 16-byte accesses");
         int64_t blocks = (NG + 7) / 8;
         KBN_REQUIRE(blocks < (1ll << 31), KBN_ERR_ARG, "kbn_quant_1x128: too many groups");
         if (ue8m0)

@@ -51,8 +51,10 @@ def _scale_strides(scale: torch.Tensor, rows: int, groups: int) -> tuple[int, in
 
 
 def per_token_group_quant_fp8(x: torch.Tensor, out_fp8: torch.Tensor, out_scale: torch.Tensor,
-                              use_ue8m0: bool = True, eps: float = 1e-10) -> None:
-    """In-place 1x128 quantisation: x bf16 [M,K] -> out_fp8 [M,K], out_scale fp32 [M,ceil(K/128)] (any strides)."""
+                              use_ue8m0: bool = True, eps: float = 1e-10, packed_sf: torch.Tensor | None = None) -> None:
+    """In-place 1x128 quantisation: x bf16 [M,K] -> out_fp8 [M,K], out_scale fp32 [M,ceil(K/128)] (any strides).
+    packed_sf (uint8, packed_sf_rows_bytes(M, K) bytes; UE8M0 only) also receives the scales in the packed form the
+    *_ue8m0 GEMMs read."""
     dev = _cuda(x, out_fp8, out_scale)
     if x.dim() != 2 or x.dtype != torch.bfloat16:
         raise ValueError(f"x must be bf16 [M,K], got {x.dtype} {tuple(x.shape)}")
@@ -62,6 +64,15 @@ def per_token_group_quant_fp8(x: torch.Tensor, out_fp8: torch.Tensor, out_scale:
         raise ValueError("x and out_fp8 must be contiguous along K")
     m, k = x.shape
     s_row, s_grp = _scale_strides(out_scale, m, (k + GROUP - 1) // GROUP)
+    if packed_sf is not None:
+        if not use_ue8m0:
+            raise ValueError("packed scales need UE8M0 scales")
+        _check_packed(packed_sf, m, k, dev)
+        with _on(dev):
+            _lib.check(_lib.load().kbn_quant_1x128_sf(x.data_ptr(), m, k, x.stride(0) if m > 1 else k, out_fp8.data_ptr(),
+                                                      out_fp8.stride(0) if m > 1 else k, out_scale.data_ptr(), s_row, s_grp,
+                                                      eps, packed_sf.data_ptr(), _stream(x)))
+        return
     with _on(dev):
         _lib.check(_lib.load().kbn_quant_1x128(x.data_ptr(), m, k, x.stride(0) if m > 1 else k, out_fp8.data_ptr(),
                                                out_fp8.stride(0) if m > 1 else k, out_scale.data_ptr(), s_row, s_grp,
@@ -481,6 +492,30 @@ def m_grouped_gemm1_silu_quant_masked_ue8m0(a_q, sfa_packed, w13_q, sfb_packed, 
         _lib.check(_lib.load().kbn_fp8_grouped_gemm_masked_ue8m0_silu(
             a_q.data_ptr(), sfa_packed.data_ptr(), w13_q.data_ptr(), sfb_packed.data_ptr(), out_fp8.data_ptr(),
             out_scale.data_ptr(), sf_ptr, masked_m.data_ptr(), e, max_m, i, k, _stream(out_fp8)))
+
+
+_LINEAR_SF: dict = {}
+
+
+def fp8_linear(x: torch.Tensor, a_q: torch.Tensor, a_s: torch.Tensor, b_q: torch.Tensor, b_s: torch.Tensor, out: torch.Tensor) -> None:
+    """The FP8 linear layer in two launches: 1x128 quantisation of x into a_q / a_s, then the GEMM against b_q / b_s
+    into out.  With power-of-two weight scales and more than 8 rows the quantiser writes the packed scales the
+    block-scaled GEMM reads itself (no packing launch); 8 rows or fewer take the weight-streaming kernel."""
+    m, k = x.shape
+    n = b_q.shape[0]
+    packed_w = packed_weight_scales(b_s, n, k) if m > 8 else None
+    if packed_w is None or k % 8 or x.stride(0) % 8 or a_q.stride(0) % 8 or x.data_ptr() % 16:
+        per_token_group_quant_fp8(x, a_q, a_s)
+        fp8_gemm_nt_auto(a_q, a_s, b_q, b_s, out)
+        return
+    need = packed_sf_rows_bytes(m, k)
+    key = (str(x.device), torch.cuda.current_stream(x.device).cuda_stream)
+    buf = _LINEAR_SF.get(key)
+    if buf is None or buf.numel() < need:
+        buf = torch.empty(max(need, 1 << 20), dtype=torch.uint8, device=x.device)     # one per device and stream, grown on demand
+        _LINEAR_SF[key] = buf
+    per_token_group_quant_fp8(x, a_q, a_s, packed_sf=buf)
+    fp8_gemm_nt_ue8m0(a_q, buf, b_q, packed_w, out)
 
 
 def fp8_gemm_nt_auto(a_q: torch.Tensor, a_s: torch.Tensor, b_q: torch.Tensor, b_s: torch.Tensor, out: torch.Tensor) -> None:

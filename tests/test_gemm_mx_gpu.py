@@ -218,3 +218,24 @@ def test_postprocess_then_fp8_linear(cuda_dev):
     w3_q, w3_s = torch.stack([w_q, w_q]).to(d), torch.stack([w_s, w_s]).to(d)
     mod.postprocess_fp8_weights_batched(w3_q, w3_s)
     assert bool((w3_q[1].view(torch.uint8) == nw.view(torch.uint8)).all()) and bool((w3_s[0] == ns).all())
+
+
+@pytest.mark.parametrize("m", [5, 200, 512])
+def test_fp8_linear_two_launches(cuda_dev, m):
+    """ops.fp8_linear (quantiser emitting packed scales + block-scaled GEMM, or the weight-streaming kernel for few
+    rows) against the oracle; the library counts two kernel launches."""
+    from kb_nano_b200 import _lib, inputs, ops
+    n, k, d = 1024, 2048, cuda_dev
+    x = inputs.activations(m, k, seed=m, device=d)
+    w_q, w_s = inputs.weight(n, k, seed=m + 1, device=d)
+    a_q = torch.empty(m, k, dtype=FP8, device=d)
+    a_s = torch.empty(k // 128, m, device=d).t()
+    out = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=d)
+    ops.fp8_linear(x, a_q, a_s, w_q, w_s, out)             # first call packs the weight scales
+    l0 = _lib.launch_count()
+    ops.fp8_linear(x, a_q, a_s, w_q, w_s, out)
+    assert _lib.launch_count() - l0 == 2
+    assert ops.gemm_status(d) == 0
+    rq, rs = to.quant_1x128(x.cpu())
+    assert torch.equal(a_q.cpu().view(torch.uint8), rq.view(torch.uint8))
+    assert_gemm_close(out.cpu(), to.gemm_nt_dequant(rq, rs, w_q.cpu(), w_s.cpu()), f"fp8_linear M={m}")

@@ -289,3 +289,31 @@ def test_silu_mul_quant_row_list(cuda_dev, m, n2):
     done[rows[rows >= 0].numpy()] = True
     assert_quant_equal(q.cpu().view(torch.uint8).numpy()[done], s.cpu().numpy()[done], qr[done], np.ascontiguousarray(sr)[done], "row list")
     assert (q.cpu().view(torch.uint8).numpy()[~done] == 0x55).all() and (s.cpu().numpy()[~done] == 7.0).all()
+
+
+@pytest.mark.parametrize("m,k", [(1, 128), (200, 7168), (129, 1040), (512, 4096)])
+def test_quant_emits_packed_scales(cuda_dev, m, k):
+    """kbn_quant_1x128_sf: same bytes and scales as the plain call, and the packed copy of the scales equals packing
+    them afterwards (rows of the last 128-row block past M are not written)."""
+    from kb_nano_b200 import inputs, ops
+    x = inputs.activations(m, k, seed=m + k, device=cuda_dev)
+    g = (k + 127) // 128
+    q0 = torch.empty(m, k, dtype=FP8, device=cuda_dev)
+    s0 = torch.empty(g, m, device=cuda_dev).t()
+    ops.per_token_group_quant_fp8(x, q0, s0)
+    q1 = torch.empty(m, k, dtype=FP8, device=cuda_dev)
+    s1 = torch.empty(g, m, device=cuda_dev).t()
+    ref = ops.pack_sf_rows(s0, k)
+    sf = ref.clone()                       # pre-filled with the reference so that the unwritten padding rows compare equal
+    sf.view(torch.int32)[:] ^= 0x01010101
+    pad_rows = (-m) % 128
+    ops.per_token_group_quant_fp8(x, q1, s1, packed_sf=sf)
+    assert torch.equal(q0.view(torch.uint8), q1.view(torch.uint8)) and torch.equal(s0, s1)
+    words, refw = sf.view(torch.int32).view(-1, g, 32, 4), ref.view(torch.int32).view(-1, g, 32, 4)
+    rows = torch.arange(128, device=cuda_dev)
+    valid = torch.ones(words.shape[0], 128, dtype=torch.bool, device=cuda_dev)
+    if pad_rows:
+        valid[-1, 128 - pad_rows:] = False
+    vmask = valid[:, rows % 32 + 32 * (rows // 32)].view(-1, 1, 4, 32).transpose(2, 3).expand_as(words)   # word (l, i) <-> row 32 i + l
+    assert torch.equal(words[vmask], refw[vmask])
+    assert bool((words[~vmask] == (refw[~vmask] ^ 0x01010101)).all())
