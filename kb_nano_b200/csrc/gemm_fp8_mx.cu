@@ -41,6 +41,17 @@ struct Cfg {
     static constexpr size_t kSmemBytes = (size_t)kStages * (kStageBytes + kSfStage) + 1024 + 256 + kEpiScratch;
 };
 constexpr int kABytes = kBlockM * kBlockK;          // 16 KB
+// Swapped form: the ring is cut into 5 slots while blocks have at most 64 live rows (32 KB of weights, an 8 KB
+// token box, 1.5 KB of scales, padded to a multiple of 1 KB) and into 4 slots when a block needs the 128-row box.
+constexpr int kSwapWBytes = 256 * kBlockK;
+constexpr int kSwapSlotsMax = 5;
+__host__ __device__ constexpr uint32_t swap_slots(int cls) { return cls ? 4u : 5u; }
+__host__ __device__ constexpr uint32_t swap_a_bytes(int cls) { return (cls ? 128u : 64u) * kBlockK; }
+__host__ __device__ constexpr uint32_t swap_slot_bytes(int cls) { return cls ? 51200u : 43008u; }
+constexpr int kSwapRing = 5 * 43008;
+constexpr size_t kSwapSmemBytes = (size_t)kSwapRing + 1024 + 256 + 1024;   // slack, barriers, activation exchange
+static_assert(kSwapWBytes + swap_a_bytes(0) + 1536 <= swap_slot_bytes(0) && kSwapWBytes + swap_a_bytes(1) + 1536 <= swap_slot_bytes(1), "slot");
+static_assert(swap_slots(0) * swap_slot_bytes(0) <= kSwapRing && swap_slots(1) * swap_slot_bytes(1) <= kSwapRing, "ring");
 constexpr int kSfaBytes = 512;
 constexpr int kEpiWarps = 8;
 constexpr int kThreads = 32 * (2 + kEpiWarps);
@@ -60,11 +71,24 @@ struct MxExtra {
 // EPI == kEpiCombine: instead of storing to C, every result row is written to the rank it came from (see
 // CombineEpilogue); 32x32 chunks are transposed through shared memory so that four lanes write 64 contiguous
 // bytes of one row, and the grid signals the peers when its last CTA is done.
-template <int BN, int EPI>
+//
+// SWAP (masked form with at most 256 rows per expert, BN = 256): the operands trade places.  The tile's 256 weight
+// rows become the M operand of two 128-row MMAs (accumulators at TMEM columns 0 and 128) and the expert's tokens the
+// N operand, N = the live rows of the block rounded up to 16; the weights' scale blocks are the A scales, the tokens'
+// block the B scales.  A block with 4 live rows then costs an eighth of the tensor work of a 128-row MMA, which is
+// what keeps a long run of decode steps under the board's power limit at full clocks.  The accumulator comes out
+// transposed: a lane is a weight row = an output column, a TMEM column is a token, so a warp's 32 lanes write 64
+// contiguous bytes (bf16) or 32 contiguous bytes (fp8) of one output row.  Without the staging transposes of the
+// plain epilogues the shared memory goes to the ring instead: a slot is 32 KB of weights, the token box and the
+// scales, and the ring holds five of them while blocks have at most 64 live rows (8 KB box) and four when a block
+// needs the 128-row box; when the next tile's class differs the producer lets the ring run empty and cuts it anew.
+// The epilogue loops over 32-token chunks without unrolling (the common block has one chunk; the code stays small).
+template <int BN, int EPI, bool SWAP>
 __global__ void __launch_bounds__(kThreads, 1)
 fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmA64,
                    const __grid_constant__ CUtensorMap tmA32, const __grid_constant__ CUtensorMap tmB, const GemmParams p,
                    const MxExtra x, const CombineEpilogue cb) {
+    static_assert(!SWAP || BN == 256, "the swapped form uses 256 weight rows per tile");
     constexpr bool ACT = EPI == kEpiAct;
     constexpr int kBN = Cfg<BN>::kBN, kStages = Cfg<BN>::kStages, kStageBytes = Cfg<BN>::kStageBytes;
     constexpr int kSfbBytes = Cfg<BN>::kSfbBytes, kSfStage = Cfg<BN>::kSfStage, kTxBytes = Cfg<BN>::kTxBytes;
@@ -72,26 +96,27 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~(uintptr_t)1023u);
     uint8_t* sf_smem = smem + (size_t)kStages * kStageBytes;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sf_smem + (size_t)kStages * kSfStage);
-    // bars: full[kStages], empty[kStages], tmem_full, tmem_empty, pair[4] (the two epilogue warps of a lane quarter)
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 6);
+    constexpr int kBars = SWAP ? kSwapSlotsMax : kStages;     // ring barriers of each kind
+    uint64_t* bars = reinterpret_cast<uint64_t*>(SWAP ? smem + kSwapRing : sf_smem + (size_t)kStages * kSfStage);
+    // bars: full[kBars], empty[kBars], tmem_full, tmem_empty, pair[4] (the two epilogue warps of a lane quarter)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kBars + 6);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     float* xch = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + 256);     // [parity][half][128 rows]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t bar_full = ptx::smem_u32(bars), bar_empty = ptx::smem_u32(bars + kStages);
-    const uint32_t bar_tfull = ptx::smem_u32(bars + 2 * kStages), bar_tempty = ptx::smem_u32(bars + 2 * kStages + 1);
-    const uint32_t bar_pair = ptx::smem_u32(bars + 2 * kStages + 2);
+    const uint32_t bar_full = ptx::smem_u32(bars), bar_empty = ptx::smem_u32(bars + kBars);
+    const uint32_t bar_tfull = ptx::smem_u32(bars + 2 * kBars), bar_tempty = ptx::smem_u32(bars + 2 * kBars + 1);
+    const uint32_t bar_pair = ptx::smem_u32(bars + 2 * kBars + 2);
     const uint32_t smem_tiles = ptx::smem_u32(smem), smem_sf = ptx::smem_u32(sf_smem);
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) {
+        for (int s = 0; s < kBars; ++s) {
             ptx::mbar_init(bar_full + 8 * s, 1);
             ptx::mbar_init(bar_empty + 8 * s, 1);
         }
         ptx::mbar_init(bar_tfull, 1);
         ptx::mbar_init(bar_tempty, kEpiWarps);
-        for (int q = 0; q < 4; ++q) ptx::mbar_init(bar_pair + 8 * q, 2);
+        for (int q = 0; q < 4; ++q) ptx::mbar_init(bar_pair + 8 * q, SWAP ? 4 : 2);   // SWAP: the four quarter warps of a token half
         *abort_flag = 0;
         ptx::fence_barrier_init();
         ptx::fence_proxy_async();
@@ -120,6 +145,8 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         TileWalk walk(p);
         Tile tile;
         uint32_t it = 0;
+        uint32_t slot = 0, fills = 0;     // SWAP: next ring slot; bit s = parity of the number of fills of slot s
+        int cur_cls = -1;                 // SWAP: how the ring is cut at the moment
         bool ok = true;
         for (int64_t t = blockIdx.x; ok && walk.get(t, tile); t += gridDim.x) {
             if (!tile.compute) continue;
@@ -143,14 +170,32 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                 const uint8_t* sfb = x.sfb + (((int64_t)tile.expert * KB) * x.nb_pad + (ACT ? 1 : BN / 128) * tile.n_blk) * (int64_t)kSfaBytes;
                 const CUtensorMap* tma = live <= 32 ? &tmA32 : (live <= 64 ? &tmA64 : &tmA);
                 const uint32_t tx = (uint32_t)(kTxBytes - kABytes) + (live <= 32 ? 32u : (live <= 64 ? 64u : 128u)) * (uint32_t)kBlockK;
-                for (int kb = 0; kb < KB; ++kb, ++it) {
-                    const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
-                    if (!wait_bar(bar_empty + 8 * s, ph ^ 1u, w)) { ok = false; break; }
+                const int cls = live <= 64 ? 0 : 1;
+                if (SWAP && cls != cur_cls) {
+                    // the ring is cut differently from here on: wait until every slot in use has been consumed
+                    for (int s = 0; s < kBars && ok; ++s) ok = wait_bar(bar_empty + 8 * s, ((fills >> s) & 1u) ^ 1u, w);
+                    cur_cls = cls;
+                    slot = 0;
+                }
+                for (int kb = 0; ok && kb < KB; ++kb, ++it) {
+                    uint32_t s, dst, a_dst, sdst;
+                    if (SWAP) {
+                        s = slot;
+                        slot = slot + 1 == swap_slots(cls) ? 0u : slot + 1;
+                        if (!wait_bar(bar_empty + 8 * s, ((fills >> s) & 1u) ^ 1u, w)) { ok = false; break; }
+                        fills ^= 1u << s;
+                        dst = smem_tiles + s * swap_slot_bytes(cls) - kABytes;      // the weights sit at dst + kABytes
+                        a_dst = dst + kABytes + kSwapWBytes;
+                        sdst = a_dst + swap_a_bytes(cls);
+                    } else {
+                        s = it % kStages;
+                        if (!wait_bar(bar_empty + 8 * s, ((it / kStages) & 1u) ^ 1u, w)) { ok = false; break; }
+                        dst = a_dst = smem_tiles + s * kStageBytes;
+                        sdst = smem_sf + s * kSfStage;
+                    }
                     const uint32_t bar = bar_full + 8 * s;
                     ptx::mbar_arrive_expect_tx(bar, tx);
-                    const uint32_t dst = smem_tiles + s * kStageBytes;
-                    ptx::tma_load_2d(dst, tma, kb * kBlockK, tile.row0, bar);
-                    const uint32_t sdst = smem_sf + s * kSfStage;
+                    ptx::tma_load_2d(a_dst, tma, kb * kBlockK, tile.row0, bar);
                     ptx::bulk_load(sdst, sfa + (int64_t)kb * kSfaBytes, kSfaBytes, bar);
                     if (ACT) {
                         // tmB's box is 128 rows here: gate rows fill the first half of the B tile, up rows the second
@@ -178,6 +223,8 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             TileWalk walk(p);
             Tile tile;
             uint32_t it = 0, tile_it = 0;
+            uint32_t slot = 0, drains = 0;    // SWAP: next ring slot; bit s = parity of the number of times slot s was consumed
+            int cur_cls = -1;
             constexpr uint32_t idesc = ptx::umma_idesc_mx_e4m3(kBlockM, kBN, 0, 0);
             bool ok = true;
             for (int64_t t = blockIdx.x; ok && walk.get(t, tile); t += gridDim.x) {
@@ -185,22 +232,55 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                 // the single accumulator must have been drained by the epilogue of the previous tile
                 if (!wait_bar(bar_tempty, (tile_it & 1u) ^ 1u, w)) { ok = false; break; }
                 ptx::tc_fence_after();
+                // SWAP: N of the instruction = live rows of the block, rounded up to 16
+                const uint32_t swap_idesc =
+                    ptx::umma_idesc_mx_e4m3(kBlockM, (uint32_t)max(16, (min(tile.row_end - tile.row0, kBlockM) + 15) & ~15), 0, 0);
+                const int cls = min(tile.row_end - tile.row0, kBlockM) <= 64 ? 0 : 1;
+                if (SWAP && cls != cur_cls) {     // the producer cuts the ring anew and starts at its first slot
+                    cur_cls = cls;
+                    slot = 0;
+                }
                 for (int kb = 0; kb < KB; ++kb, ++it) {
-                    const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+                    uint32_t s, ph, a_addr, sf_addr;
+                    if (SWAP) {
+                        s = slot;
+                        slot = slot + 1 == swap_slots(cls) ? 0u : slot + 1;
+                        ph = (drains >> s) & 1u;
+                        drains ^= 1u << s;
+                        // a_addr + kABytes = the weights, as in the plain layout; the tokens and the scales follow them
+                        a_addr = smem_tiles + s * swap_slot_bytes(cls) - kABytes;
+                        sf_addr = a_addr + kABytes + kSwapWBytes + swap_a_bytes(cls);
+                    } else {
+                        s = it % kStages;
+                        ph = (it / kStages) & 1u;
+                        a_addr = smem_tiles + s * kStageBytes;
+                        sf_addr = smem_sf + s * kSfStage;
+                    }
                     if (!wait_bar(bar_full + 8 * s, ph, w)) { ok = false; break; }
                     ptx::tc_fence_after();
-                    const uint32_t a_addr = smem_tiles + s * kStageBytes;
-                    const uint32_t sf_addr = smem_sf + s * kSfStage;
                     ptx::tmem_cp_32x128b_warpx4(tmem_base + kColSfa, ptx::umma_desc_sf(sf_addr));
                     ptx::tmem_cp_32x128b_warpx4(tmem_base + kColSfb, ptx::umma_desc_sf(sf_addr + kSfaBytes));
                     if (BN == 256)
                         ptx::tmem_cp_32x128b_warpx4(tmem_base + kColSfb + 4, ptx::umma_desc_sf(sf_addr + 2 * kSfaBytes));
-                    const uint64_t a_desc = ptx::umma_desc_k_sw128(a_addr);
+                    const uint64_t a_desc = ptx::umma_desc_k_sw128(SWAP ? a_addr + kABytes + kSwapWBytes : a_addr);
                     const uint64_t b_desc = ptx::umma_desc_k_sw128(a_addr + kABytes);
+                    if (SWAP) {
+                        // weights (two 128-row blocks) x tokens^T: the tokens' scale block is the B scale
+                        // the two accumulators take turns, so that consecutive instructions do not depend on each other
+                        const uint64_t w_desc = ptx::umma_desc_k_sw128(a_addr + kABytes);
+                        constexpr uint64_t kSubDesc = (128 * kBlockK) >> 4;          // second 128 weight rows, in descriptor units
 #pragma unroll
-                    for (int k = 0; k < kBlockK / 32; ++k)
-                        ptx::mma_mxf8f6f4_block_scale(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc, tmem_base + kColSfa,
-                                                      tmem_base + kColSfb, (kb > 0 || k > 0) ? 1u : 0u);
+                        for (int k = 0; k < kBlockK / 32; ++k)
+#pragma unroll
+                            for (int sub = 0; sub < 2; ++sub)
+                                ptx::mma_mxf8f6f4_block_scale(tmem_base + sub * 128, w_desc + sub * kSubDesc + 2 * k, a_desc + 2 * k, swap_idesc,
+                                                              tmem_base + kColSfb + 4 * sub, tmem_base + kColSfa, (kb > 0 || k > 0) ? 1u : 0u);
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < kBlockK / 32; ++k)
+                            ptx::mma_mxf8f6f4_block_scale(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc, tmem_base + kColSfa,
+                                                          tmem_base + kColSfb, (kb > 0 || k > 0) ? 1u : 0u);
+                    }
                     ptx::mma_commit(bar_empty + 8 * s);
                 }
                 if (!ok) break;
@@ -216,7 +296,7 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         WaitCtx w{abort_flag, p.status, 6};
         TileWalk walk(p);
         Tile tile;
-        uint32_t tile_it = 0;
+        uint32_t tile_it = 0, act_it = 0;
         bool ok = true;
         for (int64_t t = blockIdx.x; ok && walk.get(t, tile); t += gridDim.x) {
             if (!tile.compute) continue;
@@ -225,6 +305,157 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             if (p.mode == kContig && row_ok) row_ok = p.row_expert[row] >= 0;
             if (!wait_bar(bar_tfull, tile_it & 1u, w)) { ok = false; break; }
             ptx::tc_fence_after();
+            if (SWAP) {
+                // Transposed accumulators: lane = weight row (output column), TMEM column = token of the block.
+                const int32_t live = min(tile.row_end - tile.row0, kBlockM);
+                const int32_t nchunks = (live + 31) >> 5;                 // 32-token chunks that hold data
+                const uint32_t tlane = tmem_base + ((uint32_t)(quarter * 32) << 16);
+                if (!ACT) {
+                    // warps 2..5 drain the first 128 weight rows (columns 0..127), warps 6..9 the second 128; one 32-token chunk
+                    // at a time in a loop that is not unrolled (small code), the accumulator is handed back after the last read
+                    const int sub = half;
+                    const int32_t n = tile.n_blk * kBN + sub * 128 + quarter * 32 + lane;        // output column
+#pragma unroll 1
+                    for (int c = 0; c < nchunks; ++c) {
+                        uint32_t r[32];
+                        ptx::tmem_ld_32x32(tlane + sub * 128 + 32 * c, r);
+                        ptx::tmem_ld_wait(r);
+                        if (c == nchunks - 1) {
+                            ptx::tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) ptx::mbar_arrive(bar_tempty);
+                        }
+                        if (n >= p.N) continue;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const int32_t t = 32 * c + j;
+                            if (t >= live) break;
+                            const __nv_bfloat16 v = __float2bfloat16_rn(__uint_as_float(r[j]));
+                            if (EPI == kEpiCombine) {
+                                const int32_t meta = cb.meta[tile.row0 + t];               // same word for the whole warp
+                                __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(cb.peer_comb[meta >> 20]) + (int64_t)(meta & 0xfffff) * p.N;
+                                dst[n] = v;                                                  // 64 contiguous bytes per warp
+                            } else {
+                                p.C[(int64_t)(tile.row0 + t) * p.ldc + n] = v;
+                            }
+                        }
+                    }
+                } else {
+                    // ACT: gate accumulators at columns 0.., up at 128.. .  The two warps of a lane quarter split every 32-token
+                    // chunk of the block: warp `half` takes tokens 16 * half .. + 15 of chunk c, for its 32 weight rows, from both
+                    // accumulators (one warp per scheduler partition working alone runs at the latency of its own dependent
+                    // instructions, so the work is spread over all eight warps and kept short).
+                    const int32_t my_chunks = (live - 16 * half + 31) >> 5;                      // chunks with tokens for this warp
+                    if (my_chunks <= 0) {
+                        ptx::tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) ptx::mbar_arrive(bar_tempty);
+                    }
+                    uint32_t* xq = reinterpret_cast<uint32_t*>(xch);                              // [parity][half][quarter][8 words]
+                    float* inv_s = xch + 128 + (warp - 2) * 16;                                  // [warp][16 tokens]
+                    // One chunk at a time, as a loop that is not unrolled: the code of a chunk is fetched once and stays in
+                    // the instruction cache next to the producer's and the MMA issuer's loops.  The accumulator goes back to
+                    // the MMA warp when the last chunk has been read.
+#pragma unroll 1
+                    for (int c = 0; c < my_chunks; ++c) {
+                        uint32_t g[16], u[16];
+                        ptx::tmem_ld_32x16(tlane + 32 * c + 16 * half, g);
+                        ptx::tmem_ld_32x16(tlane + 128 + 32 * c + 16 * half, u);
+                        ptx::tmem_ld_wait(g);
+                        ptx::tmem_ld_wait(u);
+                        if (c == my_chunks - 1) {
+                            ptx::tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) ptx::mbar_arrive(bar_tempty);
+                        }
+                        const int32_t t0 = 32 * c + 16 * half;                                   // first token of the warp's 16
+                        // y for 16 tokens of this weight row, two tokens per word
+                        uint32_t y[8];
+#pragma unroll
+                        for (int j = 0; j < 16; j += 8) {
+                            uint4 g4, u4;
+                            g4.x = pack_bf16x2(__uint_as_float(g[j + 0]), __uint_as_float(g[j + 1]));
+                            g4.y = pack_bf16x2(__uint_as_float(g[j + 2]), __uint_as_float(g[j + 3]));
+                            g4.z = pack_bf16x2(__uint_as_float(g[j + 4]), __uint_as_float(g[j + 5]));
+                            g4.w = pack_bf16x2(__uint_as_float(g[j + 6]), __uint_as_float(g[j + 7]));
+                            u4.x = pack_bf16x2(__uint_as_float(u[j + 0]), __uint_as_float(u[j + 1]));
+                            u4.y = pack_bf16x2(__uint_as_float(u[j + 2]), __uint_as_float(u[j + 3]));
+                            u4.z = pack_bf16x2(__uint_as_float(u[j + 4]), __uint_as_float(u[j + 5]));
+                            u4.w = pack_bf16x2(__uint_as_float(u[j + 6]), __uint_as_float(u[j + 7]));
+                            uint32_t y4[4];
+                            silu_mul_8(g4, u4, p.act_table, y4);
+#pragma unroll
+                            for (int q4 = 0; q4 < 4; ++q4) y[j / 2 + q4] = y4[q4];
+                        }
+                        // Per-token absmax over the 128 weight rows of the group.  Within the warp a halving exchange: each
+                        // round a lane keeps half of its words and gets the partner's maxima for them (4 + 2 + 1 shuffles), two
+                        // plain rounds finish; lane l then holds word 4*bit4(l) + 2*bit3(l) + bit2(l), reduced over all 32 lanes.
+                        uint32_t m4[4], m2[2], m1;
+                        {
+                            const bool hi = (lane & 16) != 0;
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const uint32_t send = hi ? y[i] : y[i + 4], keep = hi ? y[i + 4] : y[i];
+                                m4[i] = absmax_bf16x2(keep, __shfl_xor_sync(0xffffffffu, send, 16));
+                            }
+                        }
+                        {
+                            const bool hi = (lane & 8) != 0;
+#pragma unroll
+                            for (int i = 0; i < 2; ++i) {
+                                const uint32_t send = hi ? m4[i] : m4[i + 2], keep = hi ? m4[i + 2] : m4[i];
+                                m2[i] = absmax_bf16x2(keep, __shfl_xor_sync(0xffffffffu, send, 8));
+                            }
+                        }
+                        {
+                            const bool hi = (lane & 4) != 0;
+                            const uint32_t send = hi ? m2[0] : m2[1], keep = hi ? m2[1] : m2[0];
+                            m1 = absmax_bf16x2(keep, __shfl_xor_sync(0xffffffffu, send, 4));
+                        }
+                        m1 = absmax_bf16x2(m1, __shfl_xor_sync(0xffffffffu, m1, 2));
+                        m1 = absmax_bf16x2(m1, __shfl_xor_sync(0xffffffffu, m1, 1));
+                        // the four quarter warps of this half meet in shared memory
+                        const uint32_t par = act_it & 1u;
+                        ++act_it;
+                        uint32_t* grp = xq + (par * 2u + (uint32_t)half) * 32u;
+                        if ((lane & 3) == 0) grp[quarter * 8 + (lane >> 2)] = abs_bf16x2(m1);
+                        __syncwarp();
+                        if (lane == 0) ptx::mbar_arrive(bar_pair + 8 * half);
+                        if (!wait_bar(bar_pair + 8 * half, par, w)) { ok = false; break; }
+                        // lane t < 16: scale of token t0 + t
+                        const int tl = lane & 15;
+                        uint32_t wmax = 0;
+#pragma unroll
+                        for (int qq = 0; qq < 4; ++qq) wmax = max_bf16x2(wmax, grp[qq * 8 + (tl >> 1)]);
+                        const float amax = fmaxf((tl & 1) ? bf16_hi(wmax) : bf16_lo(wmax), 1e-10f);
+                        const uint32_t f = ue8m0_scale_field(amax);
+                        if (lane < 16) inv_s[lane] = __uint_as_float((254u - f) << 23);
+                        const int32_t trow = tile.row0 + t0 + lane;
+                        if (quarter == 0 && lane < 16 && t0 + lane < live) {
+                            p.act_scale[(int64_t)trow * p.act_s_row + (int64_t)tile.n_blk * p.act_s_grp] = __uint_as_float(f << 23);
+                            if (p.act_packed != nullptr)
+                                p.act_packed[((size_t)(trow >> 7) * p.num_n_blocks + tile.n_blk) * 128u + (trow & 31) * 4 + ((trow & 127) >> 5)] =
+                                    f * 0x01010101u;
+                        }
+                        __syncwarp();
+                        // this lane's weight row for every token: one fp8 byte each, 32 contiguous bytes per warp and token
+                        uint8_t* qcol = p.act_q + tile.n_blk * 128 + quarter * 32 + lane;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const int32_t t = t0 + 2 * i;
+                            if (t >= live) break;
+                            const float2 is = reinterpret_cast<const float2*>(inv_s)[i];
+                            const uint32_t b2 = pack_e4m3x2(__fmul_rn(bf16_lo(y[i]), is.x), __fmul_rn(bf16_hi(y[i]), is.y));
+                            qcol[(int64_t)(tile.row0 + t) * p.act_ld] = (uint8_t)(b2 & 0xffu);
+                            if (t + 1 < live) qcol[(int64_t)(tile.row0 + t + 1) * p.act_ld] = (uint8_t)(b2 >> 8);
+                        }
+                        __syncwarp();
+                    }
+                    if (!ok) break;
+                }
+                ++tile_it;
+                continue;
+            }
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + half * kHalfCols;
             const int32_t n0 = tile.n_blk * kBN + half * kHalfCols;
             __nv_bfloat16* crow = p.C + (int64_t)row * p.ldc + n0;
@@ -275,7 +506,8 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                 m2 = abs_bf16x2(m2);
                 float amax = fmaxf(bf16_lo(m2), bf16_hi(m2));
                 // the other half of the row's 128 outputs sits in the partner warp of this lane quarter
-                const uint32_t par = tile_it & 1u;
+                const uint32_t par = act_it & 1u;
+                ++act_it;
                 xch[(par * 2u + (uint32_t)half) * 128u + (uint32_t)r_in_tile] = amax;
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(bar_pair + 8 * quarter);
@@ -650,10 +882,13 @@ static int check_device() {
         int major = 0;
         KBN_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
         KBN_REQUIRE(major == 10, KBN_ERR_UNSUPPORTED, "kbn_fp8 GEMMs need an sm_100 device (found major %d)", major);
-        KBN_CUDA(cudaFuncSetAttribute(fp8_gemm_mx_kernel<256, kEpiStore>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<256>::kSmemBytes));
-        KBN_CUDA(cudaFuncSetAttribute(fp8_gemm_mx_kernel<256, kEpiAct>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<256>::kSmemBytes));
-        KBN_CUDA(cudaFuncSetAttribute(fp8_gemm_mx_kernel<256, kEpiCombine>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<256>::kSmemBytes));
-        KBN_CUDA(cudaFuncSetAttribute(fp8_gemm_mx_kernel<128, kEpiStore>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<128>::kSmemBytes));
+        KBN_CUDA(cudaFuncSetAttribute(fp8_gemm_mx_kernel<256, kEpiStore, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<256>::kSmemBytes));
+        KBN_CUDA(cudaFuncSetAttribute(fp8_gemm_mx_kernel<256, kEpiAct, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<256>::kSmemBytes));
+        KBN_CUDA(cudaFuncSetAttribute(fp8_gemm_mx_kernel<256, kEpiCombine, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<256>::kSmemBytes));
+        KBN_CUDA(cudaFuncSetAttribute(fp8_gemm_mx_kernel<128, kEpiStore, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<128>::kSmemBytes));
+        KBN_CUDA(cudaFuncSetAttribute(fp8_gemm_mx_kernel<256, kEpiStore, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSwapSmemBytes));
+        KBN_CUDA(cudaFuncSetAttribute(fp8_gemm_mx_kernel<256, kEpiAct, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSwapSmemBytes));
+        KBN_CUDA(cudaFuncSetAttribute(fp8_gemm_mx_kernel<256, kEpiCombine, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSwapSmemBytes));
         KBN_CUDA(cudaFuncSetAttribute(fp8_gemm_mx_splitk_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<256>::kSmemBytes));
         KBN_CUDA(cudaFuncSetAttribute(fp8_gemm_mx_splitk_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<128>::kSmemBytes));
         ok[dev] = 1;
@@ -770,14 +1005,22 @@ static int launch(const void* A, int64_t a_rows, const void* B, int64_t b_rows, 
     if (split > 1)
         return bn == 256 ? launch_splitk<256>(tmA, tmA64, tmA32, tmB, p, x, split, max_tiles, st)
                          : launch_splitk<128>(tmA, tmA64, tmA32, tmB, p, x, split, max_tiles, st);
-    if (combine)
-        fp8_gemm_mx_kernel<256, kEpiCombine><<<(unsigned)grid, kThreads, Cfg<256>::kSmemBytes, st>>>(tmA, tmA64, tmA32, tmB, p, x, cb);
+    // masked layout with at most 256 rows per expert (decode batches): the operands trade places, see the kernel
+    const bool swap = p.mode == kMasked && p.max_m <= 256 && bn == 256;
+    if (swap && combine)
+        fp8_gemm_mx_kernel<256, kEpiCombine, true><<<(unsigned)grid, kThreads, kSwapSmemBytes, st>>>(tmA, tmA64, tmA32, tmB, p, x, cb);
+    else if (swap && act)
+        fp8_gemm_mx_kernel<256, kEpiAct, true><<<(unsigned)grid, kThreads, kSwapSmemBytes, st>>>(tmA, tmA64, tmA32, tmB, p, x, cb);
+    else if (swap)
+        fp8_gemm_mx_kernel<256, kEpiStore, true><<<(unsigned)grid, kThreads, kSwapSmemBytes, st>>>(tmA, tmA64, tmA32, tmB, p, x, cb);
+    else if (combine)
+        fp8_gemm_mx_kernel<256, kEpiCombine, false><<<(unsigned)grid, kThreads, Cfg<256>::kSmemBytes, st>>>(tmA, tmA64, tmA32, tmB, p, x, cb);
     else if (act)
-        fp8_gemm_mx_kernel<256, kEpiAct><<<(unsigned)grid, kThreads, Cfg<256>::kSmemBytes, st>>>(tmA, tmA64, tmA32, tmB, p, x, cb);
+        fp8_gemm_mx_kernel<256, kEpiAct, false><<<(unsigned)grid, kThreads, Cfg<256>::kSmemBytes, st>>>(tmA, tmA64, tmA32, tmB, p, x, cb);
     else if (bn == 256)
-        fp8_gemm_mx_kernel<256, kEpiStore><<<(unsigned)grid, kThreads, Cfg<256>::kSmemBytes, st>>>(tmA, tmA64, tmA32, tmB, p, x, cb);
+        fp8_gemm_mx_kernel<256, kEpiStore, false><<<(unsigned)grid, kThreads, Cfg<256>::kSmemBytes, st>>>(tmA, tmA64, tmA32, tmB, p, x, cb);
     else
-        fp8_gemm_mx_kernel<128, kEpiStore><<<(unsigned)grid, kThreads, Cfg<128>::kSmemBytes, st>>>(tmA, tmA64, tmA32, tmB, p, x, cb);
+        fp8_gemm_mx_kernel<128, kEpiStore, false><<<(unsigned)grid, kThreads, Cfg<128>::kSmemBytes, st>>>(tmA, tmA64, tmA32, tmB, p, x, cb);
     KBN_CHECK_LAUNCH();
     return KBN_OK;
 }

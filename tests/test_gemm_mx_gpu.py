@@ -91,10 +91,15 @@ def test_mx_grouped_contiguous(cuda_dev, counts):
     assert bool((out[~valid] == 7.0).all())
 
 
-@pytest.mark.parametrize("masked", [[0, 1, 128, 129, 256, 77], [256] * 4, [0] * 3, [5, 200]])
-def test_mx_grouped_masked(cuda_dev, masked):
+# 64 experts x 4 column tiles: every CTA walks several tiles whose row blocks alternate between at most 64 and more than
+# 64 live rows (the kernel cuts its shared-memory ring differently for the two), with fewer K blocks than ring slots
+MIXED = [3, 100, 70, 64, 65, 256, 0, 31, 129, 16, 200, 1, 128, 33, 90, 7] * 4
+
+
+@pytest.mark.parametrize("masked,n", [([0, 1, 128, 129, 256, 77], 384), ([256] * 4, 384), ([0] * 3, 384), ([5, 200], 384), (MIXED, 1024)])
+def test_mx_grouped_masked(cuda_dev, masked, n):
     from kb_nano_b200 import inputs, ops
-    e, max_m, n, k = len(masked), 256, 384, 512
+    e, max_m, k = len(masked), 256, 512
     b_q, b_s = inputs.expert_weights(e, n, k, seed=len(masked))
     a_q, a_s = to.quant_1x128(inputs.activations(e * max_m, k, seed=17))
     a_q, a_s = a_q.view(e, max_m, k), a_s.view(e, max_m, k // 128)
@@ -139,10 +144,10 @@ def test_gemm1_with_fused_activation_contiguous(cuda_dev, counts, i_sz, k):
     assert bool((q.view(torch.uint8).cpu()[valid] != 0x55).any()) and bool((s.cpu()[~valid] == 7.0).all())
 
 
-@pytest.mark.parametrize("masked", [[0, 1, 128, 129, 256, 77], [256] * 3, [5, 200]])
-def test_gemm1_with_fused_activation_masked(cuda_dev, masked):
+@pytest.mark.parametrize("masked,i_sz", [([0, 1, 128, 129, 256, 77], 256), ([256] * 3, 256), ([5, 200], 256), (MIXED, 512)])
+def test_gemm1_with_fused_activation_masked(cuda_dev, masked, i_sz):
     from kb_nano_b200 import inputs, ops
-    e, max_m, i_sz, k, d = len(masked), 256, 256, 512, cuda_dev
+    e, max_m, k, d = len(masked), 256, 512, cuda_dev
     b_q, b_s = inputs.expert_weights(e, 2 * i_sz, k, seed=len(masked) + 9)
     a_q, a_s = to.quant_1x128(inputs.activations(e * max_m, k, seed=23))
     a_q, mm = a_q.view(e, max_m, k).to(d), torch.tensor(masked, dtype=torch.int32, device=d)
