@@ -41,17 +41,19 @@ struct Cfg {
     static constexpr size_t kSmemBytes = (size_t)kStages * (kStageBytes + kSfStage) + 1024 + 256 + kEpiScratch;
 };
 constexpr int kABytes = kBlockM * kBlockK;          // 16 KB
-// Swapped form: the ring is cut into 5 slots while blocks have at most 64 live rows (32 KB of weights, an 8 KB
-// token box, 1.5 KB of scales, padded to a multiple of 1 KB) and into 4 slots when a block needs the 128-row box.
+// Swapped form: a ring slot is 32 KB of weights followed by the token box, and the ring is cut by the live rows of the
+// block: 6 slots with a 32-row box, 5 with a 64-row box, 4 with the 128-row box.  The scales (1.5 KB per slot) have
+// their own area behind the ring.
 constexpr int kSwapWBytes = 256 * kBlockK;
-constexpr int kSwapSlotsMax = 5;
-__host__ __device__ constexpr uint32_t swap_slots(int cls) { return cls ? 4u : 5u; }
-__host__ __device__ constexpr uint32_t swap_a_bytes(int cls) { return (cls ? 128u : 64u) * kBlockK; }
-__host__ __device__ constexpr uint32_t swap_slot_bytes(int cls) { return cls ? 51200u : 43008u; }
-constexpr int kSwapRing = 5 * 43008;
-constexpr size_t kSwapSmemBytes = (size_t)kSwapRing + 1024 + 256 + 1024;   // slack, barriers, activation exchange
-static_assert(kSwapWBytes + swap_a_bytes(0) + 1536 <= swap_slot_bytes(0) && kSwapWBytes + swap_a_bytes(1) + 1536 <= swap_slot_bytes(1), "slot");
-static_assert(swap_slots(0) * swap_slot_bytes(0) <= kSwapRing && swap_slots(1) * swap_slot_bytes(1) <= kSwapRing, "ring");
+constexpr int kSwapSlotsMax = 6;
+__host__ __device__ constexpr int swap_class(int live) { return live <= 32 ? 0 : (live <= 64 ? 1 : 2); }
+__host__ __device__ constexpr uint32_t swap_slots(int cls) { return 6u - (uint32_t)cls; }
+__host__ __device__ constexpr uint32_t swap_slot_bytes(int cls) { return (uint32_t)kSwapWBytes + (32u << cls) * kBlockK; }
+constexpr int kSwapRing = 6 * (kSwapWBytes + 32 * kBlockK);      // 221,184 B
+constexpr int kSwapSfBytes = 1536;
+// ring, scales, alignment slack, barriers, activation exchange: 232,192 B of the 232,448 a CTA can have
+constexpr size_t kSwapSmemBytes = (size_t)kSwapRing + kSwapSlotsMax * kSwapSfBytes + 1024 + 256 + 512;
+static_assert(swap_slots(1) * swap_slot_bytes(1) <= kSwapRing && swap_slots(2) * swap_slot_bytes(2) <= kSwapRing, "ring");
 constexpr int kSfaBytes = 512;
 constexpr int kEpiWarps = 8;
 constexpr int kThreads = 32 * (2 + kEpiWarps);
@@ -79,8 +81,8 @@ struct MxExtra {
 // what keeps a long run of decode steps under the board's power limit at full clocks.  The accumulator comes out
 // transposed: a lane is a weight row = an output column, a TMEM column is a token, so a warp's 32 lanes write 64
 // contiguous bytes (bf16) or 32 contiguous bytes (fp8) of one output row.  Without the staging transposes of the
-// plain epilogues the shared memory goes to the ring instead: a slot is 32 KB of weights, the token box and the
-// scales, and the ring holds five of them while blocks have at most 64 live rows (8 KB box) and four when a block
+// plain epilogues the shared memory goes to the ring instead: a slot is 32 KB of weights and the token box, and the
+// ring holds six of them while blocks have at most 32 live rows (4 KB box), five up to 64 rows and four when a block
 // needs the 128-row box; when the next tile's class differs the producer lets the ring run empty and cuts it anew.
 // The epilogue loops over 32-token chunks without unrolling (the common block has one chunk; the code stays small).
 template <int BN, int EPI, bool SWAP>
@@ -97,7 +99,7 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~(uintptr_t)1023u);
     uint8_t* sf_smem = smem + (size_t)kStages * kStageBytes;
     constexpr int kBars = SWAP ? kSwapSlotsMax : kStages;     // ring barriers of each kind
-    uint64_t* bars = reinterpret_cast<uint64_t*>(SWAP ? smem + kSwapRing : sf_smem + (size_t)kStages * kSfStage);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(SWAP ? smem + kSwapRing + kSwapSlotsMax * kSwapSfBytes : sf_smem + (size_t)kStages * kSfStage);
     // bars: full[kBars], empty[kBars], tmem_full, tmem_empty, pair[4] (the two epilogue warps of a lane quarter)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kBars + 6);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -170,7 +172,7 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                 const uint8_t* sfb = x.sfb + (((int64_t)tile.expert * KB) * x.nb_pad + (ACT ? 1 : BN / 128) * tile.n_blk) * (int64_t)kSfaBytes;
                 const CUtensorMap* tma = live <= 32 ? &tmA32 : (live <= 64 ? &tmA64 : &tmA);
                 const uint32_t tx = (uint32_t)(kTxBytes - kABytes) + (live <= 32 ? 32u : (live <= 64 ? 64u : 128u)) * (uint32_t)kBlockK;
-                const int cls = live <= 64 ? 0 : 1;
+                const int cls = swap_class(live);
                 if (SWAP && cls != cur_cls) {
                     // the ring is cut differently from here on: wait until every slot in use has been consumed
                     for (int s = 0; s < kBars && ok; ++s) ok = wait_bar(bar_empty + 8 * s, ((fills >> s) & 1u) ^ 1u, w);
@@ -186,7 +188,7 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                         fills ^= 1u << s;
                         dst = smem_tiles + s * swap_slot_bytes(cls) - kABytes;      // the weights sit at dst + kABytes
                         a_dst = dst + kABytes + kSwapWBytes;
-                        sdst = a_dst + swap_a_bytes(cls);
+                        sdst = smem_tiles + kSwapRing + s * kSwapSfBytes;
                     } else {
                         s = it % kStages;
                         if (!wait_bar(bar_empty + 8 * s, ((it / kStages) & 1u) ^ 1u, w)) { ok = false; break; }
@@ -235,7 +237,7 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                 // SWAP: N of the instruction = live rows of the block, rounded up to 16
                 const uint32_t swap_idesc =
                     ptx::umma_idesc_mx_e4m3(kBlockM, (uint32_t)max(16, (min(tile.row_end - tile.row0, kBlockM) + 15) & ~15), 0, 0);
-                const int cls = min(tile.row_end - tile.row0, kBlockM) <= 64 ? 0 : 1;
+                const int cls = swap_class(min(tile.row_end - tile.row0, kBlockM));
                 if (SWAP && cls != cur_cls) {     // the producer cuts the ring anew and starts at its first slot
                     cur_cls = cls;
                     slot = 0;
@@ -249,7 +251,7 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                         drains ^= 1u << s;
                         // a_addr + kABytes = the weights, as in the plain layout; the tokens and the scales follow them
                         a_addr = smem_tiles + s * swap_slot_bytes(cls) - kABytes;
-                        sf_addr = a_addr + kABytes + kSwapWBytes + swap_a_bytes(cls);
+                        sf_addr = smem_tiles + kSwapRing + s * kSwapSfBytes;
                     } else {
                         s = it % kStages;
                         ph = (it / kStages) & 1u;
@@ -352,7 +354,6 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                         if (lane == 0) ptx::mbar_arrive(bar_tempty);
                     }
                     uint32_t* xq = reinterpret_cast<uint32_t*>(xch);                              // [parity][half][quarter][8 words]
-                    float* inv_s = xch + 128 + (warp - 2) * 16;                                  // [warp][16 tokens]
                     // One chunk at a time, as a loop that is not unrolled: the code of a chunk is fetched once and stays in
                     // the instruction cache next to the producer's and the MMA issuer's loops.  The accumulator goes back to
                     // the MMA warp when the last chunk has been read.
@@ -429,7 +430,7 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                         for (int qq = 0; qq < 4; ++qq) wmax = max_bf16x2(wmax, grp[qq * 8 + (tl >> 1)]);
                         const float amax = fmaxf((tl & 1) ? bf16_hi(wmax) : bf16_lo(wmax), 1e-10f);
                         const uint32_t f = ue8m0_scale_field(amax);
-                        if (lane < 16) inv_s[lane] = __uint_as_float((254u - f) << 23);
+                        const float inv = __uint_as_float((254u - f) << 23);                    // lanes t and t + 16: token t0 + t
                         const int32_t trow = tile.row0 + t0 + lane;
                         if (quarter == 0 && lane < 16 && t0 + lane < live) {
                             p.act_scale[(int64_t)trow * p.act_s_row + (int64_t)tile.n_blk * p.act_s_grp] = __uint_as_float(f << 23);
@@ -437,15 +438,14 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                                 p.act_packed[((size_t)(trow >> 7) * p.num_n_blocks + tile.n_blk) * 128u + (trow & 31) * 4 + ((trow & 127) >> 5)] =
                                     f * 0x01010101u;
                         }
-                        __syncwarp();
                         // this lane's weight row for every token: one fp8 byte each, 32 contiguous bytes per warp and token
                         uint8_t* qcol = p.act_q + tile.n_blk * 128 + quarter * 32 + lane;
 #pragma unroll
                         for (int i = 0; i < 8; ++i) {
                             const int32_t t = t0 + 2 * i;
                             if (t >= live) break;
-                            const float2 is = reinterpret_cast<const float2*>(inv_s)[i];
-                            const uint32_t b2 = pack_e4m3x2(__fmul_rn(bf16_lo(y[i]), is.x), __fmul_rn(bf16_hi(y[i]), is.y));
+                            const float i0 = __shfl_sync(0xffffffffu, inv, 2 * i), i1 = __shfl_sync(0xffffffffu, inv, 2 * i + 1);
+                            const uint32_t b2 = pack_e4m3x2(__fmul_rn(bf16_lo(y[i]), i0), __fmul_rn(bf16_hi(y[i]), i1));
                             qcol[(int64_t)(tile.row0 + t) * p.act_ld] = (uint8_t)(b2 & 0xffu);
                             if (t + 1 < live) qcol[(int64_t)(tile.row0 + t + 1) * p.act_ld] = (uint8_t)(b2 >> 8);
                         }
