@@ -142,3 +142,90 @@ class EpMoe:
             self.close()
         except Exception:
             pass
+
+
+class EpMoeHostPipeline:
+    """The layer for callers whose activations and routing live in host memory (a serving loop that samples and
+    routes on the CPU, or a test harness): every `submit` copies one step's inputs from pinned host memory to the
+    device, runs `EpMoe.forward` and copies the result back to pinned host memory.  The copies run on two streams
+    of their own over `depth` rotating device buffers, so the input copy of step i+1 and the result copy of step
+    i-1 overlap the layer of step i; only buffer reuse orders them.
+
+    Inputs travel as ONE staged host buffer per step, `blob_bytes` long: bf16 x [T, H], then fp32 topk_w [T, topk],
+    then int32 topk_ids [T, topk] (`pack` fills it), with T = the layer's max_tokens.  `begin` / `join` bracket a
+    sequence of submits on the current stream; the whole sequence can be captured in a CUDA graph."""
+
+    def __init__(self, layer: EpMoe, depth: int = 2):
+        if depth < 1:
+            raise ValueError("depth must be at least 1")
+        self.layer, self.depth = layer, depth
+        t, h, k = layer.max_tokens, layer.hidden, layer.topk
+        self.nx, self.nw = t * h * 2, t * k * 4
+        self.blob_bytes = self.nx + 2 * self.nw
+        dev = layer.device
+        self._blob = [torch.empty(self.blob_bytes, dtype=torch.uint8, device=dev) for _ in range(depth)]
+        self._out = [torch.empty(t, h, dtype=torch.bfloat16, device=dev) for _ in range(depth)]
+        self._views = [(b[:self.nx].view(torch.bfloat16).view(t, h), b[self.nx:self.nx + self.nw].view(torch.float32).view(t, k),
+                        b[self.nx + self.nw:].view(torch.int32).view(t, k)) for b in self._blob]
+        self._s_in, self._s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+        self._ev_fw = [None] * depth      # forward that last read _blob[b] and wrote _out[b]
+        self._ev_out = [None] * depth     # result copy that last read _out[b]
+        self._n = 0
+
+    def new_host_buffers(self) -> tuple[torch.Tensor, torch.Tensor]:
+        t, h = self.layer.max_tokens, self.layer.hidden
+        return torch.empty(self.blob_bytes, dtype=torch.uint8).pin_memory(), torch.empty(t, h, dtype=torch.bfloat16).pin_memory()
+
+    def pack(self, blob: torch.Tensor, x: torch.Tensor, topk_w: torch.Tensor, topk_ids: torch.Tensor) -> None:
+        t, h, k = self.layer.max_tokens, self.layer.hidden, self.layer.topk
+        blob[:self.nx].view(torch.bfloat16).view(t, h).copy_(x)
+        blob[self.nx:self.nx + self.nw].view(torch.float32).view(t, k).copy_(topk_w)
+        blob[self.nx + self.nw:].view(torch.int32).view(t, k).copy_(topk_ids)
+
+    def begin(self) -> None:
+        """The copy streams start after everything already queued on the current stream."""
+        cur = torch.cuda.current_stream(self.layer.device)
+        ev = torch.cuda.Event()
+        ev.record(cur)
+        self._s_in.wait_event(ev)
+        self._s_out.wait_event(ev)
+        self._ev_fw = [None] * self.depth
+        self._ev_out = [None] * self.depth
+        self._n = 0
+
+    def submit(self, host_blob: torch.Tensor, host_out: torch.Tensor, w13, w13_s, w2, w2_s) -> None:
+        if not (host_blob.is_pinned() and host_out.is_pinned()):
+            raise ValueError("host buffers must be pinned")
+        if host_blob.numel() != self.blob_bytes or host_blob.dtype != torch.uint8:
+            raise ValueError(f"host_blob must be uint8 [{self.blob_bytes}]")
+        b = self._n % self.depth
+        self._n += 1
+        cur = torch.cuda.current_stream(self.layer.device)
+        if self._ev_fw[b] is not None:
+            self._s_in.wait_event(self._ev_fw[b])
+        with torch.cuda.stream(self._s_in):
+            self._blob[b].copy_(host_blob, non_blocking=True)
+            ev_in = torch.cuda.Event()
+            ev_in.record(self._s_in)
+        cur.wait_event(ev_in)
+        if self._ev_out[b] is not None:
+            cur.wait_event(self._ev_out[b])
+        x, tw, ti = self._views[b]
+        self.layer.forward(x, ti, tw, w13, w13_s, w2, w2_s, out=self._out[b])
+        self._ev_fw[b] = torch.cuda.Event()
+        self._ev_fw[b].record(cur)
+        self._s_out.wait_event(self._ev_fw[b])
+        with torch.cuda.stream(self._s_out):
+            host_out.copy_(self._out[b], non_blocking=True)
+            self._ev_out[b] = torch.cuda.Event()
+            self._ev_out[b].record(self._s_out)
+
+    def join(self) -> None:
+        """The current stream waits for every copy submitted since `begin`."""
+        cur = torch.cuda.current_stream(self.layer.device)
+        for ev in self._ev_out:
+            if ev is not None:
+                cur.wait_event(ev)
+        ev = torch.cuda.Event()
+        ev.record(self._s_in)
+        cur.wait_event(ev)

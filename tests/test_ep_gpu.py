@@ -85,6 +85,46 @@ def test_ep_forward_replays_from_a_cuda_graph(cuda_dev):
     layer.close()
 
 
+def test_ep_host_pipeline_matches_forward(cuda_dev):
+    """Host-resident inputs and results: the pipeline's staged copies on side streams give the bits of forward() on
+    device tensors, step after step over its rotating buffers, eagerly and replayed from a CUDA graph."""
+    from kb_nano_b200 import ep
+    t, h, i, e, topk = 32, 512, 256, 16, 4
+    xs, routes, (w13_q, w13_s, w2_q, w2_s) = ep_case(5, t, h, i, e, topk, seed=31)
+    d = cuda_dev
+    wd = [w.to(d) for w in (w13_q, w13_s, w2_q, w2_s)]
+    layer = ep.EpMoe(0, 1, e, h, i, max_tokens=t, topk=topk, max_m=128, device=d)
+    want = [layer.forward(xs[r].to(d), routes[r][1].to(d), routes[r][0].to(d), *wd).cpu() for r in range(5)]
+    pipe = ep.EpMoeHostPipeline(layer, depth=2)
+    bufs = [pipe.new_host_buffers() for _ in range(5)]
+    for r, (blob, _) in enumerate(bufs):
+        pipe.pack(blob, xs[r], routes[r][0], routes[r][1])
+    pipe.begin()
+    for blob, hout in bufs:
+        pipe.submit(blob, hout, *wd)
+    pipe.join()
+    torch.cuda.synchronize()
+    layer.check()
+    for r, (_, hout) in enumerate(bufs):
+        assert torch.equal(hout.view(torch.int16), want[r].view(torch.int16)), f"eager step {r}"
+        hout.zero_()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        pipe.begin()
+        for blob, hout in bufs:
+            pipe.submit(blob, hout, *wd)
+        pipe.join()
+    for _ in range(2):
+        graph.replay()
+    torch.cuda.synchronize()
+    layer.check()
+    for r, (_, hout) in enumerate(bufs):
+        assert torch.equal(hout.view(torch.int16), want[r].view(torch.int16)), f"replayed step {r}"
+    with pytest.raises(ValueError):
+        pipe.submit(torch.empty(pipe.blob_bytes, dtype=torch.uint8), bufs[0][1], *wd)      # not pinned
+    layer.close()
+
+
 def test_ep_overflow_is_reported_not_fatal(cuda_dev):
     """More rows for one expert than max_m: the status word says so and the context stays usable."""
     from kb_nano_b200 import ep
