@@ -83,7 +83,8 @@ struct MxExtra {
 // contiguous bytes (bf16) or 32 contiguous bytes (fp8) of one output row.  Without the staging transposes of the
 // plain epilogues the shared memory goes to the ring instead: a slot is 32 KB of weights and the token box, and the
 // ring holds six of them while blocks have at most 32 live rows (4 KB box), five up to 64 rows and four when a block
-// needs the 128-row box; when the next tile's class differs the producer lets the ring run empty and cuts it anew.
+// needs the 128-row box; when a tile needs a larger box than any before it in this CTA the producer lets the ring
+// run empty and cuts it anew (the cut never goes back to more slots within a launch).
 // The epilogue loops over 32-token chunks without unrolling (the common block has one chunk; the code stays small).
 template <int BN, int EPI, bool SWAP>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -172,7 +173,9 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                 const uint8_t* sfb = x.sfb + (((int64_t)tile.expert * KB) * x.nb_pad + (ACT ? 1 : BN / 128) * tile.n_blk) * (int64_t)kSfaBytes;
                 const CUtensorMap* tma = live <= 32 ? &tmA32 : (live <= 64 ? &tmA64 : &tmA);
                 const uint32_t tx = (uint32_t)(kTxBytes - kABytes) + (live <= 32 ? 32u : (live <= 64 ? 64u : 128u)) * (uint32_t)kBlockK;
-                const int cls = swap_class(live);
+                // the cut only ever grows coarser within a launch: going back and forth between tiles would let the ring
+                // run empty every time
+                const int cls = max(swap_class(live), cur_cls);
                 if (SWAP && cls != cur_cls) {
                     // the ring is cut differently from here on: wait until every slot in use has been consumed
                     for (int s = 0; s < kBars && ok; ++s) ok = wait_bar(bar_empty + 8 * s, ((fills >> s) & 1u) ^ 1u, w);
@@ -237,7 +240,7 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                 // SWAP: N of the instruction = live rows of the block, rounded up to 16
                 const uint32_t swap_idesc =
                     ptx::umma_idesc_mx_e4m3(kBlockM, (uint32_t)max(16, (min(tile.row_end - tile.row0, kBlockM) + 15) & ~15), 0, 0);
-                const int cls = swap_class(min(tile.row_end - tile.row0, kBlockM));
+                const int cls = max(swap_class(min(tile.row_end - tile.row0, kBlockM)), cur_cls);
                 if (SWAP && cls != cur_cls) {     // the producer cuts the ring anew and starts at its first slot
                     cur_cls = cls;
                     slot = 0;
@@ -321,23 +324,27 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                     for (int c = 0; c < nchunks; ++c) {
                         uint32_t r[32];
                         ptx::tmem_ld_32x32(tlane + sub * 128 + 32 * c, r);
+                        // combine: where the chunk's 32 tokens go, one word per lane (read here, handed round by shuffles below:
+                        // a load per token in the store loop could not be moved above the stores before it)
+                        int32_t my_meta = 0;
+                        if (EPI == kEpiCombine && 32 * c + lane < live) my_meta = cb.meta[tile.row0 + 32 * c + lane];
                         ptx::tmem_ld_wait(r);
                         if (c == nchunks - 1) {
                             ptx::tc_fence_before();
                             __syncwarp();
                             if (lane == 0) ptx::mbar_arrive(bar_tempty);
                         }
-                        if (n >= p.N) continue;
+                        const bool n_ok = n < p.N;
 #pragma unroll
                         for (int j = 0; j < 32; ++j) {
                             const int32_t t = 32 * c + j;
                             if (t >= live) break;
                             const __nv_bfloat16 v = __float2bfloat16_rn(__uint_as_float(r[j]));
                             if (EPI == kEpiCombine) {
-                                const int32_t meta = cb.meta[tile.row0 + t];               // same word for the whole warp
+                                const int32_t meta = __shfl_sync(0xffffffffu, my_meta, j);
                                 __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(cb.peer_comb[meta >> 20]) + (int64_t)(meta & 0xfffff) * p.N;
-                                dst[n] = v;                                                  // 64 contiguous bytes per warp
-                            } else {
+                                if (n_ok) dst[n] = v;                                        // 64 contiguous bytes per warp
+                            } else if (n_ok) {
                                 p.C[(int64_t)(tile.row0 + t) * p.ldc + n] = v;
                             }
                         }
