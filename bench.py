@@ -172,16 +172,27 @@ def run_graph(world: int, step, steps: int, warmup: int, sampler: ClockSampler |
         else:
             for i in range(steps):
                 step(warmup + i)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
     graph.replay()
+    b.record()
     if world > 1:
         torch.distributed.barrier()
     torch.cuda.synchronize()
+    # about a quarter of a second of untimed replays: clocks and caches as in a running loop.  Their number is agreed
+    # between the ranks (a step of the expert-parallel layer needs every rank to take it)
+    n_pre = max(1, min(1000, int(250.0 / max(a.elapsed_time(b), 0.05))))
+    if world > 1:
+        t = torch.tensor([n_pre], dtype=torch.int64, device="cuda")
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        n_pre = int(t.item())
     if sampler is not None:
         sampler.active = True
-    t0 = time.perf_counter()
-    while time.perf_counter() - t0 < 0.25:       # a quarter of a second of untimed replays: clocks and caches as in a running loop
+    for _ in range(n_pre):
         graph.replay()
-        torch.cuda.synchronize()
+    if world > 1:
+        torch.distributed.barrier()
+    torch.cuda.synchronize()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     a.record()
     graph.replay()
@@ -557,8 +568,11 @@ def wl_ep_moe(args, rank, world, dev, sampler, name="ep_moe"):
     def step(_):
         layer.forward(x, ti, tw, w13_q, w13_s, w2_q, w2_s, out=out)
 
+    # the K steps are captured in one CUDA graph and that graph is timed with one event pair, the way kb-nano replays
+    # a decode step (infra/engine.py:2410-2427): launches counted here are the warm-up's and the capture's, replays
+    # launch the same kernels again
     l0 = _lib.launch_count()
-    ms = Timed(world, 0, dev).run(step, args.steps, args.warmup, sampler)
+    ms = run_graph(world, step, args.steps, args.warmup, sampler)
     launches = _lib.launch_count() - l0
     layer.check()
     # rows every local expert receives (routing of all ranks is reproducible from the seeds)
@@ -644,6 +658,8 @@ def wl_ep_moe(args, rank, world, dev, sampler, name="ep_moe"):
                    "parallelism": f"ep{world}", "experts_per_rank": e_l, "tokens_per_rank": t, "global_tokens": t * world,
                    "l2": f"local expert weights ({e_l * 3 * i * h / 1e9:.2f} GB) exceed the 126 MB L2",
                    "exchange": "peer stores over NVLink (dispatch fp8 rows + scales, combine bf16 rows), release/acquire flags",
+                   "timing": "K layer steps captured in one CUDA graph (the layer's step counter lives on the device), untimed replays "
+                             "for a quarter of a second, then one replay between two CUDA events; max over ranks",
                    "e2e": "EpMoeHostPipeline: per step one pinned-host -> device copy of the inputs, the layer, one device -> host copy "
                           "of the result; the copies run on their own streams over two rotating device buffers and overlap the "
                           "neighbouring steps' layer; the K steps are captured in one CUDA graph and timed with one CUDA-event pair",
