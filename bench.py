@@ -661,7 +661,7 @@ def wl_ep_moe(args, rank, world, dev, sampler, name="ep_moe"):
                    "timing": "K layer steps captured in one CUDA graph (the layer's step counter lives on the device), untimed replays "
                              "for a quarter of a second, then one replay between two CUDA events; max over ranks",
                    "e2e": "EpMoeHostPipeline: per step one pinned-host -> device copy of the inputs, the layer, one device -> host copy "
-                          "of the result; the copies run on their own streams over two rotating device buffers and overlap the "
+                          "of the result; the copies run on a stream of their own over two rotating device buffers and overlap the "
                           "neighbouring steps' layer; the K steps are captured in one CUDA graph and timed with one CUDA-event pair",
                    "layer_tflops": flop / world / (ms * 1e-3) / 1e12},
         "e2e": {"value": t * world / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": t * h * 2 + t * topk * 8, "d2h_bytes_per_step": t * h * 2},

@@ -85,7 +85,8 @@ def test_ep_forward_replays_from_a_cuda_graph(cuda_dev):
     layer.close()
 
 
-def test_ep_host_pipeline_matches_forward(cuda_dev):
+@pytest.mark.parametrize("depth,copy_streams", [(2, 2), (2, 1), (1, 1), (3, 2)])
+def test_ep_host_pipeline_matches_forward(cuda_dev, depth, copy_streams):
     """Host-resident inputs and results: the pipeline's staged copies on side streams give the bits of forward() on
     device tensors, step after step over its rotating buffers, eagerly and replayed from a CUDA graph."""
     from kb_nano_b200 import ep
@@ -95,7 +96,7 @@ def test_ep_host_pipeline_matches_forward(cuda_dev):
     wd = [w.to(d) for w in (w13_q, w13_s, w2_q, w2_s)]
     layer = ep.EpMoe(0, 1, e, h, i, max_tokens=t, topk=topk, max_m=128, device=d)
     want = [layer.forward(xs[r].to(d), routes[r][1].to(d), routes[r][0].to(d), *wd).cpu() for r in range(5)]
-    pipe = ep.EpMoeHostPipeline(layer, depth=2)
+    pipe = ep.EpMoeHostPipeline(layer, depth=depth, copy_streams=copy_streams)
     bufs = [pipe.new_host_buffers() for _ in range(5)]
     for r, (blob, _) in enumerate(bufs):
         pipe.pack(blob, xs[r], routes[r][0], routes[r][1])
