@@ -183,19 +183,20 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                     slot = 0;
                 }
                 for (int kb = 0; ok && kb < KB; ++kb, ++it) {
-                    uint32_t s, dst, a_dst, sdst;
+                    uint32_t s, w_dst, a_dst, sdst;      // ring slot; where the weight tile, the token box and the scales go
                     if (SWAP) {
                         s = slot;
                         slot = slot + 1 == swap_slots(cls) ? 0u : slot + 1;
                         if (!wait_bar(bar_empty + 8 * s, ((fills >> s) & 1u) ^ 1u, w)) { ok = false; break; }
                         fills ^= 1u << s;
-                        dst = smem_tiles + s * swap_slot_bytes(cls) - kABytes;      // the weights sit at dst + kABytes
-                        a_dst = dst + kABytes + kSwapWBytes;
+                        w_dst = smem_tiles + s * swap_slot_bytes(cls);
+                        a_dst = w_dst + kSwapWBytes;
                         sdst = smem_tiles + kSwapRing + s * kSwapSfBytes;
                     } else {
                         s = it % kStages;
                         if (!wait_bar(bar_empty + 8 * s, ((it / kStages) & 1u) ^ 1u, w)) { ok = false; break; }
-                        dst = a_dst = smem_tiles + s * kStageBytes;
+                        a_dst = smem_tiles + s * kStageBytes;
+                        w_dst = a_dst + kABytes;
                         sdst = smem_sf + s * kSfStage;
                     }
                     const uint32_t bar = bar_full + 8 * s;
@@ -204,13 +205,13 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                     ptx::bulk_load(sdst, sfa + (int64_t)kb * kSfaBytes, kSfaBytes, bar);
                     if (ACT) {
                         // tmB's box is 128 rows here: gate rows fill the first half of the B tile, up rows the second
-                        ptx::tma_load_2d(dst + kABytes, &tmB, kb * kBlockK, b_row, bar);
-                        ptx::tma_load_2d(dst + kABytes + 128 * kBlockK, &tmB, kb * kBlockK, b_row + p.N, bar);
+                        ptx::tma_load_2d(w_dst, &tmB, kb * kBlockK, b_row, bar);
+                        ptx::tma_load_2d(w_dst + 128 * kBlockK, &tmB, kb * kBlockK, b_row + p.N, bar);
                         const uint8_t* sg = sfb + (int64_t)kb * x.nb_pad * kSfaBytes;
                         ptx::bulk_load(sdst + kSfaBytes, sg, kSfaBytes, bar);
                         ptx::bulk_load(sdst + 2 * kSfaBytes, sg + (int64_t)(p.N / 128) * kSfaBytes, kSfaBytes, bar);
                     } else {
-                        ptx::tma_load_2d(dst + kABytes, &tmB, kb * kBlockK, b_row, bar);
+                        ptx::tma_load_2d(w_dst, &tmB, kb * kBlockK, b_row, bar);
                         ptx::bulk_load(sdst + kSfaBytes, sfb + (int64_t)kb * x.nb_pad * kSfaBytes, kSfbBytes, bar);
                     }
                 }
@@ -246,19 +247,20 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                     slot = 0;
                 }
                 for (int kb = 0; kb < KB; ++kb, ++it) {
-                    uint32_t s, ph, a_addr, sf_addr;
+                    uint32_t s, ph, a_addr, w_addr, sf_addr;   // ring slot, its phase; token box, weight tile, scales
                     if (SWAP) {
                         s = slot;
                         slot = slot + 1 == swap_slots(cls) ? 0u : slot + 1;
                         ph = (drains >> s) & 1u;
                         drains ^= 1u << s;
-                        // a_addr + kABytes = the weights, as in the plain layout; the tokens and the scales follow them
-                        a_addr = smem_tiles + s * swap_slot_bytes(cls) - kABytes;
+                        w_addr = smem_tiles + s * swap_slot_bytes(cls);
+                        a_addr = w_addr + kSwapWBytes;
                         sf_addr = smem_tiles + kSwapRing + s * kSwapSfBytes;
                     } else {
                         s = it % kStages;
                         ph = (it / kStages) & 1u;
                         a_addr = smem_tiles + s * kStageBytes;
+                        w_addr = a_addr + kABytes;
                         sf_addr = smem_sf + s * kSfStage;
                     }
                     if (!wait_bar(bar_full + 8 * s, ph, w)) { ok = false; break; }
@@ -267,12 +269,13 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                     ptx::tmem_cp_32x128b_warpx4(tmem_base + kColSfb, ptx::umma_desc_sf(sf_addr + kSfaBytes));
                     if (BN == 256)
                         ptx::tmem_cp_32x128b_warpx4(tmem_base + kColSfb + 4, ptx::umma_desc_sf(sf_addr + 2 * kSfaBytes));
-                    const uint64_t a_desc = ptx::umma_desc_k_sw128(SWAP ? a_addr + kABytes + kSwapWBytes : a_addr);
-                    const uint64_t b_desc = ptx::umma_desc_k_sw128(a_addr + kABytes);
+                    const uint64_t a_desc = ptx::umma_desc_k_sw128(a_addr);
+                    const uint64_t b_desc = ptx::umma_desc_k_sw128(w_addr);
                     if (SWAP) {
-                        // weights (two 128-row blocks) x tokens^T: the tokens' scale block is the B scale
-                        // the two accumulators take turns, so that consecutive instructions do not depend on each other
-                        const uint64_t w_desc = ptx::umma_desc_k_sw128(a_addr + kABytes);
+                        // weights (two 128-row blocks, one accumulator each) x tokens^T: the weights' scale blocks are the A
+                        // scales, the tokens' block the B scale; the two accumulators take turns (measured: no faster than one
+                        // after the other, kept because consecutive instructions then never depend on each other)
+                        const uint64_t w_desc = b_desc;
                         constexpr uint64_t kSubDesc = (128 * kBlockK) >> 4;          // second 128 weight rows, in descriptor units
 #pragma unroll
                         for (int k = 0; k < kBlockK / 32; ++k)
