@@ -86,6 +86,25 @@ struct MxExtra {
 // needs the 128-row box; when a tile needs a larger box than any before it in this CTA the producer lets the ring
 // run empty and cuts it anew (the cut never goes back to more slots within a launch).
 // The epilogue loops over 32-token chunks without unrolling (the common block has one chunk; the code stays small).
+// Blocks of at most 64 live rows alternate between two accumulators (AccWalk below).
+// Swapped form: which part of TMEM a tile accumulates in.  While a CTA has only seen blocks of at most 64 live rows a
+// tile needs 2 x 64 columns and the tiles alternate between columns [0, 128) and [128, 256), so the MMAs of a tile
+// start while the epilogue still reads the tile before it; from the first block with more rows on, every tile uses
+// all 256 columns (2 x 128) and waits for its predecessor's epilogue.  The MMA issuer and the epilogue warps walk the
+// same tiles and keep the same state; bit b of `phases` is the parity of the number of tiles that used accumulator b.
+struct AccWalk {
+    bool wide = false;
+    uint32_t narrow_tiles = 0, phases = 0;
+    __device__ __forceinline__ void next(int32_t live, uint32_t& buf, uint32_t& col, uint32_t& sub_stride) {
+        if (live > 64) wide = true;
+        buf = wide ? 0u : (narrow_tiles++ & 1u);
+        col = wide ? 0u : buf * 128u;
+        sub_stride = wide ? 128u : 64u;
+    }
+    __device__ __forceinline__ uint32_t parity(uint32_t buf) const { return (phases >> buf) & 1u; }
+    __device__ __forceinline__ void used(uint32_t buf) { phases ^= 1u << buf; }
+};
+
 template <int BN, int EPI, bool SWAP>
 __global__ void __launch_bounds__(kThreads, 1)
 fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmA64,
@@ -101,8 +120,9 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     uint8_t* sf_smem = smem + (size_t)kStages * kStageBytes;
     constexpr int kBars = SWAP ? kSwapSlotsMax : kStages;     // ring barriers of each kind
     uint64_t* bars = reinterpret_cast<uint64_t*>(SWAP ? smem + kSwapRing + kSwapSlotsMax * kSwapSfBytes : sf_smem + (size_t)kStages * kSfStage);
-    // bars: full[kBars], empty[kBars], tmem_full, tmem_empty, pair[4] (the two epilogue warps of a lane quarter)
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kBars + 6);
+    // bars: full[kBars], empty[kBars], tmem_full, tmem_empty, pair[4] (the two epilogue warps of a lane quarter),
+    // tmem_full and tmem_empty of the second accumulator (swapped form)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kBars + 8);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     float* xch = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + 256);     // [parity][half][128 rows]
 
@@ -110,6 +130,7 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     const uint32_t bar_full = ptx::smem_u32(bars), bar_empty = ptx::smem_u32(bars + kBars);
     const uint32_t bar_tfull = ptx::smem_u32(bars + 2 * kBars), bar_tempty = ptx::smem_u32(bars + 2 * kBars + 1);
     const uint32_t bar_pair = ptx::smem_u32(bars + 2 * kBars + 2);
+    const uint32_t bar_tfull1 = ptx::smem_u32(bars + 2 * kBars + 6), bar_tempty1 = ptx::smem_u32(bars + 2 * kBars + 7);
     const uint32_t smem_tiles = ptx::smem_u32(smem), smem_sf = ptx::smem_u32(sf_smem);
 
     if (threadIdx.x == 0) {
@@ -119,6 +140,8 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         }
         ptx::mbar_init(bar_tfull, 1);
         ptx::mbar_init(bar_tempty, kEpiWarps);
+        ptx::mbar_init(bar_tfull1, 1);
+        ptx::mbar_init(bar_tempty1, kEpiWarps);
         for (int q = 0; q < 4; ++q) ptx::mbar_init(bar_pair + 8 * q, SWAP ? 4 : 2);   // SWAP: the four quarter warps of a token half
         *abort_flag = 0;
         ptx::fence_barrier_init();
@@ -231,12 +254,20 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             uint32_t it = 0, tile_it = 0;
             uint32_t slot = 0, drains = 0;    // SWAP: next ring slot; bit s = parity of the number of times slot s was consumed
             int cur_cls = -1;
+            AccWalk acc;                      // SWAP: which accumulator the tile uses
             constexpr uint32_t idesc = ptx::umma_idesc_mx_e4m3(kBlockM, kBN, 0, 0);
             bool ok = true;
             for (int64_t t = blockIdx.x; ok && walk.get(t, tile); t += gridDim.x) {
                 if (!tile.compute) continue;
-                // the single accumulator must have been drained by the epilogue of the previous tile
-                if (!wait_bar(bar_tempty, (tile_it & 1u) ^ 1u, w)) { ok = false; break; }
+                // the tile's accumulator must have been drained by the epilogue of the tile that used it last
+                const int32_t live_rows = min(tile.row_end - tile.row0, kBlockM);
+                uint32_t acc_col = 0, acc_sub = 128, acc_buf = 0;
+                if (SWAP) {
+                    const bool was_wide = acc.wide;
+                    acc.next(live_rows, acc_buf, acc_col, acc_sub);
+                    if (acc.wide && !was_wide && !wait_bar(bar_tempty1, acc.parity(1) ^ 1u, w)) { ok = false; break; }   // both halves of TMEM from here on
+                    if (!wait_bar(acc_buf ? bar_tempty1 : bar_tempty, acc.parity(acc_buf) ^ 1u, w)) { ok = false; break; }
+                } else if (!wait_bar(bar_tempty, (tile_it & 1u) ^ 1u, w)) { ok = false; break; }
                 ptx::tc_fence_after();
                 // SWAP: N of the instruction = live rows of the block, rounded up to 16
                 const uint32_t swap_idesc =
@@ -281,7 +312,7 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                         for (int k = 0; k < kBlockK / 32; ++k)
 #pragma unroll
                             for (int sub = 0; sub < 2; ++sub)
-                                ptx::mma_mxf8f6f4_block_scale(tmem_base + sub * 128, w_desc + sub * kSubDesc + 2 * k, a_desc + 2 * k, swap_idesc,
+                                ptx::mma_mxf8f6f4_block_scale(tmem_base + acc_col + sub * acc_sub, w_desc + sub * kSubDesc + 2 * k, a_desc + 2 * k, swap_idesc,
                                                               tmem_base + kColSfb + 4 * sub, tmem_base + kColSfa, (kb > 0 || k > 0) ? 1u : 0u);
                     } else {
 #pragma unroll
@@ -292,7 +323,8 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                     ptx::mma_commit(bar_empty + 8 * s);
                 }
                 if (!ok) break;
-                ptx::mma_commit(bar_tfull);
+                ptx::mma_commit(acc_buf ? bar_tfull1 : bar_tfull);
+                if (SWAP) acc.used(acc_buf);
                 ++tile_it;
             }
         }
@@ -305,19 +337,26 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         TileWalk walk(p);
         Tile tile;
         uint32_t tile_it = 0, act_it = 0;
+        AccWalk acc;                                  // SWAP: which accumulator the tile uses (same walk as the MMA issuer's)
         bool ok = true;
         for (int64_t t = blockIdx.x; ok && walk.get(t, tile); t += gridDim.x) {
             if (!tile.compute) continue;
             const int32_t row = tile.row0 + r_in_tile;
             bool row_ok = row < tile.row_end;
             if (p.mode == kContig && row_ok) row_ok = p.row_expert[row] >= 0;
-            if (!wait_bar(bar_tfull, tile_it & 1u, w)) { ok = false; break; }
+            uint32_t acc_col = 0, acc_sub = 128, acc_buf = 0;
+            if (SWAP) {
+                acc.next(min(tile.row_end - tile.row0, kBlockM), acc_buf, acc_col, acc_sub);
+                if (!wait_bar(acc_buf ? bar_tfull1 : bar_tfull, acc.parity(acc_buf), w)) { ok = false; break; }
+                acc.used(acc_buf);
+            } else if (!wait_bar(bar_tfull, tile_it & 1u, w)) { ok = false; break; }
             ptx::tc_fence_after();
             if (SWAP) {
                 // Transposed accumulators: lane = weight row (output column), TMEM column = token of the block.
                 const int32_t live = min(tile.row_end - tile.row0, kBlockM);
                 const int32_t nchunks = (live + 31) >> 5;                 // 32-token chunks that hold data
-                const uint32_t tlane = tmem_base + ((uint32_t)(quarter * 32) << 16);
+                const uint32_t tlane = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc_col;
+                const uint32_t bar_acc_empty = acc_buf ? bar_tempty1 : bar_tempty;
                 if (!ACT) {
                     // warps 2..5 drain the first 128 weight rows (columns 0..127), warps 6..9 the second 128; one 32-token chunk
                     // at a time in a loop that is not unrolled (small code), the accumulator is handed back after the last read
@@ -326,7 +365,7 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 #pragma unroll 1
                     for (int c = 0; c < nchunks; ++c) {
                         uint32_t r[32];
-                        ptx::tmem_ld_32x32(tlane + sub * 128 + 32 * c, r);
+                        ptx::tmem_ld_32x32(tlane + sub * acc_sub + 32 * c, r);
                         // combine: where the chunk's 32 tokens go, one word per lane (read here, handed round by shuffles below:
                         // a load per token in the store loop could not be moved above the stores before it)
                         int32_t my_meta = 0;
@@ -335,7 +374,7 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                         if (c == nchunks - 1) {
                             ptx::tc_fence_before();
                             __syncwarp();
-                            if (lane == 0) ptx::mbar_arrive(bar_tempty);
+                            if (lane == 0) ptx::mbar_arrive(bar_acc_empty);
                         }
                         const bool n_ok = n < p.N;
 #pragma unroll
@@ -361,7 +400,7 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                     if (my_chunks <= 0) {
                         ptx::tc_fence_before();
                         __syncwarp();
-                        if (lane == 0) ptx::mbar_arrive(bar_tempty);
+                        if (lane == 0) ptx::mbar_arrive(bar_acc_empty);
                     }
                     uint32_t* xq = reinterpret_cast<uint32_t*>(xch);                              // [parity][half][quarter][8 words]
                     // One chunk at a time, as a loop that is not unrolled: the code of a chunk is fetched once and stays in
@@ -371,13 +410,13 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                     for (int c = 0; c < my_chunks; ++c) {
                         uint32_t g[16], u[16];
                         ptx::tmem_ld_32x16(tlane + 32 * c + 16 * half, g);
-                        ptx::tmem_ld_32x16(tlane + 128 + 32 * c + 16 * half, u);
+                        ptx::tmem_ld_32x16(tlane + acc_sub + 32 * c + 16 * half, u);
                         ptx::tmem_ld_wait(g);
                         ptx::tmem_ld_wait(u);
                         if (c == my_chunks - 1) {
                             ptx::tc_fence_before();
                             __syncwarp();
-                            if (lane == 0) ptx::mbar_arrive(bar_tempty);
+                            if (lane == 0) ptx::mbar_arrive(bar_acc_empty);
                         }
                         const int32_t t0 = 32 * c + 16 * half;                                   // first token of the warp's 16
                         // y for 16 tokens of this weight row, two tokens per word
