@@ -38,7 +38,11 @@ int silu_mul_quant_masked(const void* in, int64_t E, int64_t max_m, int64_t N2, 
 
 namespace mx {
 int gemm_masked_ue8m0_combine(const void* A, const void* sfa_packed, const void* B, const void* sfb_packed, const int32_t* masked_m,
-                              int64_t E, int64_t max_m, int64_t N, int64_t K, const CombineEpilogue& cb, cudaStream_t st);   // gemm_fp8_mx.cu
+                              int64_t E, int64_t max_m, int64_t N, int64_t K, const CombineEpilogue& cb, int64_t expected_m,
+                              cudaStream_t st);   // gemm_fp8_mx.cu
+int gemm1_masked_ue8m0_silu(const void* A, const void* sfa_packed, const void* W13, const void* sfb_packed, void* q, float* scale,
+                            void* sf_packed, const int32_t* masked_m, int64_t E, int64_t max_m, int64_t I, int64_t K, int64_t expected_m,
+                            cudaStream_t st);     // gemm_fp8_mx.cu
 }
 
 constexpr int kMaxRanks = kMaxPeerRanks;
@@ -222,8 +226,6 @@ __global__ void ep_iota_kernel(int32_t* p, int n) {
 
 extern "C" int kbn_moe_unpermute_combine(const void*, int64_t, const int32_t*, const float*, int64_t, int64_t, int64_t, void*, kbn_stream_t);
 extern "C" int kbn_quant_1x128(const void*, int64_t, int64_t, int64_t, void*, int64_t, float*, int64_t, int64_t, float, int, kbn_stream_t);
-extern "C" int kbn_fp8_grouped_gemm_masked_ue8m0_silu(const void*, const void*, const void*, const void*, void*, float*, void*, const int32_t*,
-                                                      int64_t, int64_t, int64_t, int64_t, kbn_stream_t);
 
 extern "C" int kbn_ep_create(int rank, int world, int64_t experts_total, int64_t max_m, int64_t hidden, int64_t inter,
                              int64_t max_tokens, int64_t topk, kbn_ep_ctx** out) {
@@ -335,12 +337,14 @@ extern "C" int kbn_ep_moe_forward(kbn_ep_ctx* c, const void* x_bf16, const int32
     // 3. wait for every source's rows
     ep_wait_kernel<<<1, kMaxRanks, 0, st>>>(reinterpret_cast<const int32_t*>(mine + c->lay.flags_dispatch), c->world, epoch, 1, c->status, 0);
     KBN_CHECK_LAUNCH();
-    // 4. local experts on the received rows
+    // 4. local experts on the received rows.  Rows per expert to expect if every rank brings as many tokens as this one and
+    //    the routing is even: it decides the operand order of the masked GEMMs (few rows: weights as the M operand)
+    const int64_t expected_m = std::max<int64_t>(1, (T * c->world * c->topk + c->experts_total - 1) / c->experts_total);
     const float* recv_s = reinterpret_cast<const float*>(mine + c->lay.recv_s);
     if (ue8m0) {
         // GEMM1 with SiLU(gate)*up and the 1x128 quantisation in its epilogue
-        rc = kbn_fp8_grouped_gemm_masked_ue8m0_silu(mine + c->lay.recv_q, mine + c->lay.recv_sf, w13, w13_sf_packed, c->a2_q, c->a2_s, c->sf2,
-                                                    counters, c->e_local, c->max_m, I, H, stream);
+        rc = mx::gemm1_masked_ue8m0_silu(mine + c->lay.recv_q, mine + c->lay.recv_sf, w13, w13_sf_packed, c->a2_q, c->a2_s, c->sf2, counters,
+                                         c->e_local, c->max_m, I, H, expected_m, st);
         if (rc != KBN_OK) return rc;
     } else {
         if (!c->mm1) {
@@ -374,7 +378,7 @@ extern "C" int kbn_ep_moe_forward(kbn_ep_ctx* c, const void* x_bf16, const int32
         cb.n_counters = (int32_t)c->e_local;
         cb.world = c->world;
         cb.epoch = epoch;              // the device word
-        rc = mx::gemm_masked_ue8m0_combine(c->a2_q, c->sf2, w2, w2_sf_packed, counters, c->e_local, c->max_m, H, I, cb, st);
+        rc = mx::gemm_masked_ue8m0_combine(c->a2_q, c->sf2, w2, w2_sf_packed, counters, c->e_local, c->max_m, H, I, cb, expected_m, st);
         if (rc != KBN_OK) return rc;
     } else {
         rc = kbn_fp8_grouped_gemm_masked(c->a2_q, c->a2_s, c->max_m * (I / 128), I / 128, 1, w2, w2_s, c->mm2, counters, c->e_local, c->max_m, H, I, stream);

@@ -20,6 +20,7 @@ struct GemmParams {
     int64_t ldc;
     const int32_t* row_expert;
     const int32_t* masked_m;
+    int32_t expected_m;        // masked layout, host side only: rows per expert the caller expects (0: unknown)
     int32_t* status;
     int32_t rows_total;   // rows of the 2-D view of A / C
     int32_t N, K, E, max_m;

@@ -17,6 +17,8 @@
 // tcgen05.cp.32x128b.warpx4 spreads a 512-byte block over TMEM lanes and columns.
 #include <cuda.h>
 
+#include <algorithm>
+
 #include "gemm_common.cuh"
 #include "silu_exact.cuh"
 
@@ -46,6 +48,7 @@ constexpr int kABytes = kBlockM * kBlockK;          // 16 KB
 // their own area behind the ring.
 constexpr int kSwapWBytes = 256 * kBlockK;
 constexpr int kSwapSlotsMax = 6;
+constexpr int kSwapMaxExpectedRows = 56;
 __host__ __device__ constexpr int swap_class(int live) { return live <= 32 ? 0 : (live <= 64 ? 1 : 2); }
 __host__ __device__ constexpr uint32_t swap_slots(int cls) { return 6u - (uint32_t)cls; }
 __host__ __device__ constexpr uint32_t swap_slot_bytes(int cls) { return (uint32_t)kSwapWBytes + (32u << cls) * kBlockK; }
@@ -1054,8 +1057,10 @@ static int launch(const void* A, int64_t a_rows, const void* B, int64_t b_rows, 
     if (split > 1)
         return bn == 256 ? launch_splitk<256>(tmA, tmA64, tmA32, tmB, p, x, split, max_tiles, st)
                          : launch_splitk<128>(tmA, tmA64, tmA32, tmB, p, x, split, max_tiles, st);
-    // masked layout with at most 256 rows per expert (decode batches): the operands trade places, see the kernel
-    const bool swap = p.mode == kMasked && p.max_m <= 256 && bn == 256;
+    // masked layout with at most 256 rows per expert (decode batches): the operands trade places, see the kernel.
+    // A caller that knows its load says so: above about 56 expected rows per expert many blocks have more than 64 live
+    // rows, and those are faster in the plain order.
+    const bool swap = p.mode == kMasked && p.max_m <= 256 && bn == 256 && (p.expected_m <= 0 || p.expected_m <= kSwapMaxExpectedRows);
     if (swap && combine)
         fp8_gemm_mx_kernel<256, kEpiCombine, true><<<(unsigned)grid, kThreads, kSwapSmemBytes, st>>>(tmA, tmA64, tmA32, tmB, p, x, cb);
     else if (swap && act)
@@ -1179,7 +1184,7 @@ namespace mx {
 
 // Not part of the C ABI: called by the expert-parallel layer, which owns the peer mappings.
 int gemm_masked_ue8m0_combine(const void* A, const void* sfa_packed, const void* B, const void* sfb_packed, const int32_t* masked_m,
-                              int64_t E, int64_t max_m, int64_t N, int64_t K, const CombineEpilogue& cb, cudaStream_t st) {
+                              int64_t E, int64_t max_m, int64_t N, int64_t K, const CombineEpilogue& cb, int64_t expected_m, cudaStream_t st) {
     const char* who = "fp8 gemm (ue8m0, combine epilogue)";
     KBN_REQUIRE(E > 0 && max_m > 0 && N > 0 && K > 0 && A && B && masked_m, KBN_ERR_ARG, "%s: bad arguments", who);
     KBN_REQUIRE(max_m % 128 == 0 && N % 32 == 0, KBN_ERR_ARG, "%s: max_m must be a multiple of 128 and N of 32", who);
@@ -1188,6 +1193,7 @@ int gemm_masked_ue8m0_combine(const void* A, const void* sfa_packed, const void*
     GemmParams p{};
     fill_params(p, nullptr, N, E * max_m, N, K, E, max_m, kMasked);
     p.masked_m = masked_m;
+    p.expected_m = (int32_t)std::min<int64_t>(std::max<int64_t>(expected_m, 0), 1 << 30);
     // the grid is never empty here: the last CTA must signal the peers even when no expert has rows
     return launch(A, E * max_m, B, E * N, p, sfa_packed, sfb_packed, E * (max_m / 128), st, false, &cb);
 }
@@ -1237,21 +1243,32 @@ extern "C" int kbn_fp8_grouped_gemm_contig_ue8m0_silu(const void* A, const void*
     return mx::launch(A, M_sum, W13, E * 2 * I, p, sfa_packed, sfb_packed, p.num_m_blocks, st, true);
 }
 
-extern "C" int kbn_fp8_grouped_gemm_masked_ue8m0_silu(const void* A, const void* sfa_packed, const void* W13, const void* sfb_packed,
-                                                      void* q, float* scale, void* sf_packed, const int32_t* masked_m, int64_t E,
-                                                      int64_t max_m, int64_t I, int64_t K, kbn_stream_t stream) {
-    using namespace kbn;
+namespace kbn {
+namespace mx {
+// The masked GEMM1 + activation with the caller's expected rows per expert (0: unknown), which picks the operand order.
+int gemm1_masked_ue8m0_silu(const void* A, const void* sfa_packed, const void* W13, const void* sfb_packed, void* q, float* scale,
+                            void* sf_packed, const int32_t* masked_m, int64_t E, int64_t max_m, int64_t I, int64_t K, int64_t expected_m,
+                            cudaStream_t st) {
     const char* who = "kbn_fp8_grouped_gemm_masked_ue8m0_silu";
     KBN_REQUIRE(E >= 0 && max_m >= 0 && I >= 0 && K >= 0, KBN_ERR_ARG, "%s: negative size", who);
     if (E == 0 || max_m == 0 || I == 0) return KBN_OK;
     KBN_REQUIRE(A && W13 && masked_m, KBN_ERR_ARG, "%s: null pointer", who);
     KBN_REQUIRE(max_m % 128 == 0, KBN_ERR_ARG, "%s: max_m=%lld must be a multiple of 128", who, (long long)max_m);
     KBN_REQUIRE(E * 2 * I < (1ll << 31) && E * max_m < (1ll << 31), KBN_ERR_ARG, "%s: too large", who);
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
     GemmParams p{};
-    mx::fill_params(p, nullptr, 0, E * max_m, I, K, E, max_m, kMasked);
+    fill_params(p, nullptr, 0, E * max_m, I, K, E, max_m, kMasked);
     p.masked_m = masked_m;
-    int rc = mx::fill_act(p, who, q, I, scale, I / 128, 1, sf_packed, I, st);
+    p.expected_m = (int32_t)std::min<int64_t>(std::max<int64_t>(expected_m, 0), 1 << 30);
+    int rc = fill_act(p, who, q, I, scale, I / 128, 1, sf_packed, I, st);
     if (rc != KBN_OK) return rc;
-    return mx::launch(A, E * max_m, W13, E * 2 * I, p, sfa_packed, sfb_packed, E * (max_m / 128), st, true);
+    return launch(A, E * max_m, W13, E * 2 * I, p, sfa_packed, sfb_packed, E * (max_m / 128), st, true);
+}
+}  // namespace mx
+}  // namespace kbn
+
+extern "C" int kbn_fp8_grouped_gemm_masked_ue8m0_silu(const void* A, const void* sfa_packed, const void* W13, const void* sfb_packed,
+                                                      void* q, float* scale, void* sf_packed, const int32_t* masked_m, int64_t E,
+                                                      int64_t max_m, int64_t I, int64_t K, kbn_stream_t stream) {
+    return kbn::mx::gemm1_masked_ue8m0_silu(A, sfa_packed, W13, sfb_packed, q, scale, sf_packed, masked_m, E, max_m, I, K, 0,
+                                            static_cast<cudaStream_t>(stream));
 }

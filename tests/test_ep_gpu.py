@@ -55,6 +55,29 @@ def test_ep_world1_matches_oracle(cuda_dev):
     layer.close()
 
 
+def test_ep_many_rows_per_expert_uses_the_plain_operand_order(cuda_dev):
+    """256 tokens x top-2 over 4 experts: about 128 rows per expert, more than the layer expects the swapped operand
+    order of the masked GEMMs to pay for, so it runs them in the plain order; same bits as the one-GPU pipeline."""
+    from kb_nano_b200 import ep, moe
+    t, h, i, e, topk = 256, 512, 256, 4, 2
+    xs, routes, (w13_q, w13_s, w2_q, w2_s) = ep_case(1, t, h, i, e, topk, seed=41)
+    d = cuda_dev
+    wd = [w.to(d) for w in (w13_q, w13_s, w2_q, w2_s)]
+    layer = ep.EpMoe(0, 1, e, h, i, max_tokens=t, topk=topk, max_m=256, device=d)
+    out = layer.forward(xs[0].to(d), routes[0][1].to(d), routes[0][0].to(d), *wd)
+    layer.check()
+    ref = to.moe_layer(xs[0], w13_q, w13_s, w2_q, w2_s, routes[0][0], routes[0][1])
+    assert_gemm_close(out.cpu(), ref, "EP world=1, 128 rows per expert")
+    single = moe.fused_experts_fp8(xs[0].to(d), wd[0], wd[2], routes[0][0].to(d), routes[0][1].to(d), e, wd[1], wd[3])
+    assert torch.equal(out.view(torch.int16), single.view(torch.int16))
+    # the same layer with a handful of tokens takes the swapped order: same bits again
+    out5 = layer.forward(xs[0][:5].to(d), routes[0][1][:5].to(d), routes[0][0][:5].to(d), *wd)
+    layer.check()
+    single5 = moe.fused_experts_fp8(xs[0][:5].to(d), wd[0], wd[2], routes[0][0][:5].to(d), routes[0][1][:5].to(d), e, wd[1], wd[3])
+    assert torch.equal(out5.view(torch.int16), single5.view(torch.int16))
+    layer.close()
+
+
 def test_ep_forward_replays_from_a_cuda_graph(cuda_dev):
     """kb-nano runs decode steps from CUDA graphs (infra/engine.py:2410-2427): the layer's step counter lives on the
     device, so a captured forward can be replayed with new inputs in the same buffers."""
