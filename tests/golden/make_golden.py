@@ -1,8 +1,8 @@
 """Generate the golden fixtures in this directory by running kb-nano's own Python reference.
 
-Run once in a container that has the kb-nano tree (argument or $KB_NANO_REF, default
-/root/reference); the .npz files it writes are committed and are what the tests read, so the
-tests never need the reference tree.
+Run once in a container that has the kb-nano tree (first argument, or $KB_NANO_REF); the .npz
+files it writes are committed and are what the tests read, so the tests never need the reference
+tree.
 
     python tests/golden/make_golden.py [/path/to/kb_nano]
 
@@ -31,7 +31,9 @@ import numpy as np
 import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = os.path.abspath(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("KB_NANO_REF", "/root/reference"))
+if len(sys.argv) < 2 and "KB_NANO_REF" not in os.environ:
+    sys.exit("usage: make_golden.py /path/to/kb_nano   (or set KB_NANO_REF)")
+REF = os.path.abspath(sys.argv[1] if len(sys.argv) > 1 else os.environ["KB_NANO_REF"])
 
 
 def _load(path: str, name: str):
