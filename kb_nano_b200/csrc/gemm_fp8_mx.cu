@@ -361,25 +361,16 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                 const uint32_t tlane = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc_col;
                 const uint32_t bar_acc_empty = acc_buf ? bar_tempty1 : bar_tempty;
                 if (!ACT) {
-                    // warps 2..5 drain the first 128 weight rows (columns 0..127), warps 6..9 the second 128; one 32-token chunk
-                    // at a time in a loop that is not unrolled (small code), the accumulator is handed back after the last read
+                    // warps 2..5 drain the first 128 weight rows, warps 6..9 the second 128, in 32-token chunks
                     const int sub = half;
                     const int32_t n = tile.n_blk * kBN + sub * 128 + quarter * 32 + lane;        // output column
-#pragma unroll 1
-                    for (int c = 0; c < nchunks; ++c) {
-                        uint32_t r[32];
-                        ptx::tmem_ld_32x32(tlane + sub * acc_sub + 32 * c, r);
-                        // combine: where the chunk's 32 tokens go, one word per lane (read here, handed round by shuffles below:
-                        // a load per token in the store loop could not be moved above the stores before it)
-                        int32_t my_meta = 0;
-                        if (EPI == kEpiCombine && 32 * c + lane < live) my_meta = cb.meta[tile.row0 + 32 * c + lane];
-                        ptx::tmem_ld_wait(r);
-                        if (c == nchunks - 1) {
-                            ptx::tc_fence_before();
-                            __syncwarp();
-                            if (lane == 0) ptx::mbar_arrive(bar_acc_empty);
-                        }
-                        const bool n_ok = n < p.N;
+                    const bool n_ok = n < p.N;
+                    // combine: where a chunk's 32 tokens go is read with one load per lane and handed round by shuffles (a load
+                    // per token in the store loop could not be moved above the stores before it)
+                    auto chunk_meta = [&](int c) -> int32_t {
+                        return (EPI == kEpiCombine && 32 * c + lane < live) ? cb.meta[tile.row0 + 32 * c + lane] : 0;
+                    };
+                    auto store_chunk = [&](int c, const uint32_t (&r)[32], int32_t my_meta) {
 #pragma unroll
                         for (int j = 0; j < 32; ++j) {
                             const int32_t t = 32 * c + j;
@@ -393,6 +384,42 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                                 p.C[(int64_t)(tile.row0 + t) * p.ldc + n] = v;
                             }
                         }
+                    };
+                    if (nchunks <= 2) {
+                        // the common block: one chunk at a time in a loop that is not unrolled (small code; the producer's and the
+                        // MMA issuer's loops stay in the instruction cache), the accumulator handed back after the last read
+#pragma unroll 1
+                        for (int c = 0; c < nchunks; ++c) {
+                            uint32_t r[32];
+                            ptx::tmem_ld_32x32(tlane + sub * acc_sub + 32 * c, r);
+                            const int32_t my_meta = chunk_meta(c);
+                            ptx::tmem_ld_wait(r);
+                            if (c == nchunks - 1) {
+                                ptx::tc_fence_before();
+                                __syncwarp();
+                                if (lane == 0) ptx::mbar_arrive(bar_acc_empty);
+                            }
+                            store_chunk(c, r, my_meta);
+                        }
+                    } else {
+                        // 65..128 live rows: everything into registers first, so that the accumulator goes back before the stores
+                        uint32_t r[4][32];
+                        int32_t mm[4];
+#pragma unroll
+                        for (int c = 0; c < 4; ++c)
+                            if (c < nchunks) {
+                                ptx::tmem_ld_32x32(tlane + sub * acc_sub + 32 * c, r[c]);
+                                mm[c] = chunk_meta(c);
+                            }
+#pragma unroll
+                        for (int c = 0; c < 4; ++c)
+                            if (c < nchunks) ptx::tmem_ld_wait(r[c]);
+                        ptx::tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) ptx::mbar_arrive(bar_acc_empty);
+#pragma unroll
+                        for (int c = 0; c < 4; ++c)
+                            if (c < nchunks) store_chunk(c, r[c], mm[c]);
                     }
                 } else {
                     // ACT: gate accumulators at columns 0.., up at 128.. .  The two warps of a lane quarter split every 32-token
