@@ -210,6 +210,20 @@ def run_graph(world: int, step, steps: int, warmup: int, sampler: ClockSampler |
     return total_ms / steps
 
 
+def measured_traffic(kernel: str, scale: float):
+    """dram read + write bytes per launch of `kernel` from the profiler summary kept with the repository (one line per
+    kernel: name, workload, bytes), times `scale`; None when there is no such line."""
+    path = os.path.join(ROOT, "profiles", "dram_traffic.txt")
+    try:
+        for line in open(path):
+            f = line.split()
+            if len(f) >= 3 and not line.startswith("#") and f[0] == kernel:
+                return float(f[2]) * scale
+    except OSError:
+        pass
+    return None
+
+
 def cpu_threads() -> int:
     n = os.cpu_count() or 1
     try:
@@ -288,19 +302,22 @@ def cpu_moe(t: int, h: int, i: int, e: int, topk: int, routing: str, n_experts_s
     def one():
         return to.moe_layer(x, _Pick(store13, 0), _Pick(store13, 1), _Pick(store2, 0), _Pick(store2, 1), tw, ti, experts=chosen)
 
-    one()
-    t0 = time.perf_counter()
+    one()                                   # warm-up pass
+    times = []
     for _ in range(reps):
+        t0 = time.perf_counter()
         one()
-    dt = (time.perf_counter() - t0) / reps
+        times.append(time.perf_counter() - t0)
+    dt = sorted(times)[len(times) // 2]     # median pass
     share = float(counts[chosen].sum()) / float(counts.sum())
     # dequantising an expert's weights costs the same however few rows it has: scale by experts, not pairs,
     # when rows per expert are few
     active = int((counts > 0).sum())
-    est_full = dt * max(active / len(chosen), 1.0) if t * topk / e < 64 else dt / share
+    factor = max(active / len(chosen), 1.0) if t * topk / e < 64 else 1.0 / share
+    est_full = dt * factor
     del w13_q
-    return t / est_full, dt, (f"{len(chosen)} of {active} active experts with their routed rows ({share * 100:.1f}% of pairs), "
-                              f"{reps} passes, torch CPU port; whole layer extrapolated")
+    return t / est_full, dt, (f"{len(chosen)} of {active} active experts with their routed rows ({share * 100:.1f}% of pairs), median of "
+                              f"{reps} passes after one warm-up pass ({dt * 1e3:.0f} ms), torch CPU port; whole layer = sample x {factor:.2f}")
 
 
 # ------------------------------------------------------------------------------------------------
@@ -529,8 +546,50 @@ def wl_moe_single(args, rank, world, dev, sampler, name):
         "e2e": {"value": t / (ms_e2e * 1e-3) * world, "unit": "tokens/s", "h2d_bytes_per_step": t * h * 2 + t * topk * 8, "d2h_bytes_per_step": t * h * 2},
         "gpu_launches": launches // (args.steps + args.warmup) * args.steps,
         "roofline": roof,
-        "_cpu": lambda: cpu_moe(t, h, i, e, topk, routing, n_cpu, 1),
+        "_cpu": lambda: cpu_moe(t, h, i, e, topk, routing, n_cpu, 3),
     }
+
+
+def ep_parity(out, x, tw, ti, h, i, dev, world, n_tokens=2):
+    """A few of this rank's tokens of the expert-parallel result against the CPU oracle's single-process layer: the
+    experts those tokens route to are generated again from their seeds (on this rank's GPU, whose generator gives the
+    bits the owning rank's gave) and brought to the host.  Tolerance: |d| <= 1e-2 + 1e-2 |ref| element-wise,
+    max|d| / max|ref| <= 1e-2, cosine > 0.9999.  Returns the worst figures over all ranks."""
+    from kb_nano_b200 import inputs
+    from oracle import torch_oracle as to
+    torch.set_num_threads(max(1, cpu_threads() // world))
+    t = x.shape[0]
+    sel = torch.linspace(0, t - 1, steps=min(n_tokens, t)).long().unique()
+    xs, tws, tis = x[sel].cpu(), tw[sel].cpu(), ti[sel].cpu()
+    need = sorted(set(int(v) for v in tis.flatten()))
+    w13, w2 = {}, {}
+    for ex in need:
+        q, s_ = inputs.weight(2 * i, h, seed=1 * 1000003 + ex, device=dev)
+        w13[ex] = (q.cpu(), s_.cpu())
+        q, s_ = inputs.weight(h, i, seed=2 * 1000003 + ex, device=dev)
+        w2[ex] = (q.cpu(), s_.cpu())
+
+    class _Pick:
+        def __init__(self, d, j):
+            self.d, self.j = d, j
+
+        def __getitem__(self, ex):
+            return self.d[ex][self.j]
+
+    ref = to.moe_layer(xs, _Pick(w13, 0), _Pick(w13, 1), _Pick(w2, 0), _Pick(w2, 1), tws, tis, experts=need).float().flatten()
+    got = out[sel].float().cpu().flatten()
+    d = (got - ref).abs()
+    ratio = float((d / (1e-2 + 1e-2 * ref.abs())).max())
+    rel_inf = float(d.max() / ref.abs().max().clamp_min(1e-30))
+    cos = float(torch.nn.functional.cosine_similarity(got.double(), ref.double(), dim=0))
+    finite = bool(torch.isfinite(got).all())
+    worst = torch.tensor([ratio, rel_inf, -cos, 0.0 if finite else 1.0], dtype=torch.float64, device=dev)
+    if world > 1:
+        torch.distributed.all_reduce(worst, op=torch.distributed.ReduceOp.MAX)
+    ratio, rel_inf, cos, bad = float(worst[0]), float(worst[1]), -float(worst[2]), float(worst[3])
+    ok = bad == 0.0 and ratio <= 1.0 and rel_inf <= 1e-2 and cos > 0.9999
+    return {"against": "CPU oracle, single-process layer on the same seeded inputs", "tokens_per_rank": int(sel.numel()), "ranks": world,
+            "experts_regenerated_per_rank": len(need), "ratio": ratio, "rel_inf": rel_inf, "cos": cos, "ok": ok}
 
 
 EP_SHAPES = {
@@ -582,41 +641,37 @@ def wl_ep_moe(args, rank, world, dev, sampler, name="ep_moe"):
         counts += torch.bincount(ti_r.reshape(-1).long(), minlength=e)
     local = counts[lo:hi]
     assert int(local.max()) <= max_m
-    # dominant kernel: the two masked grouped GEMM launches, timed alone on buffers of the same shape and row counts
+    # dominant kernels: the two masked grouped GEMM launches (GEMM1 with the activation epilogue, GEMM2 with the combine
+    # epilogue, the second started while the first still runs) as the layer launches them, on the rows the last step left
+    # in the receive buffers; the pair is timed with CUDA events on the launching stream
     masked = local.to(torch.int32).to(dev)
-    a1 = torch.empty(e_l, max_m, h, dtype=torch.uint8, device=dev).random_(0, 120).view(FP8)
-    s1 = ops.pack_sf_rows(torch.full((e_l * max_m, h // 128), 2.0 ** -7, device=dev), h)
-    q1 = torch.empty(e_l, max_m, i, dtype=FP8, device=dev)
-    qs1 = torch.empty(e_l, max_m, i // 128, dtype=torch.float32, device=dev)
-    a2 = torch.empty(e_l, max_m, i, dtype=torch.uint8, device=dev).random_(0, 120).view(FP8)
-    s2 = ops.pack_sf_rows(torch.full((e_l * max_m, i // 128), 2.0 ** -7, device=dev), i)
-    p13, p2 = ops.packed_weight_scales(w13_s, 2 * i, h), ops.packed_weight_scales(w2_s, h, i)
-    o2 = torch.empty(e_l, max_m, h, dtype=torch.bfloat16, device=dev)
+    expected_m = max(1, -(-t * world * topk // e))
     evs = []
-    for k_ in range(3 + max(3, min(args.steps, 10))):
-        a, b, c, d = (torch.cuda.Event(enable_timing=True) for _ in range(4))
+    for k_ in range(3 + max(5, min(args.steps, 20))):
+        a, b = (torch.cuda.Event(enable_timing=True) for _ in range(2))
         a.record()
-        ops.m_grouped_gemm1_silu_quant_masked_ue8m0(a1, s1, w13_q, p13, q1, qs1, masked, s2)   # GEMM1 + activation epilogue, as the layer runs it
+        layer.expert_phase(w13_q, w13_s, w2_q, w2_s, masked, expected_m)
         b.record()
-        c.record()
-        ops.m_grouped_fp8_gemm_nt_masked_ue8m0(a2, s2, w2_q, p2, o2, masked)
-        d.record()
         if k_ >= 3:
-            evs.append((a, b, c, d))
+            evs.append((a, b))
+    if world > 1:
+        torch.distributed.barrier()
     torch.cuda.synchronize()
-    gemm_ms = sum(a.elapsed_time(b) + c.elapsed_time(d) for a, b, c, d in evs) / len(evs) / 2.0
-    del a1, a2, q1, o2
+    gemm_ms = sum(a.elapsed_time(b) for a, b in evs) / len(evs) / 2.0         # per launch
+    if world > 1:
+        tmax = torch.tensor([gemm_ms], dtype=torch.float64, device=dev)
+        torch.distributed.all_reduce(tmax, op=torch.distributed.ReduceOp.MAX)
+        gemm_ms = float(tmax.item())
     active, rows = int((local > 0).sum()), int(local.sum())
     g1 = active * 2 * i * h + rows * h + rows * i + 4 * rows * (i // 128) + 4 * rows * (h // 128)
     g2 = active * h * i + rows * i + rows * h * 2 + 4 * rows * (i // 128)
     peaks = measured_peaks()
     ach = (g1 + g2) / 2.0 / (gemm_ms * 1e-3) / 1e9
     gemm_tflops = 2.0 * rows * 3 * i * h / 2.0 / (gemm_ms * 1e-3) / 1e12
-    assert ops.gemm_status(dev) == 0
     # e2e: pinned host activations and routing in, result back to the host, through the package's host pipeline: the
     # three inputs travel as one staged buffer (one H2D copy per step), the copies of neighbouring steps overlap the
-    # layer of the current one over two rotating device buffers
-    pipe = ep.EpMoeHostPipeline(layer, depth=2)
+    # layer of the current one over three rotating device buffers
+    pipe = ep.EpMoeHostPipeline(layer, depth=3)
     hblob, hout = pipe.new_host_buffers()
     pipe.pack(hblob, x.cpu(), tw.cpu(), ti.cpu())
 
@@ -632,23 +687,27 @@ def wl_ep_moe(args, rank, world, dev, sampler, name="ep_moe"):
     assert_close_to_device = (hout.to(dev).view(torch.int16) == out.view(torch.int16)).all()
     assert bool(assert_close_to_device), "host pipeline result differs from the device-resident run"
     layer.check()
+    assert ops.gemm_status(dev) == 0
+    # the outputs of the timed configuration against the oracle, on every rank (outside every timed region)
+    parity = ep_parity(out, x, tw, ti, h, i, dev, world) if args.parity else None
     layer.close()
+    if parity is not None and not parity["ok"]:
+        raise SystemExit(f"expert-parallel output differs from the oracle beyond the tolerance: {parity}")
     flop = 2.0 * t * topk * world * 3 * i * h
     # rows per streamed expert decide the bound: below ~560 rows per weight pass the weights' HBM traffic dominates
     tensor_bound = rows / max(active, 1) >= 560
     if tensor_bound:
         fp8_peak = 2.0 * peaks["bf16_tflops_sustained"]
-        roof = {"bound": "tensor", "kernel": "fp8_gemm_mx_kernel (masked grouped; GEMM1 with the activation epilogue and GEMM2, 2 launches per layer; rank 0)", "achieved": gemm_tflops,
+        roof = {"bound": "tensor", "kernel": "fp8_gemm_mx_kernel (masked grouped; GEMM1 with the activation epilogue and GEMM2 with the combine epilogue, 2 overlapping launches per layer; max over ranks)", "achieved": gemm_tflops,
                 "peak": fp8_peak, "unit": "TFLOP/s", "frac": gemm_tflops / fp8_peak, "traffic": None,
                 "peak_source": peaks["source"] + " (2 x sustained bf16 cuBLAS figure; no FP8 figure is measured)",
                 "algorithmic_flop_per_launch": 2.0 * rows * 3 * i * h / 2.0, "gemm_ms_per_launch": gemm_ms}
     else:
-        roof = {"bound": "hbm", "kernel": "fp8_gemm_mx_kernel (masked grouped; GEMM1 with the activation epilogue and GEMM2, 2 launches per layer; rank 0)", "achieved": ach,
+        roof = {"bound": "hbm", "kernel": "fp8_gemm_mx_kernel (masked grouped; GEMM1 with the activation epilogue and GEMM2 with the combine epilogue, 2 overlapping launches per layer; rank 0's bytes over the slowest rank's time)", "achieved": ach,
                 "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"],
-                # dram read+write bytes per launch from the ncu capture summarised in
-                # profiles/fp8_gemm_mx_masked_ep_moe.md (0.745 GB per launch with 32 local DeepSeek-V3-shaped experts;
-                # proportional to the bytes of the experts whose weights are streamed)
-                "traffic": 0.745e9 / 32.0 * active * (3.0 * i * h) / (3.0 * 2048 * 7168), "peak_source": peaks["source"],
+                # DRAM bytes per launch as a profiler capture of the 32-expert case counted them, scaled by the bytes of the
+                # experts whose weights are streamed (the traffic is proportional to them)
+                "traffic": measured_traffic("fp8_gemm_mx_masked", active * (3.0 * i * h) / (32 * 3.0 * 2048 * 7168)), "peak_source": peaks["source"],
                 "algorithmic_bytes_per_launch": (g1 + g2) / 2.0, "gemm_ms_per_launch": gemm_ms}
     return {
         "metric": "EP FP8 MoE layer throughput", "value": t * world / (ms * 1e-3), "unit": "tokens/s", "ms_per_step": ms,
@@ -661,13 +720,14 @@ def wl_ep_moe(args, rank, world, dev, sampler, name="ep_moe"):
                    "timing": "K layer steps captured in one CUDA graph (the layer's step counter lives on the device), untimed replays "
                              "for a quarter of a second, then one replay between two CUDA events; max over ranks",
                    "e2e": "EpMoeHostPipeline: per step one pinned-host -> device copy of the inputs, the layer, one device -> host copy "
-                          "of the result; the copies run on a stream of their own over two rotating device buffers and overlap the "
+                          "of the result; the copies run on a stream of their own over three rotating device buffers and overlap the "
                           "neighbouring steps' layer; the K steps are captured in one CUDA graph and timed with one CUDA-event pair",
                    "layer_tflops": flop / world / (ms * 1e-3) / 1e12},
         "e2e": {"value": t * world / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": t * h * 2 + t * topk * 8, "d2h_bytes_per_step": t * h * 2},
         "gpu_launches": launches // (args.steps + args.warmup) * args.steps,
         "roofline": roof,
-        "_cpu": lambda: cpu_moe(t, h, i, e, topk, routing, 8 if routing == "sigmoid" else 1, 1),
+        "parity": parity,
+        "_cpu": lambda: cpu_moe(t, h, i, e, topk, routing, 8 if routing == "sigmoid" else 1, 5 if routing == "sigmoid" else 3),
     }
 
 
@@ -730,7 +790,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-components", action="store_true",
-                    help="default workload at N=1 only: skip the GEMM / quantiser figures reported beside the headline number")
+                    help="default workload only: skip the other configurations' figures reported beside the headline number")
+    ap.add_argument("--no-parity", dest="parity", action="store_false",
+                    help="expert-parallel workloads: skip the comparison of the timed configuration's output with the CPU oracle")
     ap.add_argument("--experts", type=int, default=256,
                     help="ep_moe and moe_c3: total experts (256 = the benchmark configuration; 32 on one GPU reproduces the "
                          "per-rank load of the 8-GPU run with 1.4 GB of weights, small enough for a profiler capture; moe_c3 "
@@ -758,17 +820,28 @@ def main():
             "ms_per_step": res["ms_per_step"], "higher_is_better": True, "scaling": res["scaling"], "vs_baseline": None, "dtype": res["dtype"],
             "data": "synthetic", "config": res["config"], "e2e": res["e2e"], "gpu_launches": res["gpu_launches"], "roofline": res["roofline"],
             "clocks": clocks}
-    if world == 1 and args.workload == DEFAULT_WORKLOAD and args.experts == 256 and not args.no_components:
-        # the other parts of the composite metric (GEMM TFLOP/s and quantiser GB/s against their peaks), each measured
-        # by its own workload function exactly as `--workload <name>` would, reported beside the headline number
+    if "parity" in res:
+        line["parity"] = res["parity"]
+    if args.workload == DEFAULT_WORKLOAD and args.experts == 256 and not args.no_components:
+        # The other parts of the composite metric, each measured by its own workload function exactly as
+        # `--workload <name>` would and under a clock-sampling window of its own, reported beside the headline number:
+        # at N=1 the GEMM TFLOP/s, the quantiser GB/s and the one-GPU MoE layers of configs[2] and configs[4]; at N>1 the
+        # expert-parallel layer at a fixed global batch and the expert-parallel configs[4] (both strong scaling).
         comp = {}
         sub = argparse.Namespace(**vars(args))
         sub.steps, sub.warmup = 20, 3
-        for name in ("gemm_c1", "silu_c2", "quant_c3", "quant_c1"):
+        names = ("gemm_c1", "silu_c2", "quant_c3", "quant_c1", "moe_c3", "moe_c5") if world == 1 else ("ep_moe_1024", "ep_c5")
+        for name in names:
             torch.cuda.empty_cache()
-            r = WORKLOADS[name](sub, rank, world, dev, None)
-            comp[name] = {"value": r["value"], "unit": r["unit"], "us_per_step": r["ms_per_step"] * 1e3, "bound": r["roofline"]["bound"],
-                          "peak": r["roofline"]["peak"], "frac": r["roofline"]["frac"], "e2e": r["e2e"]["value"]}
+            cs = ClockSampler(local)
+            cs.start()
+            r = WORKLOADS[name](sub, rank, world, dev, cs)
+            entry = {"value": r["value"], "unit": r["unit"], "us_per_step": r["ms_per_step"] * 1e3, "bound": r["roofline"]["bound"],
+                     "achieved": r["roofline"]["achieved"], "peak": r["roofline"]["peak"], "frac": r["roofline"]["frac"],
+                     "e2e": r["e2e"]["value"], "scaling": r["scaling"], "clocks": cs.stop()}
+            if r.get("parity") is not None:
+                entry["parity_ok"] = r["parity"]["ok"]
+            comp[name] = entry
         line["components"] = comp
     if rank == 0 and world == 1 and cpu_fn is not None and not args.no_cpu_baseline:
         torch.set_num_threads(cpu_threads())

@@ -213,6 +213,8 @@ int kbn_requant_weights_ue8m0(void* w_fp8, float* scale, int64_t E, int64_t N, i
 /* Device status word of the GEMM kernels' bounded waits: 0 = no wait ever ran out in this
  * process.  Host pointer out; synchronises `stream` first. */
 int kbn_gemm_status(int32_t* host_out, kbn_stream_t stream);
+/* Sets the word back to 0 (stream-ordered), so that one expired wait does not mark every later check. */
+int kbn_gemm_clear_status(kbn_stream_t stream);
 
 /*
  * Token permutation around the two grouped GEMMs of the FP8 MoE expert pipeline.  Together they
@@ -240,16 +242,16 @@ int kbn_moe_permute(const void* a_q, const float* a_s, const int32_t* topk_ids, 
                     int64_t topk, int64_t K, int64_t E, void* a_perm, float* a_s_perm,
                     int32_t* row_expert, int32_t* dest_row, int64_t M_cap, void* workspace,
                     int64_t workspace_bytes, kbn_stream_t stream);
+int kbn_moe_permute_sf(const void* a_q, const float* a_s, const int32_t* topk_ids, int64_t T,
+                       int64_t topk, int64_t K, int64_t E, void* a_perm, float* a_s_perm,
+                       int32_t* row_expert, int32_t* dest_row, int64_t M_cap, void* workspace,
+                       int64_t workspace_bytes, void* a_sf_packed, kbn_stream_t stream);
 /* kbn_moe_permute for callers that cannot allocate device memory (a plug-in that only receives its
  * input and output tensors, a host that has frozen its memory map): identical outputs, the scratch is
  * a ~264 KB device array built into the library.  No counterpart in kb-nano.  Limits: T*topk <= 65536
  * and E <= 1024 (KBN_ERR_UNSUPPORTED beyond).  Allocates nothing; the first call on a device resolves
  * the array's address and should come before any stream capture; calls that overlap on one GPU race
  * on the shared scratch. */
-int kbn_moe_permute_sf(const void* a_q, const float* a_s, const int32_t* topk_ids, int64_t T,
-                       int64_t topk, int64_t K, int64_t E, void* a_perm, float* a_s_perm,
-                       int32_t* row_expert, int32_t* dest_row, int64_t M_cap, void* workspace,
-                       int64_t workspace_bytes, void* a_sf_packed, kbn_stream_t stream);
 int kbn_moe_permute_static(const void* a_q, const float* a_s, const int32_t* topk_ids, int64_t T,
                            int64_t topk, int64_t K, int64_t E, void* a_perm, float* a_s_perm,
                            int32_t* row_expert, int32_t* dest_row, int64_t M_cap, kbn_stream_t stream);
@@ -298,7 +300,14 @@ int kbn_moe_route_topk(const void* logits, int logits_bf16, int64_t ld, int64_t 
  *   the same number of times (also with T == 0).  An expert can take at most max_m rows per call.
  * kbn_ep_status: 4 int32 {code, phase, peer, detail}; code 0 = ok, 10 = an expert overflowed max_m
  *   rows (detail = expert), 11 = expert id out of range, 20 = a wait on peer `peer` ran out in
- *   phase 1 (dispatch) or 2 (combine).  Synchronises `stream`.
+ *   phase 1 (dispatch) or 2 (combine).  Synchronises `stream`.  The first code of a context sticks
+ *   until kbn_ep_clear_status (stream-ordered) sets the four words back to 0.
+ * kbn_ep_expert_phase: measurement aid.  Runs the two expert GEMMs of the UE8M0 path once more, exactly as a
+ *   layer call launches them (GEMM1 with the activation epilogue, GEMM2 with the combine epilogue started
+ *   while GEMM1 still runs), on the rows the last kbn_ep_moe_forward left in the receive buffers, with
+ *   rows_per_expert int32 [E/R] (device) as the row counts; it exchanges no flags and leaves the step
+ *   counter alone, so a caller can bracket it with events.  Every rank may call it at the same time; the
+ *   result rows it re-sends are the ones the last step already delivered.
  */
 typedef struct kbn_ep_ctx kbn_ep_ctx;
 int kbn_ep_create(int rank, int world, int64_t experts_total, int64_t max_m, int64_t hidden,
@@ -311,6 +320,10 @@ int kbn_ep_moe_forward(kbn_ep_ctx* ctx, const void* x_bf16, const int32_t* topk_
                        const void* w2, const float* w2_s, const void* w13_sf_packed,
                        const void* w2_sf_packed, void* out_bf16, kbn_stream_t stream);
 int kbn_ep_status(kbn_ep_ctx* ctx, int32_t* host_out4, kbn_stream_t stream);
+int kbn_ep_clear_status(kbn_ep_ctx* ctx, kbn_stream_t stream);
+int kbn_ep_expert_phase(kbn_ep_ctx* ctx, const void* w13, const void* w13_sf_packed, const void* w2,
+                        const void* w2_sf_packed, const int32_t* rows_per_expert, int64_t expected_m,
+                        kbn_stream_t stream);
 int kbn_ep_destroy(kbn_ep_ctx* ctx);
 
 #ifdef __cplusplus

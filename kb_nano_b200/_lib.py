@@ -31,6 +31,7 @@ SIGNATURES = {
     "kbn_fp8_grouped_gemm_contig": (_i32, [_ptr, _ptr, _i64, _i64, _ptr, _ptr, _ptr, _i64, _ptr, _i64, _i64, _i64, _i64, _ptr]),
     "kbn_fp8_grouped_gemm_masked": (_i32, [_ptr, _ptr, _i64, _i64, _i64, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _ptr]),
     "kbn_gemm_status": (_i32, [_ptr, _ptr]),
+    "kbn_gemm_clear_status": (_i32, [_ptr]),
     "kbn_requant_weights_ue8m0": (_i32, [_ptr, _ptr, _i64, _i64, _i64, _f32, _ptr]),
     "kbn_packed_sf_rows_bytes": (_i64, [_i64, _i64]),
     "kbn_packed_sf_weights_bytes": (_i64, [_i64, _i64, _i64]),
@@ -52,6 +53,8 @@ SIGNATURES = {
     "kbn_ep_symmetric_bytes": (_i64, [_ptr]),
     "kbn_ep_moe_forward": (_i32, [_ptr, _ptr, _ptr, _ptr, _i64, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr]),
     "kbn_ep_status": (_i32, [_ptr, _ptr, _ptr]),
+    "kbn_ep_clear_status": (_i32, [_ptr, _ptr]),
+    "kbn_ep_expert_phase": (_i32, [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _ptr]),
     "kbn_ep_destroy": (_i32, [_ptr]),
     "kbn_moe_route_topk": (_i32, [_ptr, _i32, _i64, _i64, _i64, _i32, _ptr, _i64, _i64, _i64, _i32, _f32, _f32, _i32, _ptr, _ptr, _ptr]),
     "kbn_moe_permute_static": (_i32, [_ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _ptr, _ptr, _ptr, _ptr, _i64, _ptr]),

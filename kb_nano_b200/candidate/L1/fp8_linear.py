@@ -34,10 +34,17 @@ def unpack_ue8m0_packed_scales(sf: torch.Tensor, N: int, K: int) -> torch.Tensor
     """fp32 [ceil(N/128), ceil(K/128)] block scales from the packed layout DeepGEMM's sm_100
     ``transform_sf_into_required_layout`` emits for weights: int32 [N, ceil(K/128/4)], one row per
     output channel, each int32 holding the UE8M0 exponent bytes of four consecutive K-blocks
-    (lowest byte first).  Assumed layout; kb-nano itself only passes the tensor through
-    (tasks/baseline/L1/fp8_linear.py:502-512)."""
+    (lowest byte first).  Assumed layout (DeepGEMM is not part of the kb-nano tree; kb-nano itself only passes
+    the tensor through, tasks/baseline/L1/fp8_linear.py:502-512): any other shape is refused rather than
+    guessed at, and the 128 rows of a block must agree."""
     nb, kb = math.ceil(N / _GROUP), math.ceil(K / _GROUP)
+    if sf.dtype != torch.int32 or sf.dim() != 2 or tuple(sf.shape) != (N, math.ceil(kb / 4)):
+        raise ValueError(f"packed UE8M0 weight scales must be int32 [{N}, {math.ceil(kb / 4)}] for a [{N}, {K}] weight, "
+                         f"got {sf.dtype} {tuple(sf.shape)}")
     rows = sf[::_GROUP][:nb].contiguous()
+    last = sf[torch.arange(nb, device=sf.device).mul(_GROUP).add(_GROUP - 1).clamp_max(N - 1)]
+    if not torch.equal(rows, last):
+        raise ValueError("packed UE8M0 weight scales: rows of one 128-row block differ; not a 128x128 block-scale layout")
     exps = rows.view(torch.uint8).view(nb, -1)[:, :kb].to(torch.int32)
     return torch.pow(2.0, (exps - 127).float())
 
@@ -46,11 +53,14 @@ def postprocess_fp8_weights(weight_fp8: torch.Tensor, scale_inv: torch.Tensor) -
     """Load-time step of the same name in the baseline (tasks/baseline/L1/fp8_linear.py:453-512): re-quantise
     a checkpoint's block-scaled FP8 weight to power-of-two scales.  Returns (new weight, fp32 scales
     [ceil(N/128), ceil(K/128)]) -- the layout this file's Fp8Linear reads; no DeepGEMM layout transform is
-    needed (the packed form the tensor core reads is built once per weight inside the GEMM call path)."""
+    needed.  The packed form the tensor core reads is built here as well (and kept with the scales), so that no
+    later call, eager or captured, has to check the scales again."""
     N, K = weight_fp8.shape
     w = weight_fp8.clone() if weight_fp8.is_contiguous() else weight_fp8.contiguous()
     s = scale_inv[: math.ceil(N / _GROUP), : math.ceil(K / _GROUP)].to(torch.float32).contiguous().clone()
     ops.requant_weights_ue8m0(w, s)
+    if N % _GROUP == 0 and K % _GROUP == 0:
+        ops.packed_weight_scales(s, N, K)
     return w, s
 
 
@@ -61,6 +71,7 @@ def postprocess_fp8_weights_batched(weight_fp8: torch.Tensor, scale_inv: torch.T
     s = scale_inv[:, : math.ceil(N / _GROUP), : math.ceil(K / _GROUP)]
     if s.is_contiguous() and s.dtype == torch.float32 and weight_fp8.is_contiguous():
         ops.requant_weights_ue8m0(weight_fp8, s)
+        ops.packed_weight_scales(s, N, K)      # packed copy for the tensor core, made at load time
     else:
         w, s2 = weight_fp8.contiguous(), s.to(torch.float32).contiguous()
         ops.requant_weights_ue8m0(w, s2)
@@ -112,10 +123,11 @@ class Fp8Linear(nn.Module):
         if weight_scale_inv.dtype == torch.float32:
             return weight_scale_inv[: math.ceil(N / _GROUP), : math.ceil(K / _GROUP)]
         if weight_scale_inv.dtype == torch.int32:
-            key = (weight_scale_inv.data_ptr(), N, K)
+            # keyed by address, shape and version; the entry keeps the int32 tensor alive so the address cannot be reused
+            key = (weight_scale_inv.data_ptr(), N, K, weight_scale_inv._version)
             if key not in self._sf_cache:
-                self._sf_cache[key] = unpack_ue8m0_packed_scales(weight_scale_inv, N, K)
-            return self._sf_cache[key]
+                self._sf_cache[key] = (unpack_ue8m0_packed_scales(weight_scale_inv, N, K), weight_scale_inv)
+            return self._sf_cache[key][0]
         raise TypeError(f"unsupported weight_scale_inv dtype {weight_scale_inv.dtype}")
 
     def forward(self, input_bf16: torch.Tensor, weight_fp8: torch.Tensor, weight_scale_inv: torch.Tensor,

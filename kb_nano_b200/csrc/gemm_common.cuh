@@ -53,6 +53,27 @@ struct CombineEpilogue {
 
 enum GemmEpilogue : int { kEpiStore = 0, kEpiAct = 1, kEpiCombine = 2 };
 
+// Hooks that tie the two masked grouped GEMMs of the expert-parallel layer to the kernels around them, so that the
+// layer needs no kernel of its own between them (all null / zero for every other caller):
+//   wait_flags   the kernel does not read the per-expert row counts before every flag [0, wait_world) holds the
+//                running step's number (*epoch + 1): the rows of every source rank have arrived.  Bounded; on expiry
+//                {20, wait_phase, peer} goes to ep_status and the kernel carries on.
+//   sched        tiles are handed out by an atomic counter instead of round-robin, so that CTAs that become resident
+//                late (the kernel is launched while its predecessor still runs) take fewer tiles.
+//   tile_done    one counter per 128-row block of the masked layout.  done_signal: every epilogue warp adds one after
+//                its stores of a tile (GEMM1 + activation).  done_target: the producer loads a tile's rows only once the
+//                block's counter has reached it (GEMM2, which reads what GEMM1 wrote while GEMM1 may still run).
+struct EpHooks {
+    const int32_t* wait_flags;
+    const int32_t* epoch;
+    int32_t* ep_status;
+    int32_t* sched;
+    int32_t* tile_done;
+    int32_t wait_world, wait_phase;
+    int32_t done_signal, done_target;
+    unsigned long long* trace;   // debug builds (-DKBN_TRACE) only
+};
+
 struct Tile {
     int32_t row0;      // first row in the 2-D view of A and C
     int32_t row_end;   // rows >= row_end are not written
@@ -134,6 +155,56 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, const Wa
     }
 }
 
+
+// Bounded wait until the counter at `p` (written by other CTAs with release semantics) has reached `target`.
+__device__ __forceinline__ bool wait_count(const int32_t* p, int32_t target, const WaitCtx& w) {
+    if (ptx::ld_acquire_gpu(p) >= target) return true;
+    const long long t0 = clock64();
+    for (uint32_t it = 1;; ++it) {
+        if (ptx::ld_acquire_gpu(p) >= target) return true;
+        if ((it & 63u) == 0u) {
+            if (*w.abort_flag) return false;
+            if (clock64() - t0 > kWaitLimitCycles) {
+                *w.abort_flag = 1;
+                atomicCAS(w.status, 0, w.code | (int)(blockIdx.x << 8));
+                return false;
+            }
+        }
+        __nanosleep(32);
+    }
+}
+
+// Thread `r` of the callers waits until flag r holds the running step's number; see EpHooks.
+__device__ __forceinline__ void wait_step_flag(const EpHooks& h, int r) {
+    const int32_t want = *h.epoch + 1;
+    const long long t0 = clock64();
+    while (ptx::ld_acquire_sys(h.wait_flags + r) != want) {
+        if (clock64() - t0 > kWaitLimitCycles) {
+            if (atomicCAS(h.ep_status, 0, 20) == 0) {
+                h.ep_status[1] = h.wait_phase;
+                h.ep_status[2] = r;
+            }
+            break;
+        }
+        __nanosleep(64);
+    }
+}
+
+#ifdef KBN_TRACE
+// Debug build only: per kernel (4) and CTA (256) four time stamps of the global timer, in a buffer the
+// expert-parallel context owns (EpHooks::trace).
+__device__ __forceinline__ unsigned long long trace_now() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define KBN_TRACE_MARK(buf, k, slot) do { if ((buf) != nullptr && threadIdx.x == 0 && blockIdx.x < 256 && blockIdx.y == 0) (buf)[((k) * 256 + blockIdx.x) * 4 + (slot)] = trace_now(); } while (0)
+// the same with the step's parity as a fifth index: two consecutive steps are kept
+#define KBN_TRACE_MARK2(buf, epoch_ptr, k, slot) do { if ((buf) != nullptr && threadIdx.x == 0 && blockIdx.x < 256 && blockIdx.y == 0) (buf)[4096 * (*(epoch_ptr) & 1) + ((k) * 256 + blockIdx.x) * 4 + (slot)] = trace_now(); } while (0)
+#else
+#define KBN_TRACE_MARK2(buf, epoch_ptr, k, slot) do { } while (0)
+#define KBN_TRACE_MARK(buf, k, slot) do { } while (0)
+#endif
 
 // Device status word shared by all GEMM launches of the process (lives in runtime.cu).
 int gemm_status_ptr(int32_t** out);

@@ -60,6 +60,9 @@ static_assert(swap_slots(1) * swap_slot_bytes(1) <= kSwapRing && swap_slots(2) *
 constexpr int kSfaBytes = 512;
 constexpr int kEpiWarps = 8;
 constexpr int kThreads = 32 * (2 + kEpiWarps);
+// The persistent kernel has one more warp, the tile scheduler of the dynamic schedule (it leaves at once otherwise).
+constexpr int kThreadsMain = kThreads + 32;
+constexpr int kSchedDepth = 2;                      // tile numbers the scheduler warp may be ahead of their consumers
 constexpr int kTmemCols = 512;
 constexpr int kColSfa = 256, kColSfb = 260;         // TMEM columns of the scale factors
 
@@ -109,11 +112,13 @@ struct AccWalk {
 };
 
 template <int BN, int EPI, bool SWAP>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreadsMain, 1)
 fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmA64,
                    const __grid_constant__ CUtensorMap tmA32, const __grid_constant__ CUtensorMap tmB, const GemmParams p,
-                   const MxExtra x, const CombineEpilogue cb) {
+                   const MxExtra x, const CombineEpilogue cb, const EpHooks h) {
     static_assert(!SWAP || BN == 256, "the swapped form uses 256 weight rows per tile");
+    ptx::launch_dependents();
+    KBN_TRACE_MARK2(h.trace, h.epoch, EPI == kEpiCombine ? 2 : 1, 0);
     constexpr bool ACT = EPI == kEpiAct;
     constexpr int kBN = Cfg<BN>::kBN, kStages = Cfg<BN>::kStages, kStageBytes = Cfg<BN>::kStageBytes;
     constexpr int kSfbBytes = Cfg<BN>::kSfbBytes, kSfStage = Cfg<BN>::kSfStage, kTxBytes = Cfg<BN>::kTxBytes;
@@ -124,9 +129,15 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     constexpr int kBars = SWAP ? kSwapSlotsMax : kStages;     // ring barriers of each kind
     uint64_t* bars = reinterpret_cast<uint64_t*>(SWAP ? smem + kSwapRing + kSwapSlotsMax * kSwapSfBytes : sf_smem + (size_t)kStages * kSfStage);
     // bars: full[kBars], empty[kBars], tmem_full, tmem_empty, pair[4] (the two epilogue warps of a lane quarter),
-    // tmem_full and tmem_empty of the second accumulator (swapped form)
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kBars + 8);
+    // tmem_full and tmem_empty of the second accumulator (swapped form), tile-queue full[kSchedDepth] and empty[kSchedDepth]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kBars + 8 + 2 * kSchedDepth);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    // Tile queue (dynamic schedule only): the scheduler warp takes tile numbers from the global counter -- and, where a
+    // tile's rows come from a kernel that may still be running, waits for them -- and hands the numbers to the producer,
+    // the MMA issuer and the epilogue warps through these slots, so that neither the atomic's round trip nor that wait
+    // is ever on the path of the thread that keeps the loads in flight.
+    volatile int32_t* sched_ids = reinterpret_cast<volatile int32_t*>(tmem_slot + 2);
+    static_assert((2 * kBars + 8 + 2 * kSchedDepth) * 8 + 8 + 4 * kSchedDepth <= 256, "barrier block");
     float* xch = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + 256);     // [parity][half][128 rows]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -134,6 +145,8 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     const uint32_t bar_tfull = ptx::smem_u32(bars + 2 * kBars), bar_tempty = ptx::smem_u32(bars + 2 * kBars + 1);
     const uint32_t bar_pair = ptx::smem_u32(bars + 2 * kBars + 2);
     const uint32_t bar_tfull1 = ptx::smem_u32(bars + 2 * kBars + 6), bar_tempty1 = ptx::smem_u32(bars + 2 * kBars + 7);
+    const uint32_t bar_sfull = ptx::smem_u32(bars + 2 * kBars + 8), bar_sempty = ptx::smem_u32(bars + 2 * kBars + 8 + kSchedDepth);
+    const bool dyn = h.sched != nullptr;
     const uint32_t smem_tiles = ptx::smem_u32(smem), smem_sf = ptx::smem_u32(sf_smem);
 
     if (threadIdx.x == 0) {
@@ -146,6 +159,10 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         ptx::mbar_init(bar_tfull1, 1);
         ptx::mbar_init(bar_tempty1, kEpiWarps);
         for (int q = 0; q < 4; ++q) ptx::mbar_init(bar_pair + 8 * q, SWAP ? 4 : 2);   // SWAP: the four quarter warps of a token half
+        for (int q = 0; q < kSchedDepth; ++q) {
+            ptx::mbar_init(bar_sfull + 8 * q, 1);
+            ptx::mbar_init(bar_sempty + 8 * q, 2 + kEpiWarps);       // producer, MMA issuer, epilogue warps
+        }
         *abort_flag = 0;
         ptx::fence_barrier_init();
         ptx::fence_proxy_async();
@@ -154,11 +171,25 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         ptx::tmem_alloc(ptx::smem_u32(tmem_slot), kTmemCols);
         ptx::tmem_relinquish();
     }
+    // expert-parallel layer: the row counts and the rows themselves are final once every source rank's flag is up
+    if (h.wait_flags != nullptr && warp == 2 && lane < h.wait_world) wait_step_flag(h, lane);
     ptx::tc_fence_before();
     __syncthreads();
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const int KB = p.num_k_blocks;
+    KBN_TRACE_MARK2(h.trace, h.epoch, EPI == kEpiCombine ? 2 : 1, 1);
+    // n-th tile of this CTA for the producer (whole warp), the MMA issuer (one thread) and the epilogue warps (whole
+    // warp): round-robin, or the number the scheduler warp has put into the queue
+    auto next_tile = [&](uint32_t n, const WaitCtx& w, bool& ok) -> int64_t {
+        if (!dyn) return (int64_t)blockIdx.x + (int64_t)n * gridDim.x;
+        const uint32_t s = n % kSchedDepth;
+        if (!wait_bar(bar_sfull + 8 * s, (n / kSchedDepth) & 1u, w)) { ok = false; return 0; }
+        const int32_t t = sched_ids[s];
+        if (warp != 1) __syncwarp();
+        if (warp == 1 || lane == 0) ptx::mbar_arrive(bar_sempty + 8 * s);
+        return t;
+    };
 
     if (warp == 0) {
         // ---------------- producer ----------------
@@ -177,7 +208,9 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         uint32_t slot = 0, fills = 0;     // SWAP: next ring slot; bit s = parity of the number of fills of slot s
         int cur_cls = -1;                 // SWAP: how the ring is cut at the moment
         bool ok = true;
-        for (int64_t t = blockIdx.x; ok && walk.get(t, tile); t += gridDim.x) {
+        for (uint32_t n_tile = 0; ok; ++n_tile) {
+            const int64_t t = next_tile(n_tile, w, ok);
+            if (!ok || !walk.get(t, tile)) break;
             if (!tile.compute) continue;
             // Rows of the block that hold data: a block with few of them (decode batches, the last block
             // of an expert) fetches a 32- or 64-row box of A instead of 128 rows.  The rest of the stage
@@ -201,6 +234,9 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                 const uint32_t tx = (uint32_t)(kTxBytes - kABytes) + (live <= 32 ? 32u : (live <= 64 ? 64u : 128u)) * (uint32_t)kBlockK;
                 // the cut only ever grows coarser within a launch: going back and forth between tiles would let the ring
                 // run empty every time
+                // the block's rows may have been written a moment ago by the kernel before this one (the scheduler warp
+                // has seen them counted): order those generic-proxy writes before this thread's bulk loads
+                if (h.done_target > 0) ptx::fence_proxy_async_global();
                 const int cls = max(swap_class(live), cur_cls);
                 if (SWAP && cls != cur_cls) {
                     // the ring is cut differently from here on: wait until every slot in use has been consumed
@@ -260,7 +296,9 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             AccWalk acc;                      // SWAP: which accumulator the tile uses
             constexpr uint32_t idesc = ptx::umma_idesc_mx_e4m3(kBlockM, kBN, 0, 0);
             bool ok = true;
-            for (int64_t t = blockIdx.x; ok && walk.get(t, tile); t += gridDim.x) {
+            for (uint32_t n_tile = 0; ok; ++n_tile) {
+                const int64_t t = next_tile(n_tile, w, ok);
+                if (!ok || !walk.get(t, tile)) break;
                 if (!tile.compute) continue;
                 // the tile's accumulator must have been drained by the epilogue of the tile that used it last
                 const int32_t live_rows = min(tile.row_end - tile.row0, kBlockM);
@@ -331,6 +369,25 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                 ++tile_it;
             }
         }
+    } else if (warp == 2 + kEpiWarps) {
+        // ---------------- tile scheduler (dynamic schedule only) ----------------
+        if (dyn && lane == 0) {
+            WaitCtx w{abort_flag, p.status, 7};
+            TileWalk walk(p);
+            Tile tile;
+            for (uint32_t n = 0;; ++n) {
+                const uint32_t s = n % kSchedDepth;
+                if (!wait_bar(bar_sempty + 8 * s, ((n / kSchedDepth) & 1u) ^ 1u, w)) break;
+                const int32_t t = atomicAdd(h.sched, 1);
+                const bool more = walk.get(t, tile);
+                // GEMM2 of the expert-parallel layer: the tile's rows are complete once every epilogue warp of every
+                // GEMM1 tile of the block has counted itself
+                if (more && tile.compute && h.done_target > 0 && !wait_count(h.tile_done + (tile.row0 >> 7), h.done_target, w)) break;
+                sched_ids[s] = t;
+                ptx::mbar_arrive(bar_sfull + 8 * s);
+                if (!more) break;          // the consumers see the same number and stop as well
+            }
+        }
     } else {
         // ---------------- epilogue ----------------
         const int quarter = warp & 3;
@@ -342,7 +399,17 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         uint32_t tile_it = 0, act_it = 0;
         AccWalk acc;                                  // SWAP: which accumulator the tile uses (same walk as the MMA issuer's)
         bool ok = true;
-        for (int64_t t = blockIdx.x; ok && walk.get(t, tile); t += gridDim.x) {
+        // GEMM1 of the expert-parallel layer: this warp's stores of a tile are done, count it for the block's rows
+        auto tile_stored = [&](const Tile& tl) {
+            if (h.done_signal) {
+                ptx::fence_proxy_async_global();
+                __syncwarp();
+                if (lane == 0) ptx::red_release_gpu_add(h.tile_done + (tl.row0 >> 7), 1);
+            }
+        };
+        for (uint32_t n_tile = 0; ok; ++n_tile) {
+            const int64_t t = next_tile(n_tile, w, ok);
+            if (!ok || !walk.get(t, tile)) break;
             if (!tile.compute) continue;
             const int32_t row = tile.row0 + r_in_tile;
             bool row_ok = row < tile.row_end;
@@ -532,6 +599,7 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                     }
                     if (!ok) break;
                 }
+                tile_stored(tile);
                 ++tile_it;
                 continue;
             }
@@ -664,29 +732,45 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                     }
                 }
             }
+            tile_stored(tile);
             ++tile_it;
         }
     }
 
-    if (EPI == kEpiCombine) __threadfence_system();     // this thread's rows are on their way to the peers
+    // Started while the kernel before it in the stream was still running: this grid must not be seen as complete before
+    // that one is, because the kernel after both of them reuses the counters of both.
     ptx::tc_fence_before();
     __syncthreads();
+    KBN_TRACE_MARK2(h.trace, h.epoch, EPI == kEpiCombine ? 2 : 1, 2);
+    if (h.tile_done != nullptr) {
+        ptx::grid_dependency_wait();
+        __syncthreads();
+    }
     if (warp == 1) {
         ptx::tc_fence_after();
         ptx::tmem_dealloc(tmem_base, kTmemCols);
     }
     if (EPI == kEpiCombine) {
-        // last CTA of the grid: every CTA has read the row counts and sent its rows
+        // Last CTA of the grid: every CTA has read the row counts and sent its rows.  One system-wide fence per CTA,
+        // by the thread that counts the CTA: the barrier above has ordered every other thread's peer stores before it
+        // (a fence by each of the CTA's threads costs ten microseconds at the end of every launch).
         __shared__ int last;
-        if (threadIdx.x == 0) last = (atomicAdd(cb.done, 1) == (int)gridDim.x - 1);
+        if (threadIdx.x == 0) {
+            __threadfence_system();
+            last = (atomicAdd(cb.done, 1) == (int)gridDim.x - 1);
+        }
         __syncthreads();
         if (!last) return;
         for (int i = threadIdx.x; i < cb.n_counters; i += blockDim.x) cb.counters[i] = 0;
-        __threadfence_system();
         __syncthreads();
-        if ((int)threadIdx.x < cb.world)
-            asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(cb.peer_flag[threadIdx.x]), "r"(*cb.epoch + 1) : "memory");
-        if (threadIdx.x == 0) *cb.done = 0;
+        if (threadIdx.x == 0) {
+            // one fence: acquire side of the count just read, release side of the flags that follow
+            __threadfence_system();
+            const int32_t step = *cb.epoch + 1;
+            for (int r = 0; r < cb.world; ++r)
+                asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(cb.peer_flag[r]), "r"(step) : "memory");
+            *cb.done = 0;
+        }
     }
 }
 
@@ -1028,8 +1112,11 @@ static int launch_splitk(const CUtensorMap& tmA, const CUtensorMap& tmA64, const
 // m_blocks_upper: number of 128-row blocks (an upper bound in the masked form).
 // act: fused activation epilogue (p.act_* filled in, p.N = output columns, B has 2*p.N rows per expert).
 // combine: epilogue that sends the rows to their source ranks (masked form, 256-wide tiles).
+// hooks: the expert-parallel layer's ties to its neighbouring kernels (see EpHooks); with them the kernel is launched
+// with programmatic stream serialisation, i.e. it may start while the kernel before it in the stream still runs.
 static int launch(const void* A, int64_t a_rows, const void* B, int64_t b_rows, GemmParams& p, const void* sfa, const void* sfb,
-                  int64_t m_blocks_upper, cudaStream_t st, bool act = false, const CombineEpilogue* combine = nullptr) {
+                  int64_t m_blocks_upper, cudaStream_t st, bool act = false, const CombineEpilogue* combine = nullptr,
+                  const EpHooks* hooks = nullptr) {
     int rc = check_device();
     if (rc != KBN_OK) return rc;
     KBN_REQUIRE(sfa && sfb, KBN_ERR_ARG, "fp8 gemm (ue8m0): null packed scales");
@@ -1081,6 +1168,8 @@ static int launch(const void* A, int64_t a_rows, const void* B, int64_t b_rows, 
     if (grid <= 0) return KBN_OK;
     CombineEpilogue cb{};
     if (combine) cb = *combine;
+    EpHooks hk{};
+    if (hooks) hk = *hooks;
     if (split > 1)
         return bn == 256 ? launch_splitk<256>(tmA, tmA64, tmA32, tmB, p, x, split, max_tiles, st)
                          : launch_splitk<128>(tmA, tmA64, tmA32, tmB, p, x, split, max_tiles, st);
@@ -1088,20 +1177,26 @@ static int launch(const void* A, int64_t a_rows, const void* B, int64_t b_rows, 
     // A caller that knows its load says so: above about 56 expected rows per expert many blocks have more than 64 live
     // rows, and those are faster in the plain order.
     const bool swap = p.mode == kMasked && p.max_m <= 256 && bn == 256 && (p.expected_m <= 0 || p.expected_m <= kSwapMaxExpectedRows);
-    if (swap && combine)
-        fp8_gemm_mx_kernel<256, kEpiCombine, true><<<(unsigned)grid, kThreads, kSwapSmemBytes, st>>>(tmA, tmA64, tmA32, tmB, p, x, cb);
-    else if (swap && act)
-        fp8_gemm_mx_kernel<256, kEpiAct, true><<<(unsigned)grid, kThreads, kSwapSmemBytes, st>>>(tmA, tmA64, tmA32, tmB, p, x, cb);
-    else if (swap)
-        fp8_gemm_mx_kernel<256, kEpiStore, true><<<(unsigned)grid, kThreads, kSwapSmemBytes, st>>>(tmA, tmA64, tmA32, tmB, p, x, cb);
-    else if (combine)
-        fp8_gemm_mx_kernel<256, kEpiCombine, false><<<(unsigned)grid, kThreads, Cfg<256>::kSmemBytes, st>>>(tmA, tmA64, tmA32, tmB, p, x, cb);
-    else if (act)
-        fp8_gemm_mx_kernel<256, kEpiAct, false><<<(unsigned)grid, kThreads, Cfg<256>::kSmemBytes, st>>>(tmA, tmA64, tmA32, tmB, p, x, cb);
-    else if (bn == 256)
-        fp8_gemm_mx_kernel<256, kEpiStore, false><<<(unsigned)grid, kThreads, Cfg<256>::kSmemBytes, st>>>(tmA, tmA64, tmA32, tmB, p, x, cb);
-    else
-        fp8_gemm_mx_kernel<128, kEpiStore, false><<<(unsigned)grid, kThreads, Cfg<128>::kSmemBytes, st>>>(tmA, tmA64, tmA32, tmB, p, x, cb);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(kThreadsMain);
+    cfg.dynamicSmemBytes = swap ? kSwapSmemBytes : (bn == 256 ? Cfg<256>::kSmemBytes : Cfg<128>::kSmemBytes);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = hooks ? 1 : 0;
+    auto go = [&](auto kernel) { return cudaLaunchKernelEx(&cfg, kernel, tmA, tmA64, tmA32, tmB, p, x, cb, hk); };
+    cudaError_t le;
+    if (swap && combine) le = go(fp8_gemm_mx_kernel<256, kEpiCombine, true>);
+    else if (swap && act) le = go(fp8_gemm_mx_kernel<256, kEpiAct, true>);
+    else if (swap) le = go(fp8_gemm_mx_kernel<256, kEpiStore, true>);
+    else if (combine) le = go(fp8_gemm_mx_kernel<256, kEpiCombine, false>);
+    else if (act) le = go(fp8_gemm_mx_kernel<256, kEpiAct, false>);
+    else if (bn == 256) le = go(fp8_gemm_mx_kernel<256, kEpiStore, false>);
+    else le = go(fp8_gemm_mx_kernel<128, kEpiStore, false>);
+    KBN_CUDA(le);
     KBN_CHECK_LAUNCH();
     return KBN_OK;
 }
@@ -1211,18 +1306,19 @@ namespace mx {
 
 // Not part of the C ABI: called by the expert-parallel layer, which owns the peer mappings.
 int gemm_masked_ue8m0_combine(const void* A, const void* sfa_packed, const void* B, const void* sfb_packed, const int32_t* masked_m,
-                              int64_t E, int64_t max_m, int64_t N, int64_t K, const CombineEpilogue& cb, int64_t expected_m, cudaStream_t st) {
+                              int64_t E, int64_t max_m, int64_t N, int64_t K, const CombineEpilogue& cb, int64_t expected_m,
+                              const EpHooks* hooks, cudaStream_t st) {
     const char* who = "fp8 gemm (ue8m0, combine epilogue)";
     KBN_REQUIRE(E > 0 && max_m > 0 && N > 0 && K > 0 && A && B && masked_m, KBN_ERR_ARG, "%s: bad arguments", who);
     KBN_REQUIRE(max_m % 128 == 0 && N % 32 == 0, KBN_ERR_ARG, "%s: max_m must be a multiple of 128 and N of 32", who);
     KBN_REQUIRE(E * N < (1ll << 31) && E * max_m < (1ll << 31), KBN_ERR_ARG, "%s: too large", who);
-    KBN_REQUIRE(cb.world >= 1 && cb.world <= kMaxPeerRanks && cb.meta && cb.done && cb.epoch, KBN_ERR_ARG, "%s: bad peer description", who);
+    KBN_REQUIRE(cb.world >= 0 && cb.world <= kMaxPeerRanks && cb.meta && cb.done && cb.epoch, KBN_ERR_ARG, "%s: bad peer description", who);
     GemmParams p{};
     fill_params(p, nullptr, N, E * max_m, N, K, E, max_m, kMasked);
     p.masked_m = masked_m;
     p.expected_m = (int32_t)std::min<int64_t>(std::max<int64_t>(expected_m, 0), 1 << 30);
     // the grid is never empty here: the last CTA must signal the peers even when no expert has rows
-    return launch(A, E * max_m, B, E * N, p, sfa_packed, sfb_packed, E * (max_m / 128), st, false, &cb);
+    return launch(A, E * max_m, B, E * N, p, sfa_packed, sfb_packed, E * (max_m / 128), st, false, &cb, hooks);
 }
 
 }  // namespace mx
@@ -1275,7 +1371,7 @@ namespace mx {
 // The masked GEMM1 + activation with the caller's expected rows per expert (0: unknown), which picks the operand order.
 int gemm1_masked_ue8m0_silu(const void* A, const void* sfa_packed, const void* W13, const void* sfb_packed, void* q, float* scale,
                             void* sf_packed, const int32_t* masked_m, int64_t E, int64_t max_m, int64_t I, int64_t K, int64_t expected_m,
-                            cudaStream_t st) {
+                            const EpHooks* hooks, cudaStream_t st) {
     const char* who = "kbn_fp8_grouped_gemm_masked_ue8m0_silu";
     KBN_REQUIRE(E >= 0 && max_m >= 0 && I >= 0 && K >= 0, KBN_ERR_ARG, "%s: negative size", who);
     if (E == 0 || max_m == 0 || I == 0) return KBN_OK;
@@ -1288,7 +1384,7 @@ int gemm1_masked_ue8m0_silu(const void* A, const void* sfa_packed, const void* W
     p.expected_m = (int32_t)std::min<int64_t>(std::max<int64_t>(expected_m, 0), 1 << 30);
     int rc = fill_act(p, who, q, I, scale, I / 128, 1, sf_packed, I, st);
     if (rc != KBN_OK) return rc;
-    return launch(A, E * max_m, W13, E * 2 * I, p, sfa_packed, sfb_packed, E * (max_m / 128), st, true);
+    return launch(A, E * max_m, W13, E * 2 * I, p, sfa_packed, sfb_packed, E * (max_m / 128), st, true, nullptr, hooks);
 }
 }  // namespace mx
 }  // namespace kbn
@@ -1296,6 +1392,6 @@ int gemm1_masked_ue8m0_silu(const void* A, const void* sfa_packed, const void* W
 extern "C" int kbn_fp8_grouped_gemm_masked_ue8m0_silu(const void* A, const void* sfa_packed, const void* W13, const void* sfb_packed,
                                                       void* q, float* scale, void* sf_packed, const int32_t* masked_m, int64_t E,
                                                       int64_t max_m, int64_t I, int64_t K, kbn_stream_t stream) {
-    return kbn::mx::gemm1_masked_ue8m0_silu(A, sfa_packed, W13, sfb_packed, q, scale, sf_packed, masked_m, E, max_m, I, K, 0,
+    return kbn::mx::gemm1_masked_ue8m0_silu(A, sfa_packed, W13, sfb_packed, q, scale, sf_packed, masked_m, E, max_m, I, K, 0, nullptr,
                                             static_cast<cudaStream_t>(stream));
 }

@@ -267,20 +267,20 @@ static __device__ __align__(256) int32_t g_permute_scratch[kStaticPermuteWords];
 // handle for the symbol, not an address a kernel may use, so the address is looked up once per device
 // (with that device current) and remembered.
 static int static_permute_scratch(int32_t** out) {
-    static int32_t* addr[64] = {nullptr};
+    static std::atomic<int32_t*> addr[64];      // host threads that race here store the same value
     int dev = 0;
     KBN_CUDA(cudaGetDevice(&dev));
     KBN_REQUIRE(dev >= 0 && dev < 64, KBN_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
-    if (addr[dev] == nullptr) {
-        int32_t* p = nullptr;
+    int32_t* p = addr[dev].load(std::memory_order_acquire);
+    if (p == nullptr) {
         cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_permute_scratch);
         if (e != cudaSuccess || p == nullptr) {
             set_error("kbn_moe_permute_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
             return KBN_ERR_CUDA;
         }
-        addr[dev] = p;
+        addr[dev].store(p, std::memory_order_release);
     }
-    *out = addr[dev];
+    *out = p;
     return KBN_OK;
 }
 
@@ -296,10 +296,10 @@ extern "C" int kbn_moe_permute_static(const void* a_q, const float* a_s, const i
                                       int32_t* dest_row, int64_t M_cap, kbn_stream_t stream) {
     using namespace kbn;
     KBN_REQUIRE(T >= 0 && topk > 0 && E > 0, KBN_ERR_ARG, "kbn_moe_permute_static: bad sizes");
-    KBN_REQUIRE(T * topk <= kStaticPermutePairs && E <= kStaticPermuteExperts, KBN_ERR_UNSUPPORTED,
+    KBN_REQUIRE(topk <= kStaticPermutePairs && T <= kStaticPermutePairs / topk && E <= kStaticPermuteExperts, KBN_ERR_UNSUPPORTED,
                 "kbn_moe_permute_static: T*topk=%lld (limit %lld) or E=%lld (limit %lld) beyond the built-in scratch; "
                 "use kbn_moe_permute with a caller-provided workspace",
-                (long long)(T * topk), (long long)kStaticPermutePairs, (long long)E, (long long)kStaticPermuteExperts);
+                (long long)(T <= kStaticPermutePairs ? T * topk : -1), (long long)kStaticPermutePairs, (long long)E, (long long)kStaticPermuteExperts);
     int32_t* scratch = nullptr;
     int rc = static_permute_scratch(&scratch);
     if (rc != KBN_OK) return rc;

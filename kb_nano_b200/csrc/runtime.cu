@@ -2,7 +2,7 @@
 #include <atomic>
 #include <stdarg.h>
 
-#include "common.cuh"
+#include "gemm_common.cuh"
 
 namespace kbn {
 int gemm_status_ptr(int32_t** out);
@@ -34,8 +34,19 @@ int sm_count() {
 
 __device__ int32_t g_gemm_status = 0;
 
+
+// The word's device address, looked up once per device (the same value whichever host thread stores it first).
 int gemm_status_ptr(int32_t** out) {
-    KBN_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(out), g_gemm_status));
+    static std::atomic<int32_t*> cached[64];
+    int dev = 0;
+    KBN_CUDA(cudaGetDevice(&dev));
+    KBN_REQUIRE(dev >= 0 && dev < 64, KBN_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+    int32_t* p = cached[dev].load(std::memory_order_acquire);
+    if (p == nullptr) {
+        KBN_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_gemm_status));
+        cached[dev].store(p, std::memory_order_release);
+    }
+    *out = p;
     return KBN_OK;
 }
 
@@ -54,5 +65,15 @@ int kbn_gemm_status(int32_t* host_out, kbn_stream_t stream) {
     KBN_CUDA(cudaMemcpyFromSymbol(host_out, g_gemm_status, sizeof(int32_t)));
     return KBN_OK;
 }
+
+int kbn_gemm_clear_status(kbn_stream_t stream) {
+    using namespace kbn;
+    int32_t* p = nullptr;
+    int rc = gemm_status_ptr(&p);
+    if (rc != KBN_OK) return rc;
+    KBN_CUDA(cudaMemsetAsync(p, 0, sizeof(int32_t), static_cast<cudaStream_t>(stream)));
+    return KBN_OK;
+}
+
 
 }  // extern "C"

@@ -129,7 +129,28 @@ class EpMoe:
         if s["code"] != 0:
             raise EpStatusError(f"expert-parallel layer on rank {self.rank}: {s}")
 
-    LAUNCHES_PER_FORWARD = 7   # quant, dispatch, wait, GEMM1 (+activation), GEMM2 (+combine stores), wait, sum
+    def expert_phase(self, w13: torch.Tensor, w13_s: torch.Tensor, w2: torch.Tensor, w2_s: torch.Tensor,
+                     rows_per_expert: torch.Tensor, expected_m: int = 0) -> None:
+        """Measurement aid: the two expert GEMMs once more, launched as forward() launches them, on the rows the last
+        forward() received, with `rows_per_expert` (int32 [E/R], on the device) as the row counts.  No flags are
+        exchanged and the step counter stays, so the call can be bracketed by CUDA events."""
+        p13 = _ops.packed_weight_scales(w13_s, 2 * self.inter, self.hidden)
+        p2 = _ops.packed_weight_scales(w2_s, self.hidden, self.inter)
+        if p13 is None or p2 is None or self.max_m % 128:
+            raise ValueError("expert_phase needs power-of-two weight scales and max_m a multiple of 128")
+        if rows_per_expert.dtype != torch.int32 or rows_per_expert.numel() != self.hi - self.lo or not rows_per_expert.is_cuda:
+            raise ValueError("rows_per_expert must be int32 [E/R] on the device")
+        with _on(self.device):
+            _lib.check(self._lib.kbn_ep_expert_phase(self._ctx, w13.data_ptr(), p13.data_ptr(), w2.data_ptr(), p2.data_ptr(),
+                                                     rows_per_expert.data_ptr(), expected_m, _stream(w13)))
+
+    def clear_status(self) -> None:
+        """Sets the status words back to 0 (ordered on the current stream): after an overflow or a time-out has been
+        handled, later checks report later steps only."""
+        with _on(self.device):
+            _lib.check(self._lib.kbn_ep_clear_status(self._ctx, torch.cuda.current_stream(self.device).cuda_stream))
+
+    LAUNCHES_PER_FORWARD = 4   # quantise + dispatch, GEMM1 (+activation), GEMM2 (+combine stores), weighted sum
 
     def close(self) -> None:
         if self._ctx:

@@ -14,11 +14,12 @@ FP8 = torch.float8_e4m3fn
 
 
 class MoeScratch:
-    """Reusable device buffers for one (T, topk, E, H, I) problem size.  Layers run one after the
-    other, so one set per shape is shared (kb-nano does the same, fused_experts.py:139-206)."""
+    """Device buffers of the pipeline for up to `t` tokens of one (topk, E, H, I) layer shape.  Layers run one
+    after the other, so one set per shape is shared (kb-nano does the same, fused_experts.py:139-206)."""
 
     def __init__(self, t: int, topk: int, e: int, h: int, i: int, device: torch.device):
         self.key = (t, topk, e, h, i, str(device))
+        self.t_cap, self.topk, self.e, self.h, self.i = t, topk, e, h, i
         m_cap = ops.moe_aligned_rows(t, topk, e)
         self.m_cap = m_cap
         self.a_q = torch.empty(t, h, dtype=FP8, device=device)
@@ -42,18 +43,52 @@ class MoeScratch:
     def mm2(self, h: int) -> torch.Tensor:
         return self.mm[: self.m_cap * h].view(self.m_cap, h)
 
+    def for_tokens(self, t: int) -> "MoeScratch":
+        """The same memory cut down to `t` <= capacity tokens: every tensor a leading slice of the full one (all layouts
+        here are addressed by row, so a prefix of the rows is a valid smaller buffer)."""
+        if t == self.t_cap:
+            return self
+        if t > self.t_cap:
+            raise ValueError(f"scratch holds {self.t_cap} tokens, {t} asked for")
+        v = object.__new__(MoeScratch)
+        v.key = (t,) + self.key[1:]
+        v.t_cap, v.topk, v.e, v.h, v.i = t, self.topk, self.e, self.h, self.i
+        m = ops.moe_aligned_rows(t, self.topk, self.e)
+        v.m_cap = m
+        v.a_q, v.a_s = self.a_q[:t], self.a_s[:t]
+        v.a_perm, v.a_s_perm, v.row_expert = self.a_perm[:m], self.a_s_perm[:m], self.row_expert[:m]
+        v.dest_row = self.dest_row[:t]
+        v.workspace = self.workspace
+        v.mm = self.mm
+        v.a2_q, v.a2_s = self.a2_q[:m], self.a2_s[:m]
+        v.sf1, v.sf2 = self.sf1, self.sf2
+        return v
+
 
 _SCRATCH: dict = {}
+_RETIRED: list = []      # outgrown sets stay alive: a captured CUDA graph may hold pointers into them
 
 
-def get_scratch(t: int, topk: int, e: int, h: int, i: int, device: torch.device) -> MoeScratch:
-    key = (t, topk, e, h, i, str(device))
+def reserve(t: int, topk: int, e: int, h: int, i: int, device: torch.device) -> MoeScratch:
+    """Makes the shared scratch of this layer shape hold at least `t` tokens (the `_ensure_buffers` of this pipeline:
+    call it with the largest batch before capturing CUDA graphs)."""
+    key = (topk, e, h, i, str(device))
     s = _SCRATCH.get(key)
-    if s is None:
-        _SCRATCH.clear()          # keep one size alive: the buffers are large
+    if s is None or s.t_cap < t:
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("the MoE scratch must grow, which a CUDA-graph capture does not allow: call moe.reserve() "
+                               "(or the layer, eagerly) with the largest batch first")
+        if s is not None:
+            _RETIRED.append(s)
         s = MoeScratch(t, topk, e, h, i, device)
         _SCRATCH[key] = s
     return s
+
+
+def get_scratch(t: int, topk: int, e: int, h: int, i: int, device: torch.device) -> MoeScratch:
+    """Scratch for `t` tokens: a view of the shared grow-only set of this layer shape.  A smaller batch never frees
+    or moves what a larger one allocated, so pointers baked into captured graphs stay valid."""
+    return reserve(t, topk, e, h, i, device).for_tokens(t)
 
 
 def fused_experts_fp8(hidden_states: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, topk_weights: torch.Tensor,

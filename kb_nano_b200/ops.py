@@ -5,6 +5,7 @@ sm_100a kernels on the current stream of the tensors' device and returns without
 """
 from __future__ import annotations
 
+import collections
 import ctypes
 
 import torch
@@ -254,6 +255,14 @@ def gemm_status(device: torch.device | str = "cuda") -> int:
     return int(out.value)
 
 
+def gemm_clear_status(device: torch.device | str = "cuda") -> None:
+    """Sets the GEMM status word back to 0 (ordered on the device's current stream)."""
+    dev = torch.device(device)
+    dev = dev if dev.index is not None else torch.device("cuda", torch.cuda.current_device())
+    with _on(dev):
+        _lib.check(_lib.load().kbn_gemm_clear_status(torch.cuda.current_stream(dev).cuda_stream))
+
+
 def moe_aligned_rows(t: int, topk: int, e: int) -> int:
     return int(_lib.load().kbn_moe_aligned_rows(t, topk, e))
 
@@ -371,17 +380,26 @@ def pack_sf_rows(scale: torch.Tensor, k: int) -> torch.Tensor:
     return out
 
 
-_WEIGHT_SF_CACHE: dict = {}
+_WEIGHT_SF_CACHE: "collections.OrderedDict" = collections.OrderedDict()
+_WEIGHT_SF_CACHE_MAX = 16384      # far above the number of FP8 weight tensors of any model; least recently used goes first
 
 
 def packed_weight_scales(b_s: torch.Tensor, n: int, k: int):
     """(packed buffer or None) for fp32 weight scales [E?, N/128, K/128].  None when some scale is not a
     power of two, in which case the fp32-scale kernel must be used.  Checked and packed once per tensor
-    (keyed by storage address, shape and version); the check synchronises the stream that one time."""
+    (keyed by storage address, shape and version; the entry keeps the tensor alive, so the address cannot be
+    reused).  That first call launches two small kernels and synchronises the stream; it cannot happen inside a
+    CUDA-graph capture: load-time code (``postprocess_fp8_weights*`` of the drop-in linear layer, or one eager
+    warm-up call) makes it happen before."""
     key = (b_s.data_ptr(), tuple(b_s.shape), b_s._version, str(b_s.device))
     hit = _WEIGHT_SF_CACHE.get(key)
     if hit is not None:
+        _WEIGHT_SF_CACHE.move_to_end(key)
         return hit[0]
+    if torch.cuda.is_current_stream_capturing():
+        raise RuntimeError("packed_weight_scales: these weight scales have not been seen before and checking them needs a "
+                           "host synchronisation, which a CUDA-graph capture does not allow; call the layer once eagerly "
+                           "(or ops.packed_weight_scales on its scales) before capturing")
     s = b_s if b_s.is_contiguous() else b_s.contiguous()
     e = s.shape[0] if s.dim() == 3 else 1
     lib = _lib.load()
@@ -392,9 +410,9 @@ def packed_weight_scales(b_s: torch.Tensor, n: int, k: int):
         if int(cnt.item()) == 0:
             packed = torch.empty(int(lib.kbn_packed_sf_weights_bytes(e, n, k)), dtype=torch.uint8, device=s.device)
             _lib.check(lib.kbn_pack_sf_weights(s.data_ptr(), e, n, k, packed.data_ptr(), _stream(s)))
-    if len(_WEIGHT_SF_CACHE) >= 64:
-        _WEIGHT_SF_CACHE.pop(next(iter(_WEIGHT_SF_CACHE)))
-    _WEIGHT_SF_CACHE[key] = (packed, b_s)      # keep the tensor alive so the address cannot be reused
+    while len(_WEIGHT_SF_CACHE) >= _WEIGHT_SF_CACHE_MAX:
+        _WEIGHT_SF_CACHE.popitem(last=False)
+    _WEIGHT_SF_CACHE[key] = (packed, b_s)
     return packed
 
 
@@ -495,6 +513,7 @@ def m_grouped_gemm1_silu_quant_masked_ue8m0(a_q, sfa_packed, w13_q, sfb_packed, 
 
 
 _LINEAR_SF: dict = {}
+_LINEAR_SF_RETIRED: list = []     # outgrown buffers stay alive: a captured CUDA graph may still write into them
 
 
 def fp8_linear(x: torch.Tensor, a_q: torch.Tensor, a_s: torch.Tensor, b_q: torch.Tensor, b_s: torch.Tensor, out: torch.Tensor) -> None:
@@ -512,7 +531,12 @@ def fp8_linear(x: torch.Tensor, a_q: torch.Tensor, a_s: torch.Tensor, b_q: torch
     key = (str(x.device), torch.cuda.current_stream(x.device).cuda_stream)
     buf = _LINEAR_SF.get(key)
     if buf is None or buf.numel() < need:
-        buf = torch.empty(max(need, 1 << 20), dtype=torch.uint8, device=x.device)     # one per device and stream, grown on demand
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("fp8_linear: the packed-scale buffer must grow, which a CUDA-graph capture does not allow; "
+                               "call the layer eagerly with the largest batch first")
+        if buf is not None:
+            _LINEAR_SF_RETIRED.append(buf)
+        buf = torch.empty(max(need, 1 << 20), dtype=torch.uint8, device=x.device)     # one per device and stream, grow-only
         _LINEAR_SF[key] = buf
     per_token_group_quant_fp8(x, a_q, a_s, packed_sf=buf)
     fp8_gemm_nt_ue8m0(a_q, buf, b_q, packed_w, out)

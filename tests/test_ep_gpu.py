@@ -162,6 +162,11 @@ def test_ep_overflow_is_reported_not_fatal(cuda_dev):
     assert st["code"] == 10 and st["detail"] == 0
     with pytest.raises(ep.EpStatusError):
         layer.check()
+    # the report is cleared on request and a well-formed step then passes its check
+    layer.clear_status()
+    ids = (torch.arange(t, dtype=torch.int32) % e).view(t, 1)     # 16 tokens per expert would still overflow: send 8 x 4
+    layer.forward(xs[0][:32].to(d), ids[:32].to(d), torch.ones(32, 1).to(d), w13_q.to(d), w13_s.to(d), w2_q.to(d), w2_s.to(d))
+    layer.check()
     layer.close()
 
 
