@@ -117,7 +117,7 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                    const __grid_constant__ CUtensorMap tmA32, const __grid_constant__ CUtensorMap tmB, const GemmParams p,
                    const MxExtra x, const CombineEpilogue cb, const EpHooks h) {
     static_assert(!SWAP || BN == 256, "the swapped form uses 256 weight rows per tile");
-    ptx::launch_dependents();
+    if (h.tile_done != nullptr) ptx::launch_dependents();     // expert-parallel layer: the next kernel may come in under this one
     KBN_TRACE_MARK2(h.trace, h.epoch, EPI == kEpiCombine ? 2 : 1, 0);
     constexpr bool ACT = EPI == kEpiAct;
     constexpr int kBN = Cfg<BN>::kBN, kStages = Cfg<BN>::kStages, kStageBytes = Cfg<BN>::kStageBytes;
@@ -1179,7 +1179,7 @@ static int launch(const void* A, int64_t a_rows, const void* B, int64_t b_rows, 
     const bool swap = p.mode == kMasked && p.max_m <= 256 && bn == 256 && (p.expected_m <= 0 || p.expected_m <= kSwapMaxExpectedRows);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
-    cfg.blockDim = dim3(kThreadsMain);
+    cfg.blockDim = dim3(hk.sched != nullptr ? kThreadsMain : kThreads);      // the scheduler warp only where tiles come from a counter
     cfg.dynamicSmemBytes = swap ? kSwapSmemBytes : (bn == 256 ? Cfg<256>::kSmemBytes : Cfg<128>::kSmemBytes);
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
