@@ -224,6 +224,28 @@ def measured_traffic(kernel: str, scale: float):
     return None
 
 
+def triton_ref(name: str):
+    """kb-nano's own Triton kernel file `name` from oracle/_ref (the reference's GPU implementation of the operation,
+    timed beside this library's as the competitor; never on the product path), or None when it is not there."""
+    if not os.path.isfile(os.path.join(ROOT, "oracle", "_ref", name + ".py")):
+        return None
+    try:
+        import importlib
+        return importlib.import_module("oracle._ref." + name)
+    except Exception:
+        return None
+
+
+def time_competitor(world, step, steps, warmup):
+    """run_graph on the reference's kernel; None when it does not launch on this machine."""
+    try:
+        step(0)
+        torch.cuda.synchronize()
+        return run_graph(world, step, steps, warmup)
+    except Exception:
+        return None
+
+
 def cpu_threads() -> int:
     n = os.cpu_count() or 1
     try:
@@ -351,7 +373,15 @@ def wl_silu_c2(args, rank, world, dev, sampler):
     ms_e2e = Timed(world, 0, dev).run(e2e_step, max(3, args.steps // 4), 2)
     peaks = measured_peaks()
     gbs = byts / (ms * 1e-3) / 1e9
+    # the same operation by kb-nano's Triton kernel (tasks/baseline/L1/silu_mul_quant_fp8.py), same inputs, same timing
+    vs_triton = None
+    mod = triton_ref("silu_mul_quant_fp8")
+    if mod is not None:
+        smq = mod.SiluMulQuantFp8()
+        ms_t = time_competitor(world, lambda i: smq(xs[i % nbuf], qs[i % nbuf]), args.steps, args.warmup)
+        vs_triton = ms_t / ms if ms_t else None
     return {
+        "vs_triton": vs_triton,
         "metric": "fused SiLU*Mul+FP8 quant throughput", "value": gbs * world, "unit": "GB/s", "ms_per_step": ms,
         "dtype": "bf16->e4m3 (fp32 math)", "scaling": "weak",
         "config": {"workload": "silu_c2: BASELINE configs[1], bf16 [16384, 2x2048] -> e4m3 [16384,2048] + UE8M0 scales [16384,16]",
@@ -393,7 +423,18 @@ def wl_quant_c1(args, rank, world, dev, sampler, m=512, k=7168):
     ms_e2e = Timed(world, 256 << 20, dev).run(e2e_step, args.steps, 2)
     peaks = measured_peaks()
     gbs = byts / (ms * 1e-3) / 1e9
+    # the same operation by kb-nano's Triton kernel (tasks/baseline/L1/fp8_linear.py:181-215, launched as :269-279 does)
+    vs_triton = None
+    mod = triton_ref("fp8_group_quant")
+    if mod is not None:
+        def tq(i):
+            xi, qi, si = xs[i % nbuf], qs[i % nout], ss[i % nout]
+            mod._fp8_group_quant_kernel[(m * (k // 128),)](xi, qi, si, xi.stride(0), qi.stride(0), si.stride(0), si.stride(1), k,
+                                                          fp8_max=448.0, GROUP_SIZE=128, USE_UE8M0=True)
+        ms_t = time_competitor(world, tq, args.steps, args.warmup)
+        vs_triton = ms_t / ms if ms_t else None
     return {
+        "vs_triton": vs_triton,
         "metric": "1x128 FP8 activation quant throughput", "value": gbs * world, "unit": "GB/s", "ms_per_step": ms,
         "dtype": "bf16->e4m3", "scaling": "weak",
         "config": {"workload": f"quant_{'c1' if m == 512 else 'c3'}: activation of BASELINE configs[{0 if m == 512 else 2}], bf16 [{m},{k}], column-major UE8M0 scales",
@@ -524,6 +565,51 @@ def wl_moe_single(args, rank, world, dev, sampler, name):
         hout.copy_(out, non_blocking=True)
 
     ms_e2e = Timed(world, 0, dev).run(e2e_step, max(3, args.steps // 2), 2)
+    # the two grouped GEMMs by kb-nano's Triton kernel (tasks/baseline/L1/moe_grouped_gemm.py:86-189 through its
+    # MoeGroupedGemm module, sorted-token layout, the module's own default configuration), same operands
+    vs_triton = None
+    mod = triton_ref("moe_grouped_gemm")
+    if mod is not None:
+        try:
+            gg = mod.MoeGroupedGemm()
+            cfg = gg.get_config(t, 2 * i, e, use_fp8=True, block_shape=[128, 128])
+            bm = cfg["BLOCK_SIZE_M"]
+            flat = ti.reshape(-1).long()
+            order = torch.argsort(flat, stable=True)
+            cnt = torch.bincount(flat, minlength=e)
+            padded = (cnt + bm - 1) // bm * bm
+            starts = torch.cumsum(padded, 0) - padded
+            sorted_ids = torch.full((int(padded.sum()),), pairs, dtype=torch.int32, device=dev)
+            rank_in_e = torch.arange(pairs, device=dev) - (torch.cumsum(cnt, 0) - cnt)[flat[order]]
+            sorted_ids[(starts[flat[order]] + rank_in_e)] = order.to(torch.int32)
+            blk_e = torch.repeat_interleave(torch.arange(e, device=dev, dtype=torch.int32), (padded // bm))
+            ntpp = torch.tensor([sorted_ids.numel()], dtype=torch.int32, device=dev)
+            a_s_rm = sc.a_s.contiguous()
+            c1 = sc.mm1(i)[:pairs]
+            a2_s_rm = sc.a2_s[:pairs].contiguous()
+            c2 = sc.mm2(h)[:pairs]
+            twf = tw.float().contiguous()
+
+            def tri(_):
+                gg(sc.a_q, w13_q, c1, twf, sorted_ids, blk_e, ntpp, False, topk, config=cfg, a_scale=a_s_rm, b_scale=w13_s,
+                   use_fp8_w8a8=True, block_shape=[128, 128])
+                gg(sc.a2_q[:pairs], w2_q, c2, twf, sorted_ids, blk_e, ntpp, True, 1, config=cfg, a_scale=a2_s_rm, b_scale=w2_s,
+                   use_fp8_w8a8=True, block_shape=[128, 128])
+
+            tri(0)
+            torch.cuda.synchronize()
+            tev = []
+            for _ in range(5):
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                tri(0)
+                b.record()
+                tev.append((a, b))
+            torch.cuda.synchronize()
+            tri_ms = sorted(a.elapsed_time(b) for a, b in tev)[len(tev) // 2]
+            vs_triton = tri_ms / (2.0 * gemm_ms)
+        except Exception:
+            vs_triton = None
     hbm_bound = (pairs / e) < 562      # rows per expert below the machine balance: weights dominate
     if hbm_bound:
         ach = (g1 + g2) / 2.0 / (gemm_ms * 1e-3) / 1e9
@@ -538,6 +624,7 @@ def wl_moe_single(args, rank, world, dev, sampler, name):
                 "frac_of_nominal_4500": ach / 4500.0, "algorithmic_flop_per_launch": flop / 2.0}
     n_cpu = 4 if name == "moe_c3" else 1
     return {
+        "vs_triton": vs_triton,
         "metric": "FP8 MoE layer throughput", "value": t / (ms * 1e-3) * world, "unit": "tokens/s", "ms_per_step": ms,
         "dtype": "e4m3 x e4m3 -> fp32 -> bf16", "scaling": "weak",
         "config": {"workload": desc, "l2": "expert weights (>= 1.4 GB) exceed the 126 MB L2", "replicas": world,
@@ -822,6 +909,8 @@ def main():
             "clocks": clocks}
     if "parity" in res:
         line["parity"] = res["parity"]
+    if res.get("vs_triton") is not None:
+        line["vs_triton"] = res["vs_triton"]
     if args.workload == DEFAULT_WORKLOAD and args.experts == 256 and not args.no_components:
         # The other parts of the composite metric, each measured by its own workload function exactly as
         # `--workload <name>` would and under a clock-sampling window of its own, reported beside the headline number:
@@ -841,6 +930,9 @@ def main():
                      "e2e": r["e2e"]["value"], "scaling": r["scaling"], "clocks": cs.stop()}
             if r.get("parity") is not None:
                 entry["parity_ok"] = r["parity"]["ok"]
+            if r.get("vs_triton") is not None:
+                # time of kb-nano's own Triton kernel(s) for the same operation on this GPU / time of this library's
+                entry["vs_triton"] = r["vs_triton"]
             comp[name] = entry
         line["components"] = comp
     if rank == 0 and world == 1 and cpu_fn is not None and not args.no_cpu_baseline:

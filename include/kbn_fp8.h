@@ -120,10 +120,13 @@ int kbn_silu_bf16_table(void* out_u16, kbn_stream_t stream);
  */
 
 /* Dense linear.  Stands behind torch.ops.kb_nano_fp8.fp8_gemm_nt, i.e. deep_gemm.fp8_gemm_nt as
- * called by Fp8Linear.forward (tasks/baseline/L1/fp8_linear.py:91-110,443-445). */
+ * called by Fp8Linear.forward (tasks/baseline/L1/fp8_linear.py:91-110,443-447).  bias: bf16 [N] or
+ * null; it is added to the fp32 accumulator before the one rounding to bf16, as the reference's
+ * F.linear(x, w, bias) does (tasks/reference/L1/fp8_linear.py:103), so the layer needs no separate
+ * `output + bias` pass over [M, N]. */
 int kbn_fp8_gemm_nt(const void* A, const float* sa, int64_t sa_row, int64_t sa_grp, const void* B,
-                    const float* sb, void* C, int64_t ldc, int64_t M, int64_t N, int64_t K,
-                    kbn_stream_t stream);
+                    const float* sb, const void* bias, void* C, int64_t ldc, int64_t M, int64_t N,
+                    int64_t K, kbn_stream_t stream);
 
 /* Grouped, expert-contiguous rows.  Stands behind m_grouped_fp8_gemm_nt_contiguous
  * (tasks/baseline/L1/moe_grouped_gemm.py:71-83; tasks/baseline/L1/fp8_grouped_gemm_contiguous.py:102-118).
@@ -168,8 +171,8 @@ int kbn_pack_sf_weights(const float* sb, int64_t E, int64_t N, int64_t K, void* 
                         kbn_stream_t stream);
 int kbn_count_non_pow2_scales(const float* s, int64_t n, int32_t* device_count, kbn_stream_t stream);
 int kbn_fp8_gemm_nt_ue8m0(const void* A, const void* sfa_packed, const void* B,
-                          const void* sfb_packed, void* C, int64_t ldc, int64_t M, int64_t N,
-                          int64_t K, kbn_stream_t stream);
+                          const void* sfb_packed, const void* bias, void* C, int64_t ldc, int64_t M,
+                          int64_t N, int64_t K, kbn_stream_t stream);
 int kbn_fp8_grouped_gemm_contig_ue8m0(const void* A, const void* sfa_packed, const void* B,
                                       const void* sfb_packed, void* C, int64_t ldc,
                                       const int32_t* row_expert, int64_t M_sum, int64_t N, int64_t K,

@@ -27,7 +27,7 @@ SIGNATURES = {
     "kbn_silu_mul_quant_1x128_rows": (_i32, [_ptr, _i64, _i64, _i64, _ptr, _i64, _ptr, _i64, _i64, _f32, _i32, _ptr, _ptr]),
     "kbn_silu_mul_quant_1x128_list": (_i32, [_ptr, _i64, _i64, _ptr, _i64, _ptr, _i64, _i64, _f32, _i32, _ptr, _i64, _ptr, _ptr]),
     "kbn_silu_mul_quant_1x128_masked": (_i32, [_ptr, _i64, _i64, _i64, _ptr, _ptr, _ptr, _ptr]),
-    "kbn_fp8_gemm_nt": (_i32, [_ptr, _ptr, _i64, _i64, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _ptr]),
+    "kbn_fp8_gemm_nt": (_i32, [_ptr, _ptr, _i64, _i64, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _ptr]),
     "kbn_fp8_grouped_gemm_contig": (_i32, [_ptr, _ptr, _i64, _i64, _ptr, _ptr, _ptr, _i64, _ptr, _i64, _i64, _i64, _i64, _ptr]),
     "kbn_fp8_grouped_gemm_masked": (_i32, [_ptr, _ptr, _i64, _i64, _i64, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _ptr]),
     "kbn_gemm_status": (_i32, [_ptr, _ptr]),
@@ -38,7 +38,7 @@ SIGNATURES = {
     "kbn_pack_sf_rows": (_i32, [_ptr, _i64, _i64, _i64, _i64, _ptr, _ptr]),
     "kbn_pack_sf_weights": (_i32, [_ptr, _i64, _i64, _i64, _ptr, _ptr]),
     "kbn_count_non_pow2_scales": (_i32, [_ptr, _i64, _ptr, _ptr]),
-    "kbn_fp8_gemm_nt_ue8m0": (_i32, [_ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _ptr]),
+    "kbn_fp8_gemm_nt_ue8m0": (_i32, [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _ptr]),
     "kbn_fp8_grouped_gemm_contig_ue8m0": (_i32, [_ptr, _ptr, _ptr, _ptr, _ptr, _i64, _ptr, _i64, _i64, _i64, _i64, _ptr]),
     "kbn_fp8_grouped_gemm_masked_ue8m0": (_i32, [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _ptr]),
     "kbn_fp8_grouped_gemm_contig_ue8m0_silu": (_i32, [_ptr, _ptr, _ptr, _ptr, _ptr, _i64, _ptr, _i64, _i64, _ptr, _ptr, _i64, _i64, _i64, _i64, _ptr]),

@@ -42,8 +42,7 @@ def unpack_ue8m0_packed_scales(sf: torch.Tensor, N: int, K: int) -> torch.Tensor
         raise ValueError(f"packed UE8M0 weight scales must be int32 [{N}, {math.ceil(kb / 4)}] for a [{N}, {K}] weight, "
                          f"got {sf.dtype} {tuple(sf.shape)}")
     rows = sf[::_GROUP][:nb].contiguous()
-    last = sf[torch.arange(nb, device=sf.device).mul(_GROUP).add(_GROUP - 1).clamp_max(N - 1)]
-    if not torch.equal(rows, last):
+    if not torch.equal(rows.repeat_interleave(_GROUP, dim=0)[:N], sf):
         raise ValueError("packed UE8M0 weight scales: rows of one 128-row block differ; not a 128x128 block-scale layout")
     exps = rows.view(torch.uint8).view(nb, -1)[:, :kb].to(torch.int32)
     return torch.pow(2.0, (exps - 127).float())
@@ -149,11 +148,16 @@ class Fp8Linear(nn.Module):
             output = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
         input_scale = _alloc_colmajor_scale(M, num_groups, dev)
         w_scale = self._block_scales(weight_scale_inv, N, K)
+        # the bias rides in the GEMM's epilogue (added in fp32 before the rounding to bf16, like the reference's
+        # F.linear); under torch.compile the opaque ops have no bias argument and the add stays a torch op
+        fused_bias = None
+        if bias is not None and not compiling and bias.dtype == torch.bfloat16 and bias.is_contiguous():
+            fused_bias = bias
         if compiling:
             torch.ops.kbn_b200.per_token_group_quant_fp8(input_2d, q_input, input_scale)
             torch.ops.kbn_b200.fp8_gemm_nt(q_input, input_scale, weight_fp8, w_scale, output)
         else:
-            ops.fp8_linear(input_2d, q_input, input_scale, weight_fp8, w_scale, output)
-        if bias is not None:
+            ops.fp8_linear(input_2d, q_input, input_scale, weight_fp8, w_scale, output, fused_bias)
+        if bias is not None and fused_bias is None:
             output = output + bias
         return output.view(*input_bf16.shape[:-1], N)

@@ -16,6 +16,7 @@ struct GemmParams {
     const float* sa;
     int64_t sa_exp, sa_row, sa_grp;
     const float* sb;
+    const __nv_bfloat16* bias;   // dense form only, may be null: bf16 [N], added in fp32 before the result is rounded to bf16
     __nv_bfloat16* C;
     int64_t ldc;
     const int32_t* row_expert;

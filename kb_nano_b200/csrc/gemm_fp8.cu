@@ -180,6 +180,11 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             if (!ok) break;
             if (row_ok) {
                 const int32_t n0 = tile.n_blk * kBlockN + half * 64;
+                if (p.bias != nullptr) {
+#pragma unroll
+                    for (int j = 0; j < 64; ++j)
+                        if (n0 + j < p.N) acc[j] += __bfloat162float(p.bias[n0 + j]);
+                }
                 __nv_bfloat16* crow = p.C + (int64_t)row * p.ldc + n0;
                 if (n0 + 64 <= p.N && ((reinterpret_cast<uintptr_t>(crow) & 15u) == 0)) {
 #pragma unroll
@@ -284,12 +289,12 @@ static inline int32_t cdiv32(int64_t a, int64_t b) { return (int32_t)((a + b - 1
 }  // namespace kbn
 
 namespace kbn {
-int fp8_gemm_small_m(const void* A, const float* sa, int64_t sa_row, int64_t sa_grp, const void* B, const float* sb, void* C,
-                     int64_t ldc, int64_t M, int64_t N, int64_t K, cudaStream_t st);   // gemm_fp8_small_m.cu
+int fp8_gemm_small_m(const void* A, const float* sa, int64_t sa_row, int64_t sa_grp, const void* B, const float* sb, const void* bias,
+                     void* C, int64_t ldc, int64_t M, int64_t N, int64_t K, cudaStream_t st);   // gemm_fp8_small_m.cu
 }
 
 extern "C" int kbn_fp8_gemm_nt(const void* A, const float* sa, int64_t sa_row, int64_t sa_grp, const void* B,
-                               const float* sb, void* C, int64_t ldc, int64_t M, int64_t N, int64_t K,
+                               const float* sb, const void* bias, void* C, int64_t ldc, int64_t M, int64_t N, int64_t K,
                                kbn_stream_t stream) {
     using namespace kbn;
     KBN_REQUIRE(M >= 0 && N >= 0 && K >= 0, KBN_ERR_ARG, "kbn_fp8_gemm_nt: negative size");
@@ -298,9 +303,10 @@ extern "C" int kbn_fp8_gemm_nt(const void* A, const float* sa, int64_t sa_row, i
     KBN_REQUIRE(ldc >= N, KBN_ERR_ARG, "kbn_fp8_gemm_nt: ldc < N");
     // decode-sized batches: a weight-streaming kernel instead of 128-row tiles
     if (M <= 16 && K >= 16 && K % 16 == 0 && aligned16(A) && aligned16(B))
-        return fp8_gemm_small_m(A, sa, sa_row, sa_grp, B, sb, C, ldc, M, N, K, static_cast<cudaStream_t>(stream));
+        return fp8_gemm_small_m(A, sa, sa_row, sa_grp, B, sb, bias, C, ldc, M, N, K, static_cast<cudaStream_t>(stream));
     GemmParams p{};
     p.sa = sa; p.sa_exp = 0; p.sa_row = sa_row; p.sa_grp = sa_grp; p.sb = sb;
+    p.bias = static_cast<const __nv_bfloat16*>(bias);
     p.C = static_cast<__nv_bfloat16*>(C); p.ldc = ldc;
     p.rows_total = (int32_t)M; p.N = (int32_t)N; p.K = (int32_t)K; p.E = 1; p.max_m = 0;
     p.num_m_blocks = cdiv32(M, kBlockM); p.num_n_blocks = cdiv32(N, kBlockN); p.num_k_blocks = cdiv32(K, kBlockK);

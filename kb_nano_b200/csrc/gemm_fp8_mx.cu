@@ -715,6 +715,13 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             } else if (row_ok) {
 #pragma unroll
                 for (int c = 0; c < kChunks; ++c) {
+                    if (p.bias != nullptr) {
+                        // dense linear layer with a bias: added to the fp32 accumulators, one rounding to bf16 afterwards
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (n0 + 32 * c + j < p.N)
+                                r[c][j] = __float_as_uint(__uint_as_float(r[c][j]) + __bfloat162float(p.bias[n0 + 32 * c + j]));
+                    }
                     if (n0 + 32 * c + 32 <= p.N && vec_ok) {
 #pragma unroll
                         for (int j = 0; j < 32; j += 8) {
@@ -939,6 +946,12 @@ fp8_gemm_mx_splitk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
                     const float4 v0 = ptx::ld_shared_v4(src), v1 = ptx::ld_shared_v4(src + 16u);
                     a0.x += v0.x; a0.y += v0.y; a0.z += v0.z; a0.w += v0.w;
                     a1.x += v1.x; a1.y += v1.y; a1.z += v1.z; a1.w += v1.w;
+                }
+                if (p.bias != nullptr) {
+                    float* af[8] = {&a0.x, &a0.y, &a0.z, &a0.w, &a1.x, &a1.y, &a1.z, &a1.w};
+#pragma unroll
+                    for (int q = 0; q < 8; ++q)
+                        if (n0 + j + q < p.N) *af[q] += __bfloat162float(p.bias[n0 + j + q]);
                 }
                 if (n0 + j + 8 <= p.N && vec_ok) {
                     uint4 v;
@@ -1202,7 +1215,7 @@ static int launch(const void* A, int64_t a_rows, const void* B, int64_t b_rows, 
 }
 
 static void fill_params(GemmParams& p, void* C, int64_t ldc, int64_t rows, int64_t N, int64_t K, int64_t E, int64_t max_m, int mode) {
-    p.sa = nullptr; p.sb = nullptr; p.sa_exp = p.sa_row = p.sa_grp = 0;
+    p.sa = nullptr; p.sb = nullptr; p.bias = nullptr; p.sa_exp = p.sa_row = p.sa_grp = 0;
     p.C = static_cast<__nv_bfloat16*>(C); p.ldc = ldc;
     p.rows_total = (int32_t)rows; p.N = (int32_t)N; p.K = (int32_t)K; p.E = (int32_t)E; p.max_m = (int32_t)max_m;
     p.num_m_blocks = mode == kMasked ? 0 : cdiv32(rows, kBlockM);
@@ -1259,14 +1272,15 @@ extern "C" int kbn_count_non_pow2_scales(const float* s, int64_t n, int32_t* dev
     return KBN_OK;
 }
 
-extern "C" int kbn_fp8_gemm_nt_ue8m0(const void* A, const void* sfa_packed, const void* B, const void* sfb_packed, void* C,
-                                     int64_t ldc, int64_t M, int64_t N, int64_t K, kbn_stream_t stream) {
+extern "C" int kbn_fp8_gemm_nt_ue8m0(const void* A, const void* sfa_packed, const void* B, const void* sfb_packed, const void* bias,
+                                     void* C, int64_t ldc, int64_t M, int64_t N, int64_t K, kbn_stream_t stream) {
     using namespace kbn;
     KBN_REQUIRE(M >= 0 && N >= 0 && K >= 0, KBN_ERR_ARG, "kbn_fp8_gemm_nt_ue8m0: negative size");
     if (M == 0 || N == 0) return KBN_OK;
     KBN_REQUIRE(A && B && C && ldc >= N, KBN_ERR_ARG, "kbn_fp8_gemm_nt_ue8m0: null pointer or ldc < N");
     GemmParams p{};
     mx::fill_params(p, C, ldc, M, N, K, 1, 0, kDense);
+    p.bias = static_cast<const __nv_bfloat16*>(bias);
     return mx::launch(A, M, B, N, p, sfa_packed, sfb_packed, p.num_m_blocks, static_cast<cudaStream_t>(stream));
 }
 

@@ -38,8 +38,8 @@ constexpr int kSmallMWarps = 8;
 template <int NT>
 __global__ void __launch_bounds__(32 * kSmallMWarps)
 fp8_gemm_small_m_kernel(const uint8_t* __restrict__ A, const float* __restrict__ sa, int64_t sa_row, int64_t sa_grp,
-                        const uint8_t* __restrict__ W, const float* __restrict__ sw, __nv_bfloat16* __restrict__ C, int64_t ldc,
-                        int M, int N, int K) {
+                        const uint8_t* __restrict__ W, const float* __restrict__ sw, const __nv_bfloat16* __restrict__ bias,
+                        __nv_bfloat16* __restrict__ C, int64_t ldc, int M, int N, int K) {
     __shared__ float red[kSmallMWarps][NT * 4][32];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -117,13 +117,13 @@ fp8_gemm_small_m_kernel(const uint8_t* __restrict__ A, const float* __restrict__
         const int nt = v >> 2, i = v & 3;
         const int row = n0 + (l >> 2) + ((i & 2) ? 8 : 0);          // weight row = output column
         const int tok = nt * 8 + 2 * (l & 3) + (i & 1);
-        if (row < N && tok < M) C[(int64_t)tok * ldc + row] = __float2bfloat16_rn(sum);
+        if (row < N && tok < M) C[(int64_t)tok * ldc + row] = __float2bfloat16_rn(bias != nullptr ? sum + __bfloat162float(bias[row]) : sum);
     }
 }
 
 // Dense fp32-scale GEMM for M <= 16: returns KBN_OK after launching, or a negative code.
-int fp8_gemm_small_m(const void* A, const float* sa, int64_t sa_row, int64_t sa_grp, const void* B, const float* sb, void* C,
-                     int64_t ldc, int64_t M, int64_t N, int64_t K, cudaStream_t st) {
+int fp8_gemm_small_m(const void* A, const float* sa, int64_t sa_row, int64_t sa_grp, const void* B, const float* sb, const void* bias,
+                     void* C, int64_t ldc, int64_t M, int64_t N, int64_t K, cudaStream_t st) {
     KBN_REQUIRE(M >= 1 && M <= 16 && N >= 1 && K >= 16 && K % 16 == 0, KBN_ERR_ARG, "fp8 gemm (small M): M=%lld N=%lld K=%lld", (long long)M,
                 (long long)N, (long long)K);
     KBN_REQUIRE(aligned16(A) && aligned16(B), KBN_ERR_ARG, "fp8 gemm (small M): A and B must be 16-byte aligned");
@@ -132,10 +132,11 @@ int fp8_gemm_small_m(const void* A, const float* sa, int64_t sa_row, int64_t sa_
     const auto* a = static_cast<const uint8_t*>(A);
     const auto* w = static_cast<const uint8_t*>(B);
     auto* c = static_cast<__nv_bfloat16*>(C);
+    const auto* b = static_cast<const __nv_bfloat16*>(bias);
     if (M <= 8)
-        fp8_gemm_small_m_kernel<1><<<blocks, 32 * kSmallMWarps, 0, st>>>(a, sa, sa_row, sa_grp, w, sb, c, ldc, (int)M, (int)N, (int)K);
+        fp8_gemm_small_m_kernel<1><<<blocks, 32 * kSmallMWarps, 0, st>>>(a, sa, sa_row, sa_grp, w, sb, b, c, ldc, (int)M, (int)N, (int)K);
     else
-        fp8_gemm_small_m_kernel<2><<<blocks, 32 * kSmallMWarps, 0, st>>>(a, sa, sa_row, sa_grp, w, sb, c, ldc, (int)M, (int)N, (int)K);
+        fp8_gemm_small_m_kernel<2><<<blocks, 32 * kSmallMWarps, 0, st>>>(a, sa, sa_row, sa_grp, w, sb, b, c, ldc, (int)M, (int)N, (int)K);
     KBN_CHECK_LAUNCH();
     return KBN_OK;
 }

@@ -190,8 +190,18 @@ def _check_sb(sb: torch.Tensor, lead: tuple, n: int, k: int) -> torch.Tensor:
     return sb if sb.is_contiguous() else sb.contiguous()
 
 
-def fp8_gemm_nt(a_q: torch.Tensor, a_s: torch.Tensor, b_q: torch.Tensor, b_s: torch.Tensor, out: torch.Tensor) -> None:
-    """out bf16 [M,N] = (a_q, a_s [M,K/128]) @ (b_q [N,K], b_s [N/128,K/128])^T, written in place."""
+def _bias_ptr(bias: torch.Tensor | None, n: int, dev) -> int | None:
+    if bias is None:
+        return None
+    if bias.dtype != torch.bfloat16 or bias.numel() != n or not bias.is_contiguous() or bias.device != dev:
+        raise ValueError(f"bias must be contiguous bf16 [{n}] on {dev}")
+    return bias.data_ptr()
+
+
+def fp8_gemm_nt(a_q: torch.Tensor, a_s: torch.Tensor, b_q: torch.Tensor, b_s: torch.Tensor, out: torch.Tensor,
+                bias: torch.Tensor | None = None) -> None:
+    """out bf16 [M,N] = (a_q, a_s [M,K/128]) @ (b_q [N,K], b_s [N/128,K/128])^T (+ bias, in fp32, before the rounding),
+    written in place."""
     dev = _cuda(a_q, a_s, b_q, b_s, out)
     m, k = a_q.shape
     n = b_q.shape[0]
@@ -202,8 +212,8 @@ def fp8_gemm_nt(a_q: torch.Tensor, a_s: torch.Tensor, b_q: torch.Tensor, b_s: to
         raise ValueError("out must be bf16 [M,N], contiguous along N")
     with _on(dev):
         _lib.check(_lib.load().kbn_fp8_gemm_nt(a_q.data_ptr(), a_s.data_ptr(), sa_row, sa_grp, b_q.data_ptr(),
-                                               b_s.data_ptr(), out.data_ptr(), out.stride(0) if m > 1 else n, m, n, k,
-                                               _stream(out)))
+                                               b_s.data_ptr(), _bias_ptr(bias, n, dev), out.data_ptr(), out.stride(0) if m > 1 else n,
+                                               m, n, k, _stream(out)))
 
 
 def m_grouped_fp8_gemm_nt_contiguous(a_q, a_s, b_q, b_s, out, expert_ids) -> None:
@@ -416,7 +426,7 @@ def packed_weight_scales(b_s: torch.Tensor, n: int, k: int):
     return packed
 
 
-def fp8_gemm_nt_ue8m0(a_q, sfa_packed, b_q, sfb_packed, out) -> None:
+def fp8_gemm_nt_ue8m0(a_q, sfa_packed, b_q, sfb_packed, out, bias: torch.Tensor | None = None) -> None:
     dev = _cuda(a_q, sfa_packed, b_q, sfb_packed, out)
     m, k = a_q.shape
     n = b_q.shape[0]
@@ -425,7 +435,8 @@ def fp8_gemm_nt_ue8m0(a_q, sfa_packed, b_q, sfb_packed, out) -> None:
         raise ValueError("out must be bf16 [M,N], contiguous along N")
     with _on(dev):
         _lib.check(_lib.load().kbn_fp8_gemm_nt_ue8m0(a_q.data_ptr(), sfa_packed.data_ptr(), b_q.data_ptr(), sfb_packed.data_ptr(),
-                                                     out.data_ptr(), out.stride(0) if m > 1 else n, m, n, k, _stream(out)))
+                                                     _bias_ptr(bias, n, dev), out.data_ptr(), out.stride(0) if m > 1 else n, m, n, k,
+                                                     _stream(out)))
 
 
 def m_grouped_fp8_gemm_nt_contiguous_ue8m0(a_q, sfa_packed, b_q, sfb_packed, out, expert_ids) -> None:
@@ -516,7 +527,8 @@ _LINEAR_SF: dict = {}
 _LINEAR_SF_RETIRED: list = []     # outgrown buffers stay alive: a captured CUDA graph may still write into them
 
 
-def fp8_linear(x: torch.Tensor, a_q: torch.Tensor, a_s: torch.Tensor, b_q: torch.Tensor, b_s: torch.Tensor, out: torch.Tensor) -> None:
+def fp8_linear(x: torch.Tensor, a_q: torch.Tensor, a_s: torch.Tensor, b_q: torch.Tensor, b_s: torch.Tensor, out: torch.Tensor,
+               bias: torch.Tensor | None = None) -> None:
     """The FP8 linear layer in two launches: 1x128 quantisation of x into a_q / a_s, then the GEMM against b_q / b_s
     into out.  With power-of-two weight scales and more than 8 rows the quantiser writes the packed scales the
     block-scaled GEMM reads itself (no packing launch); 8 rows or fewer take the weight-streaming kernel."""
@@ -525,7 +537,7 @@ def fp8_linear(x: torch.Tensor, a_q: torch.Tensor, a_s: torch.Tensor, b_q: torch
     packed_w = packed_weight_scales(b_s, n, k) if m > 8 else None
     if packed_w is None or k % 8 or x.stride(0) % 8 or a_q.stride(0) % 8 or x.data_ptr() % 16:
         per_token_group_quant_fp8(x, a_q, a_s)
-        fp8_gemm_nt_auto(a_q, a_s, b_q, b_s, out)
+        fp8_gemm_nt_auto(a_q, a_s, b_q, b_s, out, bias)
         return
     need = packed_sf_rows_bytes(m, k)
     key = (str(x.device), torch.cuda.current_stream(x.device).cuda_stream)
@@ -539,10 +551,11 @@ def fp8_linear(x: torch.Tensor, a_q: torch.Tensor, a_s: torch.Tensor, b_q: torch
         buf = torch.empty(max(need, 1 << 20), dtype=torch.uint8, device=x.device)     # one per device and stream, grow-only
         _LINEAR_SF[key] = buf
     per_token_group_quant_fp8(x, a_q, a_s, packed_sf=buf)
-    fp8_gemm_nt_ue8m0(a_q, buf, b_q, packed_w, out)
+    fp8_gemm_nt_ue8m0(a_q, buf, b_q, packed_w, out, bias)
 
 
-def fp8_gemm_nt_auto(a_q: torch.Tensor, a_s: torch.Tensor, b_q: torch.Tensor, b_s: torch.Tensor, out: torch.Tensor) -> None:
+def fp8_gemm_nt_auto(a_q: torch.Tensor, a_s: torch.Tensor, b_q: torch.Tensor, b_s: torch.Tensor, out: torch.Tensor,
+                     bias: torch.Tensor | None = None) -> None:
     """Dense block-scaled GEMM for activations quantised with power-of-two (UE8M0) scales, which is what
     per_token_group_quant_fp8 produces by default: takes the block-scaled tensor-core path when the weight
     scales are powers of two as well (checked once per weight tensor), the fp32-scale kernel otherwise."""
@@ -550,13 +563,13 @@ def fp8_gemm_nt_auto(a_q: torch.Tensor, a_s: torch.Tensor, b_q: torch.Tensor, b_
     if a_q.shape[0] <= 8:
         # decode-sized batch: the fp32-scale entry point streams the weights with a kernel of its own, as fast as the
         # block-scaled path at this size and without the scale-packing launch
-        fp8_gemm_nt(a_q, a_s, b_q, b_s, out)
+        fp8_gemm_nt(a_q, a_s, b_q, b_s, out, bias)
         return
     packed = packed_weight_scales(b_s, n, k)
     if packed is not None:
-        fp8_gemm_nt_ue8m0(a_q, pack_sf_rows(a_s, k), b_q, packed, out)
+        fp8_gemm_nt_ue8m0(a_q, pack_sf_rows(a_s, k), b_q, packed, out, bias)
     else:
-        fp8_gemm_nt(a_q, a_s, b_q, b_s, out)
+        fp8_gemm_nt(a_q, a_s, b_q, b_s, out, bias)
 
 
 def rmsnorm_quant_fp8(x: torch.Tensor, weight: torch.Tensor, out_fp8: torch.Tensor, out_scale: torch.Tensor, eps: float = 1e-6,

@@ -223,3 +223,40 @@ def route_topk(logits: torch.Tensor, topk: int, scoring: str = "softmax", bias: 
     if scale != 1.0:
         w = w * scale
     return w.to(torch.float32), ids.to(torch.int32)
+
+
+def qwen3_moe_forward(x, gate_w, w13_q, w13_s, w2_q, w2_s, top_k, renormalize=True, router_logits=None, cast_weights=False):
+    """Qwen3MoE.forward_impl (tasks/baseline/L2/qwen3_moe.py:161-188) on one rank: gate linear in the activations'
+    dtype, TopKSoftmax, the FP8 experts; no all-reduce with one rank.  cast_weights=True is MixtralMoE.forward_impl
+    (tasks/baseline/L2/mixtral_moe.py:64-83): router weights rounded to the activations' dtype (:72).
+    router_logits: logits computed elsewhere (a test passes the GPU's own, so that a near tie in the top-k is not
+    decided by the two sides' different bf16 GEMMs, which are not what is under test)."""
+    logits = torch.nn.functional.linear(x, gate_w) if router_logits is None else router_logits
+    tw, ti = route_topk(logits, top_k, "softmax", renormalize=renormalize, renorm_floor=1e-20)
+    if cast_weights:
+        tw = tw.to(x.dtype).float()
+    return moe_layer(x, w13_q, w13_s, w2_q, w2_s, tw, ti)
+
+
+def swiglu_mlp_fp8(x, gate_up_q, gate_up_s, down_q, down_s):
+    """LlamaMLP with FP8 block-scaled linears (tasks/baseline/L2/llama_mlp.py:17-39 over Fp8Linear,
+    tasks/baseline/L1/fp8_linear.py:371-450): quantise, GEMM, SiLU(gate)*up + quantise, GEMM."""
+    a_q, sa = quant_1x128(x)
+    h1 = gemm_nt_dequant(a_q, sa, gate_up_q, gate_up_s)
+    q2, s2 = silu_mul_quant_1x128(h1)
+    return gemm_nt_dequant(q2, s2, down_q, down_s)
+
+
+def deepseek_moe_forward(x, gate_w, bias, n_group, topk_group, top_k, scoring, norm_topk_prob, routed_scaling_factor,
+                         w13_q, w13_s, w2_q, w2_s, shared=None, router_logits=None):
+    """DeepSeekMoE.forward_impl, FP8 path (tasks/baseline/L2/deepseek_moe.py:209-304): router logits in bf16 (:246-251),
+    GroupedTopK with the scaling factor left at 1 (:143-147, :252-255), fp32 router weights into the experts (:266-284),
+    x routed_scaling_factor after the experts (:293-295), + shared expert (:297-300).  shared = (gate_up_q, gate_up_s,
+    down_q, down_s) or None."""
+    logits = torch.nn.functional.linear(x, gate_w) if router_logits is None else router_logits
+    tw, ti = route_topk(logits, top_k, scoring, bias=bias, n_group=n_group, topk_group=topk_group, renormalize=norm_topk_prob,
+                        score_in_input_dtype=True)
+    out = moe_layer(x, w13_q, w13_s, w2_q, w2_s, tw, ti) * routed_scaling_factor
+    if shared is not None:
+        out = out + swiglu_mlp_fp8(x, *shared)
+    return out

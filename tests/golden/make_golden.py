@@ -17,6 +17,11 @@ Every array is produced by reference code, imported from the tree as it lies:
   fused_experts.npz   the op sequence of tasks/reference/L2/fused_experts.py FusedExperts._forward_triton, run
                       with that file's own MoeAlign / MoeGroupedGemm / SiluAndMul / PerTokenGroupQuantFp8 / MoeSum
   routing.npz         tasks/reference/L1/topk_softmax.py TopKSoftmax.forward (renormalised and raw weights)
+  grouped_topk.npz    tasks/baseline/L1/grouped_topk.py GroupedTopK.forward, eager branch (:117-174; kb-nano has no
+                      reference/ edition of this operator).  The file imports a compiled extension at module level
+                      that only its CUDA fast path uses: the import is satisfied with an empty stand-in and, with no
+                      CUDA device, forward() takes the eager branch.  VLLM_BATCH_INVARIANT=1 makes its top-k sorted.
+                      `--only-grouped-topk` writes this fixture alone.
 Inputs are seeded; bf16 tensors are stored as uint16 bit patterns, fp8 as uint8.
 """
 from __future__ import annotations
@@ -31,9 +36,11 @@ import numpy as np
 import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-if len(sys.argv) < 2 and "KB_NANO_REF" not in os.environ:
-    sys.exit("usage: make_golden.py /path/to/kb_nano   (or set KB_NANO_REF)")
-REF = os.path.abspath(sys.argv[1] if len(sys.argv) > 1 else os.environ["KB_NANO_REF"])
+ONLY_GROUPED_TOPK = "--only-grouped-topk" in sys.argv
+_args = [a for a in sys.argv[1:] if not a.startswith("--")]
+if not _args and "KB_NANO_REF" not in os.environ:
+    sys.exit("usage: make_golden.py [--only-grouped-topk] /path/to/kb_nano   (or set KB_NANO_REF)")
+REF = os.path.abspath(_args[0] if _args else os.environ["KB_NANO_REF"])
 
 
 def _load(path: str, name: str):
@@ -42,6 +49,39 @@ def _load(path: str, name: str):
     sys.modules[name] = mod
     spec.loader.exec_module(mod)
     return mod
+
+
+def make_grouped_topk():
+    import types
+    os.environ["VLLM_BATCH_INVARIANT"] = "1"
+    pkg = types.ModuleType("_ref_l1")
+    pkg.__path__ = [os.path.join(REF, "tasks", "baseline", "L1")]
+    sys.modules["_ref_l1"] = pkg
+    csrc = types.ModuleType("_ref_l1.csrc")
+    csrc._C = None                                 # the compiled extension: used by the CUDA fast path only
+    sys.modules["_ref_l1.csrc"] = csrc
+    spec = importlib.util.spec_from_file_location("_ref_l1.grouped_topk", os.path.join(REF, "tasks/baseline/L1/grouped_topk.py"))
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[spec.name] = mod
+    spec.loader.exec_module(mod)
+    assert not torch.cuda.is_available(), "the eager branch is what is recorded: run without a CUDA device"
+    gen = torch.Generator().manual_seed(20250)
+    out = {}
+    # DeepSeek-V3-like: 256 experts in 8 groups, 4 groups kept, top-8, sigmoid, selection bias, x 2.5
+    lg = torch.randn(48, 256, generator=gen)
+    bias = torch.randn(256, generator=gen) * 0.1
+    w, ids = mod.GroupedTopK("sigmoid", True, 2.5)(lg, bias, 8, 4, 8)
+    out.update(a_logits=bits(lg), a_bias=bits(bias), a_w=bits(w), a_ids=bits(ids))
+    # no bias (group score = max), softmax, no renormalisation
+    lg = torch.randn(32, 64, generator=gen)
+    w, ids = mod.GroupedTopK("softmax", False, 1.0)(lg, None, 4, 2, 6)
+    out.update(b_logits=bits(lg), b_w=bits(w), b_ids=bits(ids))
+    # bf16 logits: the scores are computed in bf16 (ids can tie there; the fixture keeps the weights' multiset per token)
+    lg = torch.randn(40, 128, generator=gen).to(torch.bfloat16)
+    bias = torch.randn(128, generator=gen) * 0.05
+    w, ids = mod.GroupedTopK("sigmoid", True, 1.0)(lg, bias, 4, 2, 8)
+    out.update(c_logits=bits(lg), c_bias=bits(bias), c_w=bits(w), c_ids=bits(ids))
+    np.savez_compressed(os.path.join(HERE, "grouped_topk.npz"), **out)
 
 
 def bits(t: torch.Tensor) -> np.ndarray:
@@ -210,10 +250,15 @@ def main() -> None:
     w256n, i256n = router(lg256, 8, False)
     np.savez_compressed(os.path.join(HERE, "routing.npz"), logits8=bits(lg8), w8=bits(w8), ids8=bits(i8), logits256=bits(lg256),
                         w256=bits(w256), ids256=bits(i256), w256_raw=bits(w256n.clone()), ids256_raw=bits(i256n.clone()))
+    make_grouped_topk()
     for f in sorted(os.listdir(HERE)):
         if f.endswith(".npz"):
             print(f, os.path.getsize(os.path.join(HERE, f)))
 
 
 if __name__ == "__main__":
-    main()
+    if ONLY_GROUPED_TOPK:
+        make_grouped_topk()
+        print("grouped_topk.npz", os.path.getsize(os.path.join(HERE, "grouped_topk.npz")))
+    else:
+        main()

@@ -1,0 +1,144 @@
+"""Host-side logic that needs no GPU: the packed weight-scale decoder, the layers' expert placement and loaders
+under two gloo ranks, and -- where a kb-nano tree is present -- the drop-in files going through kb-nano's own
+kernel swapper."""
+import importlib.util
+import math
+import os
+import sys
+from types import SimpleNamespace
+
+import pytest
+import torch
+
+
+def _candidate(level, name):
+    from kb_nano_b200 import candidate_dir
+    spec = importlib.util.spec_from_file_location(f"_candidate_impl_{level}_{name}_cpu", os.path.join(candidate_dir(), level, name + ".py"))
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[spec.name] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def _pack_like_deepgemm(scales: torch.Tensor, n: int) -> torch.Tensor:
+    """fp32 power-of-two block scales [N/128, K/128] -> int32 [N, ceil(K/128/4)]: one row per output channel, four
+    consecutive K-blocks' UE8M0 exponent bytes per word, lowest byte first (the layout the decoder assumes)."""
+    nb, kb = scales.shape
+    exps = ((scales.view(torch.int32) >> 23) & 0xFF).to(torch.uint8)
+    padded = torch.zeros(nb, (kb + 3) // 4 * 4, dtype=torch.uint8)
+    padded[:, :kb] = exps
+    return padded.repeat_interleave(128, dim=0)[:n].contiguous().view(torch.int32)
+
+
+def test_unpack_packed_weight_scales_round_trip():
+    mod = _candidate("L1", "fp8_linear")
+    g = torch.Generator().manual_seed(0)
+    for n, k in ((256, 512), (384, 7168), (200, 1152)):
+        nb, kb = math.ceil(n / 128), math.ceil(k / 128)
+        scales = torch.pow(2.0, torch.randint(-20, 5, (nb, kb), generator=g).float())
+        packed = _pack_like_deepgemm(scales, n)
+        assert tuple(packed.shape) == (n, math.ceil(kb / 4))
+        assert torch.equal(mod.unpack_ue8m0_packed_scales(packed, n, k), scales)
+    with pytest.raises(ValueError):
+        mod.unpack_ue8m0_packed_scales(packed[:, :1].contiguous() if packed.shape[1] > 1 else packed[:10], n, k)   # wrong shape
+    with pytest.raises(ValueError):
+        mod.unpack_ue8m0_packed_scales(packed.float(), n, k)                                                       # wrong dtype
+    bad = _pack_like_deepgemm(scales, n).clone()
+    bad[1, 0] += 1                                                                                                 # rows of a block disagree
+    with pytest.raises(ValueError):
+        mod.unpack_ue8m0_packed_scales(bad, n, k)
+
+
+def _layer_worker(rank, world, port, q):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from kb_nano_b200 import layers
+        e, h, i, topk = 8, 256, 128, 2
+        cfg = SimpleNamespace(num_experts=e, num_experts_per_tok=topk, hidden_size=h, moe_intermediate_size=i, norm_topk_prob=True)
+        layer = layers.Qwen3MoE(cfg, {"weight_block_size": [128, 128]})
+        ok = layer.ep_size == world and layer.tp_size == world and (layer.expert_lo, layer.expert_hi) == (rank * e // world, (rank + 1) * e // world)
+        ok = ok and tuple(layer.w13.shape) == (e // world, 2 * i, h) and tuple(layer.w2_scale.shape) == (e // world, h // 128, i // 128)
+        layer.w13.data.view(torch.uint8).zero_()
+        layer.w13_scale.data.zero_()
+        for ex in range(e):                                   # every rank is offered every expert, as a checkpoint loader does
+            w1 = torch.full((i, h), ex + 1, dtype=torch.uint8).view(torch.float8_e4m3fn)
+            w3 = torch.full((i, h), 100 + ex, dtype=torch.uint8).view(torch.float8_e4m3fn)
+            layer.w13.weight_loader(layer.w13, w1, ex, True)
+            layer.w13.weight_loader(layer.w13, w3, ex, False)
+            layer.w13_scale.weight_loader(layer.w13_scale, torch.full((i // 128, h // 128), float(ex + 1)), ex, True)
+            layer.w13_scale.weight_loader(layer.w13_scale, torch.full((i // 128, h // 128), float(-ex - 1)), ex, False)
+        raw = layer.w13.data.view(torch.uint8)
+        for le in range(e // world):
+            ex = layer.expert_lo + le
+            ok = ok and bool((raw[le, :i] == ex + 1).all()) and bool((raw[le, i:] == 100 + ex).all())
+            ok = ok and bool((layer.w13_scale[le, : i // 128] == ex + 1).all()) and bool((layer.w13_scale[le, i // 128:] == -ex - 1).all())
+        try:
+            layers.Qwen3MoE(cfg, None)
+            ok = False
+        except NotImplementedError:
+            pass
+        q.put((rank, ok))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_layers_place_whole_experts_on_each_rank():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_layer_worker, args=(r, 2, 29641, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=120)
+    res = sorted(q.get(timeout=5) for _ in range(2))
+    assert res == [(0, True), (1, True)]
+
+
+def test_candidates_go_through_kb_nanos_kernel_swapper():
+    """kb-nano's own loader (infra/kernel_swapper.py:328-355 `load_candidate`, :278-305 `patch_class`, :308-311
+    `restore`) pointed at this package's candidate directory: it finds the class by the target's name, and patching
+    replaces the baseline class wherever kb-nano references it.  kb-nano's target discovery imports every model of
+    the tree (diffusers, deep_gemm, compiled extensions ...), which this machine cannot; the target list is
+    therefore seeded with the targets whose baseline modules do import here (Triton-only files), built the way
+    discovery builds them, and everything after that is kb-nano's unmodified code.  Needs a kb-nano tree
+    ($KB_NANO_REF or /root/reference); skipped otherwise."""
+    root = os.path.abspath(os.environ.get("KB_NANO_REF", "/root/reference"))
+    if not os.path.isfile(os.path.join(root, "infra", "kernel_swapper.py")):
+        pytest.skip("no kb-nano tree")
+    from pathlib import Path
+    from kb_nano_b200 import candidate_dir
+    if "kb_nano" not in sys.modules:      # the tree is the package `kb_nano`, whatever its directory is called
+        spec = importlib.util.spec_from_file_location("kb_nano", os.path.join(root, "__init__.py"), submodule_search_locations=[root])
+        pkg = importlib.util.module_from_spec(spec)
+        sys.modules["kb_nano"] = pkg
+        spec.loader.exec_module(pkg)
+    try:
+        ks = importlib.import_module("kb_nano.infra.kernel_swapper")
+    except Exception as ex:
+        pytest.skip(f"kb-nano's kernel swapper does not import here: {type(ex).__name__}: {str(ex)[:150]}")
+    seeded = []
+    for name, cls_name in (("silu_mul_quant_fp8", "SiluMulQuantFp8"), ("topk_softmax", "TopKSoftmax")):
+        try:
+            mod = importlib.import_module(f"kb_nano.tasks.baseline.L1.{name}")
+        except Exception:
+            continue                      # this baseline module needs something the machine does not have
+        seeded.append(ks.BenchTarget(name=name, level=1, module_path=f"tasks/baseline/L1/{name}.py", models=[], target_cls=getattr(mod, cls_name)))
+    if not seeded:
+        pytest.skip("no baseline module of a swap target imports on this machine")
+    old_targets, old_dir = ks._TARGETS, ks._CANDIDATE_DIR
+    ks._TARGETS, ks._CANDIDATE_DIR = seeded, Path(candidate_dir())
+    try:
+        for target in seeded:
+            assert ks.get(target.name) is target
+            cls = ks.load_candidate(target.name)
+            assert cls is not None and cls.__name__ == target.target_cls.__name__ and cls is not target.target_cls
+            assert cls.__module__ == f"_candidate_impl_L1_{target.name}"
+            home = sys.modules[target.target_cls.__module__]
+            with ks.replacement_context(target, cls):
+                assert getattr(home, cls.__name__) is cls
+            assert getattr(home, cls.__name__) is target.target_cls
+    finally:
+        ks._TARGETS, ks._CANDIDATE_DIR = old_targets, old_dir

@@ -166,3 +166,19 @@ def test_routing_oracle_matches_reference_fixture():
     w, ids = to.route_topk(lg, 4, "sigmoid", None, 8, 2, True)
     assert all(len(set((ids[r] // 8).tolist())) <= 2 for r in range(16))
     assert torch.allclose(w.sum(dim=1), torch.ones(16))
+
+
+def test_grouped_topk_oracle_matches_the_baselines_eager_branch():
+    """GroupedTopK has no reference/ edition in kb-nano: the fixture holds the output of the baseline file's own
+    eager branch (tasks/baseline/L1/grouped_topk.py:117-174, run on CPU by tests/golden/make_golden.py) and the
+    oracle's restatement reproduces it bit for bit: ids and fp32 weights, with and without the selection bias,
+    fp32 and bf16 gating outputs."""
+    g = golden("grouped_topk")
+    w, ids = to.route_topk(torch.from_numpy(g["a_logits"]), 8, "sigmoid", bias=torch.from_numpy(g["a_bias"]), n_group=8, topk_group=4,
+                           renormalize=True, scale=2.5, score_in_input_dtype=True)
+    assert (ids.numpy() == g["a_ids"]).all() and (w.numpy().view(np.uint32) == g["a_w"].view(np.uint32)).all()
+    w, ids = to.route_topk(torch.from_numpy(g["b_logits"]), 6, "softmax", n_group=4, topk_group=2, renormalize=False, score_in_input_dtype=True)
+    assert (ids.numpy() == g["b_ids"]).all() and (w.numpy().view(np.uint32) == g["b_w"].view(np.uint32)).all()
+    w, ids = to.route_topk(bf16_from_bits(g["c_logits"]), 8, "sigmoid", bias=torch.from_numpy(g["c_bias"]), n_group=4, topk_group=2,
+                           renormalize=True, score_in_input_dtype=True)
+    assert (ids.numpy() == g["c_ids"]).all() and (w.numpy().view(np.uint32) == g["c_w"].view(np.uint32)).all()

@@ -84,3 +84,24 @@ def test_grouped_topk_candidate_bf16(cuda_dev):
     assert bool(torch.allclose(torch.sort(w, dim=1).values, torch.sort(rw, dim=1).values, rtol=2e-2, atol=1e-6))
     with pytest.raises(ValueError):
         mod.GroupedTopK("tanh")
+
+
+def test_grouped_topk_against_the_baselines_eager_branch(cuda_dev):
+    """The routing kernel and the GroupedTopK drop-in against the fixture recorded from the baseline file's own eager
+    branch (tasks/baseline/L1/grouped_topk.py:117-174): fp32 gating outputs with and without the selection bias."""
+    import importlib.util, os, sys
+    from kb_nano_b200 import candidate_dir, ops
+    from tests.util import bf16_from_bits
+    spec = importlib.util.spec_from_file_location("_candidate_impl_L1_grouped_topk_g", os.path.join(candidate_dir(), "L1", "grouped_topk.py"))
+    mod = importlib.util.module_from_spec(spec); sys.modules[spec.name] = mod; spec.loader.exec_module(mod)
+    g = golden("grouped_topk")
+    d = cuda_dev
+    w, ids = mod.GroupedTopK("sigmoid", True, 2.5)(torch.from_numpy(g["a_logits"]).to(d), torch.from_numpy(g["a_bias"]).to(d), 8, 4, 8)
+    check(w, ids, torch.from_numpy(g["a_w"]), torch.from_numpy(g["a_ids"]), "GroupedTopK fixture, sigmoid + bias + groups")
+    w, ids = mod.GroupedTopK("softmax", False, 1.0)(torch.from_numpy(g["b_logits"]).to(d), None, 4, 2, 6)
+    check(w, ids, torch.from_numpy(g["b_w"]), torch.from_numpy(g["b_ids"]), "GroupedTopK fixture, softmax, no bias")
+    # bf16 gating output: scores tie often in bf16, so the chosen sets are compared through their sorted weights
+    w, ids = mod.GroupedTopK("sigmoid", True, 1.0)(bf16_from_bits(g["c_logits"]).to(d), torch.from_numpy(g["c_bias"]).to(d), 4, 2, 8)
+    rw, ri = torch.from_numpy(g["c_w"]), torch.from_numpy(g["c_ids"])
+    assert float((ids.cpu() == ri).float().mean()) > 0.9
+    assert bool(torch.allclose(torch.sort(w.cpu(), dim=1).values, torch.sort(rw, dim=1).values, rtol=2e-2, atol=1e-6))
