@@ -301,6 +301,12 @@ int kbn_moe_route_topk(const void* logits, int logits_bf16, int64_t ld, int64_t 
  *   w2_sf_packed (kbn_pack_sf_weights of the same scales) are given and max_m % 128 == 0, the expert
  *   GEMMs take the UE8M0 fast path and the fp32 scale pointers may be null.  Every rank must call it
  *   the same number of times (also with T == 0).  An expert can take at most max_m rows per call.
+ * kbn_ep_moe_forward_routed: the same layer call from the router's logits instead of its choice: logits
+ *   [T, E] (fp32 or bf16, row stride ld) go through the routing of kbn_moe_route_topk (same arguments, same
+ *   arithmetic: tasks/baseline/L1/topk_softmax.py:37-60, tasks/baseline/L1/grouped_topk.py:75-174) inside the
+ *   dispatch kernel -- one warp of the token's CTA routes while the others quantise the row -- so the layer
+ *   stays at four launches with the router included.  topk is the context's.  kbn_ep_last_routing copies the
+ *   weights fp32 [T, topk] and expert ids int32 [T, topk] that call chose (device to device, stream-ordered).
  * kbn_ep_status: 4 int32 {code, phase, peer, detail}; code 0 = ok, 10 = an expert overflowed max_m
  *   rows (detail = expert), 11 = expert id out of range, 20 = a wait on peer `peer` ran out in
  *   phase 1 (dispatch) or 2 (combine).  Synchronises `stream`.  The first code of a context sticks
@@ -322,6 +328,13 @@ int kbn_ep_moe_forward(kbn_ep_ctx* ctx, const void* x_bf16, const int32_t* topk_
                        const float* topk_w, int64_t T, const void* w13, const float* w13_s,
                        const void* w2, const float* w2_s, const void* w13_sf_packed,
                        const void* w2_sf_packed, void* out_bf16, kbn_stream_t stream);
+int kbn_ep_moe_forward_routed(kbn_ep_ctx* ctx, const void* x_bf16, const void* logits, int logits_bf16,
+                              int64_t ld, int64_t T, int softmax, const float* bias, int64_t n_group,
+                              int64_t topk_group, int renormalize, float renorm_floor, float scale,
+                              int round_bf16, const void* w13, const float* w13_s, const void* w2,
+                              const float* w2_s, const void* w13_sf_packed, const void* w2_sf_packed,
+                              void* out_bf16, kbn_stream_t stream);
+int kbn_ep_last_routing(kbn_ep_ctx* ctx, float* out_w, int32_t* out_ids, int64_t T, kbn_stream_t stream);
 int kbn_ep_status(kbn_ep_ctx* ctx, int32_t* host_out4, kbn_stream_t stream);
 int kbn_ep_clear_status(kbn_ep_ctx* ctx, kbn_stream_t stream);
 int kbn_ep_expert_phase(kbn_ep_ctx* ctx, const void* w13, const void* w13_sf_packed, const void* w2,

@@ -52,6 +52,9 @@ SIGNATURES = {
     "kbn_ep_attach": (_i32, [_ptr, _ptr]),
     "kbn_ep_symmetric_bytes": (_i64, [_ptr]),
     "kbn_ep_moe_forward": (_i32, [_ptr, _ptr, _ptr, _ptr, _i64, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr]),
+    "kbn_ep_moe_forward_routed": (_i32, [_ptr, _ptr, _ptr, _i32, _i64, _i64, _i32, _ptr, _i64, _i64, _i32, _f32, _f32, _i32, _ptr, _ptr, _ptr, _ptr,
+                                         _ptr, _ptr, _ptr, _ptr]),
+    "kbn_ep_last_routing": (_i32, [_ptr, _ptr, _ptr, _i64, _ptr]),
     "kbn_ep_status": (_i32, [_ptr, _ptr, _ptr]),
     "kbn_ep_clear_status": (_i32, [_ptr, _ptr]),
     "kbn_ep_expert_phase": (_i32, [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _ptr]),

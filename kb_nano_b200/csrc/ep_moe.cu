@@ -33,6 +33,7 @@
 #include <new>
 
 #include "gemm_common.cuh"
+#include "moe_route.cuh"
 #include "quant_common.cuh"
 
 extern "C" int kbn_fp8_grouped_gemm_masked(const void*, const float*, int64_t, int64_t, int64_t, const void*, const float*,
@@ -79,6 +80,7 @@ struct kbn_ep_ctx {
     __nv_bfloat16* mm1; uint8_t* a2_q; float* a2_s; __nv_bfloat16* mm2;
     uint8_t* sf2;                      // packed UE8M0 scales of the activation between the GEMMs (UE8M0 GEMM path)
     int32_t* done;                     // [4] block-completion counters of dispatch and combine, the step counter, counter of the sum
+    float* route_w; int32_t* route_ids; // [max_tokens*topk] router weights and expert ids of the last routed call
     int32_t* hooks;                    // [2 + e_local*max_m/128] tile counters of the two GEMMs, then one counter per 128-row block
     int64_t n_hooks;
     unsigned long long* trace;         // debug builds (-DKBN_TRACE) only: time stamps, else null
@@ -133,9 +135,14 @@ __device__ __forceinline__ void signal_when_grid_done(int32_t* done, const EpPee
 }
 
 // One CTA per token (one CTA that only signals when the rank has no tokens).  Dynamic shared memory: the quantised
-// row [hidden], its scales fp32 [hidden/128], the row slot of every top-k slot int32 [topk].
+// row [hidden], its scales fp32 [hidden/128], the row slot and the expert of every top-k slot int32 [2 * topk].
+// PER > 0: the kernel routes as well -- warp 0 turns the token's router logits into its top-k experts and weights
+// (route_token; PER = experts per lane, BF16_IN = logits' dtype) while the other seven warps quantise the row; the
+// weights and ids also go to route_w / route_ids for the weighted sum at the end of the layer.  PER == 0: `ids` given.
+template <int PER, bool BF16_IN>
 __global__ void __launch_bounds__(256)
-ep_dispatch_quant_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ ids, int T, int topk, int hidden, int e_local,
+ep_dispatch_quant_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ ids, const RouteArgs ra,
+                         float* __restrict__ route_w, int32_t* __restrict__ route_ids, int T, int topk, int hidden, int e_local,
                          int max_m, int experts_total, EpPeers peers, EpLayout lay, int rank, int world, const int32_t* epoch,
                          int32_t* done, int32_t* status, int32_t* hooks, int n_hooks, unsigned long long* trace) {
     ptx::launch_dependents();
@@ -145,6 +152,7 @@ ep_dispatch_quant_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __r
     uint8_t* row_q = dsm;
     float* row_s = reinterpret_cast<float*>(dsm + hidden);
     int32_t* pos_s = reinterpret_cast<int32_t*>(row_s + G);
+    int32_t* ids_s = pos_s + topk;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     // the tile and block counters of this step's two GEMMs start at zero; the GEMMs touch them only after they have
     // seen this grid's flag, which is published after these stores
@@ -152,9 +160,9 @@ ep_dispatch_quant_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __r
         for (int i = tid; i < n_hooks; i += blockDim.x) hooks[i] = 0;
     const int t = blockIdx.x;
     if (t < T) {
-        // row slots first: the round trips of the remote atomics overlap the quantisation below
-        for (int s = tid; s < topk; s += blockDim.x) {
-            const int e = ids[t * topk + s];
+        // a row slot for slot s of the token: a remote atomicAdd on the owner's per-expert counter, whose round trip
+        // overlaps the quantisation below
+        auto take_slot = [&](int s, int e) {
             int pos = -1;
             if (e >= 0 && e < experts_total) {
                 const int dst = e / e_local, le = e - dst * e_local;
@@ -168,28 +176,48 @@ ep_dispatch_quant_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __r
                 atomicCAS(status, 0, 11);              // expert id out of range
                 status[3] = e;
             }
+            ids_s[s] = e;
             pos_s[s] = pos;
+        };
+        constexpr int kFirstQuantWarp = PER > 0 ? 1 : 0;
+        if (PER > 0) {
+            if (warp == 0) {
+                float w;
+                int id;
+                route_token<(PER > 0 ? PER : 1), BF16_IN>(ra, t, lane, w, id);
+                if (lane < topk) {
+                    route_w[t * topk + lane] = w;
+                    route_ids[t * topk + lane] = id;
+                    take_slot(lane, id);
+                }
+            }
+        } else {
+            for (int s = tid; s < topk; s += blockDim.x) take_slot(s, ids[t * topk + s]);
         }
         // 1x128 quantisation of the token's row, a half-warp per group, four groups' loads in flight per half-warp
-        const uint32_t j = tid & 15u, hw = tid >> 4;
-        const __nv_bfloat16* xr = x + (int64_t)t * hidden;
-        for (int g0 = 0; g0 < G; g0 += 64) {
-            uint4 v[4];
+        if (warp >= kFirstQuantWarp) {
+            const int nhw = 2 * (8 - kFirstQuantWarp);
+            const uint32_t j = tid & 15u;
+            const int hw = (tid >> 4) - 2 * kFirstQuantWarp;
+            const __nv_bfloat16* xr = x + (int64_t)t * hidden;
+            for (int g0 = 0; g0 < G; g0 += 4 * nhw) {
+                uint4 v[4];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const int g = g0 + 16 * u + (int)hw;
-                v[u] = g < G ? __ldcs(reinterpret_cast<const uint4*>(xr + g * 128 + j * 8)) : make_uint4(0, 0, 0, 0);
-            }
+                for (int u = 0; u < 4; ++u) {
+                    const int g = g0 + nhw * u + hw;
+                    v[u] = g < G ? __ldcs(reinterpret_cast<const uint4*>(xr + g * 128 + j * 8)) : make_uint4(0, 0, 0, 0);
+                }
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const int g = g0 + 16 * u + (int)hw;
-                const GroupScale sc = make_scale<true>(halfwarp_absmax(v[u]), 1e-10f);
-                if (g < G) {
-                    uint2 o;
-                    o.x = quant_pair<true>(v[u].x, sc) | (quant_pair<true>(v[u].y, sc) << 16);
-                    o.y = quant_pair<true>(v[u].z, sc) | (quant_pair<true>(v[u].w, sc) << 16);
-                    *reinterpret_cast<uint2*>(row_q + g * 128 + j * 8) = o;
-                    if (j == 0) row_s[g] = sc.scale;
+                for (int u = 0; u < 4; ++u) {
+                    const int g = g0 + nhw * u + hw;
+                    const GroupScale sc = make_scale<true>(halfwarp_absmax(v[u]), 1e-10f);
+                    if (g < G) {
+                        uint2 o;
+                        o.x = quant_pair<true>(v[u].x, sc) | (quant_pair<true>(v[u].y, sc) << 16);
+                        o.y = quant_pair<true>(v[u].z, sc) | (quant_pair<true>(v[u].w, sc) << 16);
+                        *reinterpret_cast<uint2*>(row_q + g * 128 + j * 8) = o;
+                        if (j == 0) row_s[g] = sc.scale;
+                    }
                 }
             }
         }
@@ -199,7 +227,7 @@ ep_dispatch_quant_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __r
         for (int s = warp; s < topk; s += (int)(blockDim.x >> 5)) {
             const int pos = pos_s[s];
             if (pos < 0) continue;
-            const int e = ids[t * topk + s];
+            const int e = ids_s[s];
             const int dst = e / e_local, le = e - dst * e_local;
             uint8_t* pb = peers.base[dst];
             const int64_t row = (int64_t)le * max_m + pos;
@@ -362,6 +390,8 @@ static int ep_allocate(kbn_ep_ctx* c) {
     c->n_hooks = 2 + c->e_local * ((c->max_m + 127) / 128);
     KBN_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->hooks), (size_t)c->n_hooks * 4));
     KBN_CUDA(cudaMemset(c->hooks, 0, (size_t)c->n_hooks * 4));
+    KBN_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->route_w), (size_t)(c->max_tokens * c->topk) * 4));
+    KBN_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->route_ids), (size_t)(c->max_tokens * c->topk) * 4));
 #ifdef KBN_TRACE
     KBN_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->trace), 2 * 4 * 256 * 4 * 8));
     KBN_CUDA(cudaMemset(c->trace, 0, 2 * 4 * 256 * 4 * 8));
@@ -390,7 +420,7 @@ extern "C" int kbn_ep_create(int rank, int world, int64_t experts_total, int64_t
     KBN_REQUIRE(hidden % 128 == 0 && inter % 128 == 0 && hidden > 0 && inter > 0, KBN_ERR_ARG, "kbn_ep_create: hidden and inter must be multiples of 128");
     KBN_REQUIRE(max_m > 0 && max_tokens > 0 && topk > 0 && max_tokens < (1 << 20) && topk < (1 << 20) && max_tokens * topk < (1 << 20), KBN_ERR_ARG,
                 "kbn_ep_create: bad max_m/max_tokens/topk");
-    KBN_REQUIRE(hidden + 4 * (hidden / 128) + 4 * topk <= 48 * 1024, KBN_ERR_UNSUPPORTED, "kbn_ep_create: hidden=%lld too large for the dispatch kernel",
+    KBN_REQUIRE(hidden + 4 * (hidden / 128) + 8 * topk <= 48 * 1024, KBN_ERR_UNSUPPORTED, "kbn_ep_create: hidden=%lld too large for the dispatch kernel",
                 (long long)hidden);
     kbn_ep_ctx* c = new (std::nothrow) kbn_ep_ctx();
     KBN_REQUIRE(c, KBN_ERR_CUDA, "kbn_ep_create: out of host memory");
@@ -489,9 +519,56 @@ static int ep_expert_gemms(kbn_ep_ctx* c, const void* w13, const void* w13_sf_pa
 }
 }  // namespace kbn
 
+namespace kbn {
+struct EpRouteCall {       // the router logits of a call that routes inside the dispatch kernel
+    RouteArgs args;
+    int logits_bf16;
+};
+static int ep_forward(kbn_ep_ctx* c, const void* x_bf16, const int32_t* topk_ids, const float* topk_w, const EpRouteCall* route, int64_t T,
+                      const void* w13, const float* w13_s, const void* w2, const float* w2_s, const void* w13_sf_packed,
+                      const void* w2_sf_packed, void* out_bf16, kbn_stream_t stream);
+}  // namespace kbn
+
 extern "C" int kbn_ep_moe_forward(kbn_ep_ctx* c, const void* x_bf16, const int32_t* topk_ids, const float* topk_w, int64_t T,
                                   const void* w13, const float* w13_s, const void* w2, const float* w2_s,
                                   const void* w13_sf_packed, const void* w2_sf_packed, void* out_bf16, kbn_stream_t stream) {
+    using namespace kbn;
+    if (T > 0) KBN_REQUIRE(topk_ids && topk_w, KBN_ERR_ARG, "kbn_ep_moe_forward: null routing pointer");
+    return ep_forward(c, x_bf16, topk_ids, topk_w, nullptr, T, w13, w13_s, w2, w2_s, w13_sf_packed, w2_sf_packed, out_bf16, stream);
+}
+
+extern "C" int kbn_ep_moe_forward_routed(kbn_ep_ctx* c, const void* x_bf16, const void* logits, int logits_bf16, int64_t ld, int64_t T,
+                                         int softmax, const float* bias, int64_t n_group, int64_t topk_group, int renormalize,
+                                         float renorm_floor, float scale, int round_bf16, const void* w13, const float* w13_s,
+                                         const void* w2, const float* w2_s, const void* w13_sf_packed, const void* w2_sf_packed,
+                                         void* out_bf16, kbn_stream_t stream) {
+    using namespace kbn;
+    KBN_REQUIRE(c, KBN_ERR_ARG, "kbn_ep_moe_forward_routed: null context");
+    const int64_t E = c->experts_total, topk = c->topk;
+    if (T > 0) KBN_REQUIRE(logits, KBN_ERR_ARG, "kbn_ep_moe_forward_routed: null logits");
+    KBN_REQUIRE(E <= 32 * kRouteMaxPerLane && topk <= 32 && topk <= E, KBN_ERR_UNSUPPORTED, "kbn_ep_moe_forward_routed: at most %d experts and top-32",
+                32 * kRouteMaxPerLane);
+    KBN_REQUIRE(ld >= E, KBN_ERR_ARG, "kbn_ep_moe_forward_routed: row stride of the logits below E");
+    KBN_REQUIRE(n_group >= 1 && n_group <= 32 && E % n_group == 0 && topk_group >= 1 && topk_group <= n_group && topk <= topk_group * (E / n_group),
+                KBN_ERR_ARG, "kbn_ep_moe_forward_routed: n_group=%lld must divide E and be at most 32, topk_group=%lld in [1, n_group], with topk experts left",
+                (long long)n_group, (long long)topk_group);
+    EpRouteCall rc{RouteArgs{logits, ld, (int)E, softmax, bias, (int)n_group, (int)topk_group, (int)topk, renormalize, renorm_floor, scale, round_bf16},
+                   logits_bf16};
+    return ep_forward(c, x_bf16, nullptr, nullptr, &rc, T, w13, w13_s, w2, w2_s, w13_sf_packed, w2_sf_packed, out_bf16, stream);
+}
+
+extern "C" int kbn_ep_last_routing(kbn_ep_ctx* c, float* out_w, int32_t* out_ids, int64_t T, kbn_stream_t stream) {
+    using namespace kbn;
+    KBN_REQUIRE(c && out_w && out_ids && T >= 0 && T <= c->max_tokens, KBN_ERR_ARG, "kbn_ep_last_routing: bad arguments");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    KBN_CUDA(cudaMemcpyAsync(out_w, c->route_w, (size_t)(T * c->topk) * 4, cudaMemcpyDeviceToDevice, st));
+    KBN_CUDA(cudaMemcpyAsync(out_ids, c->route_ids, (size_t)(T * c->topk) * 4, cudaMemcpyDeviceToDevice, st));
+    return KBN_OK;
+}
+
+static int kbn::ep_forward(kbn_ep_ctx* c, const void* x_bf16, const int32_t* topk_ids, const float* topk_w, const EpRouteCall* route, int64_t T,
+                           const void* w13, const float* w13_s, const void* w2, const float* w2_s, const void* w13_sf_packed,
+                           const void* w2_sf_packed, void* out_bf16, kbn_stream_t stream) {
     using namespace kbn;
     KBN_REQUIRE(c, KBN_ERR_ARG, "kbn_ep_moe_forward: null context");
     KBN_REQUIRE(c->attached, KBN_ERR_ARG, "kbn_ep_moe_forward: peers not attached (call kbn_ep_attach)");
@@ -499,7 +576,8 @@ extern "C" int kbn_ep_moe_forward(kbn_ep_ctx* c, const void* x_bf16, const int32
     const bool ue8m0 = w13_sf_packed && w2_sf_packed;
     KBN_REQUIRE(w13 && w2 && (ue8m0 || (w13_s && w2_s)), KBN_ERR_ARG, "kbn_ep_moe_forward: null weight pointer");
     KBN_REQUIRE(!ue8m0 || c->max_m % 128 == 0, KBN_ERR_ARG, "kbn_ep_moe_forward: the UE8M0 path needs max_m to be a multiple of 128");
-    if (T > 0) KBN_REQUIRE(x_bf16 && topk_ids && topk_w && out_bf16, KBN_ERR_ARG, "kbn_ep_moe_forward: null pointer");
+    if (T > 0) KBN_REQUIRE(x_bf16 && out_bf16, KBN_ERR_ARG, "kbn_ep_moe_forward: null pointer");
+    if (route) topk_w = c->route_w;
     if (T > 0) KBN_REQUIRE(aligned16(x_bf16) && aligned16(out_bf16), KBN_ERR_ARG, "kbn_ep_moe_forward: x and out must be 16-byte aligned");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     int32_t* epoch = c->epoch;
@@ -510,10 +588,32 @@ extern "C" int kbn_ep_moe_forward(kbn_ep_ctx* c, const void* x_bf16, const int32
     const int32_t* flags_combine = reinterpret_cast<const int32_t*>(mine + c->lay.flags_combine);
     int rc;
     // 1. quantise + dispatch + signal (one block even with no tokens, so that peers are not left waiting)
-    const size_t dsmem = (size_t)H + 4 * (size_t)G + 4 * (size_t)c->topk;
-    ep_dispatch_quant_kernel<<<(unsigned)std::max<int64_t>(T, 1), 256, dsmem, st>>>(
-        static_cast<const __nv_bfloat16*>(x_bf16), topk_ids, (int)T, (int)c->topk, H, (int)c->e_local, (int)c->max_m, (int)c->experts_total,
-        c->peers, c->lay, c->rank, c->world, epoch, c->done, c->status, c->hooks, (int)c->n_hooks, c->trace);
+    const size_t dsmem = (size_t)H + 4 * (size_t)G + 8 * (size_t)c->topk;
+    const unsigned dgrid = (unsigned)std::max<int64_t>(T, 1);
+    const RouteArgs no_route{};
+#define KBN_EP_DISPATCH(P, B, RA, IDS)                                                                                              \
+    ep_dispatch_quant_kernel<P, B><<<dgrid, 256, dsmem, st>>>(static_cast<const __nv_bfloat16*>(x_bf16), IDS, RA, c->route_w, c->route_ids, \
+                                                              (int)T, (int)c->topk, H, (int)c->e_local, (int)c->max_m, (int)c->experts_total, \
+                                                              c->peers, c->lay, c->rank, c->world, epoch, c->done, c->status, c->hooks,      \
+                                                              (int)c->n_hooks, c->trace)
+    if (!route) {
+        KBN_EP_DISPATCH(0, false, no_route, topk_ids);
+    } else {
+        const int per = (int)((c->experts_total + 31) / 32);
+#define KBN_EP_ROUTED(P)                                                              \
+    do {                                                                              \
+        if (route->logits_bf16) KBN_EP_DISPATCH(P, true, route->args, nullptr);       \
+        else KBN_EP_DISPATCH(P, false, route->args, nullptr);                         \
+    } while (0)
+        if (per <= 1) KBN_EP_ROUTED(1);
+        else if (per <= 2) KBN_EP_ROUTED(2);
+        else if (per <= 4) KBN_EP_ROUTED(4);
+        else if (per <= 8) KBN_EP_ROUTED(8);
+        else if (per <= 16) KBN_EP_ROUTED(16);
+        else KBN_EP_ROUTED(32);
+#undef KBN_EP_ROUTED
+    }
+#undef KBN_EP_DISPATCH
     KBN_CHECK_LAUNCH();
     // 2. local experts on the received rows.  Rows per expert to expect if every rank brings as many tokens as this one and
     //    the routing is even: it decides the operand order of the masked GEMMs (few rows: weights as the M operand)
@@ -607,7 +707,7 @@ extern "C" int kbn_ep_destroy(kbn_ep_ctx* c) {
     for (int r = 0; r < c->world; ++r)
         if (r != c->rank && c->peers.base[r] && c->peers.base[r] != c->sym) cudaIpcCloseMemHandle(c->peers.base[r]);
     cudaFree(c->sym); cudaFree(c->mm1); cudaFree(c->a2_q); cudaFree(c->a2_s);
-    cudaFree(c->mm2); cudaFree(c->sf2); cudaFree(c->done); cudaFree(c->status); cudaFree(c->hooks); cudaFree(c->trace);
+    cudaFree(c->mm2); cudaFree(c->sf2); cudaFree(c->done); cudaFree(c->status); cudaFree(c->hooks); cudaFree(c->trace); cudaFree(c->route_w); cudaFree(c->route_ids);
     delete c;
     cudaGetLastError();        // a failed release must not surface as the next launch's error
     return KBN_OK;

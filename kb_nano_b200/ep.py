@@ -80,11 +80,7 @@ class EpMoe:
     def symmetric_bytes(self) -> int:
         return int(self._lib.kbn_ep_symmetric_bytes(self._ctx))
 
-    def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_w: torch.Tensor, w13: torch.Tensor, w13_s: torch.Tensor,
-                w2: torch.Tensor, w2_s: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-        """x bf16 [T,H] (this rank's tokens), topk_ids [T,topk] global expert ids, topk_w [T,topk];
-        w13/w2 (+ scales) of this rank's experts only -> bf16 [T,H]."""
-        t = x.shape[0]
+    def _check_operands(self, x, w13, w13_s, w2, w2_s):
         e_l = self.hi - self.lo
         if x.dtype != torch.bfloat16 or x.dim() != 2 or x.shape[1] != self.hidden or not x.is_contiguous():
             raise ValueError("x must be contiguous bf16 [T, hidden]")
@@ -95,6 +91,58 @@ class EpMoe:
         for s_, n_, k_ in ((w13_s, 2 * self.inter, self.hidden), (w2_s, self.hidden, self.inter)):
             if s_.dtype != torch.float32 or tuple(s_.shape) != (e_l, n_ // 128, k_ // 128) or not s_.is_contiguous():
                 raise ValueError("weight scales must be contiguous float32 [E/R, N/128, K/128]")
+
+    def _packed(self, w13_s, w2_s):
+        """(p13, p2) packed power-of-two weight scales (checked and packed once per tensor), or (None, None)."""
+        if self.use_ue8m0 and self.max_m % 128 == 0:
+            p13 = _ops.packed_weight_scales(w13_s, 2 * self.inter, self.hidden)
+            p2 = _ops.packed_weight_scales(w2_s, self.hidden, self.inter)
+            if p13 is not None and p2 is not None:
+                return p13, p2
+        return None, None
+
+    def forward_routed(self, x: torch.Tensor, router_logits: torch.Tensor, w13: torch.Tensor, w13_s: torch.Tensor, w2: torch.Tensor,
+                       w2_s: torch.Tensor, scoring: str = "softmax", bias: torch.Tensor | None = None, n_group: int = 1,
+                       topk_group: int = 1, renormalize: bool = True, renorm_floor: float = 0.0, scale: float = 1.0,
+                       round_bf16: bool = False, out: torch.Tensor | None = None) -> torch.Tensor:
+        """The layer from the router's logits [T, E] (fp32 or bf16): the dispatch kernel routes on the way (the arguments
+        and the arithmetic of ops.moe_route_topk), so the router adds no launch.  `last_routing` returns what it chose."""
+        t = x.shape[0]
+        self._check_operands(x, w13, w13_s, w2, w2_s)
+        if scoring not in ("softmax", "sigmoid"):
+            raise ValueError(f"unsupported scoring function {scoring!r}")
+        lg = router_logits
+        if lg.dim() != 2 or tuple(lg.shape) != (t, self.experts_total) or lg.dtype not in (torch.float32, torch.bfloat16) or lg.stride(1) != 1:
+            raise ValueError("router_logits must be fp32 or bf16 [T, experts], contiguous along the experts")
+        if lg.device != x.device:
+            raise ValueError("router_logits must be on x's device")
+        if bias is not None and (bias.dtype != torch.float32 or bias.numel() != self.experts_total or not bias.is_contiguous() or bias.device != x.device):
+            raise ValueError("bias must be contiguous float32 [experts] on x's device")
+        if out is None:
+            out = torch.empty(t, self.hidden, dtype=torch.bfloat16, device=x.device)
+        p13, p2 = self._packed(w13_s, w2_s)
+        with _on(self.device):
+            _lib.check(self._lib.kbn_ep_moe_forward_routed(
+                self._ctx, x.data_ptr(), lg.data_ptr(), int(lg.dtype == torch.bfloat16), lg.stride(0) if t > 1 else self.experts_total, t,
+                int(scoring == "softmax"), bias.data_ptr() if bias is not None else None, n_group, topk_group, int(renormalize), renorm_floor,
+                scale, int(round_bf16), w13.data_ptr(), w13_s.data_ptr(), w2.data_ptr(), w2_s.data_ptr(),
+                p13.data_ptr() if p13 is not None else None, p2.data_ptr() if p2 is not None else None, out.data_ptr(), _stream(x)))
+        return out
+
+    def last_routing(self, t: int) -> tuple[torch.Tensor, torch.Tensor]:
+        """(weights fp32 [t, topk], expert ids int32 [t, topk]) chosen by the last forward_routed call."""
+        w = torch.empty(t, self.topk, dtype=torch.float32, device=self.device)
+        ids = torch.empty(t, self.topk, dtype=torch.int32, device=self.device)
+        with _on(self.device):
+            _lib.check(self._lib.kbn_ep_last_routing(self._ctx, w.data_ptr(), ids.data_ptr(), t, torch.cuda.current_stream(self.device).cuda_stream))
+        return w, ids
+
+    def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_w: torch.Tensor, w13: torch.Tensor, w13_s: torch.Tensor,
+                w2: torch.Tensor, w2_s: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        """x bf16 [T,H] (this rank's tokens), topk_ids [T,topk] global expert ids, topk_w [T,topk];
+        w13/w2 (+ scales) of this rank's experts only -> bf16 [T,H]."""
+        t = x.shape[0]
+        self._check_operands(x, w13, w13_s, w2, w2_s)
         ids = topk_ids if topk_ids.dtype == torch.int32 else topk_ids.to(torch.int32)
         ids = ids if ids.is_contiguous() else ids.contiguous()
         w = topk_w if topk_w.dtype == torch.float32 else topk_w.float()
@@ -104,11 +152,8 @@ class EpMoe:
         if out is None:
             out = torch.empty(t, self.hidden, dtype=torch.bfloat16, device=x.device)
         # power-of-two weight scales (checked and packed once per tensor) take the UE8M0 GEMM path
-        p13 = p2 = None
-        if self.use_ue8m0 and self.max_m % 128 == 0:
-            p13 = _ops.packed_weight_scales(w13_s, 2 * self.inter, self.hidden)
-            p2 = _ops.packed_weight_scales(w2_s, self.hidden, self.inter)
-        fast = p13 is not None and p2 is not None
+        p13, p2 = self._packed(w13_s, w2_s)
+        fast = p13 is not None
         with _on(self.device):
             _lib.check(self._lib.kbn_ep_moe_forward(self._ctx, x.data_ptr(), ids.data_ptr(), w.data_ptr(), t, w13.data_ptr(),
                                                     w13_s.data_ptr(), w2.data_ptr(), w2_s.data_ptr(),

@@ -117,10 +117,7 @@ class _MoeBlock(nn.Module):
             self._ep_layer.close()
             self._ep_layer = None
 
-    def _run_experts(self, x: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor) -> torch.Tensor:
-        w13_s, w2_s = getattr(self, self._scale_names[0]), getattr(self, self._scale_names[1])
-        if self.ep_size == 1:
-            return _moe.fused_experts_fp8(x, self.w13, self.w2, topk_weights, topk_ids, self.num_experts, w13_s, w2_s)
+    def _ep(self, x: torch.Tensor) -> "_ep.EpMoe":
         t = x.shape[0]
         if t > self.ep_max_tokens:
             raise ValueError(f"{t} tokens in one call, the expert-parallel context holds {self.ep_max_tokens}: call configure_ep() "
@@ -129,7 +126,23 @@ class _MoeBlock(nn.Module):
             self._ep_layer = _ep.EpMoe(self.ep_rank, self.ep_size, self.num_experts, self.hidden_size, self.moe_intermediate,
                                        max_tokens=self.ep_max_tokens, topk=self.top_k, max_m=self.ep_max_m, group=self._group,
                                        device=x.device)
-        return self._ep_layer.forward(x, topk_ids, topk_weights, self.w13, w13_s, self.w2, w2_s)
+        return self._ep_layer
+
+    def _route_and_run(self, x: torch.Tensor, router_logits: torch.Tensor, **route) -> torch.Tensor:
+        """Router logits -> experts.  One rank: the routing kernel, then the single-GPU pipeline.  Several ranks: the
+        expert-parallel layer routes inside its dispatch kernel."""
+        if self.ep_size == 1:
+            tw, ti = _ops.moe_route_topk(router_logits, self.top_k, **route)
+            return self._run_experts(x, tw, ti)
+        w13_s, w2_s = getattr(self, self._scale_names[0]), getattr(self, self._scale_names[1])
+        lg = router_logits if router_logits.stride(-1) == 1 else router_logits.contiguous()
+        return self._ep(x).forward_routed(x, lg, self.w13, w13_s, self.w2, w2_s, **route)
+
+    def _run_experts(self, x: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor) -> torch.Tensor:
+        w13_s, w2_s = getattr(self, self._scale_names[0]), getattr(self, self._scale_names[1])
+        if self.ep_size == 1:
+            return _moe.fused_experts_fp8(x, self.w13, self.w2, topk_weights, topk_ids, self.num_experts, w13_s, w2_s)
+        return self._ep(x).forward(x, topk_ids, topk_weights, self.w13, w13_s, self.w2, w2_s)
 
     def forward(self, hidden_states: torch.Tensor) -> torch.Tensor:
         if self._use_custom_op:
@@ -168,8 +181,7 @@ class Qwen3MoE(_MoeBlock):
         x = x if x.is_contiguous() else x.contiguous()
         router_logits = self.gate(x)
         # TopKSoftmax (tasks/baseline/L1/topk_softmax.py:37-60): fp32 softmax, top-k, division by the sum clamped at 1e-20
-        tw, ti = _ops.moe_route_topk(router_logits, self.top_k, "softmax", renormalize=self.renormalize, renorm_floor=1e-20)
-        out = self._run_experts(x, tw, ti)
+        out = self._route_and_run(x, router_logits, scoring="softmax", renormalize=self.renormalize, renorm_floor=1e-20)
         return out.view(orig_shape)
 
 
@@ -280,10 +292,9 @@ class DeepSeekMoE(_MoeBlock):
         # (:143-147), fp32 router weights straight into the experts (:266-284)
         router_logits = F.linear(x, self.gate_weight)
         bias = self.e_score_correction_bias
-        tw, ti = _ops.moe_route_topk(router_logits, self.top_k, self.scoring_func, bias=bias.float().contiguous() if bias is not None else None,
-                                     n_group=self.n_group, topk_group=self.topk_group, renormalize=self.norm_topk_prob,
-                                     round_bf16=router_logits.dtype == torch.bfloat16)
-        out = self._run_experts(x, tw, ti)
+        out = self._route_and_run(x, router_logits, scoring=self.scoring_func, bias=bias.float().contiguous() if bias is not None else None,
+                                  n_group=self.n_group, topk_group=self.topk_group, renormalize=self.norm_topk_prob,
+                                  round_bf16=router_logits.dtype == torch.bfloat16)
         out = out * self.routed_scaling_factor               # after the experts (:293-295)
         if shared_out is not None:
             if side:

@@ -22,6 +22,11 @@ def ep_case(world, t_per_rank, h, i, e, topk, seed):
     return xs, routes, (w13_q, w13_s, w2_q, w2_s)
 
 
+def inputs_logits(rank, t, e, seed):
+    from kb_nano_b200 import inputs
+    return inputs.router_logits(t, e, seed=seed + rank)
+
+
 def test_ep_world1_matches_oracle(cuda_dev):
     from kb_nano_b200 import ep, ops
     t, h, i, e, topk = 96, 512, 256, 16, 4
@@ -149,6 +154,45 @@ def test_ep_host_pipeline_matches_forward(cuda_dev, depth, copy_streams):
     layer.close()
 
 
+@pytest.mark.parametrize("e,topk,scoring,n_group,topk_group,use_bias,bf16_logits", [
+    (16, 4, "softmax", 1, 1, False, False),          # TopKSoftmax-style routing (Qwen3 / Mixtral layers)
+    (64, 6, "sigmoid", 8, 3, True, True),            # GroupedTopK-style routing on bf16 logits (DeepSeek layer)
+    (256, 8, "sigmoid", 8, 4, True, False),
+])
+def test_ep_forward_routed_equals_route_then_forward(cuda_dev, e, topk, scoring, n_group, topk_group, use_bias, bf16_logits):
+    """Routing inside the dispatch kernel: the same choice as the stand-alone routing kernel, bit for bit, and the same
+    layer output as routing first and calling forward() with the result; also replayed from a CUDA graph."""
+    from kb_nano_b200 import ep, inputs, ops
+    t, h, i = 48, 512, 256
+    d = cuda_dev
+    x = inputs.activations(t, h, seed=1).to(d)
+    lg = inputs.router_logits(t, e, seed=2).to(d)
+    lg = lg.to(torch.bfloat16) if bf16_logits else lg
+    bias = (0.1 * torch.randn(e, generator=torch.Generator().manual_seed(3))).to(d) if use_bias else None
+    w13_q, w13_s = inputs.expert_weights(e, 2 * i, h, seed=4, std=0.05)
+    w2_q, w2_s = inputs.expert_weights(e, h, i, seed=5, std=0.05)
+    wd = [w.to(d) for w in (w13_q, w13_s, w2_q, w2_s)]
+    route = dict(scoring=scoring, bias=bias, n_group=n_group, topk_group=topk_group, renormalize=True, scale=1.5, round_bf16=bf16_logits)
+    tw, ti = ops.moe_route_topk(lg, topk, **route)
+    layer = ep.EpMoe(0, 1, e, h, i, max_tokens=64, topk=topk, max_m=128, device=d)
+    want = layer.forward(x, ti, tw, *wd).clone()
+    got = layer.forward_routed(x, lg, *wd, **route)
+    layer.check()
+    rw, ri = layer.last_routing(t)
+    assert torch.equal(ri, ti) and torch.equal(rw.view(torch.int32), tw.view(torch.int32))
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+    out = torch.empty_like(got)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        layer.forward_routed(x, lg, *wd, out=out, **route)
+    graph.replay()
+    layer.check()
+    assert torch.equal(out.view(torch.int16), want.view(torch.int16))
+    with pytest.raises(ValueError):
+        layer.forward_routed(x, lg[:, :8].contiguous(), *wd, **route)
+    layer.close()
+
+
 def test_ep_overflow_is_reported_not_fatal(cuda_dev):
     """More rows for one expert than max_m: the status word says so and the context stays usable."""
     from kb_nano_b200 import ep
@@ -218,6 +262,16 @@ def _ep_worker(rank, world, port, t, h, i, e, topk, seed, q):
             except AssertionError as ex:
                 ok, msg = False, str(ex)
                 break
+        if ok:
+            # routing inside the dispatch kernel, from the logits whose sigmoid top-k is this rank's routing (the router
+            # weights may differ from torch's in the last place, so the tolerance applies, not bit equality)
+            lg = inputs_logits(rank, t, e, seed).to(d)
+            got = layer.forward_routed(xs[rank].to(d), lg, *loc, scoring="sigmoid", renormalize=True)
+            try:
+                assert layer.status()["code"] == 0, layer.status()
+                assert_gemm_close(got.cpu(), ref, f"rank {rank} forward_routed")
+            except AssertionError as ex:
+                ok, msg = False, str(ex)
         if ok:
             # the same tokens through the one-GPU pipeline with all experts on this GPU: identical bits
             from kb_nano_b200 import moe
