@@ -117,7 +117,9 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                    const __grid_constant__ CUtensorMap tmA32, const __grid_constant__ CUtensorMap tmB, const GemmParams p,
                    const MxExtra x, const CombineEpilogue cb, const EpHooks h) {
     static_assert(!SWAP || BN == 256, "the swapped form uses 256 weight rows per tile");
-    if (h.tile_done != nullptr) ptx::launch_dependents();     // expert-parallel layer: the next kernel may come in under this one
+    // expert-parallel layer, dense linear layers: the next kernel of the stream may come in under this one (it waits
+    // for this grid's results itself before it reads them)
+    if (h.tile_done != nullptr || p.mode == kDense) ptx::launch_dependents();
     KBN_TRACE_MARK2(h.trace, h.epoch, EPI == kEpiCombine ? 2 : 1, 0);
     constexpr bool ACT = EPI == kEpiAct;
     constexpr int kBN = Cfg<BN>::kBN, kStages = Cfg<BN>::kStages, kStageBytes = Cfg<BN>::kStageBytes;
@@ -205,6 +207,9 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         TileWalk walk(p);
         Tile tile;
         uint32_t it = 0;
+        // dense form: launched while the kernel before it may still be running (programmatic stream serialisation); its
+        // results (the activations this kernel reads, the buffer it writes) are final once this returns
+        if (p.mode == kDense) ptx::grid_dependency_wait();
         uint32_t slot = 0, fills = 0;     // SWAP: next ring slot; bit s = parity of the number of fills of slot s
         int cur_cls = -1;                 // SWAP: how the ring is cut at the moment
         bool ok = true;
@@ -787,10 +792,22 @@ fp8_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 // leave most of the GPU idle and stream the weights through a handful of SMs.  Here the S CTAs of a
 // cluster share one output tile: CTA r accumulates K-blocks [r*KB/S, (r+1)*KB/S) in its own TMEM,
 // then the partial tiles are exchanged through distributed shared memory -- CTA o owns columns
-// [o*BN/S, (o+1)*BN/S) of the tile and receives every CTA's partial of that slice in the (by then
+// [o*BN/S, (o+1)*BN/S) of the tile and receives every other CTA's partial of that band in the (by then
 // idle) pipeline stages -- and each owner adds the S partials in rank order and stores bf16.  No
 // workspace, no atomics, and the result does not depend on timing.  One tile per cluster.
-constexpr int kSplitPad = 16;     // bytes added to a staged row so that 16-byte stores of a warp spread over the banks
+//
+// The exchange: a CTA stages the bands it does not own in its own shared memory (compact rows of BN/S floats,
+// the 16-byte units of a row XOR-swizzled by the row number so that a lane per row stores without bank conflicts)
+// and sends each to its owner as ONE bulk copy counted on the owner's barrier.  Stores or loads of the warps
+// straight into another CTA's shared memory were measured first: with a lane per row every lane's 16 bytes cross
+// the cluster network as a packet of their own, 0.2 to 0.4 us per warp instruction.
+// Shared memory: S-1 staged and S-1 received bands of ceil32(live rows) x BN/S floats, up to 224 KB (S = 8, 256
+// columns, 128 rows), so the barriers sit behind that area and not behind the pipeline stages.
+constexpr int kSplitXchgBytes = 2 * 7 * kBlockM * (256 / 8) * 4;                 // 229,376
+constexpr size_t kSplitSmemBytes = 1024 + kSplitXchgBytes + 256;
+static_assert(kSplitSmemBytes <= 232448, "split-K exchange area exceeds the shared memory of an SM");
+static_assert((size_t)Cfg<256>::kStages * (Cfg<256>::kStageBytes + Cfg<256>::kSfStage) <= kSplitXchgBytes &&
+              (size_t)Cfg<128>::kStages * (Cfg<128>::kStageBytes + Cfg<128>::kSfStage) <= kSplitXchgBytes, "pipeline overlaps the barriers");
 
 template <int BN>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -799,18 +816,29 @@ fp8_gemm_mx_splitk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
                           const GemmParams p, const MxExtra x, const int S) {
     constexpr int kBN = Cfg<BN>::kBN, kStages = Cfg<BN>::kStages, kStageBytes = Cfg<BN>::kStageBytes;
     constexpr int kSfbBytes = Cfg<BN>::kSfbBytes, kSfStage = Cfg<BN>::kSfStage, kTxBytes = Cfg<BN>::kTxBytes;
-    constexpr int kHalfCols = BN / 2;
+    ptx::launch_dependents();      // the next kernel of the stream may come in under this one; it waits before it reads
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~(uintptr_t)1023u);
     uint8_t* sf_smem = smem + (size_t)kStages * kStageBytes;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sf_smem + (size_t)kStages * kSfStage);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kSplitXchgBytes);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t bar_full = ptx::smem_u32(bars), bar_empty = ptx::smem_u32(bars + kStages);
     const uint32_t bar_tfull = ptx::smem_u32(bars + 2 * kStages);
+    const uint32_t bar_xchg = ptx::smem_u32(bars + 2 * kStages + 1);       // the other CTAs' partials have arrived
     const uint32_t smem_tiles = ptx::smem_u32(smem), smem_sf = ptx::smem_u32(sf_smem);
+
+    const uint32_t rank = ptx::cluster_ctarank();
+    const int32_t cid = (int32_t)(blockIdx.x / (uint32_t)S);
+    const int32_t m_blk = cid % p.num_m_blocks, n_blk = cid / p.num_m_blocks;
+    const int32_t row0 = m_blk * kBlockM;
+    const int32_t live = min(p.rows_total - row0, kBlockM);                 // the same in every CTA of the cluster
+    const int32_t kbs = (p.num_k_blocks + S - 1) / S;
+    const int32_t kb0 = (int32_t)rank * kbs, kb1 = min(p.num_k_blocks, kb0 + kbs);     // host guarantees kb0 < kb1
+    const int W = kBN / S;                                                   // columns per owner (a multiple of 32)
+    const uint32_t slot_bytes = (uint32_t)((live + 31) & ~31) * (uint32_t)W * 4u;    // one band: whole lane quarters of rows
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -818,6 +846,8 @@ fp8_gemm_mx_splitk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
             ptx::mbar_init(bar_empty + 8 * s, 1);
         }
         ptx::mbar_init(bar_tfull, 1);
+        ptx::mbar_init(bar_xchg, 1);
+        ptx::mbar_arrive_expect_tx(bar_xchg, (uint32_t)(S - 1) * slot_bytes);
         *abort_flag = 0;
         ptx::fence_barrier_init();
         ptx::fence_proxy_async();
@@ -831,14 +861,6 @@ fp8_gemm_mx_splitk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    const uint32_t rank = ptx::cluster_ctarank();
-    const int32_t cid = (int32_t)(blockIdx.x / (uint32_t)S);
-    const int32_t m_blk = cid % p.num_m_blocks, n_blk = cid / p.num_m_blocks;
-    const int32_t row0 = m_blk * kBlockM;
-    const int32_t live = min(p.rows_total - row0, kBlockM);
-    const int32_t kbs = (p.num_k_blocks + S - 1) / S;
-    const int32_t kb0 = (int32_t)rank * kbs, kb1 = min(p.num_k_blocks, kb0 + kbs);     // host guarantees kb0 < kb1
-
     if (warp == 0) {
         if (lane == 0) {
             ptx::prefetch_tensormap(&tmA);
@@ -850,8 +872,25 @@ fp8_gemm_mx_splitk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
             const uint8_t* sfb = x.sfb + (int64_t)(BN / 128) * n_blk * kSfaBytes;
             const CUtensorMap* tma = live <= 32 ? &tmA32 : (live <= 64 ? &tmA64 : &tmA);
             const uint32_t tx = (uint32_t)(kTxBytes - kABytes) + (live <= 32 ? 32u : (live <= 64 ? 64u : 128u)) * (uint32_t)kBlockK;
-            uint32_t it = 0;
-            for (int kb = kb0; kb < kb1; ++kb, ++it) {
+            // This grid may have been launched while the kernel before it still runs (programmatic stream serialisation).
+            // The weights do not depend on it: the first ring-full of weight tiles and weight scales is requested at once;
+            // the activations and their scales follow when that kernel's results are final.  A stage's barrier expects
+            // all four copies from the start, so it completes only when the late ones have landed too.
+            const int pre = min(kb1 - kb0, kStages);
+            for (int i = 0; i < pre; ++i) {
+                const uint32_t bar = bar_full + 8 * i;
+                ptx::mbar_arrive_expect_tx(bar, tx);
+                ptx::tma_load_2d(smem_tiles + i * kStageBytes + kABytes, &tmB, (kb0 + i) * kBlockK, n_blk * kBN, bar);
+                ptx::bulk_load(smem_sf + i * kSfStage + kSfaBytes, sfb + (int64_t)(kb0 + i) * x.nb_pad * kSfaBytes, kSfbBytes, bar);
+            }
+            ptx::grid_dependency_wait();
+            for (int i = 0; i < pre; ++i) {
+                const uint32_t bar = bar_full + 8 * i;
+                ptx::tma_load_2d(smem_tiles + i * kStageBytes, tma, (kb0 + i) * kBlockK, row0, bar);
+                ptx::bulk_load(smem_sf + i * kSfStage, sfa + (int64_t)(kb0 + i) * kSfaBytes, kSfaBytes, bar);
+            }
+            uint32_t it = (uint32_t)pre;
+            for (int kb = kb0 + pre; kb < kb1; ++kb, ++it) {
                 const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
                 if (!wait_bar(bar_empty + 8 * s, ph ^ 1u, w)) break;
                 const uint32_t bar = bar_full + 8 * s;
@@ -897,82 +936,393 @@ fp8_gemm_mx_splitk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
         ptx::tc_fence_after();
     }
     __syncwarp();
-    ptx::cluster_sync();          // every CTA of the cluster is done with its stages: they may now be overwritten
+    // Every CTA of the cluster is done with its stages (they may now be overwritten) and has armed its exchange barrier.
+    ptx::cluster_sync();
 
-    // ---- exchange: this CTA's partial of slice o goes to CTA o, slot [rank] ----
-    const int W = kBN / S;                                  // columns per owner (a multiple of 32)
-    const uint32_t pitch = (uint32_t)W * 4u + kSplitPad;    // bytes per staged row
-    if (warp >= 2) {
-        const int quarter = warp & 3;
-        const int half = (warp - 2) >> 2;
-        const int r_in_tile = quarter * 32 + lane;
-        if (quarter * 32 < live) {                           // warp-uniform: some row of this quarter holds data
-            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + half * kHalfCols;
-            constexpr int kChunks = kHalfCols / 32;
+    // ---- exchange: the bands this CTA does not own are staged and sent; the two warps of a lane quarter take the even
+    //      and the odd 32-column chunks of the row ----
+    const uint32_t units = (uint32_t)W / 4u;                 // 16-byte units per staged row: 8, 16 or 32
+    const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const int r_in_tile = quarter * 32 + lane;
+    const uint32_t swz = (uint32_t)r_in_tile & (units - 1u);
+    const bool quarter_live = warp >= 2 && quarter * 32 < live;     // warp-uniform: some row of this quarter holds data
+    if (quarter_live) {
+#pragma unroll 1
+        for (int cc = half; cc < kBN / 32; cc += 2) {
+            const int col = 32 * cc;
+            const uint32_t o = (uint32_t)(col / W);
+            if (o == rank) continue;
+            uint32_t r[32];
+            ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + col, r);
+            ptx::tmem_ld_wait(r);
+            const uint32_t send_slot = o < rank ? o : o - 1u;
+            const uint32_t row_base = smem_tiles + send_slot * slot_bytes + (uint32_t)r_in_tile * (uint32_t)W * 4u;
+            const uint32_t u0 = (uint32_t)(col % W) / 4u;
 #pragma unroll
-            for (int c = 0; c < kChunks; ++c) {
-                uint32_t r[32];
-                ptx::tmem_ld_32x32(taddr + 32 * c, r);
-                ptx::tmem_ld_wait(r);
-                const int col = half * kHalfCols + 32 * c;   // first column of the chunk within the tile
-                const uint32_t owner = (uint32_t)(col / W);
-                const uint32_t local = smem_tiles + (rank * (uint32_t)kBlockM + (uint32_t)r_in_tile) * pitch + (uint32_t)(col % W) * 4u;
-                const uint32_t remote = ptx::mapa(local, owner);
-                if (r_in_tile < live) {
-#pragma unroll
-                    for (int j = 0; j < 32; j += 4) ptx::st_cluster_v4(remote + 4u * j, r[j], r[j + 1], r[j + 2], r[j + 3]);
-                }
-            }
+            for (int j = 0; j < 8; ++j)
+                ptx::st_shared_v4(row_base + (((u0 + (uint32_t)j) ^ swz) << 4), r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
         }
-        ptx::tc_fence_before();
+        ptx::fence_proxy_async();                            // the staged rows are read by the bulk copies below
     }
-    __syncwarp();
-    ptx::cluster_sync();          // all partials have arrived
-
-    // ---- reduce this CTA's slice in rank order and store ----
+    __syncthreads();
+    if (threadIdx.x == 64) {
+        for (uint32_t o = 0; o < (uint32_t)S; ++o) {
+            if (o == rank) continue;
+            const uint32_t send_slot = o < rank ? o : o - 1u, recv_slot = rank < o ? rank : rank - 1u;
+            ptx::bulk_copy_to_cluster(ptx::mapa(smem_tiles + ((uint32_t)(S - 1) + recv_slot) * slot_bytes, o),
+                                      smem_tiles + send_slot * slot_bytes, slot_bytes, ptx::mapa(bar_xchg, o));
+        }
+    }
     if (warp >= 2) {
-        const int e = (int)threadIdx.x - 64;                 // 0..255
-        const int row = e & 127, hsel = e >> 7;
-        const int cols = W / 2;                              // columns per thread (a multiple of 16)
-        const int c_in = hsel * cols;
-        const int32_t n0 = n_blk * kBN + (int32_t)rank * W + c_in;
-        if (row < live && *abort_flag == 0) {
-            __nv_bfloat16* crow = p.C + (int64_t)(row0 + row) * p.ldc + n0;
-            const bool vec_ok = (reinterpret_cast<uintptr_t>(crow) & 15u) == 0;
-            for (int j = 0; j < cols; j += 8) {
-                float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0;
-                for (int s = 0; s < S; ++s) {
-                    const uint32_t src = smem_tiles + ((uint32_t)s * (uint32_t)kBlockM + (uint32_t)row) * pitch + (uint32_t)(c_in + j) * 4u;
-                    const float4 v0 = ptx::ld_shared_v4(src), v1 = ptx::ld_shared_v4(src + 16u);
-                    a0.x += v0.x; a0.y += v0.y; a0.z += v0.z; a0.w += v0.w;
-                    a1.x += v1.x; a1.y += v1.y; a1.z += v1.z; a1.w += v1.w;
+        WaitCtx w{abort_flag, p.status, 7};
+        wait_bar(bar_xchg, 0u, w);
+    }
+
+    // ---- the owned band: the S partials added in rank order (this CTA's own from tensor memory), bias, bf16 ----
+    if (quarter_live) {
+#pragma unroll 1
+        for (int cc = half; cc < kBN / 32; cc += 2) {
+            const int col = 32 * cc;
+            if ((uint32_t)(col / W) != rank) continue;
+            uint32_t r[32];
+            ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + col, r);
+            ptx::tmem_ld_wait(r);
+            if (r_in_tile < live && *abort_flag == 0) {
+                const int32_t n0 = n_blk * kBN + col;
+                __nv_bfloat16* crow = p.C + (int64_t)(row0 + r_in_tile) * p.ldc + n0;
+                const bool vec_ok = (reinterpret_cast<uintptr_t>(crow) & 15u) == 0;
+                float f[32];
+#pragma unroll
+                for (int q = 0; q < 32; ++q) f[q] = 0.f;
+                const uint32_t u0 = (uint32_t)(col % W) / 4u;
+                for (uint32_t sl = 0; sl < (uint32_t)S; ++sl) {
+                    if (sl == rank) {
+#pragma unroll
+                        for (int q = 0; q < 32; ++q) f[q] += __uint_as_float(r[q]);
+                        continue;
+                    }
+                    const uint32_t recv_slot = sl < rank ? sl : sl - 1u;
+                    const uint32_t row_base = smem_tiles + ((uint32_t)(S - 1) + recv_slot) * slot_bytes + (uint32_t)r_in_tile * (uint32_t)W * 4u;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const float4 v = ptx::ld_shared_v4(row_base + (((u0 + (uint32_t)i) ^ swz) << 4));
+                        f[4 * i + 0] += v.x; f[4 * i + 1] += v.y; f[4 * i + 2] += v.z; f[4 * i + 3] += v.w;
+                    }
                 }
                 if (p.bias != nullptr) {
-                    float* af[8] = {&a0.x, &a0.y, &a0.z, &a0.w, &a1.x, &a1.y, &a1.z, &a1.w};
 #pragma unroll
-                    for (int q = 0; q < 8; ++q)
-                        if (n0 + j + q < p.N) *af[q] += __bfloat162float(p.bias[n0 + j + q]);
+                    for (int q = 0; q < 32; ++q)
+                        if (n0 + q < p.N) f[q] += __bfloat162float(p.bias[n0 + q]);
                 }
-                if (n0 + j + 8 <= p.N && vec_ok) {
-                    uint4 v;
-                    v.x = pack_bf16x2(a0.x, a0.y); v.y = pack_bf16x2(a0.z, a0.w);
-                    v.z = pack_bf16x2(a1.x, a1.y); v.w = pack_bf16x2(a1.z, a1.w);
-                    *reinterpret_cast<uint4*>(crow + j) = v;
-                } else {
-                    const float f[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
 #pragma unroll
-                    for (int q = 0; q < 8; ++q)
-                        if (n0 + j + q < p.N) crow[j + q] = __float2bfloat16_rn(f[q]);
+                for (int j = 0; j < 32; j += 8) {
+                    if (n0 + j + 8 <= p.N && vec_ok) {
+                        uint4 v;
+                        v.x = pack_bf16x2(f[j + 0], f[j + 1]); v.y = pack_bf16x2(f[j + 2], f[j + 3]);
+                        v.z = pack_bf16x2(f[j + 4], f[j + 5]); v.w = pack_bf16x2(f[j + 6], f[j + 7]);
+                        *reinterpret_cast<uint4*>(crow + j) = v;
+                    } else {
+#pragma unroll
+                        for (int q = 0; q < 8; ++q)
+                            if (n0 + j + q < p.N) crow[j + q] = __float2bfloat16_rn(f[j + q]);
+                    }
                 }
             }
         }
     }
 
     ptx::tc_fence_before();
-    __syncthreads();
+    __syncwarp();
+    // No CTA leaves while a copy out of its shared memory may still be in flight: every owner has seen its barrier
+    // complete, i.e. every copy into it has landed, before it arrives here.
+    ptx::cluster_sync();
     if (warp == 1) {
         ptx::tc_fence_after();
         ptx::tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// ---- CTA pairs: 256 x 256 output tiles on two SMs (cta_group::2), K split over the cluster ----------------
+//
+// The dense problems of a linear layer with a few hundred rows are bound by what an SM can pull from L2 per
+// clock: a 128 x 256 tile moves 48 KB of operands per 128 of K.  Here two CTAs with consecutive cluster ranks share
+// a 256 x 256 tile: each loads its own 128 rows of A and HALF of the tile's 256 weight rows (32 KB per 128 of K and
+// SM), and one tcgen05.mma.cta_group::2 issued by the even CTA multiplies the pair's 256 rows by all 256 weight
+// rows, reading the other half of B from the partner's shared memory; each CTA's tensor memory ends up with its
+// own 128 x 256 accumulator.  Every copy is a plain 2-D tiled TMA load into the issuing CTA's own shared memory
+// (no multicast); its bytes are counted on the even CTA's barrier, which the even CTA arms for both.  The scales
+// travel as 2-D tiles too (the packed arrays seen as rows of 128 words): the CTA's own row block for A, both
+// 128-column blocks for B, copied to tensor memory in both CTAs by one tcgen05.cp.cta_group::2.  The S K-slices
+// of the cluster (S = 2 or 4; ranks 2k and 2k+1 form slice k) then reduce their partial tiles: slice k owns the
+// k-th band of 256/S columns and receives the other slices' partials of that band in its shared memory.
+struct PairCfg {
+    static constexpr int kBN = 256;
+    static constexpr int kStages = 6;
+    static constexpr int kBHalf = (kBN / 2) * kBlockK;             // this CTA's half of the B tile
+    static constexpr int kStageBytes = kABytes + kBHalf;           // 32 KB
+    static constexpr int kSfStage = 512 + 512 * (kBN / 128);       // own A scale block, the tile's two B scale blocks
+    static constexpr uint32_t kTxPair = 2u * (uint32_t)(kStageBytes + kSfStage);
+    static constexpr size_t kSmemBytes = (size_t)kStages * (kStageBytes + kSfStage) + 1024 + 256;
+    // the exchange reuses the pipeline stages: S-1 staged and S-1 received partial bands of 128 x 256/S floats
+    static_assert(2 * 3 * kBlockM * (kBN / 4) * 4 <= kStages * kStageBytes && 2 * kBlockM * (kBN / 2) * 4 <= kStages * kStageBytes,
+                  "partial bands do not fit the pipeline stages");
+};
+
+#ifdef KBN_TRACE
+__device__ unsigned long long g_pair_trace[256][16];
+#define KBN_PT(slot) do { if (lane == 0 && blockIdx.x < 256) g_pair_trace[blockIdx.x][slot] = trace_now(); } while (0)
+#else
+#define KBN_PT(slot) do { } while (0)
+#endif
+
+__global__ void __launch_bounds__(kThreads, 1)
+fp8_gemm_mx_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                        const __grid_constant__ CUtensorMap tmSfa, const __grid_constant__ CUtensorMap tmSfb, const GemmParams p,
+                        const int32_t nb_pad, const int S) {
+    constexpr int kStages = PairCfg::kStages, kStageBytes = PairCfg::kStageBytes, kSfStage = PairCfg::kSfStage, kBN = PairCfg::kBN;
+    ptx::launch_dependents();      // the next kernel of the stream may come in under this one; it waits before it reads
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~(uintptr_t)1023u);
+    uint8_t* sf_smem = smem + (size_t)kStages * kStageBytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sf_smem + (size_t)kStages * kSfStage);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t bar_full = ptx::smem_u32(bars), bar_empty = ptx::smem_u32(bars + kStages);
+    const uint32_t bar_tfull = ptx::smem_u32(bars + 2 * kStages);
+    const uint32_t bar_xchg = ptx::smem_u32(bars + 2 * kStages + 1);       // the other slices' partials have arrived
+    const uint32_t smem_tiles = ptx::smem_u32(smem), smem_sf = ptx::smem_u32(sf_smem);
+
+    if (warp == 2) KBN_PT(0);
+    const uint32_t rank = ptx::cluster_ctarank();
+    const uint32_t pr = rank & 1u, ks = rank >> 1;          // place in the pair, K-slice
+    const uint32_t leader = rank & ~1u;                      // the even CTA of the pair issues the MMAs
+    const uint16_t pair_mask = (uint16_t)(3u << leader);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            ptx::mbar_init(bar_full + 8 * s, 1);             // armed by the even CTA's producer, bytes from both CTAs
+            ptx::mbar_init(bar_empty + 8 * s, 1);            // one commit, delivered to both CTAs
+        }
+        ptx::mbar_init(bar_tfull, 1);
+        ptx::mbar_init(bar_xchg, 1);
+        ptx::mbar_arrive_expect_tx(bar_xchg, (uint32_t)(S - 1) * (uint32_t)(kBlockM * (kBN / S) * 4));
+        *abort_flag = 0;
+        ptx::fence_barrier_init();
+        ptx::fence_proxy_async();
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc_pair(ptx::smem_u32(tmem_slot), kTmemCols);
+        ptx::tmem_relinquish_pair();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::cluster_sync();           // the partner's barriers exist before anything is sent to them
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    if (warp == 2) KBN_PT(1);
+
+    const int32_t cid = (int32_t)(blockIdx.x / (uint32_t)(2 * S));
+    const int32_t m_pairs = (p.rows_total + 255) / 256;
+    const int32_t m_pair = cid % m_pairs, n_blk = cid / m_pairs;
+    const int32_t row0 = m_pair * 256 + (int32_t)pr * kBlockM;
+    const int32_t live = max(0, min(p.rows_total - row0, kBlockM));
+    const int32_t kbs = (p.num_k_blocks + S - 1) / S;
+    const int32_t kb0 = (int32_t)ks * kbs, kb1 = min(p.num_k_blocks, kb0 + kbs);     // host guarantees kb0 < kb1
+
+    if (warp == 0) {
+        if (lane == 0) {
+            ptx::prefetch_tensormap(&tmA);
+            ptx::prefetch_tensormap(&tmB);
+            ptx::prefetch_tensormap(&tmSfa);
+            ptx::prefetch_tensormap(&tmSfb);
+            WaitCtx w{abort_flag, p.status, 4};
+            // The weights and their scales do not depend on the kernel before this one: the first ring-full is requested at
+            // once.  The even CTA arms each stage's barrier for all eight copies of the pair, so a stage completes only
+            // when the activations, requested after the wait below, have landed too.
+            const int pre = min(kb1 - kb0, kStages);
+            for (int i = 0; i < pre; ++i) {
+                if (pr == 0) ptx::mbar_arrive_expect_tx(bar_full + 8 * i, PairCfg::kTxPair);
+                const uint32_t bar = ptx::mapa(bar_full + 8 * i, leader);
+                ptx::tma_load_2d_pair(smem_tiles + i * kStageBytes + kABytes, &tmB, (kb0 + i) * kBlockK, n_blk * kBN + (int32_t)pr * (kBN / 2), bar);
+                ptx::tma_load_2d_pair(smem_sf + i * kSfStage + 512, &tmSfb, 0, (kb0 + i) * nb_pad + (kBN / 128) * n_blk, bar);
+            }
+            // results of the kernel before this one (the activations, the output buffer) are final from here on
+            ptx::grid_dependency_wait();
+            KBN_PT(2);
+            for (int i = 0; i < pre; ++i) {
+                const uint32_t bar = ptx::mapa(bar_full + 8 * i, leader);
+                ptx::tma_load_2d_pair(smem_tiles + i * kStageBytes, &tmA, (kb0 + i) * kBlockK, row0, bar);
+                ptx::tma_load_2d_pair(smem_sf + i * kSfStage, &tmSfa, 0, (row0 / kBlockM) * p.num_k_blocks + kb0 + i, bar);
+            }
+            uint32_t it = (uint32_t)pre;
+            for (int kb = kb0 + pre; kb < kb1; ++kb, ++it) {
+                const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+                if (!wait_bar(bar_empty + 8 * s, ph ^ 1u, w)) break;
+                if (pr == 0) ptx::mbar_arrive_expect_tx(bar_full + 8 * s, PairCfg::kTxPair);
+                const uint32_t bar = ptx::mapa(bar_full + 8 * s, leader);
+                const uint32_t dst = smem_tiles + s * kStageBytes;
+                ptx::tma_load_2d_pair(dst, &tmA, kb * kBlockK, row0, bar);
+                ptx::tma_load_2d_pair(dst + kABytes, &tmB, kb * kBlockK, n_blk * kBN + (int32_t)pr * (kBN / 2), bar);
+                const uint32_t sdst = smem_sf + s * kSfStage;
+                ptx::tma_load_2d_pair(sdst, &tmSfa, 0, (row0 / kBlockM) * p.num_k_blocks + kb, bar);
+                ptx::tma_load_2d_pair(sdst + 512, &tmSfb, 0, kb * nb_pad + (kBN / 128) * n_blk, bar);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && pr == 0) {
+            WaitCtx w{abort_flag, p.status, 5};
+            constexpr uint32_t idesc = ptx::umma_idesc_mx_e4m3(256, kBN, 0, 0);
+            uint32_t it = 0;
+            bool ok = true;
+            for (int kb = kb0; kb < kb1; ++kb, ++it) {
+                const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+                if (!wait_bar(bar_full + 8 * s, ph, w)) { ok = false; break; }
+                if (it == 0) KBN_PT(3);
+                ptx::tc_fence_after();
+                const uint32_t a_addr = smem_tiles + s * kStageBytes;
+                const uint32_t sf_addr = smem_sf + s * kSfStage;
+                ptx::tmem_cp_32x128b_warpx4_pair(tmem_base + kColSfa, ptx::umma_desc_sf(sf_addr));
+                ptx::tmem_cp_32x128b_warpx4_pair(tmem_base + kColSfb, ptx::umma_desc_sf(sf_addr + 512));
+                ptx::tmem_cp_32x128b_warpx4_pair(tmem_base + kColSfb + 4, ptx::umma_desc_sf(sf_addr + 1024));
+                const uint64_t a_desc = ptx::umma_desc_k_sw128(a_addr);
+                const uint64_t b_desc = ptx::umma_desc_k_sw128(a_addr + kABytes);
+#pragma unroll
+                for (int k = 0; k < kBlockK / 32; ++k)
+                    ptx::mma_mxf8f6f4_block_scale_pair(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc, tmem_base + kColSfa,
+                                                       tmem_base + kColSfb, (kb > kb0 || k > 0) ? 1u : 0u);
+                ptx::mma_commit_pair(bar_empty + 8 * s, pair_mask);
+            }
+            if (ok) ptx::mma_commit_pair(bar_tfull, pair_mask);
+        }
+    } else {
+        // all MMAs of the pair have finished (and with them every read of the pipeline stages of both CTAs)
+        WaitCtx w{abort_flag, p.status, 6};
+        wait_bar(bar_tfull, 0u, w);
+        ptx::tc_fence_after();
+        if (warp == 2) KBN_PT(4);
+    }
+    __syncwarp();
+    ptx::cluster_sync();          // every CTA of the cluster is done with its stages: they may now be overwritten
+    if (warp == 2) KBN_PT(5);
+
+    const int W = kBN / S;                                  // columns per owner
+    {
+        // ---- exchange: the partials of the column slices this CTA does not own are staged in its own shared memory
+        //      (compact rows of W floats, 16-byte units XOR-swizzled by the row so that a lane per row stores without
+        //      bank conflicts) and go to their owners -- the CTA of slice o in the same place of its pair -- as ONE bulk
+        //      copy each, counted on the owner's barrier.  (Remote stores and remote loads from the warps were tried
+        //      first: a strided 16-byte access per lane crosses the cluster network one small packet at a time, 0.2 to
+        //      0.4 us per warp instruction.)  The CTA's own slice stays in tensor memory.  The two warps of a lane quarter
+        //      take the even and the odd 32-column chunks of the row. ----
+        const uint32_t slot_bytes = (uint32_t)(kBlockM * W * 4);
+        const uint32_t units = (uint32_t)W / 4u;             // 16-byte units per staged row (32, 16 or 8... a power of two)
+        const int quarter = warp & 3;
+        const int half = (warp - 2) >> 2;
+        const int r_in_tile = quarter * 32 + lane;
+        const uint32_t swz = (uint32_t)r_in_tile & (units - 1u);
+        if (warp >= 2) {
+#pragma unroll 1
+            for (int cc = half; cc < kBN / 32; cc += 2) {
+                const int col = 32 * cc;
+                const uint32_t o = (uint32_t)(col / W);
+                if (o == ks) continue;
+                uint32_t r[32];
+                ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + col, r);
+                ptx::tmem_ld_wait(r);
+                if (warp == 2) KBN_PT(8);
+                const uint32_t send_slot = o < ks ? o : o - 1u;
+                const uint32_t row_base = smem_tiles + send_slot * slot_bytes + (uint32_t)r_in_tile * (uint32_t)W * 4u;
+                const uint32_t u0 = (uint32_t)(col % W) / 4u;
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    ptx::st_shared_v4(row_base + (((u0 + (uint32_t)j) ^ swz) << 4), r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+            }
+            ptx::fence_proxy_async();                        // the staged rows are read by the bulk copies below
+        }
+        if (warp == 2) KBN_PT(9);
+        __syncthreads();
+        if (threadIdx.x == 64) {
+            for (uint32_t o = 0; o < (uint32_t)S; ++o) {
+                if (o == ks) continue;
+                const uint32_t send_slot = o < ks ? o : o - 1u, recv_slot = ks < o ? ks : ks - 1u;
+                const uint32_t owner = (o << 1) | pr;
+                ptx::bulk_copy_to_cluster(ptx::mapa(smem_tiles + ((uint32_t)(S - 1) + recv_slot) * slot_bytes, owner),
+                                          smem_tiles + send_slot * slot_bytes, slot_bytes, ptx::mapa(bar_xchg, owner));
+            }
+        }
+        if (warp == 2) KBN_PT(10);
+        if (warp >= 2) {
+            WaitCtx w{abort_flag, p.status, 7};
+            wait_bar(bar_xchg, 0u, w);
+        }
+        if (warp == 2) KBN_PT(6);
+        // ---- the owned band: the S partials added in slice order (this CTA's own from tensor memory) ----
+        if (warp >= 2 && quarter * 32 < live) {
+#pragma unroll 1
+            for (int cc = half; cc < kBN / 32; cc += 2) {
+                const int col = 32 * cc;
+                if ((uint32_t)(col / W) != ks) continue;
+                uint32_t r[32];
+                ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + col, r);
+                ptx::tmem_ld_wait(r);
+                if (r_in_tile < live && *abort_flag == 0) {
+                    const int32_t n0 = n_blk * kBN + col;
+                    __nv_bfloat16* crow = p.C + (int64_t)(row0 + r_in_tile) * p.ldc + n0;
+                    const bool vec_ok = (reinterpret_cast<uintptr_t>(crow) & 15u) == 0;
+                    float f[32];
+#pragma unroll
+                    for (int q = 0; q < 32; ++q) f[q] = 0.f;
+                    const uint32_t u0 = (uint32_t)(col % W) / 4u;
+                    for (uint32_t sl = 0; sl < (uint32_t)S; ++sl) {
+                        if (sl == ks) {
+#pragma unroll
+                            for (int q = 0; q < 32; ++q) f[q] += __uint_as_float(r[q]);
+                            continue;
+                        }
+                        const uint32_t recv_slot = sl < ks ? sl : sl - 1u;
+                        const uint32_t row_base = smem_tiles + ((uint32_t)(S - 1) + recv_slot) * slot_bytes + (uint32_t)r_in_tile * (uint32_t)W * 4u;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const float4 v = ptx::ld_shared_v4(row_base + (((u0 + (uint32_t)i) ^ swz) << 4));
+                            f[4 * i + 0] += v.x; f[4 * i + 1] += v.y; f[4 * i + 2] += v.z; f[4 * i + 3] += v.w;
+                        }
+                    }
+                    if (p.bias != nullptr) {
+#pragma unroll
+                        for (int q = 0; q < 32; ++q)
+                            if (n0 + q < p.N) f[q] += __bfloat162float(p.bias[n0 + q]);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 32; j += 8) {
+                        if (n0 + j + 8 <= p.N && vec_ok) {
+                            uint4 v;
+                            v.x = pack_bf16x2(f[j + 0], f[j + 1]); v.y = pack_bf16x2(f[j + 2], f[j + 3]);
+                            v.z = pack_bf16x2(f[j + 4], f[j + 5]); v.w = pack_bf16x2(f[j + 6], f[j + 7]);
+                            *reinterpret_cast<uint4*>(crow + j) = v;
+                        } else {
+#pragma unroll
+                            for (int q = 0; q < 8; ++q)
+                                if (n0 + j + q < p.N) crow[j + q] = __float2bfloat16_rn(f[j + q]);
+                        }
+                    }
+                }
+            }
+        }
+        if (warp >= 2) ptx::tc_fence_before();
+        if (warp == 2) KBN_PT(11);
+    }
+
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 2) KBN_PT(12);
+    ptx::cluster_sync();          // neither CTA of a pair frees tensor memory while the other still reads its own
+    if (warp == 2) KBN_PT(7);
+    if (warp == 1) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc_pair(tmem_base, kTmemCols);
     }
 }
 
@@ -1049,6 +1399,20 @@ static int make_tmap(CUtensorMap* tm, const void* base, int64_t rows, int64_t K,
     return KBN_OK;
 }
 
+// Packed scale array seen as rows of 128 32-bit words (one 512-byte scale block per row): boxes of `box_rows` blocks.
+static int make_tmap_sf(CUtensorMap* tm, const void* base, int64_t blocks, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    KBN_REQUIRE(fn, KBN_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[2] = {128, (cuuint64_t)blocks};
+    cuuint64_t strides[1] = {512};
+    cuuint32_t box[2] = {128, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    KBN_REQUIRE(r == CUDA_SUCCESS, KBN_ERR_CUDA, "cuTensorMapEncodeTiled (scales) failed with CUresult %d (blocks=%lld)", (int)r, (long long)blocks);
+    return KBN_OK;
+}
+
 static int check_device() {
     static int ok[64] = {0};
     int dev = 0;
@@ -1065,8 +1429,9 @@ static int check_device() {
         KBN_CUDA(cudaFuncSetAttribute(fp8_gemm_mx_kernel<256, kEpiStore, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSwapSmemBytes));
         KBN_CUDA(cudaFuncSetAttribute(fp8_gemm_mx_kernel<256, kEpiAct, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSwapSmemBytes));
         KBN_CUDA(cudaFuncSetAttribute(fp8_gemm_mx_kernel<256, kEpiCombine, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSwapSmemBytes));
-        KBN_CUDA(cudaFuncSetAttribute(fp8_gemm_mx_splitk_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<256>::kSmemBytes));
-        KBN_CUDA(cudaFuncSetAttribute(fp8_gemm_mx_splitk_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<128>::kSmemBytes));
+        KBN_CUDA(cudaFuncSetAttribute(fp8_gemm_mx_splitk_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSplitSmemBytes));
+        KBN_CUDA(cudaFuncSetAttribute(fp8_gemm_mx_splitk_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSplitSmemBytes));
+        KBN_CUDA(cudaFuncSetAttribute(fp8_gemm_mx_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PairCfg::kSmemBytes));
         ok[dev] = 1;
     }
     return KBN_OK;
@@ -1084,7 +1449,7 @@ static int max_active_clusters(int split) {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3((unsigned)(split * 64));
         cfg.blockDim = dim3(kThreads);
-        cfg.dynamicSmemBytes = Cfg<BN>::kSmemBytes;
+        cfg.dynamicSmemBytes = kSplitSmemBytes;
         cudaLaunchAttribute attr[1];
         attr[0].id = cudaLaunchAttributeClusterDimension;
         attr[0].val.clusterDim.x = (unsigned)split;
@@ -1102,21 +1467,98 @@ static int max_active_clusters(int split) {
     return cache[dev][split] > 0 ? cache[dev][split] : 0;
 }
 
+// Clusters of 2*S CTAs of the CTA-pair kernel that can be resident at once (cached per device).
+static int max_active_pair_clusters(int S) {
+    static int cache[64][5] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || S < 2 || S > 4) return 0;
+    if (cache[dev][S] == 0) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)(2 * S * 16));
+        cfg.blockDim = dim3(kThreads);
+        cfg.dynamicSmemBytes = PairCfg::kSmemBytes;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = (unsigned)(2 * S);
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, fp8_gemm_mx_pair_kernel, &cfg) != cudaSuccess) {
+            cudaGetLastError();
+            n = -1;
+        }
+        cache[dev][S] = n > 0 ? n : -1;
+    }
+    return cache[dev][S] > 0 ? cache[dev][S] : 0;
+}
+
+// K-slices per cluster of the CTA-pair kernel for a dense problem, 0 when the problem does not suit it: more than one
+// row block, too few 256 x 256 tiles to give every SM one, and a split that puts a CTA on at least three SMs in five
+// with every cluster resident at once.
+static int pair_plan(const GemmParams& p) {
+    if (p.mode != kDense || p.rows_total <= kBlockM || p.N <= 128 || p.K % 128 != 0) return 0;
+    const int64_t pair_tiles = (int64_t)cdiv32(p.rows_total, 256) * cdiv32(p.N, PairCfg::kBN);
+    for (int S = 4; S >= 2; S /= 2) {
+        const int kbs = (p.num_k_blocks + S - 1) / S;
+        if (2 * S * pair_tiles > sm_count() || (S - 1) * kbs >= p.num_k_blocks || p.num_k_blocks < 2 * S) continue;
+        if (pair_tiles > max_active_pair_clusters(S)) continue;
+        return 2 * S * pair_tiles * 5 >= (int64_t)sm_count() * 3 ? S : 0;
+    }
+    return 0;
+}
+
+static int launch_pair(const void* A, int64_t a_rows, const void* B, int64_t b_rows, const GemmParams& p, const void* sfa, const void* sfb,
+                       int S, cudaStream_t st) {
+    constexpr int BN = PairCfg::kBN;
+    CUtensorMap tmA, tmB, tmSfa, tmSfb;
+    int rc = make_tmap(&tmA, A, a_rows, p.K, kBlockM, CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
+    if (rc != KBN_OK) return rc;
+    rc = make_tmap(&tmB, B, b_rows, p.K, BN / 2, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+    if (rc != KBN_OK) return rc;
+    const int32_t nb_pad = (cdiv32(p.N, 128) + 1) / 2 * 2;
+    rc = make_tmap_sf(&tmSfa, sfa, (int64_t)cdiv32(p.rows_total, kBlockM) * p.num_k_blocks, 1);
+    if (rc != KBN_OK) return rc;
+    rc = make_tmap_sf(&tmSfb, sfb, (int64_t)p.num_k_blocks * nb_pad, BN / 128);
+    if (rc != KBN_OK) return rc;
+    const int64_t pair_tiles = (int64_t)cdiv32(p.rows_total, 256) * cdiv32(p.N, BN);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(pair_tiles * 2 * S));
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = PairCfg::kSmemBytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)(2 * S);
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    KBN_CUDA(cudaLaunchKernelEx(&cfg, fp8_gemm_mx_pair_kernel, tmA, tmB, tmSfa, tmSfb, p, nb_pad, S));
+    KBN_CHECK_LAUNCH();
+    return KBN_OK;
+}
+
 template <int BN>
 static int launch_splitk(const CUtensorMap& tmA, const CUtensorMap& tmA64, const CUtensorMap& tmA32, const CUtensorMap& tmB,
                          const GemmParams& p, const MxExtra& x, int split, int64_t tiles, cudaStream_t st) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(tiles * split));
     cfg.blockDim = dim3(kThreads);
-    cfg.dynamicSmemBytes = Cfg<BN>::kSmemBytes;
+    cfg.dynamicSmemBytes = kSplitSmemBytes;
     cfg.stream = st;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = (unsigned)split;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = 2;
     KBN_CUDA(cudaLaunchKernelEx(&cfg, fp8_gemm_mx_splitk_kernel<BN>, tmA, tmA64, tmA32, tmB, p, x, split));
     KBN_CHECK_LAUNCH();
     return KBN_OK;
@@ -1136,6 +1578,15 @@ static int launch(const void* A, int64_t a_rows, const void* B, int64_t b_rows, 
     KBN_REQUIRE(aligned16(A) && aligned16(B) && aligned16(sfa) && aligned16(sfb), KBN_ERR_ARG, "fp8 gemm (ue8m0): pointers must be 16-byte aligned");
     KBN_REQUIRE(p.K % 16 == 0 && p.K > 0 && p.N > 0, KBN_ERR_ARG, "fp8 gemm (ue8m0): K=%d must be a positive multiple of 16", p.K);
     KBN_REQUIRE(a_rows < (1ll << 31) && b_rows < (1ll << 31), KBN_ERR_ARG, "fp8 gemm (ue8m0): more than 2^31 rows");
+    // a few hundred rows of a dense layer: 256 x 256 tiles on CTA pairs
+    if (!act && !combine && !hooks) {
+        const int S = pair_plan(p);
+        if (S > 0) {
+            rc = gemm_status_ptr(&p.status);
+            if (rc != KBN_OK) return rc;
+            return launch_pair(A, a_rows, B, b_rows, p, sfa, sfb, S, st);
+        }
+    }
     // 256-wide tiles unless that would leave SMs without a tile and 128-wide tiles fill more of them
     int bn = 256;
     if (p.mode != kMasked && p.N > 128 && m_blocks_upper * cdiv32(p.N, 256) < sm_count()) bn = 128;
@@ -1199,7 +1650,7 @@ static int launch(const void* A, int64_t a_rows, const void* B, int64_t b_rows, 
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = hooks ? 1 : 0;
+    cfg.numAttrs = (hooks || p.mode == kDense) ? 1 : 0;
     auto go = [&](auto kernel) { return cudaLaunchKernelEx(&cfg, kernel, tmA, tmA64, tmA32, tmB, p, x, cb, hk); };
     cudaError_t le;
     if (swap && combine) le = go(fp8_gemm_mx_kernel<256, kEpiCombine, true>);
@@ -1225,6 +1676,15 @@ static void fill_params(GemmParams& p, void* C, int64_t ldc, int64_t rows, int64
 
 }  // namespace mx
 }  // namespace kbn
+
+#ifdef KBN_TRACE
+extern "C" int kbn_debug_pair_trace(unsigned long long* host_out) {
+    using namespace kbn;
+    KBN_CUDA(cudaDeviceSynchronize());
+    KBN_CUDA(cudaMemcpyFromSymbol(host_out, mx::g_pair_trace, sizeof(unsigned long long) * 256 * 16));
+    return KBN_OK;
+}
+#endif
 
 extern "C" int64_t kbn_packed_sf_rows_bytes(int64_t rows, int64_t K) {
     return ((rows + 127) / 128) * ((K + 127) / 128) * 512;

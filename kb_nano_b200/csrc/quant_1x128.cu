@@ -13,6 +13,8 @@ __global__ void __launch_bounds__(256)
 quant_1x128_kernel(const __nv_bfloat16* __restrict__ x, uint32_t K, int64_t ld_x, uint8_t* __restrict__ q,
                    int64_t ld_q, float* __restrict__ scale, int64_t s_row, int64_t s_grp, float eps,
                    uint32_t G, uint32_t chunks_per_row, uint32_t n_chunks, uint32_t* __restrict__ packed) {
+    // the kernel behind this one (the GEMM that reads q) may be scheduled under it; it waits for this grid before it reads
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const uint32_t j = threadIdx.x & 15u;
     const uint32_t chunk = blockIdx.x * 16u + (threadIdx.x >> 4);
     const bool valid = chunk < n_chunks;

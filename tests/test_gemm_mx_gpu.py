@@ -51,6 +51,28 @@ def test_mx_dense_few_tiles_split_k(cuda_dev, m, n, k):
     assert torch.equal(out1.view(torch.int16), out2.view(torch.int16))
 
 
+@pytest.mark.parametrize("m,n,k,bias", [(512, 4096, 7168, False), (512, 2048, 2048, True), (300, 3000, 2048, True), (256, 4096, 1024, False),
+                                        (384, 2304, 4096, True), (129, 4096, 1024, False)])
+def test_mx_dense_cta_pairs(cuda_dev, m, n, k, bias):
+    """A few hundred rows and too few 256 x 256 tiles for every SM: two CTAs share a tile (one tensor-core instruction
+    over both SMs) and 2 or 4 pairs of a cluster split K (2 slices in the first and third case, 4 in the second and
+    fourth; ragged rows and columns, a second row block of one row in the last case).  The partials are added in slice order: two runs agree bit for bit."""
+    from kb_nano_b200 import ops
+    a_q, a_s, w_q, w_s = make_dense(m, n, k, seed=m + n + k, dev=cuda_dev)
+    b = torch.randn(n, generator=torch.Generator().manual_seed(n)).to(torch.bfloat16) if bias else None
+    ref = to.gemm_nt_dequant(a_q, a_s, w_q, w_s, b)
+    sfb = ops.packed_weight_scales(w_s.to(cuda_dev), n, k)
+    sfa = ops.pack_sf_rows(a_s.to(cuda_dev), k)
+    outs = []
+    for _ in range(2):
+        out = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=cuda_dev)
+        ops.fp8_gemm_nt_ue8m0(a_q.to(cuda_dev), sfa, w_q.to(cuda_dev), sfb, out, b.to(cuda_dev) if bias else None)
+        assert ops.gemm_status(cuda_dev) == 0
+        outs.append(out.cpu())
+    assert_gemm_close(outs[0], ref, f"dense ue8m0 CTA pairs {m}x{n}x{k}")
+    assert torch.equal(outs[0].view(torch.int16), outs[1].view(torch.int16))
+
+
 def test_mx_scales_with_wide_exponent_range(cuda_dev):
     """Each K-block and each row with a different power-of-two scale: catches any mix-up of the packed order."""
     m, n, k = 256, 512, 1024
