@@ -391,7 +391,7 @@ def wl_silu_c2(args, rank, world, dev, sampler):
                 "d2h_bytes_per_step": m * n // 2 + 4 * m * (n // 256)},
         "gpu_launches": launches // (args.steps + args.warmup) * args.steps,
         "roofline": {"bound": "hbm", "kernel": "silu_mul_quant_kernel", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                     "frac": gbs / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
+                     "frac": gbs / peaks["hbm_gbs"], "traffic": measured_traffic("silu_mul_quant", 1.0), "peak_source": peaks["source"],
                      "algorithmic_bytes_per_launch": byts},
         "_cpu": lambda: cpu_silu_c2(2048, 3),
     }
@@ -443,7 +443,8 @@ def wl_quant_c1(args, rank, world, dev, sampler, m=512, k=7168):
         "e2e": {"value": byts / (ms_e2e * 1e-3) / 1e9 * world, "unit": "GB/s", "h2d_bytes_per_step": m * k * 2, "d2h_bytes_per_step": m * k},
         "gpu_launches": launches // (args.steps + args.warmup) * args.steps,
         "roofline": {"bound": "hbm", "kernel": "quant_1x128_kernel", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                     "frac": gbs / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"], "algorithmic_bytes_per_launch": byts},
+                     "frac": gbs / peaks["hbm_gbs"], "traffic": measured_traffic("quant_1x128", 1.0) if m == 4096 else None,
+                     "peak_source": peaks["source"], "algorithmic_bytes_per_launch": byts},
         "_cpu": lambda: cpu_quant(m, k, 20 if m == 512 else 3),
     }
 
@@ -488,8 +489,8 @@ def wl_gemm_c1(args, rank, world, dev, sampler):
                    "timing": "the K steps are captured in one CUDA graph and timed with one CUDA-event pair", "replicas": world},
         "e2e": {"value": flop / (ms_e2e * 1e-3) / 1e12 * world, "unit": "TFLOP/s", "h2d_bytes_per_step": m * k * 2, "d2h_bytes_per_step": m * n * 2},
         "gpu_launches": launches // (args.steps + args.warmup) * args.steps,
-        "roofline": {"bound": "tensor", "kernel": "fp8_gemm_mx_kernel", "achieved": tf, "peak": fp8_peak, "unit": "TFLOP/s", "frac": tf / fp8_peak,
-                     "traffic": None, "peak_source": peaks["source"] + " bf16 burst x2 (no FP8 entry in MEASURED_PEAKS.json)",
+        "roofline": {"bound": "tensor", "kernel": "fp8_gemm_mx_pair_kernel", "achieved": tf, "peak": fp8_peak, "unit": "TFLOP/s", "frac": tf / fp8_peak,
+                     "traffic": measured_traffic("fp8_gemm_mx_pair", 1.0), "peak_source": peaks["source"] + " bf16 burst x2 (no FP8 entry in MEASURED_PEAKS.json)",
                      "frac_of_nominal_4500": tf / 4500.0, "algorithmic_flop_per_launch": flop},
         "_cpu": lambda: cpu_gemm_c1(512, 3),
     }
@@ -614,7 +615,8 @@ def wl_moe_single(args, rank, world, dev, sampler, name):
     if hbm_bound:
         ach = (g1 + g2) / 2.0 / (gemm_ms * 1e-3) / 1e9
         roof = {"bound": "hbm", "kernel": "fp8_gemm_mx_kernel (grouped, 2 launches per layer)", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                "frac": ach / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"], "algorithmic_bytes_per_launch": (g1 + g2) / 2.0,
+                "frac": ach / peaks["hbm_gbs"], "traffic": measured_traffic("fp8_gemm_mx_contig", (e * 3.0 * i * h) / (32 * 3.0 * 2048 * 7168)),
+                "peak_source": peaks["source"], "algorithmic_bytes_per_launch": (g1 + g2) / 2.0,
                 "tflops": flop / 2.0 / (gemm_ms * 1e-3) / 1e12}
     else:
         ach = flop / 2.0 / (gemm_ms * 1e-3) / 1e12
