@@ -59,6 +59,31 @@ static inline void count_launch(int n = 1) { g_launches.fetch_add(n, std::memory
 // ---- device helpers --------------------------------------------------------------------------
 #ifdef __CUDACC__
 
+// Launch with programmatic stream serialisation: the grid may be scheduled while the kernel before it in the stream
+// is still running (if that kernel allows it, else when it has ended).  The kernel must call pdl_prologue_done() before
+// it reads anything that kernel may have written and before its own first global write.
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+// Lets the next kernel of the stream be scheduled under this one, then waits until the kernel before this one has
+// ended and its writes are visible.  What a kernel does before this call must not depend on that kernel.
+__device__ __forceinline__ void pdl_prologue_done() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 __device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
 

@@ -123,6 +123,7 @@ silu_mul_quant_kernel(const __nv_bfloat16* __restrict__ in, uint32_t N2, int64_t
                       int64_t ld_q, float* __restrict__ scale, int64_t s_row, int64_t s_grp, float eps,
                       const uint16_t* __restrict__ table, const int32_t* __restrict__ row_info, uint32_t G,
                       uint32_t chunks_per_row, uint32_t n_chunks, uint32_t* __restrict__ packed) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");      // the GEMM behind this kernel may come in under it
     const uint32_t chunk = blockIdx.x * 16u + (threadIdx.x >> 4);
     bool valid = chunk < n_chunks;
     const uint32_t row = valid ? chunk / chunks_per_row : 0u;
@@ -222,18 +223,19 @@ silu_mul_quant_smem_kernel(const __nv_bfloat16* __restrict__ in, uint32_t N2, in
             uv[u][h] = live ? __ldcs(reinterpret_cast<const uint4*>(src + 64 * h + N2)) : make_uint4(0, 0, 0, 0);
         }
     };
-    uint32_t base = lo + (threadIdx.x >> 5) * 4u;
-    Ref cur = ref_of(base);
-#pragma unroll
-    for (int u = 0; u < U; ++u) fetch(cur, u);
-    // the first chunk's loads are in flight while the table is copied
-    // every block copies the same 128 KB; each starts at a different offset so that the SMs do not all
-    // ask L2 for the same line at the same time
+    // The table does not depend on the kernel before this one: it is copied while that kernel may still be running.
+    // Every block copies the same 128 KB; each starts at a different offset so that the SMs do not all ask L2 for
+    // the same line at the same time.
     const uint32_t rot = (blockIdx.x * 55u) & 8191u;
     for (uint32_t i = threadIdx.x; i < 8192u; i += blockDim.x) {
         const uint32_t k = (i + rot) & 8191u;
         reinterpret_cast<uint4*>(tab)[k] = __ldg(reinterpret_cast<const uint4*>(table) + k);
     }
+    pdl_prologue_done();
+    uint32_t base = lo + (threadIdx.x >> 5) * 4u;
+    Ref cur = ref_of(base);
+#pragma unroll
+    for (int u = 0; u < U; ++u) fetch(cur, u);
     __syncthreads();
     for (; base < hi; base += step) {
         const Ref nxt = ref_of(base + step);
@@ -257,6 +259,7 @@ silu_mul_quant_masked_kernel(const __nv_bfloat16* __restrict__ in, uint32_t N2, 
                              int64_t ld_q, float* __restrict__ scale, int64_t s_row, int64_t s_grp, float eps,
                              const uint16_t* __restrict__ table, const int32_t* __restrict__ masked_m, uint32_t max_m,
                              uint32_t G, uint32_t chunks_per_row, uint32_t* __restrict__ packed) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");      // the GEMM behind this kernel may come in under it
     const uint32_t e = blockIdx.y;
     const uint32_t cnt = (uint32_t)min(max(masked_m[e], 0), (int)max_m);
     const uint32_t n = cnt * chunks_per_row;
@@ -362,14 +365,14 @@ static int launch_silu_mul_quant(const char* who, const void* in, int64_t M, int
         }
         const unsigned grid = (unsigned)sm_count();
         if (rows_mode == 0)
-            silu_mul_quant_smem_kernel<U2, 0><<<grid, 1024, 131072, st>>>(ib, (uint32_t)N2, ld_in, qb, ld_q, scale, s_row, s_grp, eps, table,
-                                                                         row_info, (uint32_t)G, (uint32_t)cpr2, (uint32_t)n2c, packed);
+            KBN_CUDA(launch_pdl(silu_mul_quant_smem_kernel<U2, 0>, dim3(grid), dim3(1024), 131072, st, ib, (uint32_t)N2, ld_in, qb, ld_q, scale, s_row, s_grp,
+                                eps, table, row_info, (uint32_t)G, (uint32_t)cpr2, (uint32_t)n2c, packed));
         else if (rows_mode == 1)
-            silu_mul_quant_smem_kernel<U2, 1><<<grid, 1024, 131072, st>>>(ib, (uint32_t)N2, ld_in, qb, ld_q, scale, s_row, s_grp, eps, table,
-                                                                         row_info, (uint32_t)G, (uint32_t)cpr2, (uint32_t)n2c, packed);
+            KBN_CUDA(launch_pdl(silu_mul_quant_smem_kernel<U2, 1>, dim3(grid), dim3(1024), 131072, st, ib, (uint32_t)N2, ld_in, qb, ld_q, scale, s_row, s_grp,
+                                eps, table, row_info, (uint32_t)G, (uint32_t)cpr2, (uint32_t)n2c, packed));
         else
-            silu_mul_quant_smem_kernel<U2, 3><<<grid, 1024, 131072, st>>>(ib, (uint32_t)N2, ld_in, qb, ld_q, scale, s_row, s_grp, eps, table,
-                                                                         row_info, (uint32_t)G, (uint32_t)cpr2, (uint32_t)n2c, packed);
+            KBN_CUDA(launch_pdl(silu_mul_quant_smem_kernel<U2, 3>, dim3(grid), dim3(1024), 131072, st, ib, (uint32_t)N2, ld_in, qb, ld_q, scale, s_row, s_grp,
+                                eps, table, row_info, (uint32_t)G, (uint32_t)cpr2, (uint32_t)n2c, packed));
     } else if (rows_mode == 2) {
         KBN_REQUIRE(M / max_m <= 65535, KBN_ERR_ARG, "%s: more than 65535 experts", who);
         if (ue8m0) KBN_SMQ_MASKED(true); else KBN_SMQ_MASKED(false);
