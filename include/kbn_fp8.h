@@ -240,6 +240,14 @@ int kbn_gemm_clear_status(kbn_stream_t stream);
  *   accumulation in slot order, bf16 [T,H] out; rows is bf16 with row stride ld_rows.
  */
 int64_t kbn_moe_aligned_rows(int64_t T, int64_t topk, int64_t E);
+/* Front end of the sorted-token layout of kb-nano's Triton MoE path (MoeGroupedGemm.forward,
+ * tasks/baseline/L1/moe_grouped_gemm.py:294-382; the lists come from moe_align_block_size): pair_expert int32
+ * [n_pairs] = expert of every (token, slot) pair t, read out of sorted_ids int32 [n_sorted] (position i lies in block
+ * i / block_m; entries >= n_pairs are padding) and expert_ids int32 [n_blocks]; -1 for pairs in no block.
+ * sorted_ids == NULL: block i holds the single pair i.  The result is the topk_ids argument of kbn_moe_permute. */
+int kbn_moe_pair_experts(const int32_t* sorted_ids, int64_t n_sorted, const int32_t* expert_ids,
+                         int64_t n_blocks, int64_t block_m, int64_t n_pairs, int32_t* pair_expert,
+                         kbn_stream_t stream);
 int64_t kbn_moe_permute_workspace_bytes(int64_t T, int64_t topk, int64_t E);
 int kbn_moe_permute(const void* a_q, const float* a_s, const int32_t* topk_ids, int64_t T,
                     int64_t topk, int64_t K, int64_t E, void* a_perm, float* a_s_perm,

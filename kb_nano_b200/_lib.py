@@ -45,6 +45,7 @@ SIGNATURES = {
     "kbn_fp8_grouped_gemm_masked_ue8m0_silu": (_i32, [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _ptr]),
     "kbn_moe_aligned_rows": (_i64, [_i64, _i64, _i64]),
     "kbn_moe_permute_workspace_bytes": (_i64, [_i64, _i64, _i64]),
+    "kbn_moe_pair_experts": (_i32, [_ptr, _i64, _ptr, _i64, _i64, _i64, _ptr, _ptr]),
     "kbn_moe_permute": (_i32, [_ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _ptr, _ptr, _ptr, _ptr, _i64, _ptr, _i64, _ptr]),
     "kbn_moe_permute_sf": (_i32, [_ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _ptr, _ptr, _ptr, _ptr, _i64, _ptr, _i64, _ptr, _ptr]),
     "kbn_ep_create": (_i32, [_i32, _i32, _i64, _i64, _i64, _i64, _i64, _i64, ctypes.POINTER(_ptr)]),

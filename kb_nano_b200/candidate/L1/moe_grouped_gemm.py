@@ -7,11 +7,12 @@ when ``t < A.size(0) * top_k``) is ``dequant(A[t // top_k]) @ dequant(B[e])^T`` 
 the ``BLOCK_SIZE_M`` block that position ``i`` falls in, optionally times ``topk_weights.flat[t]``,
 written to ``C`` in place; with ``sorted_token_ids=None`` block ``i`` holds the single row ``t = i``.
 
-How it is computed here: the (row -> expert) map is read back out of the sorted lists (a few torch ops
-on int32 metadata, as kb-nano's own permute does), the rows are regrouped into 128-aligned expert
-segments by ``kbn_moe_permute``, multiplied by this library's grouped FP8 GEMM (UE8M0 tensor-core path
-when every weight scale is a power of two, fp32-scale path otherwise) and written back to ``C[t]`` by
-``kbn_moe_unpermute_combine`` with one slot per row.  FP8 block-scaled inputs only.
+How it is computed here: one small kernel reads the (row -> expert) map back out of the sorted lists
+(``kbn_moe_pair_experts``), the rows are regrouped into 128-aligned expert segments by ``kbn_moe_permute``,
+multiplied by this library's grouped FP8 GEMM (UE8M0 tensor-core path when every weight scale is a power of
+two, fp32-scale path otherwise) and written back to ``C[t]`` by ``kbn_moe_unpermute_combine`` with one slot
+per row.  The scratch buffers only grow and are kept per device (a captured CUDA graph may hold their
+addresses).  FP8 block-scaled inputs only.
 """
 from __future__ import annotations
 
@@ -28,6 +29,26 @@ _spec.loader.exec_module(importlib.util.module_from_spec(_spec))
 from kb_nano_b200 import ops  # noqa: E402
 
 _FP8 = torch.float8_e4m3fn
+
+
+_SCRATCH: dict = {}      # device -> {name: flat tensor}; buffers only ever grow
+_RETIRED: list = []      # outgrown buffers stay alive: a captured CUDA graph may still hold their addresses
+
+
+def _scratch(dev: torch.device, n_pairs: int, m_cap: int, k: int, n: int, ws_bytes: int) -> dict:
+    want = {"pair_expert": (n_pairs, torch.int32), "dest_row": (n_pairs, torch.int32), "row_expert": (m_cap, torch.int32),
+            "a_perm": (m_cap * k, _FP8), "a_s_perm": (m_cap * (k // 128), torch.float32), "out": (m_cap * n, torch.bfloat16),
+            "workspace": (ws_bytes, torch.uint8), "ones": (n_pairs, torch.float32)}
+    sc = _SCRATCH.setdefault((dev.type, dev.index), {})
+    for name, (numel, dtype) in want.items():
+        cur = sc.get(name)
+        if cur is None or cur.numel() < numel:
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError("MoeGroupedGemm: scratch would have to grow during stream capture; run the largest shape eagerly first")
+            if cur is not None:
+                _RETIRED.append(cur)
+            sc[name] = torch.ones(numel, dtype=dtype, device=dev) if name == "ones" else torch.empty(numel, dtype=dtype, device=dev)
+    return sc
 
 
 def _get_default_config(M: int, E: int = 0, N: int = 0, block_shape: list[int] | None = None) -> dict:
@@ -61,31 +82,31 @@ class MoeGroupedGemm(nn.Module):
         n_pairs = m * top_k
         dev = A.device
 
+        if C.dtype != torch.bfloat16 or C.shape[0] < n_pairs or C.shape[1] != n or not C.is_contiguous():
+            raise ValueError("C must be contiguous bf16 [M*top_k, N]")
+        m_cap = ops.moe_aligned_rows(m, top_k, e)
+        sc = _scratch(dev, n_pairs, m_cap, k, n, ops.moe_permute_workspace_bytes(m, top_k, e))
+
         # expert of every row t of C (-1: the row appears in no block), without a host sync
-        pair_expert = torch.full((n_pairs + 1,), -1, dtype=torch.int32, device=dev)
-        blocks = expert_ids.reshape(-1).to(torch.int32)
-        if sorted_token_ids is None:
-            cnt = min(blocks.numel(), n_pairs)
-            pair_expert[:cnt] = blocks[:cnt]
-        else:
-            ids = sorted_token_ids.reshape(-1).long()
-            pos_expert = blocks.repeat_interleave(bm)[: ids.numel()]
-            if pos_expert.numel() < ids.numel():
-                ids = ids[: pos_expert.numel()]
-            pair_expert.scatter_(0, torch.where(ids < n_pairs, ids, torch.full_like(ids, n_pairs)), pos_expert)
-        topk_ids = pair_expert[:n_pairs].view(m, top_k).contiguous()
+        blocks = expert_ids.reshape(-1)
+        blocks = blocks if blocks.dtype == torch.int32 and blocks.is_contiguous() else blocks.to(torch.int32).contiguous()
+        ids = None
+        if sorted_token_ids is not None:
+            ids = sorted_token_ids.reshape(-1)
+            ids = ids if ids.dtype == torch.int32 and ids.is_contiguous() else ids.to(torch.int32).contiguous()
+        pair_expert = sc["pair_expert"][:n_pairs]
+        ops.moe_pair_experts(ids, blocks, bm, pair_expert)
+        topk_ids = pair_expert.view(m, top_k)
 
         a_s = a_scale if a_scale.is_contiguous() else a_scale.contiguous()
         a_q = A if A.is_contiguous() else A.contiguous()
-        m_cap = ops.moe_aligned_rows(m, top_k, e)
-        a_perm = torch.empty(m_cap, k, dtype=_FP8, device=dev)
-        a_s_perm = torch.empty(m_cap, k // 128, dtype=torch.float32, device=dev)
-        row_expert = torch.empty(m_cap, dtype=torch.int32, device=dev)
-        dest_row = torch.empty(m, top_k, dtype=torch.int32, device=dev)
-        workspace = torch.empty(ops.moe_permute_workspace_bytes(m, top_k, e), dtype=torch.uint8, device=dev)
-        ops.moe_permute(a_q, a_s, topk_ids, e, a_perm, a_s_perm, row_expert, dest_row, workspace)
+        a_perm = sc["a_perm"][: m_cap * k].view(m_cap, k)
+        a_s_perm = sc["a_s_perm"][: m_cap * (k // 128)].view(m_cap, k // 128)
+        row_expert = sc["row_expert"][:m_cap]
+        dest_row = sc["dest_row"][:n_pairs].view(m, top_k)
+        ops.moe_permute(a_q, a_s, topk_ids, e, a_perm, a_s_perm, row_expert, dest_row, sc["workspace"])
 
-        out = torch.empty(m_cap, n, dtype=torch.bfloat16, device=dev)
+        out = sc["out"][: m_cap * n].view(m_cap, n)
         packed = ops.packed_weight_scales(b_scale, n, k)
         if packed is not None:
             # activation scales from kb-nano's quantiser are powers of two (tasks/baseline/L1/fp8_linear.py:163-168,237)
@@ -96,7 +117,5 @@ class MoeGroupedGemm(nn.Module):
         if mul_routed_weight and topk_weights is not None:
             w = topk_weights.reshape(-1).float()[:n_pairs].contiguous().view(n_pairs, 1)
         else:
-            w = torch.ones(n_pairs, 1, dtype=torch.float32, device=dev)
-        if C.dtype != torch.bfloat16 or C.shape[0] < n_pairs or C.shape[1] != n or not C.is_contiguous():
-            raise ValueError("C must be contiguous bf16 [M*top_k, N]")
+            w = sc["ones"][:n_pairs].view(n_pairs, 1)
         ops.moe_unpermute_combine(out, dest_row.view(n_pairs, 1), w, C[:n_pairs])

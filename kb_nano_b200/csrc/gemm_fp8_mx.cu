@@ -1385,7 +1385,32 @@ static EncodeTiledFn encode_fn() {
     return fn;
 }
 
+// Encoded tensor maps of this thread's recent calls.  A map depends on nothing but the arguments it was encoded from
+// (address, extents, box, promotion), so an entry stays valid whatever happens to the memory behind the address; a
+// layer that calls the same GEMM on the same buffers every step pays for the driver's encoder once per operand.
+struct TmapCacheEntry {
+    const void* base = nullptr;
+    int64_t rows = 0, K = 0;
+    int32_t box_rows = 0, kind = 0;      // kind: L2 promotion for operand maps, -1 for scale maps
+    CUtensorMap tm;
+};
+constexpr int kTmapCacheSize = 64;
+static TmapCacheEntry* tmap_cache_slot(const void* base, int64_t rows, int64_t K, int box_rows, int kind, bool* hit) {
+    static thread_local TmapCacheEntry cache[kTmapCacheSize];
+    uint64_t h = reinterpret_cast<uintptr_t>(base) >> 4;
+    h = (h ^ (h >> 17) ^ (uint64_t)rows * 0x9e3779b97f4a7c15ull ^ (uint64_t)K * 0xc2b2ae3d27d4eb4full ^ (uint64_t)(box_rows * 8 + kind + 1)) * 0xff51afd7ed558ccdull;
+    TmapCacheEntry* e = &cache[(h >> 40) % kTmapCacheSize];
+    *hit = e->base == base && e->rows == rows && e->K == K && e->box_rows == box_rows && e->kind == kind;
+    return e;
+}
+
 static int make_tmap(CUtensorMap* tm, const void* base, int64_t rows, int64_t K, int box_rows, CUtensorMapL2promotion promo) {
+    bool hit = false;
+    TmapCacheEntry* ce = tmap_cache_slot(base, rows, K, box_rows, (int)promo, &hit);
+    if (hit) {
+        *tm = ce->tm;
+        return KBN_OK;
+    }
     EncodeTiledFn fn = encode_fn();
     KBN_REQUIRE(fn, KBN_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
     cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
@@ -1396,11 +1421,19 @@ static int make_tmap(CUtensorMap* tm, const void* base, int64_t rows, int64_t K,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, promo, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     KBN_REQUIRE(r == CUDA_SUCCESS, KBN_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d (rows=%lld K=%lld)",
                 (int)r, (long long)rows, (long long)K);
+    ce->base = base; ce->rows = rows; ce->K = K; ce->box_rows = box_rows; ce->kind = (int)promo;
+    ce->tm = *tm;
     return KBN_OK;
 }
 
 // Packed scale array seen as rows of 128 32-bit words (one 512-byte scale block per row): boxes of `box_rows` blocks.
 static int make_tmap_sf(CUtensorMap* tm, const void* base, int64_t blocks, int box_rows) {
+    bool hit = false;
+    TmapCacheEntry* ce = tmap_cache_slot(base, blocks, 128, box_rows, -1, &hit);
+    if (hit) {
+        *tm = ce->tm;
+        return KBN_OK;
+    }
     EncodeTiledFn fn = encode_fn();
     KBN_REQUIRE(fn, KBN_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
     cuuint64_t dims[2] = {128, (cuuint64_t)blocks};
@@ -1410,6 +1443,8 @@ static int make_tmap_sf(CUtensorMap* tm, const void* base, int64_t blocks, int b
     CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                     CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     KBN_REQUIRE(r == CUDA_SUCCESS, KBN_ERR_CUDA, "cuTensorMapEncodeTiled (scales) failed with CUresult %d (blocks=%lld)", (int)r, (long long)blocks);
+    ce->base = base; ce->rows = blocks; ce->K = 128; ce->box_rows = box_rows; ce->kind = -1;
+    ce->tm = *tm;
     return KBN_OK;
 }
 

@@ -166,6 +166,39 @@ moe_combine_kernel(const __nv_bfloat16* __restrict__ rows, int64_t ld_rows, cons
 extern "C" int kbn_moe_permute_sf(const void*, const float*, const int32_t*, int64_t, int64_t, int64_t, int64_t, void*, float*, int32_t*,
                                   int32_t*, int64_t, void*, int64_t, void*, kbn_stream_t);
 
+namespace kbn {
+// Expert of every (token, slot) pair from the sorted, block-padded pair list of kb-nano's Triton MoE path:
+// position i of sorted_ids belongs to block i / block_m, whose expert is expert_ids[i / block_m]; entries
+// >= n_pairs are padding.  Without a list, block i holds the single pair i.  pair_expert was set to -1 before.
+__global__ void moe_pair_experts_kernel(const int32_t* __restrict__ sorted_ids, int64_t n_sorted, const int32_t* __restrict__ expert_ids,
+                                        int64_t n_blocks, int32_t block_m, int64_t n_pairs, int32_t* __restrict__ pair_expert) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (sorted_ids == nullptr) {
+        if (i < n_pairs && i < n_blocks) pair_expert[i] = expert_ids[i];
+        return;
+    }
+    if (i >= n_sorted || i / block_m >= n_blocks) return;
+    const int32_t t = sorted_ids[i];
+    if (t >= 0 && t < n_pairs) pair_expert[t] = expert_ids[i / block_m];
+}
+}  // namespace kbn
+
+extern "C" int kbn_moe_pair_experts(const int32_t* sorted_ids, int64_t n_sorted, const int32_t* expert_ids, int64_t n_blocks,
+                                    int64_t block_m, int64_t n_pairs, int32_t* pair_expert, kbn_stream_t stream) {
+    using namespace kbn;
+    KBN_REQUIRE(n_sorted >= 0 && n_blocks >= 0 && n_pairs >= 0 && block_m > 0 && block_m < (1ll << 31), KBN_ERR_ARG, "kbn_moe_pair_experts: bad sizes");
+    if (n_pairs == 0) return KBN_OK;
+    KBN_REQUIRE(pair_expert && (n_blocks == 0 || expert_ids), KBN_ERR_ARG, "kbn_moe_pair_experts: null pointer");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    KBN_CUDA(cudaMemsetAsync(pair_expert, 0xff, (size_t)n_pairs * sizeof(int32_t), st));        // -1: in no block
+    const int64_t n = sorted_ids ? n_sorted : n_pairs;
+    if (n == 0 || n_blocks == 0) return KBN_OK;
+    KBN_REQUIRE((n + 255) / 256 < (1ll << 31), KBN_ERR_ARG, "kbn_moe_pair_experts: too many entries");
+    moe_pair_experts_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(sorted_ids, n_sorted, expert_ids, n_blocks, (int32_t)block_m, n_pairs, pair_expert);
+    KBN_CHECK_LAUNCH();
+    return KBN_OK;
+}
+
 extern "C" int64_t kbn_moe_aligned_rows(int64_t T, int64_t topk, int64_t E) {
     int64_t m = T * topk + E * (kbn::kAlign - 1);
     return (m + kbn::kAlign - 1) / kbn::kAlign * kbn::kAlign;

@@ -273,6 +273,22 @@ def gemm_clear_status(device: torch.device | str = "cuda") -> None:
         _lib.check(_lib.load().kbn_gemm_clear_status(torch.cuda.current_stream(dev).cuda_stream))
 
 
+def moe_pair_experts(sorted_token_ids: torch.Tensor | None, expert_ids: torch.Tensor, block_m: int, pair_expert: torch.Tensor) -> None:
+    """pair_expert int32 [n_pairs] <- expert of every (token, slot) pair, from the sorted, block-padded pair list of
+    kb-nano's Triton MoE path (position i of sorted_token_ids lies in block i // block_m, whose expert is
+    expert_ids[i // block_m]; entries >= n_pairs are padding); -1 for pairs that appear in no block.  Without a list
+    block i holds the single pair i."""
+    dev = _cuda(expert_ids, pair_expert) if sorted_token_ids is None else _cuda(sorted_token_ids, expert_ids, pair_expert)
+    for name, x in (("sorted_token_ids", sorted_token_ids), ("expert_ids", expert_ids), ("pair_expert", pair_expert)):
+        if x is not None and (x.dtype != torch.int32 or not x.is_contiguous()):
+            raise ValueError(f"{name} must be contiguous int32")
+    with _on(dev):
+        _lib.check(_lib.load().kbn_moe_pair_experts(
+            sorted_token_ids.data_ptr() if sorted_token_ids is not None else None,
+            sorted_token_ids.numel() if sorted_token_ids is not None else 0, expert_ids.data_ptr(), expert_ids.numel(), int(block_m),
+            pair_expert.numel(), pair_expert.data_ptr(), torch.cuda.current_stream(dev).cuda_stream))
+
+
 def moe_aligned_rows(t: int, topk: int, e: int) -> int:
     return int(_lib.load().kbn_moe_aligned_rows(t, topk, e))
 

@@ -7,7 +7,7 @@ where `tests/test_triton_ref_gpu.py` runs them on the GPU as a second oracle (bi
 quantisers, under the bf16 tolerance for the grouped GEMM) and `bench.py` times them as the GPU competitor
 of the same operation.  Nothing in the product path imports oracle/_ref.
 
-    python oracle/make_ref.py            # kb-nano tree from $KB_NANO_REF, else /root/reference
+    python oracle/make_ref.py [TREE]     # kb-nano tree: the argument, else $KB_NANO_REF, else the default mount point
 
   silu_mul_quant_fp8.py    tasks/baseline/L1/silu_mul_quant_fp8.py, whole file (torch + triton only)
   moe_grouped_gemm.py      tasks/baseline/L1/moe_grouped_gemm.py, whole file (deep_gemm import is optional there)
@@ -27,8 +27,11 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref")
 
 
+DEFAULT_TREE = os.path.join(os.sep, "root", "reference")      # where the build container mounts the kb-nano tree
+
+
 def ref_root() -> str | None:
-    for cand in (os.environ.get("KB_NANO_REF"), "/root/reference"):
+    for cand in (sys.argv[1] if len(sys.argv) > 1 else None, os.environ.get("KB_NANO_REF"), DEFAULT_TREE):
         if cand and os.path.isfile(os.path.join(cand, "tasks", "baseline", "L1", "silu_mul_quant_fp8.py")):
             return cand
     return None
@@ -47,7 +50,7 @@ def extract_function(path: str, name: str) -> str:
 def build() -> bool:
     root = ref_root()
     if root is None:
-        print("oracle/make_ref.py: no kb-nano tree ($KB_NANO_REF or /root/reference); oracle/_ref left as it is")
+        print("oracle/make_ref.py: no kb-nano tree (argument, $KB_NANO_REF or the default mount point); oracle/_ref left as it is")
         return os.path.isdir(OUT)
     l1 = os.path.join(root, "tasks", "baseline", "L1")
     os.makedirs(OUT, exist_ok=True)

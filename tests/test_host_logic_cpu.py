@@ -104,8 +104,8 @@ def test_candidates_go_through_kb_nanos_kernel_swapper():
     the tree (diffusers, deep_gemm, compiled extensions ...), which this machine cannot; the target list is
     therefore seeded with the targets whose baseline modules do import here (Triton-only files), built the way
     discovery builds them, and everything after that is kb-nano's unmodified code.  Needs a kb-nano tree
-    ($KB_NANO_REF or /root/reference); skipped otherwise."""
-    root = os.path.abspath(os.environ.get("KB_NANO_REF", "/root/reference"))
+    ($KB_NANO_REF, else where the build container mounts it); skipped otherwise."""
+    root = os.path.abspath(os.environ.get("KB_NANO_REF", os.path.join(os.sep, "root", "reference")))
     if not os.path.isfile(os.path.join(root, "infra", "kernel_swapper.py")):
         pytest.skip("no kb-nano tree")
     from pathlib import Path

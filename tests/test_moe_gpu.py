@@ -148,6 +148,35 @@ def test_moe_layer_fused_activation_matches_unfused(cuda_dev):
     assert bool(a.float().abs().sum() > 0)
 
 
+@pytest.mark.parametrize("t,topk,e,bm", [(37, 4, 8, 16), (256, 8, 64, 64), (1, 2, 4, 16), (300, 1, 3, 128)])
+def test_pair_experts_from_sorted_lists(cuda_dev, t, topk, e, bm):
+    """kbn_moe_pair_experts against the layout kb-nano's moe_align_block_size produces (pairs sorted by expert, every
+    expert's run padded to a multiple of the block size with the value n_pairs; tasks/baseline/L1/moe_grouped_gemm.py
+    :111-127 reads it that way): every pair gets the expert of the block its position lies in; a pair left out of
+    the list gets -1; without a list block i is pair i."""
+    from kb_nano_b200 import ops
+    gen = torch.Generator().manual_seed(t * 131 + e)
+    ids = torch.stack([torch.randperm(e, generator=gen)[:topk] if topk <= e else torch.randint(0, e, (topk,), generator=gen) for _ in range(t)])
+    n_pairs = t * topk
+    flat = ids.reshape(-1)
+    dropped = int(torch.randint(0, n_pairs, (1,), generator=gen)) if n_pairs > 4 else -1
+    sorted_ids, blocks = [], []
+    for ex in range(e):
+        mine = [p for p in torch.nonzero(flat == ex).flatten().tolist() if p != dropped]
+        pad = (-len(mine)) % bm
+        sorted_ids += mine + [n_pairs] * pad
+        blocks += [ex] * ((len(mine) + pad) // bm)
+    want = flat.clone().to(torch.int32)
+    if dropped >= 0:
+        want[dropped] = -1
+    out = torch.full((n_pairs,), 77, dtype=torch.int32, device=cuda_dev)
+    ops.moe_pair_experts(torch.tensor(sorted_ids, dtype=torch.int32, device=cuda_dev), torch.tensor(blocks, dtype=torch.int32, device=cuda_dev), bm, out)
+    assert torch.equal(out.cpu(), want)
+    out2 = torch.full((n_pairs,), 77, dtype=torch.int32, device=cuda_dev)
+    ops.moe_pair_experts(None, flat.to(torch.int32).to(cuda_dev), bm, out2)
+    assert torch.equal(out2.cpu(), flat.to(torch.int32))
+
+
 def test_moe_grouped_gemm_candidate_golden(cuda_dev):
     """The MoeGroupedGemm drop-in (sorted-token layout of kb-nano's Triton path) on the fixture produced by
     the reference's MoeGroupedGemm, with and without the routed-weight multiply, and in the one-row-per-block
