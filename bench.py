@@ -759,8 +759,12 @@ def wl_ep_moe(args, rank, world, dev, sampler, name="ep_moe"):
     gemm_tflops = 2.0 * rows * 3 * i * h / 2.0 / (gemm_ms * 1e-3) / 1e12
     # e2e: pinned host activations and routing in, result back to the host, through the package's host pipeline: the
     # three inputs travel as one staged buffer (one H2D copy per step), the copies of neighbouring steps overlap the
-    # layer of the current one over three rotating device buffers
-    pipe = ep.EpMoeHostPipeline(layer, depth=3)
+    # layer of the current one over two or three rotating device buffers
+    # one copy stream; three device buffers for small steps (the decode layer: 1.8 MB each way), two for large ones
+    # (configs[4]: tens of MB each way) -- measured on 2 GPUs, ms per step of configs[4]: 3.98 with two buffers, 4.13 with
+    # three, 4.20-4.23 with a copy stream per direction
+    big = t * h * 2 >= (8 << 20)
+    pipe = ep.EpMoeHostPipeline(layer, depth=args.e2e_depth or (2 if big else 3), copy_streams=args.e2e_streams or 1)
     hblob, hout = pipe.new_host_buffers()
     pipe.pack(hblob, x.cpu(), tw.cpu(), ti.cpu())
 
@@ -809,7 +813,7 @@ def wl_ep_moe(args, rank, world, dev, sampler, name="ep_moe"):
                    "timing": "K layer steps captured in one CUDA graph (the layer's step counter lives on the device), untimed replays "
                              "for a quarter of a second, then one replay between two CUDA events; max over ranks",
                    "e2e": "EpMoeHostPipeline: per step one pinned-host -> device copy of the inputs, the layer, one device -> host copy "
-                          "of the result; the copies run on a stream of their own over three rotating device buffers and overlap the "
+                          "of the result; the copies run on a stream of their own over two or three rotating device buffers and overlap the "
                           "neighbouring steps' layer; the K steps are captured in one CUDA graph and timed with one CUDA-event pair",
                    "layer_tflops": flop / world / (ms * 1e-3) / 1e12},
         "e2e": {"value": t * world / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": t * h * 2 + t * topk * 8, "d2h_bytes_per_step": t * h * 2},
@@ -877,6 +881,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--e2e-depth", type=int, default=0, help="device buffers of the host pipeline in the end-to-end leg (0: by step size)")
+    ap.add_argument("--e2e-streams", type=int, default=0, help="copy streams of the host pipeline (0: by step size)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-components", action="store_true",
                     help="default workload only: skip the other configurations' figures reported beside the headline number")
