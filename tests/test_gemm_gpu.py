@@ -85,13 +85,17 @@ def test_dense_config1(cuda_dev):
     assert out.shape == (4, 128, 4096) and out.dtype == torch.bfloat16
     ref = to.fp8_linear(x, w_q, w_s)
     assert_gemm_close(out.cpu().view(512, 4096), ref, "C1 Fp8Linear")
-    bias = torch.randn(4096).to(torch.bfloat16)
+    bias = torch.randn(4096, generator=torch.Generator().manual_seed(7)).to(torch.bfloat16)
     out_b = lin(x.to(cuda_dev), w_q.to(cuda_dev), w_s.to(cuda_dev), bias.to(cuda_dev))
     # the bias is added in the GEMM's epilogue, in fp32 before the one rounding to bf16: the reference's
     # F.linear(x, w, bias) (tasks/reference/L1/fp8_linear.py:103); kb-nano's baseline class rounds first and adds in
     # bf16 (tasks/baseline/L1/fp8_linear.py:446-447), which the same tolerance covers
     assert_gemm_close(out_b.cpu(), to.fp8_linear(x, w_q, w_s, bias), "C1 Fp8Linear + bias")
-    assert_gemm_close(out_b.cpu(), out.cpu().view(512, 4096) + bias, "C1 Fp8Linear + bias vs rounding first")
+    # against rounding first: the two differ by the rounding of the bias-free result, i.e. by at most half a bf16 ulp of
+    # THAT value, which a tolerance relative to the sum does not cover where result and bias cancel
+    plain = out.cpu().view(512, 4096).float()
+    d = (out_b.cpu().float() - (plain + bias.float())).abs()
+    assert bool((d <= 2.0 ** -7 * torch.maximum(plain.abs(), (plain + bias.float()).abs()) + 1e-6).all())
 
 
 def make_grouped(e, n, k, counts, seed):
